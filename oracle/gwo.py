@@ -1,0 +1,286 @@
+"""ctypes binding of the two CPU checkers (test infrastructure; never imported by the product package).
+
+`load("port")` gives this repository's plain-C restatement (oracle/liboracle.so, built from gw_oracle.c);
+`load("ref")` gives the reference's own C code behind the same `gwo_*` ABI (oracle/_ref/libgwref.so, or the
+portable `-DRUNQ_GENERIC` build when the host CPU lacks an ISA flag the native build was compiled for).
+Both are numpy-in / numpy-out.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+F32, F16, Q8, Q4, Q4K4 = 0, 2, 3, 8, 9
+KV_NAMES = {"f32": F32, "f16": F16, "q8": Q8, "q4": Q4, "q4k4": Q4K4}
+T, P = 16, 256
+
+_vp, _i, _sz, _f, _d = C.c_void_p, C.c_int, C.c_size_t, C.c_float, C.c_double
+
+
+def _host_has_flags(path):
+    try:
+        want = set(open(path).read().split())
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("flags"):
+                return want <= set(line.split(":", 1)[1].split())
+    except OSError:
+        pass
+    return False
+
+
+def build_port():
+    subprocess.check_call(["make", "-s", "-C", HERE, "liboracle.so"])
+
+
+def ref_path():
+    """Path of the loadable reference build, or None."""
+    native = os.path.join(HERE, "_ref", "libgwref.so")
+    generic = os.path.join(HERE, "_ref", "libgwref_generic.so")
+    if os.path.exists(native) and _host_has_flags(os.path.join(HERE, "_ref", "cpuflags.txt")):
+        return native
+    if os.path.exists(generic):
+        return generic
+    return None
+
+
+class Oracle:
+    def __init__(self, path):
+        self.path = path
+        L = self.L = C.CDLL(path)
+        L.gwo_kind.restype = _i
+        L.gwo_isa.restype = _i
+        L.gwo_threads_init.restype = _i
+        L.gwo_threads_init.argtypes = [_i]
+        L.gwo_kv_tile_bytes.restype = _sz
+        L.gwo_kv_tile_bytes.argtypes = [_i, _i, _i]
+        L.gwo_kv_layer_bytes.restype = _sz
+        L.gwo_kv_layer_bytes.argtypes = [_i, _i, _i, _i, _i]
+        for n in ("gwo_f32_f16", "gwo_f16_f32", "gwo_exp_att", "gwo_sigmoid"):
+            getattr(L, n).argtypes = [_vp, _vp, _sz]
+            getattr(L, n).restype = None
+        L.gwo_kv_store.argtypes = [_i, _vp, _vp, _i, _i, _i, _vp, _vp]
+        L.gwo_kv_store.restype = None
+        L.gwo_kv_block_f32.argtypes = [_i, _vp, _vp, _i, _i, _vp, _vp]
+        L.gwo_kv_block_f32.restype = None
+        L.gwo_kv_block_f32_simd.argtypes = [_i, _vp, _vp, _i, _i, _vp, _vp]
+        L.gwo_kv_block_f32_simd.restype = _i
+        L.gwo_q_rot.argtypes = [_i, _vp, _i, _i, _i]
+        L.gwo_q_rot.restype = None
+        L.gwo_o_unrot.argtypes = [_i, _vp, _i, _i, _i]
+        L.gwo_o_unrot.restype = None
+        L.gwo_attention.argtypes = [_i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _f, _i, _i]
+        L.gwo_attention.restype = _i
+        L.gwo_bench_decode.argtypes = [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _i, _vp]
+        L.gwo_bench_decode.restype = _d
+        L.gwo_bench_prefill.argtypes = [_i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _f, _i, _vp]
+        L.gwo_bench_prefill.restype = _d
+        L.gwo_dn_new.argtypes = [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]
+        L.gwo_dn_new.restype = _vp
+        L.gwo_dn_free.argtypes = [_vp]
+        L.gwo_dn_free.restype = None
+        L.gwo_dn_state_floats.argtypes = [_vp]
+        L.gwo_dn_state_floats.restype = _sz
+        L.gwo_dn_conv_floats.argtypes = [_vp]
+        L.gwo_dn_conv_floats.restype = _sz
+        L.gwo_dn_row_floats.argtypes = [_vp]
+        L.gwo_dn_row_floats.restype = _i
+        L.gwo_dn_rec.argtypes = [_vp, _vp, _i, _vp, _sz, _vp, _sz, _i]
+        L.gwo_dn_rec.restype = None
+        L.gwo_dn_prep.argtypes = [_vp, _vp, _i, _vp, _sz, _i]
+        L.gwo_dn_prep.restype = None
+        L.gwo_dn_out.argtypes = [_vp, _vp, _sz, _vp, _sz, _i]
+        L.gwo_dn_out.restype = None
+        L.gwo_bench_dn.argtypes = [_vp, _i, _vp, _vp, _sz, _vp, _sz, _i, _i, _vp]
+        L.gwo_bench_dn.restype = _d
+        self.kind = "ref" if L.gwo_kind() == 1 else "port"
+
+    # ---- helpers
+    @staticmethod
+    def _p(a):
+        return a.ctypes.data_as(_vp) if a is not None else None
+
+    def threads(self, n=0):
+        return self.L.gwo_threads_init(n)
+
+    def tile_bytes(self, kvt, hd, is_v):
+        return self.L.gwo_kv_tile_bytes(kvt, hd, is_v)
+
+    def layer_bytes(self, kvt, kv_len, n_kv, hd, is_v):
+        return self.L.gwo_kv_layer_bytes(kvt, kv_len, n_kv, hd, is_v)
+
+    def f32_f16(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        h = np.empty(x.shape, np.uint16)
+        self.L.gwo_f32_f16(self._p(x), self._p(h), x.size)
+        return h
+
+    def f16_f32(self, h):
+        h = np.ascontiguousarray(h, np.uint16)
+        x = np.empty(h.shape, np.float32)
+        self.L.gwo_f16_f32(self._p(h), self._p(x), h.size)
+        return x
+
+    def exp_att(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty_like(x)
+        self.L.gwo_exp_att(self._p(x), self._p(y), x.size)
+        return y
+
+    def sigmoid(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty_like(x)
+        self.L.gwo_sigmoid(self._p(x), self._p(y), x.size)
+        return y
+
+    def new_cache(self, kvt, kv_len, n_kv, hd):
+        """Zeroed K and V byte buffers of one layer (kv_len a multiple of 256)."""
+        assert kv_len % P == 0
+        return (np.zeros(self.layer_bytes(kvt, kv_len, n_kv, hd, 0), np.uint8),
+                np.zeros(self.layer_bytes(kvt, kv_len, n_kv, hd, 1), np.uint8))
+
+    def kv_store(self, kvt, kl, vl, pos0, k, v, n_kv, hd):
+        """Rows k, v: [n][n_kv][hd] f32 stored at positions pos0..pos0+n-1 (either may be None)."""
+        k = None if k is None else np.ascontiguousarray(k, np.float32).reshape(-1, n_kv * hd)
+        v = None if v is None else np.ascontiguousarray(v, np.float32).reshape(-1, n_kv * hd)
+        n = (k if k is not None else v).shape[0]
+        for r in range(n):
+            self.L.gwo_kv_store(kvt, self._p(kl), self._p(vl), pos0 + r, n_kv, hd,
+                                None if k is None else k[r].ctypes.data_as(_vp),
+                                None if v is None else v[r].ctypes.data_as(_vp))
+
+    def block_f32(self, kvt, kl, vl, n_kv, hd, g, b, ntl=16, simd=False):
+        """The first ntl tiles of (kv head g, block b) as fp32 tiles: K [ntl][hd][16], V [ntl][16][hd]."""
+        tk, tv = self.tile_bytes(kvt, hd, 0), self.tile_bytes(kvt, hd, 1)
+        t0 = (b * n_kv + g) * 16
+        kf = np.empty((ntl, hd, 16), np.float32)
+        vf = np.empty((ntl, 16, hd), np.float32)
+        kb, vb = kl[t0 * tk:], vl[t0 * tv:]
+        if simd:
+            rc = self.L.gwo_kv_block_f32_simd(kvt, self._p(kb), self._p(vb), ntl, hd, self._p(kf), self._p(vf))
+            if rc:
+                return None, None
+        else:
+            self.L.gwo_kv_block_f32(kvt, self._p(kb), self._p(vb), ntl, hd, self._p(kf), self._p(vf))
+        return kf, vf
+
+    def q_rot(self, kvt, q, hd):
+        q = np.array(q, np.float32, order="C")
+        self.L.gwo_q_rot(kvt, self._p(q), q.size // hd, hd, hd)
+        return q
+
+    def o_unrot(self, kvt, o, hd):
+        o = np.array(o, np.float32, order="C")
+        self.L.gwo_o_unrot(kvt, self._p(o), o.size // hd, hd, hd)
+        return o
+
+    def attention(self, kvt, kl, vl, n_kv, n_heads, hd, q, np_rows, scale=None, gated=False, split=0, rows_per_item=0):
+        """q: [nrows][n_heads][qh] (qh = 2 hd when gated); np_rows[r] = positions row r attends. -> [nrows][n_heads][hd]"""
+        qh = 2 * hd if gated else hd
+        q = np.ascontiguousarray(q, np.float32).reshape(-1, n_heads, qh)
+        npr = np.ascontiguousarray(np_rows, np.int32)
+        assert npr.shape[0] == q.shape[0]
+        out = np.zeros((q.shape[0], n_heads, hd), np.float32)
+        scale = float(1.0 / np.sqrt(np.float32(hd))) if scale is None else scale
+        rc = self.L.gwo_attention(kvt, self._p(kl), self._p(vl), n_kv, n_heads, hd, int(gated), q.shape[0], self._p(q),
+                                  self._p(npr), self._p(out), np.float32(scale), split, rows_per_item)
+        if rc:
+            raise ValueError("gwo_attention refused the arguments")
+        return out
+
+    def bench_decode(self, kvt, n_kv, n_heads, hd, caches, ctx, q, scale, reps):
+        """caches: list of (kl, vl) per sequence; q [nseq][n_heads][hd] (rotated already for q8 / q4).
+        -> (seconds total, best single pass, out)"""
+        nseq = len(caches)
+        kls = (_vp * nseq)(*[self._p(c[0]) for c in caches])
+        vls = (_vp * nseq)(*[self._p(c[1]) for c in caches])
+        ctx = np.ascontiguousarray(ctx, np.int32)
+        q = np.ascontiguousarray(q, np.float32)
+        out = np.zeros((nseq, n_heads, hd), np.float32)
+        best = _d(0)
+        tot = self.L.gwo_bench_decode(kvt, n_kv, n_heads, hd, nseq, kls, vls, self._p(ctx), self._p(q), self._p(out),
+                                      np.float32(scale), reps, C.byref(best))
+        return tot, best.value, out
+
+    def bench_prefill(self, kvt, kl, vl, n_kv, n_heads, hd, q, np_rows, scale, reps):
+        q = np.ascontiguousarray(q, np.float32)
+        npr = np.ascontiguousarray(np_rows, np.int32)
+        out = np.zeros((npr.shape[0], n_heads, hd), np.float32)
+        best = _d(0)
+        tot = self.L.gwo_bench_prefill(kvt, self._p(kl), self._p(vl), n_kv, n_heads, hd, npr.shape[0], self._p(q),
+                                       self._p(npr), self._p(out), np.float32(scale), reps, C.byref(best))
+        return tot, best.value, out
+
+
+class DeltaNet:
+    """One Gated DeltaNet layer's shapes (and optional weights) on an Oracle."""
+
+    def __init__(self, orc, nk, nv, dk, dv, conv=4, w_conv=None, w_a=None, w_dt=None, w_norm=None):
+        self.o, self.nk, self.nv, self.dk, self.dv, self.conv = orc, nk, nv, dk, dv, conv
+        self._keep = [None if w is None else np.ascontiguousarray(w, np.float32) for w in (w_conv, w_a, w_dt, w_norm)]
+        self.h = orc.L.gwo_dn_new(nk, nv, dk, dv, conv, *[Oracle._p(w) for w in self._keep])
+        self.state_floats = orc.L.gwo_dn_state_floats(self.h)
+        self.conv_floats = orc.L.gwo_dn_conv_floats(self.h)
+        self.lw = orc.L.gwo_dn_row_floats(self.h)
+        self.conv_dim = 2 * nk * dk + nv * dv
+        self.vdim = nv * dv
+
+    def __del__(self):
+        try:
+            self.o.L.gwo_dn_free(self.h)
+        except Exception:
+            pass
+
+    def new_state(self):
+        return np.zeros(self.state_floats, np.float32)
+
+    def rec(self, state, rows, first):
+        """rows [n][lw] (post-prep) -> out [n][nv*dv]; state updated in place."""
+        rows = np.ascontiguousarray(rows, np.float32)
+        n = rows.shape[0]
+        out = np.zeros((n, self.nv * self.dv), np.float32)
+        self.o.L.gwo_dn_rec(self.h, Oracle._p(state), int(first), Oracle._p(rows), rows.shape[1], Oracle._p(out),
+                            out.shape[1], n)
+        return out
+
+    def prep(self, state, rows, first):
+        """rows [n][lw] raw projections -> prepared copy; conv state updated in place."""
+        rows = np.array(rows, np.float32, order="C")
+        self.o.L.gwo_dn_prep(self.h, Oracle._p(state), int(first), Oracle._p(rows), rows.shape[1], rows.shape[0])
+        return rows
+
+    def out(self, rows, o):
+        rows = np.ascontiguousarray(rows, np.float32)
+        o = np.array(o, np.float32, order="C")
+        self.o.L.gwo_dn_out(self.h, Oracle._p(rows), rows.shape[1], Oracle._p(o), o.shape[1], rows.shape[0])
+        return o
+
+
+_cache = {}
+
+
+def load(which="port"):
+    """which: 'port' (the restatement; built on demand), 'ref' (the reference's code; None when absent),
+    'ref-generic' (its portable build; None when absent)."""
+    if which in _cache:
+        return _cache[which]
+    if which == "port":
+        path = os.path.join(HERE, "liboracle.so")
+        src = os.path.join(HERE, "gw_oracle.c")
+        if not os.path.exists(path) or (os.path.exists(src) and os.path.getmtime(src) > os.path.getmtime(path)):
+            build_port()
+    elif which == "ref":
+        path = ref_path()
+    elif which == "ref-generic":
+        path = os.path.join(HERE, "_ref", "libgwref_generic.so")
+        path = path if os.path.exists(path) else None
+    else:
+        raise ValueError(which)
+    _cache[which] = Oracle(path) if path else None
+    return _cache[which]
+
+
+def best():
+    """The strongest checker available: the reference's own code when its build is present, else the restatement."""
+    return load("ref") or load("port")
