@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path: Qwen3-8B-shaped continuous-batch decode attention.
+
+Workload (one "step" = one decode step's attention over all layers for the whole batch):
+    64 sequences, context lengths uniform in [512, 32768] (seeded), 36 layers x (32 query heads, 8 KV heads,
+    head_dim 128), f16 KV cache in the reference's 16-position tiles, fp32 queries ~N(0,1), device-filled ~N(0,1) caches.
+    The batch is sharded by sequence over the ranks (longest first onto the least loaded rank), no data-path collective.
+Metric: decode rows/s = sequences x steps / time (a row = one sequence's attention through all 36 layers).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            this library (librq_cuda.so through the C ABI)
+    python bench.py --impl reference ...                            the reference's own CPU attention on the host cores
+
+N > 1 is launched by torchrun (one rank per GPU); torch.distributed is used for the barrier and the max over ranks
+only.  One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_SEQ, N_LAYERS, N_HEADS, N_KV, HD = 64, 36, 32, 8, 128
+CTX_LO, CTX_HI, CTX_SEED = 512, 32768, 20250
+KV_BYTES_PER_POS = 2 * N_KV * HD * 2           # f16 K + V of one position of one layer: 4096 B (the algorithmic bytes)
+METRIC = "Qwen3-8B attn: decode rows/s (B=64 ragged ctx)"
+
+
+def contexts():
+    from gwenedeg_b200 import synth
+    return synth.ragged_contexts(CTX_SEED, N_SEQ, CTX_LO, CTX_HI)
+
+
+def shard(ctx, world):
+    """Longest-first greedy packing of sequences onto ranks by context length."""
+    load = [0] * world
+    owner = [None] * len(ctx)
+    for i in sorted(range(len(ctx)), key=lambda i: -int(ctx[i])):
+        r = min(range(world), key=lambda r: load[r])
+        owner[i] = r
+        load[r] += int(ctx[i])
+    return [[i for i in range(len(ctx)) if owner[i] == r] for r in range(world)]
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu):
+        self.p = None
+        self.path = os.path.join("/tmp", f"rq_clocks_{os.getpid()}.csv")
+        try:
+            self.f = open(self.path, "w")
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                       "-i", str(gpu)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.p:
+            return out
+        time.sleep(0.25)
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1]))
+                mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if sm:
+            out = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+        return out
+
+
+def cpu_leg(ctx_all, reps, sample_every):
+    """The reference's own CPU attention (oracle/_ref; else the plain-C restatement) on a bounded sample of the
+    workload: every `sample_every`-th sequence, one layer, the reference's work items on its thread pool with all host
+    cores.  Returns (rows/s scaled to the full batch and all layers, dict describing the run)."""
+    from oracle import gwo
+    orc = gwo.best()
+    cores = orc.threads(os.cpu_count() or 1)
+    idx = list(range(0, N_SEQ, sample_every))
+    ctx = [int(ctx_all[i]) for i in idx]
+    rng = np.random.default_rng(1)
+    # one random 256-position block of all heads, tiled over a sequence's blocks (as the reference's own synthetic
+    # fill does: forward.c:2385-2416): the bandwidth and arithmetic are those of distinct data
+    blk_bytes = 16 * N_KV * orc.tile_bytes(2, HD, 0)
+    blk = orc.f32_f16(rng.standard_normal(blk_bytes // 2).astype(np.float32)).view(np.uint8)
+    caches = []
+    for n in ctx:
+        nb = (n + 255) // 256
+        kl = np.tile(blk, nb)
+        vl = np.tile(blk[::-1].copy(), nb)
+        caches.append((kl, vl))
+    q = rng.standard_normal((len(idx), N_HEADS, HD)).astype(np.float32)
+    scale = float(1.0 / np.sqrt(np.float32(HD)))
+    orc.bench_decode(2, N_KV, N_HEADS, HD, caches, ctx, q, scale, 1)  # warm-up (page faults, pool start)
+    tot, best, _ = orc.bench_decode(2, N_KV, N_HEADS, HD, caches, ctx, q, scale, reps)
+    t_layer_sample = tot / reps
+    # linear in positions: scale the sample's layer time to the full batch, all layers
+    t_step_full = t_layer_sample * (float(np.sum(ctx_all)) / float(sum(ctx))) * N_LAYERS
+    info = {"value": N_SEQ / t_step_full, "unit": "rows/s", "cores": cores, "kind": "reference" if orc.kind == "ref" else "port",
+            "sample": f"{len(idx)} of {N_SEQ} sequences (every {sample_every}th), 1 of {N_LAYERS} layers, {reps} reps, "
+                      f"mean {t_layer_sample * 1e3:.1f} ms per layer pass (best {best * 1e3:.1f}), "
+                      f"{sum(ctx) * KV_BYTES_PER_POS / t_layer_sample / 1e9:.1f} GB/s of KV; scaled by positions and layers"}
+    return info
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    ctx_all = contexts()
+    reps = max(1, args.steps)
+    t0 = time.time()
+    info = cpu_leg(ctx_all, reps, sample_every=8)
+    line = {"metric": METRIC, "value": info["value"], "unit": "rows/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * N_SEQ / info["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "impl": "reference",
+            "config": {"workload": "qwen3-8b-decode-b64-ragged", "sequences": N_SEQ, "layers": N_LAYERS, "heads": N_HEADS,
+                       "kv_heads": N_KV, "head_dim": HD, "kv_type": "f16", "ctx": f"U[{CTX_LO},{CTX_HI}] seed {CTX_SEED}"},
+            "cpu_baseline": info,
+            "e2e": {"value": info["value"], "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "wall_s": time.time() - t0}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, local_rank, world):
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if dist is not None:
+            import torch
+            torch.cuda.synchronize()
+            dist.barrier()
+
+    def reduce_max(x):
+        if dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def reduce_sum(x):
+        if dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    ctx_all = contexts()
+    mine = shard(ctx_all, world)[rank]
+    my_ctx = [int(ctx_all[i]) for i in mine]
+    my_pos = sum(my_ctx)
+
+    # distinct layer caches that fit: every layer of a rank's shard is my_pos x 4096 B (>> the 126 MB L2), so cycling
+    # fewer than 36 distinct ones changes nothing for the memory system; all 36 are distinct whenever they fit
+    probe = g.Context(local_rank, n_attn=1, n_heads=N_HEADS, n_kv_heads=N_KV, head_dim=HD, max_rows=N_SEQ)
+    free, total = probe.mem_info()
+    probe.close()
+    per_layer = sum((n + 255) // 256 * 256 for n in my_ctx) * KV_BYTES_PER_POS
+    n_distinct = int(max(1, min(N_LAYERS, (free * 0.80 - (2 << 30)) // per_layer)))
+    c = g.Context(local_rank, n_attn=n_distinct, n_heads=N_HEADS, n_kv_heads=N_KV, head_dim=HD, max_rows=N_SEQ)
+    seqs = []
+    for j, (i, n) in enumerate(zip(mine, my_ctx)):
+        s = c.new_seq(n, g.KV_F16)
+        s.fill_synthetic(n, 1000 + i)
+        seqs.append(s)
+    c.sync()
+    rows = len(seqs)
+    segs = [(s, n - 1, 1) for s, n in zip(seqs, my_ctx)]
+    qn = rows * N_HEADS * HD
+    # resident inputs: the queries of every layer, and an output buffer per layer
+    q_host = c.pinned((N_LAYERS, rows, N_HEADS, HD))
+    q_host[:] = synth.normal(7 + rank, (N_LAYERS, rows, N_HEADS, HD))
+    out_host = c.pinned((N_LAYERS, rows, N_HEADS, HD))
+    q_dev = c.malloc(q_host.nbytes)
+    out_dev = c.malloc(q_host.nbytes)
+    c.h2d(q_dev, q_host)
+    c.sync()
+
+    def step_resident():
+        c.pass_begin(segs)
+        for l in range(N_LAYERS):
+            c.attn_decode_dev(l % n_distinct, q_dev + l * qn * 4, out_dev + l * qn * 4)
+        c.pass_end(commit=False)
+
+    def step_e2e():
+        c.pass_begin(segs)
+        for l in range(N_LAYERS):
+            out_host[l] = 0
+            c.check(c.L.rq_cuda_attn_decode(c.h, l % n_distinct, q_host[l].ctypes.data, out_host[l].ctypes.data))
+        c.pass_end(commit=False)
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    c.sync()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    l0 = c.launch_count()
+    c.profile_begin(args.steps * N_LAYERS)
+    c.timer_start()
+    for _ in range(args.steps):
+        step_resident()
+    ms = c.timer_stop()
+    c.sync()
+    barrier()
+    part_ms, part_n = c.profile_end()
+    launches = c.launch_count() - l0
+    clocks = sampler.stop() if sampler else None
+    ms_max = reduce_max(ms)
+    launches = int(reduce_sum(launches))
+
+    # end to end through the host-buffer entry point: pinned host q -> device, attention, result -> host, per layer
+    step_e2e()
+    c.sync()
+    barrier()
+    t0 = time.perf_counter()
+    c.timer_start()
+    for _ in range(args.steps):
+        step_e2e()
+    ms_e2e = c.timer_stop()
+    wall_e2e = (time.perf_counter() - t0) * 1e3
+    barrier()
+    ms_e2e = reduce_max(max(ms_e2e, wall_e2e))
+
+    peak, how = peaks()
+    bytes_per_launch = my_pos * KV_BYTES_PER_POS
+    achieved = bytes_per_launch / (part_ms / max(part_n, 1) * 1e-3) / 1e9
+    achieved = reduce_sum(achieved) / world  # mean over ranks of the per-GPU figure
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            try:
+                cpu = cpu_leg(ctx_all, reps=3, sample_every=8)
+            except Exception as e:  # the baseline is reported, never required
+                cpu = {"value": None, "unit": "rows/s", "cores": 0, "kind": "unavailable", "sample": repr(e)}
+        value = N_SEQ * args.steps / (ms_max * 1e-3)
+        line = {
+            "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "qwen3-8b-decode-b64-ragged", "sequences": N_SEQ, "layers": N_LAYERS, "heads": N_HEADS,
+                       "kv_heads": N_KV, "head_dim": HD, "kv_type": "f16", "ctx": f"U[{CTX_LO},{CTX_HI}] seed {CTX_SEED}",
+                       "positions_total": int(np.sum(ctx_all)), "parallelism": f"sequence-sharded x{world}",
+                       "distinct_layer_caches_rank0": n_distinct, "l2": "inputs larger than L2 (each layer pass streams "
+                       f"{per_layer / 1e9:.2f} GB on rank 0)"},
+            "layer_rows_per_s": value * N_LAYERS,
+            "e2e": {"value": N_SEQ * args.steps / (ms_e2e * 1e-3), "unit": "rows/s",
+                    "h2d_bytes_per_step": N_LAYERS * N_SEQ * N_HEADS * HD * 4, "d2h_bytes_per_step": N_LAYERS * N_SEQ * N_HEADS * HD * 4},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": how, "kernel": "attn_part_kernel<f16,128,4>",
+                         "algorithmic_bytes_per_launch_rank0": bytes_per_launch, "launches_timed": part_n},
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    c.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        # started without torchrun: re-launch one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr",
+               "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__), "--gpus", str(args.gpus), "--steps", str(args.steps),
+               "--warmup", str(args.warmup)] + (["--no-cpu"] if args.no_cpu else [])
+        sys.exit(subprocess.call(cmd))
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,114 @@
+// Shared device helpers of librq_cuda: the reference's scalar arithmetic (softmax exponential, sigmoid, half
+// conversions), KV tile geometry, and thin wrappers over the sm_100a async-copy (TMA bulk) and mbarrier PTX.
+//
+// The whole library is compiled with -fmad=false: a * b + c written in source stays two rounded operations, and every
+// fused multiply-add is an explicit fmaf(), exactly where the reference's definition has one.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rq {
+
+constexpr int ATT_T = 16;    // positions per cache tile           (reference src/kernels_avx512.h:34)
+constexpr int ATT_P = 256;   // positions per attention block      (:36)
+constexpr int ATT_PT = 16;   // tiles per block
+constexpr int ATT_DC = 32;   // dims per fused-multiply-add chain of a score (:40)
+#define RQ_PSTRIDE(hd) ((hd) + 16)  // floats per block partial: o[hd], m, l, padding (:39)
+
+enum { KV_F32 = 0, KV_F16 = 2, KV_Q8 = 3, KV_Q4 = 8, KV_Q4K4 = 9 };
+
+__host__ __device__ constexpr bool kv_quant(int t) { return t == KV_Q8 || t == KV_Q4 || t == KV_Q4K4; }
+// element format of the K (half 0) / V (half 1) cache of a type: q4 keeps its K in 8 bits (src/kvtype.h:26)
+__host__ __device__ constexpr int kv_fmt(int t, int half) { return t == KV_Q4K4 ? KV_Q4 : (t == KV_Q4 && half == 0) ? KV_Q8 : t; }
+// bytes of one 16-position tile of one head (src/kvtype.h:34)
+__host__ __device__ constexpr int kv_tile_bytes(int t, int hd, int half) {
+    return hd * (kv_fmt(t, half) == KV_F32 ? 64 : kv_fmt(t, half) == KV_Q8 ? 17 : kv_fmt(t, half) == KV_Q4 ? 9 : 32);
+}
+// index, in tiles, of the tile holding position t of (local) head h in a layer with n_kv heads (src/forward.c:1894)
+__host__ __device__ inline size_t kv_tile_index(int t, int h, int n_kv) {
+    return ((size_t)(t / ATT_P) * n_kv + h) * ATT_PT + (size_t)(t % ATT_P) / ATT_T;
+}
+
+// ---- scalar arithmetic ------------------------------------------------------------------------------------------
+// e^x for x <= 0, operation for operation the reference's exp_att (src/forward.c:1301; constants
+// src/kernels_avx512.h:41-50): clamp at -86, n = rint(x log2 e), two-step reduction, degree-5 Horner, 2^n via the
+// exponent field.
+__device__ __forceinline__ float exp_att(float x) {
+    x = x > -86.0f ? x : -86.0f;
+    float n = rintf(x * 1.44269504088896341f);
+    float r = fmaf(n, -0.693359375f, x);
+    r = fmaf(n, 2.12194440e-4f, r);
+    float z = r * r;
+    float y = 1.9875691500e-4f;
+    y = fmaf(y, r, 1.3981999507e-3f);
+    y = fmaf(y, r, 8.3334519073e-3f);
+    y = fmaf(y, r, 4.1665795894e-2f);
+    y = fmaf(y, r, 1.6666665459e-1f);
+    y = fmaf(y, r, 5.0000001201e-1f);
+    y = fmaf(y, z, r);
+    y = y + 1.0f;
+    return __uint_as_float(__float_as_uint(y) + ((uint32_t)(int32_t)n << 23));
+}
+
+// 1 / (1 + e^-x) through e = exp(-|x|) (src/forward.c:2011)
+__device__ __forceinline__ float sigmoid_att(float x) {
+    float e = exp_att(-fabsf(x));
+    float r = 1.0f / (1.0f + e);
+    return x >= 0.0f ? r : e * r;
+}
+
+// fp32 -> IEEE half bits: round to nearest even, |x| >= 65520 saturates to 65504, NaN stays quiet (src/forward.c:1325)
+__device__ __forceinline__ uint16_t f32_to_f16_sat(float f) {
+    uint32_t u = __float_as_uint(f), sign = (u >> 16) & 0x8000u, a = u & 0x7fffffffu, h;
+    if (a > 0x7f800000u) h = 0x7e00u | ((a >> 13) & 0x3ffu);
+    else if (a >= 0x477ff000u) h = 0x7bffu;
+    else h = __half_as_ushort(__float2half_rn(__uint_as_float(a)));  // RNE, exact subnormals
+    return (uint16_t)(sign | h);
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+
+// the fixed sign vector D of the KV rotation: -1 where 1 (src/forward.c:1636)
+__device__ __forceinline__ int kvq_neg(int i) { return (int)(((uint32_t)i * 0x9E3779B9u) >> 31); }
+
+// ---- mbarrier + bulk async copy (TMA) ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Wait for a phase of the barrier with an iteration limit: on expiry the kernel records `code` in *err and the caller
+// carries on to its exit (results are then invalid and the host reports RQ_CUDA_ERR_STATE).  try_wait itself blocks
+// for a hardware-defined slice, so the limit below is many orders of magnitude beyond any healthy copy.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *err, int code) {
+    for (int it = 0; it < (1 << 22); it++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(err, code);
+    return false;
+}
+// order earlier generic-proxy accesses of shared memory before later async-proxy (bulk copy) writes to it
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// global -> shared bulk copy of `bytes` (a multiple of 16; both addresses 16-byte aligned), completion counted on bar
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+}  // namespace rq

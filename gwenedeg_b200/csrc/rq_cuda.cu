@@ -1,0 +1,692 @@
+// librq_cuda: host side of the C ABI declared in include/rq_cuda.h — contexts, device-resident sequences, the open
+// pass, and the launches of the kernels in this directory.  No PyTorch, no CPU fallback: every compute entry point
+// needs a CUDA device and fails with RQ_CUDA_ERR_DEVICE otherwise.
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+#include <vector>
+
+#include "../../include/rq_cuda.h"
+#include "attn_decode.cuh"
+#include "deltanet.cuh"
+#include "kv_store.cuh"
+
+using namespace rq;
+
+namespace rq {
+extern template cudaError_t launch_attn_part<KV_F16>(int, const AttnPartArgs &, cudaStream_t);
+extern template cudaError_t launch_attn_part<KV_Q8>(int, const AttnPartArgs &, cudaStream_t);
+extern template cudaError_t launch_attn_part<KV_Q4>(int, const AttnPartArgs &, cudaStream_t);
+extern template cudaError_t launch_attn_part<KV_Q4K4>(int, const AttnPartArgs &, cudaStream_t);
+extern template size_t attn_part_smem<KV_F16>(int, int);
+extern template size_t attn_part_smem<KV_Q8>(int, int);
+extern template size_t attn_part_smem<KV_Q4>(int, int);
+extern template size_t attn_part_smem<KV_Q4K4>(int, int);
+}  // namespace rq
+
+struct RqCudaSeq {
+    RqCuda *ctx;
+    int cap, kv_len, kvt, len;
+    uint8_t *k, *v;        // [n_attn] layers of kv_len / 16 * n_kv_local tiles
+    size_t lk, lv;         // bytes per layer
+    float *ssm;            // [n_lin] layers of ssm_floats
+    size_t ssm_floats;
+    int in_pass;
+};
+
+struct RqCuda {
+    int device;
+    RqCudaModel m;
+    int n_kv, n_heads, G, qh;  // local (this device's) KV heads / query heads, vectors per KV head, floats per q head row
+    int max_rows;
+    cudaStream_t own_stream, stream;
+    cudaEvent_t ev0, ev1;
+    char err[256];
+    unsigned long long launches;
+    // the open pass
+    int pass_open, nrows, nseg, total_blocks, pass_kvt, max_np;
+    std::vector<RqCudaSegment> segs;
+    PassRow *h_rows, *d_rows;  // nrows + 1 entries (the last one holds the total block count)
+    DnSeg *h_dseg, *d_dseg;
+    // scratch, grown on demand
+    float *d_part;  size_t part_bytes;
+    float *d_q;     size_t q_bytes;     // staging of host q rows
+    float *d_out;   size_t out_bytes;   // staging of outputs
+    float *d_k, *d_v; size_t k_bytes, v_bytes;  // staging of host K / V rows
+    float *d_dn;    size_t dn_bytes;    // staging of DeltaNet rows
+    int *d_err;
+    int *h_err;  // pinned
+    void *flush; size_t flush_bytes;
+    // optional per-launch timing of the dominant kernel (rq_cuda_profile_begin / _end)
+    std::vector<cudaEvent_t> prof_ev;
+    int prof_on, prof_n;
+};
+
+static int fail(RqCuda *c, int code, const char *fmt, ...) {
+    if (c) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(c->err, sizeof(c->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+#define CU(c, call)                                                                                          \
+    do {                                                                                                     \
+        cudaError_t e_ = (call);                                                                             \
+        if (e_ != cudaSuccess)                                                                               \
+            return fail(c, e_ == cudaErrorMemoryAllocation ? RQ_CUDA_ERR_NOMEM : RQ_CUDA_ERR_DEVICE, "%s: %s", #call, \
+                        cudaGetErrorString(e_));                                                             \
+    } while (0)
+
+static bool kvt_ok(int t, int hd) {
+    if (t == KV_F16) return hd == 64 || hd == 128 || hd == 256;
+    return kv_quant(t) && (hd == 64 || hd == 128 || hd == 256);
+}
+
+static int grow(RqCuda *c, void **p, size_t *have, size_t need) {
+    // device scratch of at least `need` bytes (contents not kept)
+    if (*have >= need) return RQ_CUDA_OK;
+    CU(c, cudaStreamSynchronize(c->stream));
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    *have = 0;
+    size_t sz = need + need / 4;
+    CU(c, cudaMalloc(p, sz));
+    *have = sz;
+    return RQ_CUDA_OK;
+}
+
+extern "C" {
+
+int rq_cuda_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+    return n;
+}
+
+int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ctx) {
+    if (!ctx) return RQ_CUDA_ERR_ARG;
+    *ctx = nullptr;
+    if (!model || max_rows < 1 || max_rows > 512) return RQ_CUDA_ERR_ARG;
+    const RqCudaModel &m = *model;
+    int nkv_local = m.kv_heads_local > 0 ? m.kv_heads_local : m.n_kv_heads;
+    if (m.n_attn < 0 || m.n_lin < 0 || (m.n_attn == 0 && m.n_lin == 0)) return RQ_CUDA_ERR_ARG;
+    if (m.n_attn > 0) {
+        if (m.n_kv_heads < 1 || m.n_heads < 1 || m.n_heads % m.n_kv_heads) return RQ_CUDA_ERR_ARG;
+        if (m.n_heads / m.n_kv_heads > 16) return RQ_CUDA_ERR_ARG;
+        if (m.head_dim != 64 && m.head_dim != 128 && m.head_dim != 256) return RQ_CUDA_ERR_ARG;
+        if (m.kv_head0 < 0 || nkv_local < 1 || m.kv_head0 + nkv_local > m.n_kv_heads) return RQ_CUDA_ERR_ARG;
+    }
+    if (m.n_lin > 0) {
+        if (m.dn_nk < 1 || m.dn_nv < 1 || m.dn_nv % m.dn_nk || m.dn_dk != 128 || m.dn_dv < 32 || m.dn_dv % 32 ||
+            m.dn_conv < 2)
+            return RQ_CUDA_ERR_ARG;
+    }
+    int ndev = rq_cuda_device_count();
+    if (ndev < 1 || device < 0 || device >= ndev) return RQ_CUDA_ERR_DEVICE;
+    if (cudaSetDevice(device) != cudaSuccess) return RQ_CUDA_ERR_DEVICE;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return RQ_CUDA_ERR_DEVICE;
+    if (prop.major != 10) return RQ_CUDA_ERR_DEVICE;  // the kernels are sm_100a only
+    RqCuda *c = new (std::nothrow) RqCuda();
+    if (!c) return RQ_CUDA_ERR_NOMEM;
+    c->device = device;
+    c->m = m;
+    c->n_kv = m.n_attn ? nkv_local : 0;
+    c->G = m.n_attn ? m.n_heads / m.n_kv_heads : 0;
+    c->n_heads = c->n_kv * c->G;
+    c->qh = (m.gated ? 2 : 1) * m.head_dim;
+    c->max_rows = max_rows;
+    c->err[0] = 0;
+    bool okk = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) == cudaSuccess &&
+               cudaEventCreate(&c->ev0) == cudaSuccess && cudaEventCreate(&c->ev1) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_rows, sizeof(PassRow) * (max_rows + 1)) == cudaSuccess &&
+               cudaMalloc((void **)&c->d_rows, sizeof(PassRow) * (max_rows + 1)) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_dseg, sizeof(DnSeg) * max_rows) == cudaSuccess &&
+               cudaMalloc((void **)&c->d_dseg, sizeof(DnSeg) * max_rows) == cudaSuccess &&
+               cudaMalloc((void **)&c->d_err, sizeof(int)) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_err, sizeof(int)) == cudaSuccess &&
+               cudaMemset(c->d_err, 0, sizeof(int)) == cudaSuccess;
+    c->stream = c->own_stream;
+    if (!okk) {
+        rq_cuda_free(c);
+        return RQ_CUDA_ERR_DEVICE;
+    }
+    *ctx = c;
+    return RQ_CUDA_OK;
+}
+
+void rq_cuda_free(RqCuda *c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    void *dev[] = {c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->flush};
+    for (void *p : dev)
+        if (p) cudaFree(p);
+    if (c->h_rows) cudaFreeHost(c->h_rows);
+    if (c->h_dseg) cudaFreeHost(c->h_dseg);
+    if (c->h_err) cudaFreeHost(c->h_err);
+    for (cudaEvent_t ev : c->prof_ev) cudaEventDestroy(ev);
+    if (c->ev0) cudaEventDestroy(c->ev0);
+    if (c->ev1) cudaEventDestroy(c->ev1);
+    if (c->own_stream) cudaStreamDestroy(c->own_stream);
+    delete c;
+}
+
+const char *rq_cuda_error(const RqCuda *c) { return c ? c->err : "no context"; }
+
+int rq_cuda_sync(RqCuda *c) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    CU(c, cudaStreamSynchronize(c->stream));
+    if (*c->h_err) {
+        int code = *c->h_err;
+        cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream);
+        return fail(c, RQ_CUDA_ERR_STATE, "a device-side wait expired (code %d): results of the last pass are invalid", code);
+    }
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_set_stream(RqCuda *c, void *s) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaStreamSynchronize(c->stream));
+    c->stream = s ? (cudaStream_t)s : c->own_stream;
+    return RQ_CUDA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------- sequences
+int rq_cuda_seq_new(RqCuda *c, int capacity, int kv_type, RqCudaSeq **seq) {
+    if (!c || !seq) return RQ_CUDA_ERR_ARG;
+    *seq = nullptr;
+    if (capacity < 1) return fail(c, RQ_CUDA_ERR_ARG, "capacity %d", capacity);
+    if (c->m.n_attn > 0 && !kvt_ok(kv_type, c->m.head_dim))
+        return fail(c, RQ_CUDA_ERR_ARG, "KV type %d with head_dim %d is not supported on the device", kv_type, c->m.head_dim);
+    CU(c, cudaSetDevice(c->device));
+    RqCudaSeq *s = new (std::nothrow) RqCudaSeq();
+    if (!s) return fail(c, RQ_CUDA_ERR_NOMEM, "host allocation");
+    s->ctx = c;
+    s->cap = capacity;
+    s->kv_len = (capacity + ATT_P - 1) / ATT_P * ATT_P;
+    s->kvt = kv_type;
+    if (c->m.n_attn > 0) {
+        s->lk = (size_t)(s->kv_len / ATT_T) * c->n_kv * kv_tile_bytes(kv_type, c->m.head_dim, 0);
+        s->lv = (size_t)(s->kv_len / ATT_T) * c->n_kv * kv_tile_bytes(kv_type, c->m.head_dim, 1);
+        cudaError_t e1 = cudaMalloc((void **)&s->k, s->lk * c->m.n_attn);
+        cudaError_t e2 = e1 == cudaSuccess ? cudaMalloc((void **)&s->v, s->lv * c->m.n_attn) : e1;
+        if (e1 != cudaSuccess || e2 != cudaSuccess) {
+            cudaGetLastError();
+            rq_cuda_seq_free(s);
+            return fail(c, RQ_CUDA_ERR_NOMEM, "KV cache of %zu bytes: %s", (s->lk + s->lv) * c->m.n_attn,
+                        cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+        }
+    }
+    if (c->m.n_lin > 0) {
+        size_t convf = ((size_t)(c->m.dn_conv - 1) * (2 * c->m.dn_nk * c->m.dn_dk + c->m.dn_nv * c->m.dn_dv) + 15) / 16 * 16;
+        s->ssm_floats = convf + (size_t)c->m.dn_nv * c->m.dn_dk * c->m.dn_dv;
+        cudaError_t e = cudaMalloc((void **)&s->ssm, s->ssm_floats * 4 * c->m.n_lin);
+        if (e == cudaSuccess) e = cudaMemsetAsync(s->ssm, 0, s->ssm_floats * 4 * c->m.n_lin, c->stream);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            rq_cuda_seq_free(s);
+            return fail(c, RQ_CUDA_ERR_NOMEM, "DeltaNet state: %s", cudaGetErrorString(e));
+        }
+    }
+    *seq = s;
+    return RQ_CUDA_OK;
+}
+
+void rq_cuda_seq_free(RqCudaSeq *s) {
+    if (!s) return;
+    cudaSetDevice(s->ctx->device);
+    cudaStreamSynchronize(s->ctx->stream);
+    if (s->k) cudaFree(s->k);
+    if (s->v) cudaFree(s->v);
+    if (s->ssm) cudaFree(s->ssm);
+    delete s;
+}
+
+int rq_cuda_seq_len(const RqCudaSeq *s) { return s ? s->len : RQ_CUDA_ERR_ARG; }
+int rq_cuda_seq_capacity(const RqCudaSeq *s) { return s ? s->cap : RQ_CUDA_ERR_ARG; }
+
+int rq_cuda_seq_truncate(RqCudaSeq *s, int n) {
+    if (!s || n < 0 || n > s->len) return RQ_CUDA_ERR_ARG;
+    if (s->in_pass) return fail(s->ctx, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
+    s->len = n;
+    return RQ_CUDA_OK;
+}
+
+size_t rq_cuda_seq_layer_bytes(const RqCudaSeq *s, int is_v) { return s ? (is_v ? s->lv : s->lk) : 0; }
+size_t rq_cuda_seq_state_floats(const RqCudaSeq *s) { return s ? s->ssm_floats : 0; }
+
+int rq_cuda_seq_copy(RqCudaSeq *dst, const RqCudaSeq *src, int n) {
+    if (!dst || !src || dst == src || dst->ctx != src->ctx) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = dst->ctx;
+    if (n < 0 || n > src->len || n > dst->cap || dst->kvt != src->kvt) return fail(c, RQ_CUDA_ERR_ARG, "copy of %d positions", n);
+    if (dst->in_pass || src->in_pass) return fail(c, RQ_CUDA_ERR_STATE, "a sequence is part of the open pass");
+    CU(c, cudaSetDevice(c->device));
+    // whole 256-position blocks holding the first n positions, layer by layer (a block's heads are contiguous)
+    size_t nblk = (size_t)(n + ATT_P - 1) / ATT_P;
+    for (int l = 0; l < c->m.n_attn; l++)
+        for (int half = 0; half < 2; half++) {
+            size_t bytes = nblk * ATT_PT * c->n_kv * kv_tile_bytes(src->kvt, c->m.head_dim, half);
+            uint8_t *d = (half ? dst->v : dst->k) + (size_t)l * (half ? dst->lv : dst->lk);
+            const uint8_t *sp = (half ? src->v : src->k) + (size_t)l * (half ? src->lv : src->lk);
+            if (bytes) CU(c, cudaMemcpyAsync(d, sp, bytes, cudaMemcpyDeviceToDevice, c->stream));
+        }
+    if (c->m.n_lin > 0) {
+        if (n == src->len)
+            CU(c, cudaMemcpyAsync(dst->ssm, src->ssm, src->ssm_floats * 4 * c->m.n_lin, cudaMemcpyDeviceToDevice, c->stream));
+        else if (n != 0)
+            return fail(c, RQ_CUDA_ERR_STATE, "the DeltaNet state exists only at the source's length %d", src->len);
+        else
+            CU(c, cudaMemsetAsync(dst->ssm, 0, dst->ssm_floats * 4 * c->m.n_lin, c->stream));
+    }
+    dst->len = n;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_seq_read_kv(RqCudaSeq *s, int layer, int is_v, void *host, size_t bytes) {
+    if (!s || !host) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    size_t lb = is_v ? s->lv : s->lk;
+    if (layer < 0 || layer >= c->m.n_attn || bytes > lb) return fail(c, RQ_CUDA_ERR_ARG, "layer %d / %zu bytes", layer, bytes);
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemcpyAsync(host, (is_v ? s->v : s->k) + (size_t)layer * lb, bytes, cudaMemcpyDeviceToHost, c->stream));
+    CU(c, cudaStreamSynchronize(c->stream));
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_seq_write_kv(RqCudaSeq *s, int layer, int is_v, const void *host, size_t bytes, int new_len) {
+    if (!s || !host) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    size_t lb = is_v ? s->lv : s->lk;
+    if (layer < 0 || layer >= c->m.n_attn || bytes > lb || new_len < 0 || new_len > s->cap)
+        return fail(c, RQ_CUDA_ERR_ARG, "layer %d / %zu bytes / length %d", layer, bytes, new_len);
+    if (s->in_pass) return fail(c, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemcpyAsync((is_v ? s->v : s->k) + (size_t)layer * lb, host, bytes, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaStreamSynchronize(c->stream));
+    s->len = new_len;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_seq_read_state(RqCudaSeq *s, int lin_layer, float *host) {
+    if (!s || !host) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    if (lin_layer < 0 || lin_layer >= c->m.n_lin) return fail(c, RQ_CUDA_ERR_ARG, "linear layer %d", lin_layer);
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemcpyAsync(host, s->ssm + (size_t)lin_layer * s->ssm_floats, s->ssm_floats * 4, cudaMemcpyDeviceToHost, c->stream));
+    CU(c, cudaStreamSynchronize(c->stream));
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_seq_write_state(RqCudaSeq *s, int lin_layer, const float *host) {
+    if (!s || !host) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    if (lin_layer < 0 || lin_layer >= c->m.n_lin) return fail(c, RQ_CUDA_ERR_ARG, "linear layer %d", lin_layer);
+    if (s->in_pass) return fail(c, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemcpyAsync(s->ssm + (size_t)lin_layer * s->ssm_floats, host, s->ssm_floats * 4, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaStreamSynchronize(c->stream));
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_seq_fill_synthetic(RqCudaSeq *s, int n, unsigned long long seed) {
+    if (!s) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    if (n < 1 || n > s->cap) return fail(c, RQ_CUDA_ERR_ARG, "fill of %d positions (capacity %d)", n, s->cap);
+    if (s->in_pass) return fail(c, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
+    CU(c, cudaSetDevice(c->device));
+    size_t ntiles = (size_t)(n + ATT_P - 1) / ATT_P * ATT_PT * c->n_kv;  // whole blocks
+    for (int l = 0; l < c->m.n_attn; l++)
+        for (int half = 0; half < 2; half++) {
+            uint8_t *base = (half ? s->v : s->k) + (size_t)l * (half ? s->lv : s->lk);
+            int fmt = kv_fmt(s->kvt, half);
+            size_t words = ntiles * kv_tile_bytes(s->kvt, c->m.head_dim, half) / 2;
+            int grid = (int)std::min<size_t>((words + 255) / 256, 148 * 16);
+            kv_fill_kernel<<<grid, 256, 0, c->stream>>>(base, ntiles, fmt, c->m.head_dim,
+                                                        seed * 0x100000001B3ull + (uint64_t)(l * 2 + half) * 0x9E3779B97F4A7C15ull);
+            c->launches++;
+        }
+    CU(c, cudaGetLastError());
+    s->len = n;
+    return RQ_CUDA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------- the pass
+int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    if (c->pass_open) return fail(c, RQ_CUDA_ERR_STATE, "a pass is already open");
+    if (!seg || nseg < 1 || nseg > c->max_rows) return fail(c, RQ_CUDA_ERR_ARG, "%d segments", nseg);
+    long total = 0;
+    int kvt = -1;
+    for (int i = 0; i < nseg; i++) {
+        const RqCudaSegment &g = seg[i];
+        if (!g.seq || g.seq->ctx != c) return fail(c, RQ_CUDA_ERR_ARG, "segment %d: not a sequence of this context", i);
+        if (g.n < 1 || g.pos0 < 0) return fail(c, RQ_CUDA_ERR_ARG, "segment %d: %d rows at position %d", i, g.n, g.pos0);
+        if ((long)g.pos0 + g.n > g.seq->cap)
+            return fail(c, RQ_CUDA_ERR_CONTEXT, "segment %d: positions %d..%d exceed the capacity %d", i, g.pos0, g.pos0 + g.n - 1,
+                        g.seq->cap);
+        if (g.pos0 > g.seq->len)
+            return fail(c, RQ_CUDA_ERR_ARG, "segment %d: position %d leaves a gap after the sequence's %d positions", i, g.pos0,
+                        g.seq->len);
+        for (int j = 0; j < i; j++)
+            if (seg[j].seq == g.seq) return fail(c, RQ_CUDA_ERR_ARG, "segment %d: its sequence appears twice", i);
+        if (kvt < 0) kvt = g.seq->kvt;
+        else if (kvt != g.seq->kvt) return fail(c, RQ_CUDA_ERR_ARG, "segment %d: all sequences of a pass share one KV type", i);
+        total += g.n;
+    }
+    if (total > c->max_rows) return fail(c, RQ_CUDA_ERR_ARG, "%ld rows exceed the context's %d", total, c->max_rows);
+    CU(c, cudaSetDevice(c->device));
+    // (the previous pass's table may still be read by kernels in flight: the copy below is stream-ordered behind
+    // them, and the pinned source is rewritten only after the stream drained it)
+    CU(c, cudaStreamSynchronize(c->stream));
+    int r = 0, blk = 0, mx = 0;
+    for (int i = 0; i < nseg; i++) {
+        const RqCudaSegment &g = seg[i];
+        for (int j = 0; j < g.n; j++, r++) {
+            PassRow &pr = c->h_rows[r];
+            pr.k = g.seq->k;
+            pr.v = g.seq->v;
+            pr.lk = g.seq->lk;
+            pr.lv = g.seq->lv;
+            pr.pos = g.pos0 + j;
+            pr.np = pr.pos + 1;
+            pr.blk0 = blk;
+            pr.seg = i;
+            blk += (pr.np + ATT_P - 1) / ATT_P;
+            mx = std::max(mx, pr.np);
+        }
+        DnSeg &d = c->h_dseg[i];
+        d.state = g.seq->ssm;
+        d.lstride = g.seq->ssm_floats;
+        d.row0 = r - g.n;
+        d.n = g.n;
+        d.first = g.pos0 == 0;
+        d.pad = 0;
+    }
+    memset(&c->h_rows[r], 0, sizeof(PassRow));
+    c->h_rows[r].blk0 = blk;
+    CU(c, cudaMemcpyAsync(c->d_rows, c->h_rows, sizeof(PassRow) * (r + 1), cudaMemcpyHostToDevice, c->stream));
+    if (c->m.n_lin > 0) CU(c, cudaMemcpyAsync(c->d_dseg, c->h_dseg, sizeof(DnSeg) * nseg, cudaMemcpyHostToDevice, c->stream));
+    c->segs.assign(seg, seg + nseg);
+    for (int i = 0; i < nseg; i++) seg[i].seq->in_pass = 1;
+    c->nrows = r;
+    c->nseg = nseg;
+    c->total_blocks = blk;
+    c->max_np = mx;
+    c->pass_kvt = kvt;
+    c->pass_open = 1;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_pass_end(RqCuda *c, int commit) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    if (!c->pass_open) return fail(c, RQ_CUDA_ERR_STATE, "no pass is open");
+    for (auto &g : c->segs) {
+        g.seq->in_pass = 0;
+        if (commit) g.seq->len = std::max(g.seq->len, g.pos0 + g.n);
+    }
+    c->pass_open = 0;
+    return RQ_CUDA_OK;
+}
+
+static int need_pass(RqCuda *c, int layer, int nlayers, const char *what) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    if (!c->pass_open) return fail(c, RQ_CUDA_ERR_STATE, "%s: no pass is open", what);
+    if (layer < 0 || layer >= nlayers) return fail(c, RQ_CUDA_ERR_ARG, "%s: layer %d of %d", what, layer, nlayers);
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_kv_store_dev(RqCuda *c, int layer, const float *k, const float *v) {
+    int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "kv_store");
+    if (rc) return rc;
+    if (!k && !v) return fail(c, RQ_CUDA_ERR_ARG, "kv_store: no rows");
+    CU(c, cudaSetDevice(c->device));
+    dim3 grid(c->nrows, c->n_kv, 2);
+    switch (c->m.head_dim) {
+        case 64: kv_store_kernel<64><<<grid, 64, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->pass_kvt, k, v); break;
+        case 128: kv_store_kernel<128><<<grid, 128, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->pass_kvt, k, v); break;
+        default: kv_store_kernel<256><<<grid, 256, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->pass_kvt, k, v); break;
+    }
+    c->launches++;
+    CU(c, cudaGetLastError());
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_kv_store(RqCuda *c, int layer, const float *k, const float *v) {
+    int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "kv_store");
+    if (rc) return rc;
+    if (!k && !v) return fail(c, RQ_CUDA_ERR_ARG, "kv_store: no rows");
+    CU(c, cudaSetDevice(c->device));
+    size_t bytes = (size_t)c->nrows * c->n_kv * c->m.head_dim * 4;
+    if ((rc = grow(c, (void **)&c->d_k, &c->k_bytes, bytes))) return rc;
+    if ((rc = grow(c, (void **)&c->d_v, &c->v_bytes, bytes))) return rc;
+    if (k) CU(c, cudaMemcpyAsync(c->d_k, k, bytes, cudaMemcpyHostToDevice, c->stream));
+    if (v) CU(c, cudaMemcpyAsync(c->d_v, v, bytes, cudaMemcpyHostToDevice, c->stream));
+    rc = rq_cuda_kv_store_dev(c, layer, k ? c->d_k : nullptr, v ? c->d_v : nullptr);
+    if (rc) return rc;
+    CU(c, cudaStreamSynchronize(c->stream));  // the host rows may be reused on return
+    return RQ_CUDA_OK;
+}
+
+static int launch_decode(RqCuda *c, int layer, const float *q, float *out) {
+    const int hd = c->m.head_dim;
+    size_t need = (size_t)c->total_blocks * c->n_heads * RQ_PSTRIDE(hd) * 4;
+    int rc = grow(c, (void **)&c->d_part, &c->part_bytes, need);
+    if (rc) return rc;
+    AttnPartArgs a;
+    a.rows = c->d_rows;
+    a.nrows = c->nrows;
+    a.total_blocks = c->total_blocks;
+    a.layer = layer;
+    a.n_kv = c->n_kv;
+    a.G = c->G;
+    a.q = q;
+    a.qh = c->qh;
+    a.n_heads = c->n_heads;
+    a.scale = 1.0f / sqrtf((float)hd);
+    a.part = c->d_part;
+    a.err = c->d_err;
+    cudaError_t e;
+    const bool prof = c->prof_on && (size_t)(2 * c->prof_n + 2) <= c->prof_ev.size();
+    if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n], c->stream);
+    switch (c->pass_kvt) {
+        case KV_F16: e = launch_attn_part<KV_F16>(hd, a, c->stream); break;
+        case KV_Q8: e = launch_attn_part<KV_Q8>(hd, a, c->stream); break;
+        case KV_Q4: e = launch_attn_part<KV_Q4>(hd, a, c->stream); break;
+        case KV_Q4K4: e = launch_attn_part<KV_Q4K4>(hd, a, c->stream); break;
+        default: e = cudaErrorInvalidValue;
+    }
+    if (e != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "attention launch: %s", cudaGetErrorString(e));
+    if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n++ + 1], c->stream);
+    c->launches++;
+    dim3 grid(c->nrows, c->n_heads);
+    const bool quant = kv_quant(c->pass_kvt);
+#define COMBINE(HD_)                                                                                                          \
+    if (quant) attn_combine_kernel<HD_, true><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, c->d_part, q, c->qh, c->m.gated, out); \
+    else attn_combine_kernel<HD_, false><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, c->d_part, q, c->qh, c->m.gated, out);
+    switch (hd) {
+        case 64: COMBINE(64) break;
+        case 128: COMBINE(128) break;
+        default: COMBINE(256) break;
+    }
+#undef COMBINE
+    c->launches++;
+    CU(c, cudaGetLastError());
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_attn_decode_dev(RqCuda *c, int layer, const float *q, float *out) {
+    int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_decode");
+    if (rc) return rc;
+    if (!q || !out) return fail(c, RQ_CUDA_ERR_ARG, "attn_decode: null rows");
+    CU(c, cudaSetDevice(c->device));
+    return launch_decode(c, layer, q, out);
+}
+
+static int stage_q(RqCuda *c, const float *q, size_t qbytes, size_t obytes) {
+    int rc;
+    if ((rc = grow(c, (void **)&c->d_q, &c->q_bytes, qbytes))) return rc;
+    if ((rc = grow(c, (void **)&c->d_out, &c->out_bytes, obytes))) return rc;
+    CU(c, cudaMemcpyAsync(c->d_q, q, qbytes, cudaMemcpyHostToDevice, c->stream));
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_attn_decode(RqCuda *c, int layer, const float *q, float *out) {
+    int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_decode");
+    if (rc) return rc;
+    if (!q || !out) return fail(c, RQ_CUDA_ERR_ARG, "attn_decode: null rows");
+    CU(c, cudaSetDevice(c->device));
+    size_t qb = (size_t)c->nrows * c->n_heads * c->qh * 4, ob = (size_t)c->nrows * c->n_heads * c->m.head_dim * 4;
+    if ((rc = stage_q(c, q, qb, ob))) return rc;
+    if ((rc = launch_decode(c, layer, c->d_q, c->d_out))) return rc;
+    CU(c, cudaMemcpyAsync(out, c->d_out, ob, cudaMemcpyDeviceToHost, c->stream));
+    return rq_cuda_sync(c);
+}
+
+int rq_cuda_attn_prefill_dev(RqCuda *c, int layer, const float *q, float *out) {
+    return rq_cuda_attn_decode_dev(c, layer, q, out);
+}
+
+int rq_cuda_attn_prefill(RqCuda *c, int layer, const float *q, float *out) { return rq_cuda_attn_decode(c, layer, q, out); }
+
+int rq_cuda_dn_rec_dev(RqCuda *c, int lin_layer, const float *rows, float *out) {
+    int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_rec");
+    if (rc) return rc;
+    if (!rows || !out) return fail(c, RQ_CUDA_ERR_ARG, "dn_rec: null rows");
+    CU(c, cudaSetDevice(c->device));
+    const RqCudaModel &m = c->m;
+    const int lw = 2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
+    size_t convf = ((size_t)(m.dn_conv - 1) * (2 * m.dn_nk * m.dn_dk + m.dn_nv * m.dn_dv) + 15) / 16 * 16;
+    dim3 grid(m.dn_nv * (m.dn_dv / DN_BW), c->nseg);
+    dn_rec_kernel<128><<<grid, 32, 0, c->stream>>>(c->d_dseg, lin_layer, m.dn_nk, m.dn_nv, m.dn_dv, convf, rows, lw, out);
+    c->launches++;
+    CU(c, cudaGetLastError());
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_dn_rec(RqCuda *c, int lin_layer, const float *rows, float *out) {
+    int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_rec");
+    if (rc) return rc;
+    if (!rows || !out) return fail(c, RQ_CUDA_ERR_ARG, "dn_rec: null rows");
+    CU(c, cudaSetDevice(c->device));
+    const RqCudaModel &m = c->m;
+    const int lw = 2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
+    size_t rb = (size_t)c->nrows * lw * 4, ob = (size_t)c->nrows * m.dn_nv * m.dn_dv * 4;
+    if ((rc = grow(c, (void **)&c->d_dn, &c->dn_bytes, rb + ob))) return rc;
+    float *d_rows = c->d_dn, *d_out = c->d_dn + (size_t)c->nrows * lw;
+    CU(c, cudaMemcpyAsync(d_rows, rows, rb, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = rq_cuda_dn_rec_dev(c, lin_layer, d_rows, d_out))) return rc;
+    CU(c, cudaMemcpyAsync(out, d_out, ob, cudaMemcpyDeviceToHost, c->stream));
+    return rq_cuda_sync(c);
+}
+
+// ---------------------------------------------------------------------------------------------------- helpers
+int rq_cuda_malloc(RqCuda *c, size_t bytes, void **dev) {
+    if (!c || !dev) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMalloc(dev, bytes));
+    return RQ_CUDA_OK;
+}
+int rq_cuda_mfree(RqCuda *c, void *dev) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaStreamSynchronize(c->stream));
+    CU(c, cudaFree(dev));
+    return RQ_CUDA_OK;
+}
+int rq_cuda_malloc_host(RqCuda *c, size_t bytes, void **host) {
+    if (!c || !host) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMallocHost(host, bytes));
+    return RQ_CUDA_OK;
+}
+int rq_cuda_mfree_host(RqCuda *c, void *host) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaFreeHost(host));
+    return RQ_CUDA_OK;
+}
+int rq_cuda_memcpy_h2d(RqCuda *c, void *dev, const void *host, size_t bytes) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, c->stream));
+    return RQ_CUDA_OK;
+}
+int rq_cuda_memcpy_d2h(RqCuda *c, void *host, const void *dev, size_t bytes) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, c->stream));
+    return RQ_CUDA_OK;
+}
+int rq_cuda_mem_info(RqCuda *c, size_t *free_bytes, size_t *total_bytes) {
+    if (!c || !free_bytes || !total_bytes) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemGetInfo(free_bytes, total_bytes));
+    return RQ_CUDA_OK;
+}
+int rq_cuda_timer_start(RqCuda *c) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaEventRecord(c->ev0, c->stream));
+    return RQ_CUDA_OK;
+}
+int rq_cuda_timer_stop(RqCuda *c, float *ms) {
+    if (!c || !ms) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaEventRecord(c->ev1, c->stream));
+    CU(c, cudaEventSynchronize(c->ev1));
+    CU(c, cudaEventElapsedTime(ms, c->ev0, c->ev1));
+    return RQ_CUDA_OK;
+}
+unsigned long long rq_cuda_launch_count(const RqCuda *c) { return c ? c->launches : 0; }
+
+int rq_cuda_profile_begin(RqCuda *c, int max_launches) {
+    if (!c || max_launches < 1 || max_launches > (1 << 16)) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    while (c->prof_ev.size() < (size_t)2 * max_launches) {
+        cudaEvent_t ev;
+        CU(c, cudaEventCreate(&ev));
+        c->prof_ev.push_back(ev);
+    }
+    c->prof_n = 0;
+    c->prof_on = 1;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_profile_end(RqCuda *c, float *total_ms, int *launches) {
+    if (!c || !total_ms || !launches) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaStreamSynchronize(c->stream));
+    c->prof_on = 0;
+    float tot = 0.0f;
+    for (int i = 0; i < c->prof_n; i++) {
+        float ms = 0.0f;
+        CU(c, cudaEventElapsedTime(&ms, c->prof_ev[2 * i], c->prof_ev[2 * i + 1]));
+        tot += ms;
+    }
+    *total_ms = tot;
+    *launches = c->prof_n;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_flush_l2(RqCuda *c) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    const size_t bytes = (size_t)256 << 20;  // twice the 126 MB L2
+    if (!c->flush) {
+        CU(c, cudaMalloc(&c->flush, bytes));
+        c->flush_bytes = bytes;
+    }
+    CU(c, cudaMemsetAsync(c->flush, 0x5a, c->flush_bytes, c->stream));
+    return RQ_CUDA_OK;
+}
+
+}  // extern "C"

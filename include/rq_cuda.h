@@ -1,0 +1,167 @@
+/* rq_cuda.h — C ABI of librq_cuda.so: gwenedeg's attention hot path on an NVIDIA B200 (sm_100a).
+ *
+ * gwenedeg (a CPU inference engine in C, API prefix rq_) computes attention inside three worker functions of its
+ * src/forward.c, per work item, with static functions.  This library replaces exactly those items: the host keeps
+ * its forward pass (embedding, matmuls, norms, RoPE, sampling, scheduling) and, once per layer, hands the rows of
+ * the pass to the GPU for (1) the K / V cache store, (2) the attention over the cached positions, or (3) the Gated
+ * DeltaNet recurrence.  The KV cache and the DeltaNet state live in device memory, in the reference's own tile
+ * layout, owned by RqCudaSeq objects that shadow the host's RqSeq.
+ *
+ * Conventions follow src/runq.h of the reference: every function returns RQ_OK (0) or a negative RQ_ERR_* code,
+ * nothing prints or exits, all arguments are checked before any work is started (a refused call leaves caches and
+ * state untouched), details of the last error of a context are in rq_cuda_error().  A context is used by one host
+ * thread at a time (runq.h:14-17).  Results of a row never depend on the other rows of the pass, on how the pass
+ * was chunked, or on the device the sequence lives on (runq.h:22).
+ *
+ * There is no CPU fallback: without a CUDA device every entry point that needs one fails with RQ_ERR_DEVICE.
+ */
+#ifndef RQ_CUDA_H
+#define RQ_CUDA_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* error codes: the values of src/runq.h:35-44, plus one of this library's own */
+enum {
+    RQ_CUDA_OK = 0,
+    RQ_CUDA_ERR_ARG = -1,     /* invalid argument */
+    RQ_CUDA_ERR_NOMEM = -2,   /* host or device allocation failed */
+    RQ_CUDA_ERR_CONTEXT = -3, /* positions do not fit in the sequence's capacity */
+    RQ_CUDA_ERR_STATE = -4,   /* not possible on this object / in this state (e.g. no pass open, device wait expired) */
+    RQ_CUDA_ERR_DEVICE = -16  /* no usable CUDA device, or a CUDA call failed (text in rq_cuda_error) */
+};
+
+/* KV cache element types: the values of RQ_KV_* (src/runq.h:214-215) for the types this library implements
+ * (the fp32-arithmetic attention over f32 / f16 / q8 / q4 / q4k4 caches; src/kvtype.h:12-29) */
+enum { RQ_CUDA_KV_F32 = 0, RQ_CUDA_KV_F16 = 2, RQ_CUDA_KV_Q8 = 3, RQ_CUDA_KV_Q4 = 8, RQ_CUDA_KV_Q4K4 = 9 };
+
+typedef struct RqCuda RqCuda;       /* a compute context on one device: stream, scratch, the open pass (RqCtx, forward.c:32) */
+typedef struct RqCudaSeq RqCudaSeq; /* a sequence's device-resident KV cache and DeltaNet state (RqSeq, internal.h:353) */
+
+/* Shapes of the model's attention path (Config / Hybrid of src/internal.h:75-104, the derived values of
+ * forward_model_init, forward.c:129).  kv_head0 / kv_heads_local select the contiguous group of KV heads this
+ * device holds (0 / n_kv_heads: all of them); q and out rows then carry only that group's query heads. */
+typedef struct {
+    int n_attn;         /* attention layers = layers of the KV cache (RqModel.n_attn) */
+    int n_heads;        /* query heads */
+    int n_kv_heads;     /* KV heads; n_heads % n_kv_heads == 0 */
+    int head_dim;       /* 64, 128 or 256 */
+    int gated;          /* Qwen3.5 gated attention: query rows are [q | gate] per head (qh = 2 head_dim, forward.c:134) */
+    int n_lin;          /* Gated DeltaNet layers (Hybrid.n_lin), 0 for Qwen3 */
+    int dn_nk, dn_nv;   /* DeltaNet key heads / value heads (nv % nk == 0) */
+    int dn_dk, dn_dv;   /* DeltaNet key / value head dims (128) */
+    int dn_conv;        /* causal conv taps (4) */
+    int kv_head0;       /* first KV head held by this context's sequences */
+    int kv_heads_local; /* KV heads held (0: all) */
+} RqCudaModel;
+
+/* One segment of a pass: n consecutive rows of one sequence at positions pos0 .. pos0 + n - 1 (RqSegment,
+ * runq.h:364-374; pos0 is the sequence's length in the reference, passed explicitly here because the host owns it).
+ * Row r of the segment attends positions 0 .. pos0 + r. */
+typedef struct {
+    RqCudaSeq *seq;
+    int pos0;
+    int n;
+} RqCudaSegment;
+
+/* ---- context (rq_ctx_new / rq_ctx_free / rq_ctx_error, runq.h:317-335) ------------------------------------ */
+int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ctx);
+void rq_cuda_free(RqCuda *ctx);
+const char *rq_cuda_error(const RqCuda *ctx);
+int rq_cuda_device_count(void);
+/* block until everything this context launched is complete; reports a device-side wait that expired as RQ_CUDA_ERR_STATE */
+int rq_cuda_sync(RqCuda *ctx);
+/* run this context's work on a caller-owned stream (a cudaStream_t; NULL: back to the context's own) */
+int rq_cuda_set_stream(RqCuda *ctx, void *cuda_stream);
+
+/* ---- sequences (rq_seq_new :148, rq_seq_free :192, rq_seq_truncate :409, rq_seq_copy :553 of forward.c) ---- */
+/* capacity positions (rounded up to whole 256-position blocks inside), cache type kv_type; DeltaNet state zeroed */
+int rq_cuda_seq_new(RqCuda *ctx, int capacity, int kv_type, RqCudaSeq **seq);
+void rq_cuda_seq_free(RqCudaSeq *seq);
+int rq_cuda_seq_len(const RqCudaSeq *seq);      /* positions stored so far (passes grow it, as seq_grow does) */
+int rq_cuda_seq_capacity(const RqCudaSeq *seq);
+int rq_cuda_seq_truncate(RqCudaSeq *seq, int n); /* keep the first n positions (attention layers only, as the reference) */
+/* the first n positions of src (same context, type and capacity class) into dst; the DeltaNet state is copied
+ * when n == rq_cuda_seq_len(src) */
+int rq_cuda_seq_copy(RqCudaSeq *dst, const RqCudaSeq *src, int n);
+/* bytes of one layer's K (is_v 0) or V (is_v 1) cache; raw transfer of one layer in the reference's byte layout
+ * (blocks of 256 positions x KV heads x 16-position tiles; forward.c:1894, kernels_avx512.h:1090-1107), the format
+ * of the reference's saved sequences (seqfile.c) */
+size_t rq_cuda_seq_layer_bytes(const RqCudaSeq *seq, int is_v);
+int rq_cuda_seq_read_kv(RqCudaSeq *seq, int layer, int is_v, void *host, size_t bytes);
+int rq_cuda_seq_write_kv(RqCudaSeq *seq, int layer, int is_v, const void *host, size_t bytes, int new_len);
+/* DeltaNet state of one linear layer (floats: conv inputs, then S per value head in [dv/32][dk][32] blocks;
+ * forward.c:125, :2090) */
+size_t rq_cuda_seq_state_floats(const RqCudaSeq *seq);
+int rq_cuda_seq_read_state(RqCudaSeq *seq, int lin_layer, float *host);
+int rq_cuda_seq_write_state(RqCudaSeq *seq, int lin_layer, const float *host);
+/* test / benchmark hook (rq_seq_fill_synthetic, forward.c:2418): n positions of seeded pseudo-random K / V written by
+ * a device kernel — f32 / f16: ~N(0,1) values; q8 / q4: uniform levels and bf16 scales ~|N(0, 0.02)| in the tile
+ * format — and the length set to n */
+int rq_cuda_seq_fill_synthetic(RqCudaSeq *seq, int n, unsigned long long seed);
+
+/* ---- a pass (rq_forward_batch, forward.c:3762; rq_decode :2815 is a pass of one row) ---------------------- */
+/* Opens a pass over the rows of nseg segments (a sequence at most once; 1 <= total rows <= max_rows; every row
+ * inside its sequence's capacity).  Row order = segment order, rows of a segment in position order.  Uploads the
+ * row table once; the per-layer calls below refer to "the rows of the pass". */
+int rq_cuda_pass_begin(RqCuda *ctx, const RqCudaSegment *seg, int nseg);
+/* closes the pass; commit != 0 grows each sequence's length to pos0 + n (seq_grow) */
+int rq_cuda_pass_end(RqCuda *ctx, int commit);
+
+/* K and V rows of the pass into the caches of attention layer `layer`, replacing kv_store (forward.c:1901; call
+ * sites :2682/:2686, :3067-3085, :3568-3578).  k, v: host fp32 [rows][kv_heads_local][head_dim], after QK-norm and
+ * RoPE; either may be NULL.  f16: round to nearest even, saturating (f32_f16 :1325); q8 / q4: rotate + quantise
+ * (kvq_store :1710). */
+int rq_cuda_kv_store(RqCuda *ctx, int layer, const float *k, const float *v);
+int rq_cuda_kv_store_dev(RqCuda *ctx, int layer, const float *k_dev, const float *v_dev);
+
+/* Attention of every row of the pass over its sequence's cache of layer `layer`: split-K flash-decode over the
+ * reference's fixed 256-position blocks with the partial results merged in block order, replacing the attention
+ * items of decode_worker (forward.c:2691-2715) and batch_decode_worker (:3582-3616): attention_part :1806 +
+ * att_combine :1405, with att_q_rot :1662 before and att_o_unrot :1672 / attn_gate :2291 after.
+ * q: host fp32 [rows][heads_local][qh] (qh = head_dim, or 2 head_dim when gated), out: host fp32
+ * [rows][heads_local][head_dim].  Softmax scale 1/sqrt(head_dim). */
+int rq_cuda_attn_decode(RqCuda *ctx, int layer, const float *q, float *out);
+int rq_cuda_attn_decode_dev(RqCuda *ctx, int layer, const float *q_dev, float *out_dev);
+
+/* The same attention for passes with many rows per sequence (prompt chunks), replacing prefill_worker's items
+ * (forward.c:3096-3146, attention_kv :1871): tensor-core tiles over the cached prefix plus the chunk's own rows,
+ * causal per row.  Same arguments and layouts as rq_cuda_attn_decode. */
+int rq_cuda_attn_prefill(RqCuda *ctx, int layer, const float *q, float *out);
+int rq_cuda_attn_prefill_dev(RqCuda *ctx, int layer, const float *q_dev, float *out_dev);
+
+/* Gated DeltaNet recurrence of linear layer `lin_layer` over the rows of the pass, replacing dn_rec_run
+ * (forward.c:2224; call sites :2640-2650, :3018-3027).  rows: fp32 [rows][lw], lw = 2 nk dk + 2 nv dv + 2 nv, laid
+ * out [q | k | v | z | exp(g) | beta] as dn_prep_part (:2104) leaves them; out: fp32 [rows][nv dv], the raw S^T q.
+ * A segment starting at position 0 clears its state first.  The state is advanced in place. */
+int rq_cuda_dn_rec(RqCuda *ctx, int lin_layer, const float *rows, float *out);
+int rq_cuda_dn_rec_dev(RqCuda *ctx, int lin_layer, const float *rows_dev, float *out_dev);
+
+/* ---- device memory and timing helpers for hosts without a CUDA runtime of their own (ctypes, cgo, JNI) ---- */
+int rq_cuda_malloc(RqCuda *ctx, size_t bytes, void **dev);
+int rq_cuda_mfree(RqCuda *ctx, void *dev);
+int rq_cuda_malloc_host(RqCuda *ctx, size_t bytes, void **host); /* pinned */
+int rq_cuda_mfree_host(RqCuda *ctx, void *host);
+int rq_cuda_memcpy_h2d(RqCuda *ctx, void *dev, const void *host, size_t bytes); /* async on the context's stream */
+int rq_cuda_memcpy_d2h(RqCuda *ctx, void *host, const void *dev, size_t bytes); /* async on the context's stream */
+int rq_cuda_mem_info(RqCuda *ctx, size_t *free_bytes, size_t *total_bytes);
+/* CUDA events on the context's stream: start, then stop returns the milliseconds between them (stop synchronises) */
+int rq_cuda_timer_start(RqCuda *ctx);
+int rq_cuda_timer_stop(RqCuda *ctx, float *ms);
+/* kernels launched by this context since it was created */
+unsigned long long rq_cuda_launch_count(const RqCuda *ctx);
+/* per-launch device time of the attention's dominant kernel (the per-block partial kernel): between _begin and _end
+ * every launch is bracketed by CUDA events on the context's stream (no synchronisation is added); _end waits for the
+ * stream and returns the summed milliseconds and the number of launches timed (at most max_launches) */
+int rq_cuda_profile_begin(RqCuda *ctx, int max_launches);
+int rq_cuda_profile_end(RqCuda *ctx, float *total_ms, int *launches);
+/* write `bytes` of device scratch (evicts the L2 between timed iterations of small workloads) */
+int rq_cuda_flush_l2(RqCuda *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RQ_CUDA_H */

@@ -1,0 +1,143 @@
+"""Parity of the CUDA decode attention (through the C ABI) with the CPU checker on identical seeded inputs.
+
+Bar (fp32 outputs): max-abs <= 2e-3 and relative L2 <= 1e-3; cache bytes and dequantised values bit-exact.  The
+kernels follow the reference's operation order, so the outputs are in fact expected to match bit for bit, which
+is asserted separately.
+"""
+import numpy as np
+import pytest
+
+from tests.helpers import assert_close, bit_equal, kv_rows, oracle_cache
+
+pytestmark = pytest.mark.gpu
+
+F16, Q8, Q4, Q4K4 = 2, 3, 8, 9
+# the contexts the reference's own invariant tests walk over: tile and 256-block edges
+CONTEXTS = [1, 15, 16, 17, 255, 256, 257, 511, 513, 700]
+
+
+def make_ctx(**kw):
+    import gwenedeg_b200 as g
+    return g.Context(0, **kw)
+
+
+@pytest.mark.parametrize("kvt", [F16, Q8, Q4, Q4K4])
+@pytest.mark.parametrize("n_heads,n_kv,hd,gated", [(4, 2, 128, False), (8, 2, 128, False), (2, 2, 64, False),
+                                                    (8, 1, 128, False), (4, 1, 256, True), (6, 2, 128, False)])
+def test_store_and_decode_match_cpu(checker, port, kvt, n_heads, n_kv, hd, gated):
+    from gwenedeg_b200 import synth
+    n = 700
+    c = make_ctx(n_attn=2, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, gated=gated, max_rows=512)
+    k, v = kv_rows(kvt * 100 + hd + n_heads, n, n_kv, hd)
+    # the device cache, written through rq_cuda_kv_store in two chunks (a prompt chunk, then the rest), layer 1
+    s = c.new_seq(n, kvt)
+    for lo, hi in ((0, 300), (300, n)):
+        c.pass_begin([(s, lo, hi - lo)])
+        c.kv_store(1, k[lo:hi], v[lo:hi])
+        c.pass_end()
+    assert s.len == n
+    kl, vl = oracle_cache(port, kvt, n_kv, hd, k, v)  # the definition's bytes (IEEE division)
+    gk, gv = s.read_kv(1, 0), s.read_kv(1, 1)
+    nbytes_k = (n + 255) // 256 * 16 * n_kv * port.tile_bytes(kvt, hd, 0)
+    # positions past n inside the last tile are never written: compare the stored positions through the dequantiser
+    for b in range((n + 255) // 256):
+        for g_ in range(n_kv):
+            ntl = min(16, (n - b * 256 + 15) // 16)
+            kf, vf = port.block_f32(kvt, kl, vl, n_kv, hd, g_, b, ntl)
+            kf2, vf2 = port.block_f32(kvt, gk[:nbytes_k], gv, n_kv, hd, g_, b, ntl)
+            last = n - b * 256 - (ntl - 1) * 16  # valid positions of the last tile
+            assert bit_equal(kf[:ntl - 1], kf2[:ntl - 1]) and bit_equal(kf[-1][:, :last], kf2[-1][:, :last])
+            assert bit_equal(vf[:ntl - 1], vf2[:ntl - 1]) and bit_equal(vf[-1][:last], vf2[-1][:last])
+    # decode rows at the edge contexts: one sequence copy per row, all in one ragged pass
+    qh = hd * (2 if gated else 1)
+    q = synth.normal(kvt * 7 + hd, (len(CONTEXTS), n_heads, qh))
+    seqs = []
+    for ctx_len in CONTEXTS:
+        t = c.new_seq(n, kvt)
+        t.copy_from(s, n)
+        seqs.append(t)
+    c.pass_begin([(t, ctx_len - 1, 1) for t, ctx_len in zip(seqs, CONTEXTS)])
+    got = c.attn_decode(1, q)
+    c.pass_end(commit=False)
+    # the CPU checker on the device's own cache bytes
+    want = checker.attention(kvt, gk, gv, n_kv, n_heads, hd, q, np.array(CONTEXTS, np.int32), gated=gated, split=1)
+    assert_close(got, want, f"decode kvt={kvt}")
+    assert bit_equal(got, want), "decode attention is expected to equal the CPU code bit for bit"
+    # a row alone gives the bits it gave in the batch
+    for i in (0, 4, 9):
+        c.pass_begin([(seqs[i], CONTEXTS[i] - 1, 1)])
+        alone = c.attn_decode(1, q[i:i + 1])
+        c.pass_end(commit=False)
+        assert bit_equal(alone[0], got[i])
+    c.close()
+
+
+def test_prompt_chunk_rows_match_cpu(checker):
+    """Rows of a chunk (consecutive positions of one sequence, causal) plus decode rows of other sequences."""
+    from gwenedeg_b200 import synth
+    n_heads, n_kv, hd, n = 4, 2, 128, 300
+    c = make_ctx(n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd)
+    k, v = kv_rows(77, n, n_kv, hd)
+    a, b = c.new_seq(n, F16), c.new_seq(n, F16)
+    c.pass_begin([(a, 0, n)])
+    c.kv_store(0, k, v)
+    c.pass_end()
+    b.copy_from(a, 260)
+    q = synth.normal(5, (21, n_heads, hd))
+    c.pass_begin([(a, 248, 20), (b, 259, 1)])   # a 20-row chunk across the 256 edge + one decode row
+    got = c.attn_prefill(0, q)
+    c.pass_end(commit=False)
+    gk, gv = a.read_kv(0, 0), a.read_kv(0, 1)
+    npr = np.array(list(range(249, 269)) + [260], np.int32)
+    want = checker.attention(F16, gk, gv, n_kv, n_heads, hd, q, npr)
+    assert_close(got, want, "chunk rows")
+    c.close()
+
+
+def test_fill_synthetic_and_large_ragged_batch(checker):
+    """Device-filled caches at Qwen3-8B head shapes, ragged contexts; the CPU checker runs on the downloaded bytes."""
+    from gwenedeg_b200 import synth
+    n_heads, n_kv, hd = 32, 8, 128
+    ctxs = [512, 777, 4096, 2049]
+    for kvt in (F16, Q8):
+        c = make_ctx(n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd)
+        seqs = []
+        for i, n in enumerate(ctxs):
+            s = c.new_seq(n, kvt)
+            s.fill_synthetic(n, 1234 + i)
+            seqs.append(s)
+        q = synth.normal(9, (len(ctxs), n_heads, hd))
+        c.pass_begin([(s, n - 1, 1) for s, n in zip(seqs, ctxs)])
+        got = c.attn_decode(0, q)
+        c.pass_end(commit=False)
+        for i, (s, n) in enumerate(zip(seqs, ctxs)):
+            want = checker.attention(kvt, s.read_kv(0, 0), s.read_kv(0, 1), n_kv, n_heads, hd, q[i:i + 1], np.array([n], np.int32),
+                                     split=1)
+            assert_close(got[i:i + 1], want, f"ragged kvt={kvt} ctx={n}")
+            assert bit_equal(got[i:i + 1], want)
+        c.close()
+
+
+def test_argument_errors_leave_state_untouched():
+    import gwenedeg_b200 as g
+    c = make_ctx(n_attn=1, n_heads=4, n_kv_heads=2, head_dim=128, max_rows=8)
+    s = c.new_seq(100, F16)
+    with pytest.raises(g.RqCudaError) as e:
+        c.pass_begin([(s, 99, 2)])           # runs past the capacity
+    assert e.value.code == -3
+    with pytest.raises(g.RqCudaError) as e:
+        c.pass_begin([(s, 0, 9)])            # more rows than the context allows
+    assert e.value.code == -1
+    with pytest.raises(g.RqCudaError) as e:
+        c.pass_begin([(s, 5, 1)])            # a gap after the sequence's length
+    assert e.value.code == -1
+    with pytest.raises(g.RqCudaError) as e:
+        c.pass_begin([(s, 0, 1), (s, 1, 1)])  # a sequence twice
+    assert e.value.code == -1
+    with pytest.raises(g.RqCudaError) as e:
+        c.attn_decode(0, np.zeros((1, 4, 128), np.float32))  # no pass open
+    assert e.value.code == -4
+    assert s.len == 0
+    with pytest.raises(g.RqCudaError):
+        c.new_seq(10, 1)                     # bf16 caches are not implemented on the device
+    c.close()
