@@ -233,7 +233,8 @@ def run_ours(args, rank, local_rank, world):
             c.check(c.L.rq_cuda_attn_decode(c.h, l % n_distinct, q_host[l].ctypes.data, out_host[l].ctypes.data))
         c.pass_end(commit=False)
 
-    for _ in range(max(args.warmup, 3)):
+    warm = args.warmup if args.small else max(args.warmup, 3)
+    for _ in range(warm):
         step_resident()
     c.sync()
     barrier()
@@ -253,17 +254,20 @@ def run_ours(args, rank, local_rank, world):
     launches = int(reduce_sum(launches))
 
     # end to end through the host-buffer entry point: pinned host q -> device, attention, result -> host, per layer
-    step_e2e()
-    c.sync()
-    barrier()
-    t0 = time.perf_counter()
-    c.timer_start()
-    for _ in range(args.steps):
+    if args.small:
+        ms_e2e = float("nan")
+    else:
         step_e2e()
-    ms_e2e = c.timer_stop()
-    wall_e2e = (time.perf_counter() - t0) * 1e3
-    barrier()
-    ms_e2e = reduce_max(max(ms_e2e, wall_e2e))
+        c.sync()
+        barrier()
+        t0 = time.perf_counter()
+        c.timer_start()
+        for _ in range(args.steps):
+            step_e2e()
+        ms_e2e = c.timer_stop()
+        wall_e2e = (time.perf_counter() - t0) * 1e3
+        barrier()
+        ms_e2e = reduce_max(max(ms_e2e, wall_e2e))
 
     peak, how = peaks()
     bytes_per_launch = my_pos * KV_BYTES_PER_POS
@@ -279,10 +283,11 @@ def run_ours(args, rank, local_rank, world):
                 cpu = {"value": None, "unit": "rows/s", "cores": 0, "kind": "unavailable", "sample": repr(e)}
         value = N_SEQ * args.steps / (ms_max * 1e-3)
         line = {
-            "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "qwen3-8b-decode-b64-ragged", "sequences": N_SEQ, "layers": N_LAYERS, "heads": N_HEADS,
+            "config": {"workload": "qwen3-8b-decode-small-profile-case" if args.small else "qwen3-8b-decode-b64-ragged",
+                       "sequences": N_SEQ, "layers": N_LAYERS, "heads": N_HEADS,
                        "kv_heads": N_KV, "head_dim": HD, "kv_type": "f16", "ctx": f"U[{CTX_LO},{CTX_HI}] seed {CTX_SEED}",
                        "positions_total": int(np.sum(ctx_all)), "parallelism": f"sequence-sharded x{world}",
                        "distinct_layer_caches_rank0": n_distinct, "l2": "inputs larger than L2 (each layer pass streams "
@@ -310,7 +315,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--small", action="store_true",
+                    help="profiling case for ncu captures: 8 sequences of 4096..8192 positions, 2 layers (about 0.4 GB of "
+                         "KV per layer: larger than the L2, small enough for a multi-pass capture), no CPU / end-to-end legs")
     args = ap.parse_args()
+    if args.small:
+        global N_SEQ, N_LAYERS, CTX_LO, CTX_HI
+        N_SEQ, N_LAYERS, CTX_LO, CTX_HI = 8, 2, 4096, 8192
+        args.no_cpu = True
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

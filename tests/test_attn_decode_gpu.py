@@ -135,6 +135,7 @@ def test_argument_errors_leave_state_untouched():
         c.pass_begin([(s, 0, 1), (s, 1, 1)])  # a sequence twice
     assert e.value.code == -1
     with pytest.raises(g.RqCudaError) as e:
+        c.nrows = 1
         c.attn_decode(0, np.zeros((1, 4, 128), np.float32))  # no pass open
     assert e.value.code == -4
     assert s.len == 0
