@@ -7,11 +7,13 @@
 // operation (fp32, fused multiply-add chains over 32-dim chunks for the scores and over the positions for the
 // outputs, the 16-lane sum of exponentials and its tree), so results agree with the CPU code to the last bit.
 //
-// attn_part_kernel: one CTA of 128 threads per (block, KV head).  The K tiles of the block (64 KB at head_dim 128,
-// f16) arrive in shared memory through bulk async copies (TMA) completing on an mbarrier; every thread scores two
-// positions for all the query heads of the KV head; the V tiles then reuse the same shared-memory buffer while the
-// softmax of the block is computed; every thread accumulates one (or two) output dims over the block's positions.
-// Three CTAs fit on an SM, so the copies of two blocks are in flight while a third computes.
+// attn_part_kernel: one CTA of 64 threads per (block, KV head).  The K tiles of the block arrive in shared memory
+// through bulk async copies (TMA) completing on an mbarrier, half a block (128 positions, 32 KB at head_dim 128, f16)
+// at a time; every thread scores two adjacent positions per half for all the query heads of the KV head with packed
+// fp32x2 fused multiply-adds (lanes = a pair of query vectors), keeping the scores in registers; the V tiles then
+// reuse the same shared-memory buffer while the softmax of the block is computed; every thread accumulates two
+// adjacent output dims over the block's positions.  The small buffer lets six CTAs share an SM: the copies of some
+// are in flight while the others compute.
 // attn_combine_kernel: one CTA per (row, query head) merges the partials, un-rotates (q8 / q4) and gates the output.
 #pragma once
 #include <type_traits>
@@ -30,93 +32,132 @@ struct PassRow {
     int pos;                     // the row's own position (np - 1)
 };
 
-constexpr int DEC_THREADS = 128;
+constexpr int DEC_THREADS = 64;
 
 template <int KVT, int HD>
 struct DecCfg {
     static constexpr int KF = kv_fmt(KVT, 0), VF = kv_fmt(KVT, 1);
     static constexpr int KTB = kv_tile_bytes(KVT, HD, 0), VTB = kv_tile_bytes(KVT, HD, 1);
     // positions per stage: a 16-bit cache at head_dim 256 is streamed in two halves of 128 positions
-    static constexpr int STAGES = (KF == KV_F16 && HD == 256) ? 2 : 1;
+    static constexpr int STAGES = (KF == KV_F16 && HD >= 128) ? 2 : 1;
     static constexpr int ST_TILES = ATT_PT / STAGES;
     static constexpr int ST_POS = ATT_P / STAGES;
+    static constexpr int PPT = ST_POS / DEC_THREADS;  // adjacent positions a thread scores per stage: 4 or 2
     // bytes the 16 positions of one dim (pair) occupy in a K tile: the padding that spreads the tiles a warp reads
-    // at once over different banks
+    // at once over different shared-memory banks
     static constexpr int KPAD = KF == KV_F16 ? 32 : 16;
     static constexpr int KSTRIDE = KTB + KPAD;
     static constexpr int KBUF = ST_TILES * KSTRIDE, VBUF = ST_TILES * VTB;
     static constexpr int BUF = (KBUF > VBUF ? KBUF : VBUF);
-    static constexpr int DPT = HD > 128 ? HD / 128 : 1;  // output dims per thread
+    static constexpr int DPT = HD / DEC_THREADS;  // adjacent output dims per thread: 1, 2 or 4
 };
 
-__host__ __device__ inline size_t dec_smem_bytes(int buf, int hd, int nvt) {
-    // kv buffer | q [groups][hd][4] | e [256][nvt] | reductions [4][nvt] + m[nvt] + l[nvt] | barrier
-    int ngrp = (nvt + 3) / 4;
-    return (size_t)buf + (size_t)ngrp * hd * 4 * 4 + (size_t)ATT_P * nvt * 4 + (size_t)6 * nvt * 4 + 16 + 64;
+// shared memory of one CTA: kv buffer | q [HD][NVT], later e [256][NVT] | rotation scratch (q8 / q4) | reductions |
+// barrier
+__host__ __device__ constexpr size_t dec_smem_bytes(int buf, int hd, int nvt, bool quant) {
+    return (size_t)buf + (size_t)ATT_P * nvt * 4 + (quant ? (size_t)nvt * hd * 4 : 0) + (size_t)4 * nvt * 4 + 16 + 32;
 }
 
-// dims i of positions (2 jp, 2 jp + 1) of a K tile
-template <int KF, int HD>
-__device__ __forceinline__ void load_k2(const uint8_t *kt, int i, int jp, float d0, float d1, float &k0, float &k1) {
+// dim i of PPT adjacent positions (first one: j0) of a K tile; d: the bf16 scales of those positions for dim i's
+// 32-dim chunk (quantised formats: value = level x scale, exact in fp32)
+template <int KF, int PPT>
+__device__ __forceinline__ void load_k(const uint8_t *kt, int i, int j0, const float *d, float *k) {
     if constexpr (KF == KV_F16) {
-        __half2 h = *reinterpret_cast<const __half2 *>(kt + (size_t)i * 32 + jp * 4);
-        k0 = __low2float(h);
-        k1 = __high2float(h);
-    } else if constexpr (KF == KV_Q8) {
-        uint32_t w = *reinterpret_cast<const uint16_t *>(kt + (size_t)i * 16 + jp * 2);
-        k0 = (float)(int)(int8_t)(w & 0xff) * d0;
-        k1 = (float)(int)(int8_t)(w >> 8) * d1;
-    } else {  // q4: byte [dim pair][position], low nibble dim 2p, high nibble dim 2p + 1
-        uint32_t w = *reinterpret_cast<const uint16_t *>(kt + (size_t)(i >> 1) * 16 + jp * 2);
-        int sh = 4 * (i & 1);
-        k0 = (float)((int)((w >> sh) & 15) - 8) * d0;
-        k1 = (float)((int)((w >> (8 + sh)) & 15) - 8) * d1;
+        if constexpr (PPT == 4) {
+            uint2 w = *reinterpret_cast<const uint2 *>(kt + (size_t)i * 32 + j0 * 2);
+            float2 f0 = __half22float2(*reinterpret_cast<__half2 *>(&w.x)), f1 = __half22float2(*reinterpret_cast<__half2 *>(&w.y));
+            k[0] = f0.x; k[1] = f0.y; k[2] = f1.x; k[3] = f1.y;
+        } else {
+            float2 f = __half22float2(*reinterpret_cast<const __half2 *>(kt + (size_t)i * 32 + j0 * 2));
+            k[0] = f.x; k[1] = f.y;
+        }
+    } else {
+        uint32_t w;
+        if constexpr (KF == KV_Q8) {
+            if constexpr (PPT == 4) w = *reinterpret_cast<const uint32_t *>(kt + (size_t)i * 16 + j0);
+            else w = *reinterpret_cast<const uint16_t *>(kt + (size_t)i * 16 + j0);
+#pragma unroll
+            for (int p = 0; p < PPT; p++) k[p] = (float)(int)(int8_t)((w >> (8 * p)) & 0xff) * d[p];
+        } else {  // q4: byte [dim pair][position], low nibble dim 2p, high nibble dim 2p + 1
+            if constexpr (PPT == 4) w = *reinterpret_cast<const uint32_t *>(kt + (size_t)(i >> 1) * 16 + j0);
+            else w = *reinterpret_cast<const uint16_t *>(kt + (size_t)(i >> 1) * 16 + j0);
+            const int sh = 4 * (i & 1);
+#pragma unroll
+            for (int p = 0; p < PPT; p++) k[p] = (float)((int)((w >> (8 * p + sh)) & 15) - 8) * d[p];
+        }
     }
 }
 
-// dim i of position j of a K tile (head_dim 256, f16 only)
-template <int KF, int HD>
-__device__ __forceinline__ float load_k1(const uint8_t *kt, int i, int j) {
-    return __half2float(*reinterpret_cast<const __half *>(kt + ((size_t)i * 16 + j) * 2));
-}
-
-// bf16 scale of (chunk c, position j) of a quantised K tile
-template <int KF, int HD>
-__device__ __forceinline__ float k_scale(const uint8_t *kt, int c, int j) {
+// the bf16 scales of chunk c for PPT adjacent positions (first one: j0) of a quantised K tile
+template <int KF, int HD, int PPT>
+__device__ __forceinline__ void k_scales(const uint8_t *kt, int c, int j0, float *d) {
     constexpr int off = (KF == KV_Q4 ? 8 : 16) * HD;
-    return bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(kt + off + (c * 16 + j) * 2));
-}
-
-// dim i of position j of a V tile
-template <int VF, int HD>
-__device__ __forceinline__ float load_v(const uint8_t *vt, int j, int i) {
-    if constexpr (VF == KV_F16) {
-        return __half2float(*reinterpret_cast<const __half *>(vt + ((size_t)j * HD + i) * 2));
-    } else if constexpr (VF == KV_Q8) {
-        float d = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(vt + 16 * HD + (j * (HD / 32) + (i >> 5)) * 2));
-        return (float)(int)*reinterpret_cast<const int8_t *>(vt + (size_t)j * HD + i) * d;
-    } else {  // q4: per position and group 16 bytes, byte l = dims 32c + l (low), 32c + 16 + l (high)
-        float d = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(vt + 8 * HD + (j * (HD / 32) + (i >> 5)) * 2));
-        uint32_t b = vt[(size_t)j * (HD / 2) + (i >> 5) * 16 + (i & 15)];
-        return (float)((int)((b >> (4 * ((i >> 4) & 1))) & 15) - 8) * d;
+    const uint8_t *p = kt + off + (c * 16 + j0) * 2;
+    if constexpr (PPT == 4) {
+        uint2 w = *reinterpret_cast<const uint2 *>(p);
+        d[0] = __uint_as_float(w.x << 16); d[1] = __uint_as_float(w.x & 0xffff0000u);
+        d[2] = __uint_as_float(w.y << 16); d[3] = __uint_as_float(w.y & 0xffff0000u);
+    } else {
+        uint32_t w = *reinterpret_cast<const uint32_t *>(p);
+        d[0] = __uint_as_float(w << 16); d[1] = __uint_as_float(w & 0xffff0000u);
     }
 }
 
-template <int KVT, int HD, int NV>
+// dims i0 .. i0 + DPT - 1 of position j of a V tile
+template <int VF, int HD, int DPT>
+__device__ __forceinline__ void load_v(const uint8_t *vt, int j, int i0, float *vv) {
+    if constexpr (VF == KV_F16) {
+        const uint8_t *p = vt + ((size_t)j * HD + i0) * 2;
+        if constexpr (DPT == 1) {
+            vv[0] = __half2float(*reinterpret_cast<const __half *>(p));
+        } else if constexpr (DPT == 2) {
+            float2 f = __half22float2(*reinterpret_cast<const __half2 *>(p));
+            vv[0] = f.x; vv[1] = f.y;
+        } else {
+            uint2 w = *reinterpret_cast<const uint2 *>(p);
+            float2 f0 = __half22float2(*reinterpret_cast<__half2 *>(&w.x)), f1 = __half22float2(*reinterpret_cast<__half2 *>(&w.y));
+            vv[0] = f0.x; vv[1] = f0.y; vv[2] = f1.x; vv[3] = f1.y;
+        }
+    } else if constexpr (VF == KV_Q8) {
+        const float d = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(vt + 16 * HD + (j * (HD / 32) + (i0 >> 5)) * 2));
+        const int8_t *p = reinterpret_cast<const int8_t *>(vt + (size_t)j * HD + i0);
+        if constexpr (DPT == 1) {
+            vv[0] = (float)(int)p[0] * d;
+        } else if constexpr (DPT == 2) {
+            uint32_t w = *reinterpret_cast<const uint16_t *>(p);
+            vv[0] = (float)(int)(int8_t)(w & 0xff) * d; vv[1] = (float)(int)(int8_t)(w >> 8) * d;
+        } else {
+            uint32_t w = *reinterpret_cast<const uint32_t *>(p);
+#pragma unroll
+            for (int x = 0; x < 4; x++) vv[x] = (float)(int)(int8_t)((w >> (8 * x)) & 0xff) * d;
+        }
+    } else {  // q4: per position and group 16 bytes, byte l = dims 32c + l (low nibble), 32c + 16 + l (high)
+        const float d = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(vt + 8 * HD + (j * (HD / 32) + (i0 >> 5)) * 2));
+        const uint8_t *p = vt + (size_t)j * (HD / 2) + (i0 >> 5) * 16 + (i0 & 15);
+        const int sh = 4 * ((i0 >> 4) & 1);
+#pragma unroll
+        for (int x = 0; x < DPT; x++) vv[x] = (float)((int)((p[x] >> sh) & 15) - 8) * d;
+    }
+}
+
+// NVT: query vectors a CTA handles (the query heads of one KV head, padded to 1, 2, 4 or 8)
+template <int KVT, int HD, int NVT>
 __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *__restrict__ rows, int nrows, int layer, int n_kv,
                                                                 int G, const float *__restrict__ q, int qh, int n_heads,
                                                                 float scale, float *__restrict__ part, int *err) {
     using C = DecCfg<KVT, HD>;
-    constexpr int KF = C::KF, VF = C::VF;
+    constexpr int KF = C::KF, VF = C::VF, PPT = C::PPT, DPT = C::DPT, NPOS = PPT * C::STAGES;
+    constexpr int NV = NVT < 4 ? NVT : 4, NGRP = NVT / NV;
+    constexpr bool QUANT = kv_quant(KVT);
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int NGRP = (G + NV - 1) / NV, NVT = NGRP * NV;
 
     uint8_t *buf = smem;
-    float *qs = reinterpret_cast<float *>(smem + C::BUF);  // [NGRP][HD][NV]
-    float *es = qs + (size_t)NGRP * HD * NV;               // [256][NVT]
-    float *red = es + (size_t)ATT_P * NVT;                 // [4][NVT]
-    float *ms = red + 4 * NVT, *ls = ms + NVT;             // [NVT] each
+    float *qs = reinterpret_cast<float *>(smem + C::BUF);  // q [NGRP][HD][NV] while scoring ...
+    float *es = qs;                                        // ... then e [256][NVT]
+    float *tmp = qs + (size_t)ATT_P * NVT;                 // [NVT][HD] (q8 / q4 only)
+    float *red = tmp + (QUANT ? NVT * HD : 0);               // [2][NVT]
+    float *ms = red + 2 * NVT, *ls = ms + NVT;               // [NVT] each
     uint64_t *bar = reinterpret_cast<uint64_t *>((reinterpret_cast<uintptr_t>(ls + NVT) + 15) & ~(uintptr_t)15);
 
     // which (row, block) is this CTA: rows[r].blk0 <= blockIdx.x < rows[r + 1].blk0
@@ -156,12 +197,11 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
 
     if (tid == 0) issue_k(0);
 
-    // ---- the query vectors of this KV head: q[i][v] per group of NV vectors; q8 / q4: rotated first (att_q_rot,
+    // ---- the query vectors of this KV head as q[group][dim][vector]; q8 / q4: rotated first (att_q_rot,
     // reference src/forward.c:1662: signs, butterflies h = 1, 2, 4, ..., then the exact scaling by 1 / head_dim)
     {
         const float *qrow = q + ((size_t)lo * n_heads + (size_t)g * G) * qh;
-        if constexpr (kv_quant(KVT)) {
-            float *tmp = es;  // [NVT][HD] scratch (the e array is not in use yet; NVT * HD <= 256 * NVT)
+        if constexpr (QUANT) {
             for (int e = tid; e < NVT * HD; e += DEC_THREADS) {
                 int v = e / HD, i = e % HD;
                 float x = qrow[(size_t)min(v, G - 1) * qh + i];
@@ -192,130 +232,138 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
     }
     __syncthreads();
 
-    // ---- scores: s[t] = (sum over 32-dim chunks, in order, of the fma chain over the chunk's dims) * scale
+    // ---- scores of this thread's positions, kept in registers:
+    // s[t] = (sum over 32-dim chunks, in order, of the fma chain over the chunk's dims) * scale
+    float sc[NVT][NPOS];
+    // the thread's positions of a stage: tile u, PPT adjacent positions from j0 on
+    const int u = PPT == 4 ? tid >> 2 : tid >> 3, j0 = PPT == 4 ? (tid & 3) * 4 : (tid & 7) * 2;
+#pragma unroll
     for (int stage = 0; stage < C::STAGES; stage++) {
-        if (stage * C::ST_POS >= n) break;
-        if (stage > 0) {
-            __syncthreads();  // everyone is done with the previous stage's tiles
-            if (tid == 0) {
-                fence_proxy_async();
-                issue_k(stage);
+        if (stage * C::ST_POS < n) {
+            if (stage > 0) {
+                __syncthreads();  // everyone is done with the previous stage's tiles
+                if (tid == 0) {
+                    fence_proxy_async();
+                    issue_k(stage);
+                }
             }
+            ok = mbar_wait_bounded(bar, phase & 1, err, 1) && ok;
+            phase++;
         }
-        ok = mbar_wait_bounded(bar, phase & 1, err, 1) && ok;
-        phase++;
-        if constexpr (C::STAGES == 1) {
-            const int u = tid >> 3, jp = tid & 7;
-            if (u < ntl) {
-                const uint8_t *kt = buf + (size_t)u * C::KSTRIDE;
-                for (int grp = 0; grp < NGRP; grp++) {
-                    const float *qg = qs + (size_t)grp * HD * NV;
-                    float a0[NV], a1[NV];
+        const bool have = stage * C::ST_TILES + u < ntl;  // (tiles past the block's last one are not loaded)
+        const uint8_t *kt = buf + (size_t)u * C::KSTRIDE;
 #pragma unroll
-                    for (int c = 0; c < HD / ATT_DC; c++) {
-                        float c0[NV], c1[NV];
+        for (int grp = 0; grp < NGRP; grp++) {
+            // packed fp32x2 fused multiply-adds over vector pairs: lanes (q[2vp], q[2vp + 1]) x (k, k) for each of the
+            // thread's positions; a single vector (NV == 1) takes the scalar path.  The loads of step i + PF are issued
+            // before the arithmetic of step i (software pipeline: few warps are resident, so the shared-memory latency
+            // has to be hidden inside the thread).
+            constexpr int NVP = NV / 2, PF = 3;
+            const float *qg = qs + (size_t)grp * HD * NV;
+            float2 a2[NVP > 0 ? NVP : 1][PPT], c2[NVP > 0 ? NVP : 1][PPT];
+            float a1[PPT], c1[PPT];
 #pragma unroll
-                        for (int v = 0; v < NV; v++) c0[v] = c1[v] = 0.0f;
-                        float d0 = 0.0f, d1 = 0.0f;
-                        if constexpr (KF != KV_F16) {
-                            d0 = k_scale<KF, HD>(kt, c, 2 * jp);
-                            d1 = k_scale<KF, HD>(kt, c, 2 * jp + 1);
-                        }
-#pragma unroll 8
-                        for (int ii = 0; ii < ATT_DC; ii++) {
-                            const int i = c * ATT_DC + ii;
-                            float k0, k1;
-                            load_k2<KF, HD>(kt, i, jp, d0, d1, k0, k1);
-                            float qq[NV];
-                            if constexpr (NV == 4) {
-                                float4 t4 = *reinterpret_cast<const float4 *>(qg + (size_t)i * 4);
-                                qq[0] = t4.x; qq[1] = t4.y; qq[2] = t4.z; qq[3] = t4.w;
-                            } else if constexpr (NV == 2) {
-                                float2 t2 = *reinterpret_cast<const float2 *>(qg + (size_t)i * 2);
-                                qq[0] = t2.x; qq[1] = t2.y;
-                            } else {
+            for (int p = 0; p < PPT; p++) {
+                a1[p] = c1[p] = 0.0f;
 #pragma unroll
-                                for (int v = 0; v < NV; v++) qq[v] = qg[(size_t)i * NV + v];
-                            }
-#pragma unroll
-                            for (int v = 0; v < NV; v++) {
-                                c0[v] = fmaf(qq[v], k0, c0[v]);
-                                c1[v] = fmaf(qq[v], k1, c1[v]);
-                            }
-                        }
-#pragma unroll
-                        for (int v = 0; v < NV; v++) {
-                            a0[v] = c ? a0[v] + c0[v] : c0[v];
-                            a1[v] = c ? a1[v] + c1[v] : c1[v];
-                        }
+                for (int vp = 0; vp < (NVP > 0 ? NVP : 1); vp++) a2[vp][p] = c2[vp][p] = make_float2(0.0f, 0.0f);
+            }
+            if (have) {
+                float kq[PF][PPT], dsc[PPT];
+                float4 qq[PF];
+                auto fetch = [&](int i, int slot) {
+                    if constexpr (KF != KV_F16) {
+                        if ((i & (ATT_DC - 1)) == 0) k_scales<KF, HD, PPT>(kt, i / ATT_DC, j0, dsc);
                     }
-                    const int t = u * ATT_T + 2 * jp;
+                    load_k<KF, PPT>(kt, i, j0, dsc, kq[slot]);
+                    if constexpr (NV == 4) qq[slot] = *reinterpret_cast<const float4 *>(qg + (size_t)i * 4);
+                    else if constexpr (NV == 2) {
+                        float2 t2 = *reinterpret_cast<const float2 *>(qg + (size_t)i * 2);
+                        qq[slot] = make_float4(t2.x, t2.y, 0.0f, 0.0f);
+                    } else qq[slot] = make_float4(qg[i], 0.0f, 0.0f, 0.0f);
+                };
 #pragma unroll
-                    for (int v = 0; v < NV; v++) {
-                        es[(size_t)t * NVT + grp * NV + v] = a0[v] * scale;
-                        es[(size_t)(t + 1) * NVT + grp * NV + v] = a1[v] * scale;
+                for (int i = 0; i < PF; i++) fetch(i, i);
+#pragma unroll
+                for (int i = 0; i < HD; i++) {
+                    const int slot = i % PF;
+                    float kk[PPT];
+#pragma unroll
+                    for (int p = 0; p < PPT; p++) kk[p] = kq[slot][p];
+                    const float4 qv = qq[slot];
+                    if (i + PF < HD) fetch(i + PF, slot);
+                    if constexpr (NVP > 0) {
+                        const float2 qp[2] = {make_float2(qv.x, qv.y), make_float2(qv.z, qv.w)};
+#pragma unroll
+                        for (int p = 0; p < PPT; p++) {
+                            const float2 kd = make_float2(kk[p], kk[p]);
+#pragma unroll
+                            for (int vp = 0; vp < NVP; vp++) c2[vp][p] = __ffma2_rn(qp[vp], kd, c2[vp][p]);  // fma(q, k, c) per lane
+                        }
+                    } else {
+#pragma unroll
+                        for (int p = 0; p < PPT; p++) c1[p] = fmaf(qv.x, kk[p], c1[p]);
+                    }
+                    if ((i & (ATT_DC - 1)) == ATT_DC - 1) {  // end of a 32-dim chunk: chunk 0 is assigned, later ones added
+#pragma unroll
+                        for (int p = 0; p < PPT; p++) {
+                            if constexpr (NVP > 0) {
+#pragma unroll
+                                for (int vp = 0; vp < NVP; vp++) {
+                                    a2[vp][p] = i >= ATT_DC ? __fadd2_rn(a2[vp][p], c2[vp][p]) : c2[vp][p];
+                                    c2[vp][p] = make_float2(0.0f, 0.0f);
+                                }
+                            } else {
+                                a1[p] = i >= ATT_DC ? a1[p] + c1[p] : c1[p];
+                                c1[p] = 0.0f;
+                            }
+                        }
                     }
                 }
             }
-        } else {
-            const int u = tid >> 4, j = tid & 15;
-            if (stage * C::ST_TILES + u < ntl) {
-                const uint8_t *kt = buf + (size_t)u * C::KSTRIDE;
-                for (int grp = 0; grp < NGRP; grp++) {
-                    const float *qg = qs + (size_t)grp * HD * NV;
-                    float a0[NV];
 #pragma unroll
-                    for (int c = 0; c < HD / ATT_DC; c++) {
-                        float c0[NV];
+            for (int p = 0; p < PPT; p++) {
+                if constexpr (NVP > 0) {
 #pragma unroll
-                        for (int v = 0; v < NV; v++) c0[v] = 0.0f;
-#pragma unroll 8
-                        for (int ii = 0; ii < ATT_DC; ii++) {
-                            const int i = c * ATT_DC + ii;
-                            float k0 = load_k1<KF, HD>(kt, i, j);
-#pragma unroll
-                            for (int v = 0; v < NV; v++) c0[v] = fmaf(qg[(size_t)i * NV + v], k0, c0[v]);
-                        }
-#pragma unroll
-                        for (int v = 0; v < NV; v++) a0[v] = c ? a0[v] + c0[v] : c0[v];
+                    for (int vp = 0; vp < NVP; vp++) {
+                        sc[grp * NV + 2 * vp][stage * PPT + p] = a2[vp][p].x * scale;
+                        sc[grp * NV + 2 * vp + 1][stage * PPT + p] = a2[vp][p].y * scale;
                     }
-                    const int t = stage * C::ST_POS + tid;
-#pragma unroll
-                    for (int v = 0; v < NV; v++) es[(size_t)t * NVT + grp * NV + v] = a0[v] * scale;
+                } else {
+                    sc[grp * NV][stage * PPT + p] = a1[p] * scale;
                 }
             }
         }
     }
-    __syncthreads();  // all scores are in es; the K tiles are free
+
+    // ---- softmax of the block: m = max over the block's positions, e = exp_att(s - m), l = 16 lane sums + tree
+    // position of register slot x of this thread
+    auto slot_pos = [&](int x) { return (x / PPT) * C::ST_POS + u * ATT_T + j0 + (x % PPT); };
+#pragma unroll
+    for (int v = 0; v < NVT; v++) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int x = 0; x < NPOS; x++)
+            if (slot_pos(x) < n) mx = fmaxf(mx, sc[v][x]);
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) red[warp * NVT + v] = mx;
+    }
+    __syncthreads();  // (also: every thread is done with the K tiles and the staged q)
     if (tid == 0) {
         fence_proxy_async();
         issue_v(0);
     }
-
-    // ---- softmax of the block (while the V tiles arrive): m = max, e = exp_att(s - m), l = 16 lane sums + tree
-    for (int v0 = 0; v0 < NVT; v0 += 4) {  // four vectors at a time keep the registers few
-        float mx[4];
+    if (tid < NVT) ms[tid] = fmaxf(red[tid], red[NVT + tid]);
 #pragma unroll
-        for (int x = 0; x < 4; x++) mx[x] = -INFINITY;
-        for (int t = tid; t < n; t += DEC_THREADS)
+    for (int x = 0; x < NPOS; x++) {
+        const int t = slot_pos(x);
+        if (t < ntl * ATT_T) {
 #pragma unroll
-            for (int x = 0; x < 4; x++)
-                if (v0 + x < NVT) mx[x] = fmaxf(mx[x], es[(size_t)t * NVT + v0 + x]);
-#pragma unroll
-        for (int x = 0; x < 4; x++) {
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], o));
-            if (lane == 0 && v0 + x < NVT) red[warp * NVT + v0 + x] = mx[x];
-        }
-    }
-    __syncthreads();
-    if (tid < NVT) ms[tid] = fmaxf(fmaxf(red[tid], red[NVT + tid]), fmaxf(red[2 * NVT + tid], red[3 * NVT + tid]));
-    __syncthreads();
-    {
-        const int npad = ntl * ATT_T;
-        for (int e = tid; e < npad * NVT; e += DEC_THREADS) {
-            int t = e / NVT, v = e % NVT;
-            es[e] = t < n ? exp_att(es[e] - ms[v]) : 0.0f;
+            for (int v = 0; v < NVT; v++) {
+                const float m = fmaxf(red[v], red[NVT + v]);
+                es[(size_t)t * NVT + v] = t < n ? exp_att(sc[v][x] - m) : 0.0f;
+            }
         }
     }
     __syncthreads();
@@ -323,7 +371,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
         // lane j of vector v adds e[t] for t = j, j + 16, ... in order; then the tree (j + 8, + 4, + 2, + 1)
         int idx = base + tid, v = min(idx >> 4, NVT - 1), j = idx & 15;
         float s = 0.0f;
-        for (int u = 0; u < ntl; u++) s = s + es[(size_t)(u * ATT_T + j) * NVT + v];
+        for (int uu = 0; uu < ntl; uu++) s = s + es[(size_t)(uu * ATT_T + j) * NVT + v];
         s = s + __shfl_down_sync(0xffffffffu, s, 8, 16);
         s = s + __shfl_down_sync(0xffffffffu, s, 4, 16);
         s = s + __shfl_down_sync(0xffffffffu, s, 2, 16);
@@ -331,19 +379,50 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
         if (j == 0 && idx < NVT * 16) ls[v] = s;
     }
 
-    // ---- outputs: o[i] = fma chain over the block's positions, in order, of e[t] * v[t][i]; then the partial result
-    // of (row, head, block): o[hd], m, l
-    const int i0 = tid * C::DPT;
-    auto pv = [&](auto nvt_c) {
-        constexpr int NVTC = decltype(nvt_c)::value;
-        float o[C::DPT][NVTC];
+    // ---- outputs: o[i] = fma chain over the block's positions, in order, of e[t] * v[t][i], for this thread's
+    // DPT adjacent dims and all vectors
+    const int i0 = tid * DPT;
+    constexpr int NVPT = NVT / 2;
+    float2 o2[DPT][NVPT > 0 ? NVPT : 1];  // lanes: vectors (2vp, 2vp + 1)
+    float o1[DPT];                        // a single vector (NVT == 1)
 #pragma unroll
-        for (int d = 0; d < C::DPT; d++)
+    for (int d = 0; d < DPT; d++) {
+        o1[d] = 0.0f;
 #pragma unroll
-            for (int x = 0; x < NVTC; x++) o[d][x] = 0.0f;
-        for (int stage = 0; stage < C::STAGES; stage++) {
-            const int p0 = stage * C::ST_POS;
-            if (p0 >= n) break;
+        for (int vp = 0; vp < (NVPT > 0 ? NVPT : 1); vp++) o2[d][vp] = make_float2(0.0f, 0.0f);
+    }
+    // one position: e[t][.] x (v, v) per dim, accumulated per vector pair
+    auto accum = [&](const float *vv, const float2 *ee) {
+        if constexpr (NVPT > 0) {
+#pragma unroll
+            for (int d = 0; d < DPT; d++) {
+                const float2 vd = make_float2(vv[d], vv[d]);
+#pragma unroll
+                for (int vp = 0; vp < NVPT; vp++) o2[d][vp] = __ffma2_rn(ee[vp], vd, o2[d][vp]);  // fma(e, v, o) per lane
+            }
+        } else {
+#pragma unroll
+            for (int d = 0; d < DPT; d++) o1[d] = fmaf(ee[0].x, vv[d], o1[d]);
+        }
+    };
+    auto fetch_e = [&](const float *et, float2 *ee) {
+        if constexpr (NVT % 4 == 0) {
+#pragma unroll
+            for (int x = 0; x < NVT / 4; x++) {
+                float4 t4 = *reinterpret_cast<const float4 *>(et + 4 * x);
+                ee[2 * x] = make_float2(t4.x, t4.y);
+                ee[2 * x + 1] = make_float2(t4.z, t4.w);
+            }
+        } else if constexpr (NVT == 2) {
+            ee[0] = *reinterpret_cast<const float2 *>(et);
+        } else {
+            ee[0] = make_float2(et[0], 0.0f);
+        }
+    };
+#pragma unroll
+    for (int stage = 0; stage < C::STAGES; stage++) {
+        const int p0 = stage * C::ST_POS;
+        if (p0 < n) {
             if (stage > 0) {
                 __syncthreads();
                 if (tid == 0) {
@@ -353,63 +432,62 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
             }
             ok = mbar_wait_bounded(bar, phase & 1, err, 2) && ok;
             phase++;
-            if (stage == 0) __syncthreads();  // (the e values and l of every thread are visible)
-            const int cnt = min(n - p0, C::ST_POS);
-            if (i0 < HD) {
-#pragma unroll 4
-                for (int t = 0; t < cnt; t++) {
-                    const uint8_t *vt = buf + (size_t)(t >> 4) * C::VTB;
-                    float vv[C::DPT];
-                    if constexpr (VF == KV_F16 && C::DPT == 2) {
-                        __half2 h = *reinterpret_cast<const __half2 *>(vt + ((size_t)(t & 15) * HD + i0) * 2);
-                        vv[0] = __low2float(h);
-                        vv[1] = __high2float(h);
-                    } else {
+            const int cnt = min(n - p0, C::ST_POS), full = cnt >> 4;
+            const uint8_t *vt = buf;
+            const float *et = es + (size_t)p0 * NVT;
+            for (int uu = 0; uu < full; uu++, vt += C::VTB, et += ATT_T * NVT) {
+                // a whole tile with constant offsets, its loads running PF positions ahead of the arithmetic
+                constexpr int PF = 3;
+                float vv[PF][DPT];
+                float2 ee[PF][NVPT > 0 ? NVPT : 1];
 #pragma unroll
-                        for (int d = 0; d < C::DPT; d++) vv[d] = load_v<VF, HD>(vt, t & 15, i0 + d);
+                for (int j = 0; j < PF; j++) {
+                    load_v<VF, HD, DPT>(vt, j, i0, vv[j]);
+                    fetch_e(et + j * NVT, ee[j]);
+                }
+#pragma unroll
+                for (int j = 0; j < ATT_T; j++) {
+                    const int slot = j % PF;
+                    float vc[DPT];
+                    float2 ec[NVPT > 0 ? NVPT : 1];
+#pragma unroll
+                    for (int d = 0; d < DPT; d++) vc[d] = vv[slot][d];
+#pragma unroll
+                    for (int vp = 0; vp < (NVPT > 0 ? NVPT : 1); vp++) ec[vp] = ee[slot][vp];
+                    if (j + PF < ATT_T) {
+                        load_v<VF, HD, DPT>(vt, j + PF, i0, vv[slot]);
+                        fetch_e(et + (j + PF) * NVT, ee[slot]);
                     }
-                    const float *et = es + (size_t)(p0 + t) * NVTC;
-                    float ee[NVTC];
-                    if constexpr (NVTC % 4 == 0) {
-#pragma unroll
-                        for (int x = 0; x < NVTC / 4; x++) {
-                            float4 t4 = *reinterpret_cast<const float4 *>(et + 4 * x);
-                            ee[4 * x] = t4.x; ee[4 * x + 1] = t4.y; ee[4 * x + 2] = t4.z; ee[4 * x + 3] = t4.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int x = 0; x < NVTC; x++) ee[x] = et[x];
-                    }
-#pragma unroll
-                    for (int d = 0; d < C::DPT; d++)
-#pragma unroll
-                        for (int x = 0; x < NVTC; x++) o[d][x] = fmaf(ee[x], vv[d], o[d][x]);
+                    accum(vc, ec);
                 }
             }
-        }
-        if (i0 < HD) {
-#pragma unroll
-            for (int x = 0; x < NVTC; x++) {
-                if (x < G) {
-                    float *p = part + ((size_t)(row.blk0 + b) * n_heads + (size_t)g * G + x) * RQ_PSTRIDE(HD);
-#pragma unroll
-                    for (int d = 0; d < C::DPT; d++) p[i0 + d] = ok ? o[d][x] : 0.0f;
-                    if (tid == 0) {
-                        p[HD] = ms[x];
-                        p[HD + 1] = ls[x];
-                    }
-                }
+            for (int j = 0; j < (cnt & 15); j++) {
+                float vc[DPT];
+                float2 ec[NVPT > 0 ? NVPT : 1];
+                load_v<VF, HD, DPT>(vt, j, i0, vc);
+                fetch_e(et + j * NVT, ec);
+                accum(vc, ec);
             }
         }
-    };
-    switch (NVT) {
-        case 1: pv(std::integral_constant<int, 1>{}); break;
-        case 2: pv(std::integral_constant<int, 2>{}); break;
-        case 3: pv(std::integral_constant<int, 3>{}); break;
-        case 4: pv(std::integral_constant<int, 4>{}); break;
-        case 8: pv(std::integral_constant<int, 8>{}); break;
-        case 12: pv(std::integral_constant<int, 12>{}); break;
-        default: pv(std::integral_constant<int, 16>{}); break;
+    }
+
+    // ---- the partial result of (row, head, block): o[hd], m, l
+#pragma unroll
+    for (int v = 0; v < NVT; v++) {
+        if (v < G) {
+            float *p = part + ((size_t)(row.blk0 + b) * n_heads + (size_t)g * G + v) * RQ_PSTRIDE(HD);
+#pragma unroll
+            for (int d = 0; d < DPT; d++) {
+                float val;
+                if constexpr (NVPT > 0) val = (v & 1) ? o2[d][v >> 1].y : o2[d][v >> 1].x;
+                else val = o1[d];
+                p[i0 + d] = ok ? val : 0.0f;
+            }
+            if (tid == 0) {
+                p[HD] = ms[v];
+                p[HD + 1] = ls[v];
+            }
+        }
     }
 }
 
@@ -494,20 +572,19 @@ template <int KVT>
 cudaError_t launch_attn_part(int hd, const AttnPartArgs &a, cudaStream_t stream);
 
 #ifdef RQ_ATTN_DECODE_INSTANTIATE
-template <int KVT, int HD, int NV>
+template <int KVT, int HD, int NVT>
 static cudaError_t launch_one(const AttnPartArgs &a, cudaStream_t stream) {
-    const int ngrp = (a.G + NV - 1) / NV, nvt = ngrp * NV;
-    const size_t smem = dec_smem_bytes(DecCfg<KVT, HD>::BUF, HD, nvt);
+    constexpr size_t smem = dec_smem_bytes(DecCfg<KVT, HD>::BUF, HD, NVT, kv_quant(KVT));
+    static_assert(smem <= 227 * 1024, "one CTA's shared memory");
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kern = attn_part_kernel<KVT, HD, NV>;
+    auto kern = attn_part_kernel<KVT, HD, NVT>;
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    if (smem > 227 * 1024) return cudaErrorInvalidValue;
     kern<<<dim3(a.total_blocks, a.n_kv), DEC_THREADS, smem, stream>>>(a.rows, a.nrows, a.layer, a.n_kv, a.G, a.q, a.qh, a.n_heads,
                                                                    a.scale, a.part, a.err);
     return cudaGetLastError();
@@ -515,10 +592,11 @@ static cudaError_t launch_one(const AttnPartArgs &a, cudaStream_t stream) {
 
 template <int KVT, int HD>
 static cudaError_t launch_hd(const AttnPartArgs &a, cudaStream_t stream) {
-    if (a.G < 1 || a.G > 16) return cudaErrorInvalidValue;
+    if (a.G < 1 || a.G > 8) return cudaErrorInvalidValue;
     if (a.G == 1) return launch_one<KVT, HD, 1>(a, stream);
     if (a.G == 2) return launch_one<KVT, HD, 2>(a, stream);
-    return launch_one<KVT, HD, 4>(a, stream);
+    if (a.G <= 4) return launch_one<KVT, HD, 4>(a, stream);
+    return launch_one<KVT, HD, 8>(a, stream);
 }
 
 template <int KVT>
@@ -531,9 +609,9 @@ cudaError_t launch_attn_part(int hd, const AttnPartArgs &a, cudaStream_t stream)
 
 template <int KVT>
 size_t attn_part_smem(int hd, int G) {
-    const int nv = G >= 3 ? 4 : G, nvt = (G + nv - 1) / nv * nv;
+    const int nvt = G == 1 ? 1 : G == 2 ? 2 : G <= 4 ? 4 : 8;
     const int buf = hd == 64 ? DecCfg<KVT, 64>::BUF : hd == 128 ? DecCfg<KVT, 128>::BUF : hd == 256 ? DecCfg<KVT, 256>::BUF : 0;
-    return buf ? dec_smem_bytes(buf, hd, nvt) : 0;
+    return buf ? dec_smem_bytes(buf, hd, nvt, kv_quant(KVT)) : 0;
 }
 #endif
 

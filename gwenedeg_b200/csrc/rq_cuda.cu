@@ -119,7 +119,7 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
     if (m.n_attn < 0 || m.n_lin < 0 || (m.n_attn == 0 && m.n_lin == 0)) return RQ_CUDA_ERR_ARG;
     if (m.n_attn > 0) {
         if (m.n_kv_heads < 1 || m.n_heads < 1 || m.n_heads % m.n_kv_heads) return RQ_CUDA_ERR_ARG;
-        if (m.n_heads / m.n_kv_heads > 16) return RQ_CUDA_ERR_ARG;
+        if (m.n_heads / m.n_kv_heads > 8) return RQ_CUDA_ERR_ARG;  // query heads per KV head the kernels are built for
         if (m.head_dim != 64 && m.head_dim != 128 && m.head_dim != 256) return RQ_CUDA_ERR_ARG;
         if (m.kv_head0 < 0 || nkv_local < 1 || m.kv_head0 + nkv_local > m.n_kv_heads) return RQ_CUDA_ERR_ARG;
     }
