@@ -55,6 +55,8 @@ PROTOTYPES = {
     "rq_cuda_kv_store_dev": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_attn_decode": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_attn_decode_dev": (_i, [_vp, _i, _vp, _vp]),
+    "rq_cuda_attn_decode_noalloc": (_i, [_vp, _i, _vp, _vp]),
+    "rq_cuda_attn_decode_noalloc_max_bytes": (_sz, []),
     "rq_cuda_attn_prefill": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_attn_prefill_dev": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_dn_rec": (_i, [_vp, _i, _vp, _vp]),

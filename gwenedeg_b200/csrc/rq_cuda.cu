@@ -477,11 +477,18 @@ int rq_cuda_kv_store(RqCuda *c, int layer, const float *k, const float *v) {
     return RQ_CUDA_OK;
 }
 
+static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, float *part);
+
 static int launch_decode(RqCuda *c, int layer, const float *q, float *out) {
     const int hd = c->m.head_dim;
     size_t need = (size_t)c->total_blocks * c->n_heads * RQ_PSTRIDE(hd) * 4;
     int rc = grow(c, (void **)&c->d_part, &c->part_bytes, need);
     if (rc) return rc;
+    return launch_decode_with(c, layer, q, out, c->d_part);
+}
+
+static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, float *part) {
+    const int hd = c->m.head_dim;
     AttnPartArgs a;
     a.rows = c->d_rows;
     a.nrows = c->nrows;
@@ -493,7 +500,7 @@ static int launch_decode(RqCuda *c, int layer, const float *q, float *out) {
     a.qh = c->qh;
     a.n_heads = c->n_heads;
     a.scale = 1.0f / sqrtf((float)hd);
-    a.part = c->d_part;
+    a.part = part;
     a.err = c->d_err;
     cudaError_t e;
     const bool prof = c->prof_on && (size_t)(2 * c->prof_n + 2) <= c->prof_ev.size();
@@ -511,8 +518,8 @@ static int launch_decode(RqCuda *c, int layer, const float *q, float *out) {
     dim3 grid(c->nrows, c->n_heads);
     const bool quant = kv_quant(c->pass_kvt);
 #define COMBINE(HD_)                                                                                                          \
-    if (quant) attn_combine_kernel<HD_, true><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, c->d_part, q, c->qh, c->m.gated, out); \
-    else attn_combine_kernel<HD_, false><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, c->d_part, q, c->qh, c->m.gated, out);
+    if (quant) attn_combine_kernel<HD_, true><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out); \
+    else attn_combine_kernel<HD_, false><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out);
     switch (hd) {
         case 64: COMBINE(64) break;
         case 128: COMBINE(128) break;
@@ -550,6 +557,41 @@ int rq_cuda_attn_decode(RqCuda *c, int layer, const float *q, float *out) {
     if ((rc = launch_decode(c, layer, c->d_q, c->d_out))) return rc;
     CU(c, cudaMemcpyAsync(out, c->d_out, ob, cudaMemcpyDeviceToHost, c->stream));
     return rq_cuda_sync(c);
+}
+
+// ---- decode attention without any allocation -------------------------------------------------------------------------
+// The per-block partial results of the split-K attention normally live in a buffer the context grows with cudaMalloc
+// when a pass needs more of it.  Some hosts cannot have that: a server that sized all device memory at start-up
+// and handed the rest to KV caches (an allocation in the middle of a pass can fail or stall there), and code that
+// runs where cudaMalloc is off limits because it synchronises the whole device.  For them the partials of this
+// entry point sit in the fixed array below, part of the library's image on every GPU that loads it, until exit.
+#define RQ_NOALLOC_PART_BYTES ((size_t)32 << 20)
+static __device__ __align__(256) unsigned char g_noalloc_part[RQ_NOALLOC_PART_BYTES];
+static float *g_noalloc_ptr[64];  // per device: the array's device address (not the host-side symbol)
+
+size_t rq_cuda_attn_decode_noalloc_max_bytes(void) { return RQ_NOALLOC_PART_BYTES; }
+
+int rq_cuda_attn_decode_noalloc(RqCuda *c, int layer, const float *q, float *out) {
+    int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_decode_noalloc");
+    if (rc) return rc;
+    if (!q || !out) return fail(c, RQ_CUDA_ERR_ARG, "attn_decode_noalloc: null rows");
+    size_t need = (size_t)c->total_blocks * c->n_heads * RQ_PSTRIDE(c->m.head_dim) * 4;
+    if (need > RQ_NOALLOC_PART_BYTES)
+        return fail(c, RQ_CUDA_ERR_ARG,
+                    "attn_decode_noalloc: the pass needs %zu bytes of partial results (%d blocks of 256 positions x %d heads), "
+                    "the fixed scratch holds %zu; use rq_cuda_attn_decode_dev or split the pass",
+                    need, c->total_blocks, c->n_heads, (size_t)RQ_NOALLOC_PART_BYTES);
+    if (c->device < 0 || c->device >= 64) return fail(c, RQ_CUDA_ERR_ARG, "attn_decode_noalloc: device %d", c->device);
+    CU(c, cudaSetDevice(c->device));
+    if (!g_noalloc_ptr[c->device]) {
+        // once per device, with that device current: the address the kernels can use (the name g_noalloc_part in
+        // host code is only a handle for this query)
+        void *p = nullptr;
+        CU(c, cudaGetSymbolAddress(&p, g_noalloc_part));
+        g_noalloc_ptr[c->device] = (float *)p;
+    }
+    // nothing in the array has to start at zero: every record the merge reads was written by this call's first kernel
+    return launch_decode_with(c, layer, q, out, g_noalloc_ptr[c->device]);
 }
 
 int rq_cuda_attn_prefill_dev(RqCuda *c, int layer, const float *q, float *out) {

@@ -127,6 +127,19 @@ int rq_cuda_kv_store_dev(RqCuda *ctx, int layer, const float *k_dev, const float
 int rq_cuda_attn_decode(RqCuda *ctx, int layer, const float *q, float *out);
 int rq_cuda_attn_decode_dev(RqCuda *ctx, int layer, const float *q_dev, float *out_dev);
 
+/* (No counterpart in the reference.)  rq_cuda_attn_decode_dev for hosts that must not allocate: a server that
+ * budgeted all device memory at start-up, or code running where cudaMalloc is not allowed or would stall the device.
+ * The per-block partial results go to a fixed 32 MiB array inside the library (held by every GPU that loads it)
+ * instead of the context's growable scratch; the call performs no cudaMalloc / cudaFree and calls no allocating
+ * routine.  q_dev and out_dev are the caller's device buffers, as for rq_cuda_attn_decode_dev, and the results are
+ * the same bits.  A pass whose (256-position blocks of all rows) x heads x (head_dim + 16) x 4 bytes exceed
+ * rq_cuda_attn_decode_noalloc_max_bytes() is refused with RQ_CUDA_ERR_ARG and a message.  The first call on a device
+ * looks up the array's device address: make that first call before any stream capture.  All calls share the one
+ * array and it keeps the last call's contents: calls that overlap on the GPU (two streams, two contexts, two host
+ * threads on one device) race; nothing in it needs to start at zero. */
+int rq_cuda_attn_decode_noalloc(RqCuda *ctx, int layer, const float *q_dev, float *out_dev);
+size_t rq_cuda_attn_decode_noalloc_max_bytes(void);
+
 /* The same attention for passes with many rows per sequence (prompt chunks), replacing prefill_worker's items
  * (forward.c:3096-3146, attention_kv :1871): tensor-core tiles over the cached prefix plus the chunk's own rows,
  * causal per row.  Same arguments and layouts as rq_cuda_attn_decode. */
