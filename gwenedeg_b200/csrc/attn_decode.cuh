@@ -494,14 +494,17 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
 // Merge of the block partials of one query vector (att_combine, reference src/forward.c:1405), then the inverse rotation
 // for q8 / q4 caches (att_o_unrot :1672: butterflies, signs, exact scaling) and the optional sigmoid gate (attn_gate
 // :2291).  One CTA of HD threads per (row, query head).
+// split_len / fixed_stride: the partials of a row are one per `split_len` positions, the first one at record index
+// row.blk0 (fixed_stride 0: the decode kernel's 256-position blocks) or r * fixed_stride (the prefill kernel's splits).
 template <int HD, bool QUANT>
 __global__ void __launch_bounds__(HD) attn_combine_kernel(const PassRow *__restrict__ rows, int n_heads, const float *__restrict__ part,
-                                                          const float *__restrict__ q, int qh, int gated, float *__restrict__ out) {
+                                                          const float *__restrict__ q, int qh, int gated, float *__restrict__ out,
+                                                          int split_len, int fixed_stride) {
     const int r = blockIdx.x, h = blockIdx.y, i = threadIdx.x;
     const PassRow row = rows[r];
-    const int nb = (row.np + ATT_P - 1) / ATT_P;
+    const int nb = (row.np + split_len - 1) / split_len;
     const size_t pst = RQ_PSTRIDE(HD);
-    const float *p0 = part + ((size_t)row.blk0 * n_heads + h) * pst;
+    const float *p0 = part + ((size_t)(fixed_stride ? r * fixed_stride : row.blk0) * n_heads + h) * pst;
     const size_t bstride = (size_t)n_heads * pst;
     float res;
     if (nb == 1) {

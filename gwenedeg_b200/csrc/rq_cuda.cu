@@ -13,6 +13,7 @@
 
 #include "../../include/rq_cuda.h"
 #include "attn_decode.cuh"
+#include "attn_prefill.cuh"
 #include "deltanet.cuh"
 #include "kv_store.cuh"
 
@@ -37,6 +38,9 @@ struct RqCudaSeq {
     float *ssm;            // [n_lin] layers of ssm_floats
     size_t ssm_floats;
     int in_pass;
+    // 2-D views of the K and V caches for the tensor-core prefill kernel (f16, head_dim 128)
+    CUtensorMap tm_k, tm_v;
+    bool has_tm;
 };
 
 struct RqCuda {
@@ -62,6 +66,11 @@ struct RqCuda {
     int *d_err;
     int *h_err;  // pinned
     void *flush; size_t flush_bytes;
+    // tensor-core prefill: the segments' tensor maps and the work list of the open pass
+    CUtensorMap *h_maps, *d_maps;  // [max_rows][2]
+    PfWork *d_work; size_t work_bytes;
+    std::vector<PfWork> h_work;
+    int pf_ready, pf_max_splits;
     // optional per-launch timing of the dominant kernel (rq_cuda_profile_begin / _end)
     std::vector<cudaEvent_t> prof_ev;
     int prof_on, prof_n;
@@ -83,6 +92,48 @@ static int fail(RqCuda *c, int code, const char *fmt, ...) {
             return fail(c, e_ == cudaErrorMemoryAllocation ? RQ_CUDA_ERR_NOMEM : RQ_CUDA_ERR_DEVICE, "%s: %s", #call, \
                         cudaGetErrorString(e_));                                                             \
     } while (0)
+
+typedef CUresult (*TmEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                               const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TmEncodeFn tm_encode() {
+    // the driver's tensor-map encoder, looked up through the runtime (no link-time dependency on libcuda)
+    static TmEncodeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        cudaDriverEntryPointQueryResult qr;
+        void *p = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+            fn = (TmEncodeFn)p;
+    }
+    return fn;
+}
+
+static bool seq_make_maps(RqCuda *c, RqCudaSeq *s) {
+    // K: rows of 16 positions x one dim (32 bytes), 32-byte swizzle, box 16 x 256 (two tiles);
+    // V: rows of one position x 128 dims (256 bytes), 128-byte swizzle, box 64 x 128
+    s->has_tm = false;
+    if (s->kvt != KV_F16 || c->m.head_dim != 128 || c->m.n_attn < 1) return true;
+    TmEncodeFn enc = tm_encode();
+    if (!enc) return false;
+    cuuint32_t es[2] = {1, 1};
+    {
+        cuuint64_t dims[2] = {16, (cuuint64_t)(s->lk * c->m.n_attn / 32)}, strides[1] = {32};
+        cuuint32_t box[2] = {16, 256};
+        if (enc(&s->tm_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, s->k, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    {
+        cuuint64_t dims[2] = {128, (cuuint64_t)(s->lv * c->m.n_attn / 256)}, strides[1] = {256};
+        cuuint32_t box[2] = {64, 128};
+        if (enc(&s->tm_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, s->v, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    s->has_tm = true;
+    return true;
+}
 
 static bool kvt_ok(int t, int hd) {
     if (t == KV_F16) return hd == 64 || hd == 128 || hd == 256;
@@ -152,6 +203,8 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
                cudaMalloc((void **)&c->d_dseg, sizeof(DnSeg) * max_rows) == cudaSuccess &&
                cudaMalloc((void **)&c->d_err, sizeof(int)) == cudaSuccess &&
                cudaMallocHost((void **)&c->h_err, sizeof(int)) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_maps, sizeof(CUtensorMap) * 2 * max_rows) == cudaSuccess &&
+               cudaMalloc((void **)&c->d_maps, sizeof(CUtensorMap) * 2 * max_rows) == cudaSuccess &&
                cudaMemset(c->d_err, 0, sizeof(int)) == cudaSuccess;
     c->stream = c->own_stream;
     if (!okk) {
@@ -166,7 +219,8 @@ void rq_cuda_free(RqCuda *c) {
     if (!c) return;
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
-    void *dev[] = {c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->flush};
+    void *dev[] = {c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->flush, c->d_maps, c->d_work};
+    if (c->h_maps) cudaFreeHost(c->h_maps);
     for (void *p : dev)
         if (p) cudaFree(p);
     if (c->h_rows) cudaFreeHost(c->h_rows);
@@ -225,6 +279,14 @@ int rq_cuda_seq_new(RqCuda *c, int capacity, int kv_type, RqCudaSeq **seq) {
             rq_cuda_seq_free(s);
             return fail(c, RQ_CUDA_ERR_NOMEM, "KV cache of %zu bytes: %s", (s->lk + s->lv) * c->m.n_attn,
                         cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+        }
+        // zeroed: positions past a row's length are masked, but the tensor-core kernels multiply them by zero weights
+        // and must not meet a NaN or infinity bit pattern there
+        cudaMemsetAsync(s->k, 0, s->lk * c->m.n_attn, c->stream);
+        cudaMemsetAsync(s->v, 0, s->lv * c->m.n_attn, c->stream);
+        if (!seq_make_maps(c, s)) {
+            rq_cuda_seq_free(s);
+            return fail(c, RQ_CUDA_ERR_DEVICE, "tensor maps of the KV cache could not be encoded");
         }
     }
     if (c->m.n_lin > 0) {
@@ -414,6 +476,36 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
     }
     memset(&c->h_rows[r], 0, sizeof(PassRow));
     c->h_rows[r].blk0 = blk;
+    // tensor-core prefill: the segments' tensor maps, and the work list (M tile of 128 / G rows, 1024-position split)
+    c->pf_ready = 0;
+    if (c->m.n_attn > 0 && c->m.head_dim == 128 && kvt == KV_F16) {
+        bool all = true;
+        for (int i = 0; i < nseg; i++) all = all && seg[i].seq->has_tm;
+        if (all) {
+            const int rpt = 128 / c->G;
+            c->h_work.clear();
+            for (int i = 0; i < nseg; i++) {
+                c->h_maps[2 * i] = seg[i].seq->tm_k;
+                c->h_maps[2 * i + 1] = seg[i].seq->tm_v;
+            }
+            int row = 0;
+            for (int i = 0; i < nseg; i++) {
+                for (int m0 = 0; m0 < seg[i].n; m0 += rpt) {
+                    int nr = std::min(rpt, seg[i].n - m0), np_max = seg[i].pos0 + m0 + nr;
+                    for (int k = 0; k * PF_SPLIT < np_max; k++) c->h_work.push_back(PfWork{i, row + m0, nr, k});
+                }
+                row += seg[i].n;
+            }
+            c->pf_max_splits = (mx + PF_SPLIT - 1) / PF_SPLIT;
+            size_t wb = c->h_work.size() * sizeof(PfWork);
+            int rc2 = grow(c, (void **)&c->d_work, &c->work_bytes, wb);
+            if (rc2) return rc2;
+            CU(c, cudaMemcpyAsync(c->d_maps, c->h_maps, sizeof(CUtensorMap) * 2 * nseg, cudaMemcpyHostToDevice, c->stream));
+            CU(c, cudaMemcpyAsync(c->d_work, c->h_work.data(), wb, cudaMemcpyHostToDevice, c->stream));
+            CU(c, cudaStreamSynchronize(c->stream));  // (the work list is pageable host memory)
+            c->pf_ready = 1;
+        }
+    }
     CU(c, cudaMemcpyAsync(c->d_rows, c->h_rows, sizeof(PassRow) * (r + 1), cudaMemcpyHostToDevice, c->stream));
     if (c->m.n_lin > 0) CU(c, cudaMemcpyAsync(c->d_dseg, c->h_dseg, sizeof(DnSeg) * nseg, cudaMemcpyHostToDevice, c->stream));
     c->segs.assign(seg, seg + nseg);
@@ -478,6 +570,7 @@ int rq_cuda_kv_store(RqCuda *c, int layer, const float *k, const float *v) {
 }
 
 static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, float *part);
+static int launch_combine(RqCuda *c, const float *q, float *out, const float *part, int split_len, int fixed_stride);
 
 static int launch_decode(RqCuda *c, int layer, const float *q, float *out) {
     const int hd = c->m.head_dim;
@@ -515,11 +608,16 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
     if (e != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "attention launch: %s", cudaGetErrorString(e));
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n++ + 1], c->stream);
     c->launches++;
+    return launch_combine(c, q, out, part, ATT_P, 0);
+}
+
+static int launch_combine(RqCuda *c, const float *q, float *out, const float *part, int split_len, int fixed_stride) {
+    const int hd = c->m.head_dim;
     dim3 grid(c->nrows, c->n_heads);
     const bool quant = kv_quant(c->pass_kvt);
 #define COMBINE(HD_)                                                                                                          \
-    if (quant) attn_combine_kernel<HD_, true><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out); \
-    else attn_combine_kernel<HD_, false><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out);
+    if (quant) attn_combine_kernel<HD_, true><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride); \
+    else attn_combine_kernel<HD_, false><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride);
     switch (hd) {
         case 64: COMBINE(64) break;
         case 128: COMBINE(128) break;
@@ -594,11 +692,57 @@ int rq_cuda_attn_decode_noalloc(RqCuda *c, int layer, const float *q, float *out
     return launch_decode_with(c, layer, q, out, g_noalloc_ptr[c->device]);
 }
 
-int rq_cuda_attn_prefill_dev(RqCuda *c, int layer, const float *q, float *out) {
-    return rq_cuda_attn_decode_dev(c, layer, q, out);
+static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
+    // tensor-core tiles where the pass qualifies (f16 cache, head_dim 128); other shapes take the split-K kernels,
+    // which compute the same attention on the CUDA cores
+    if (!c->pf_ready) return launch_decode(c, layer, q, out);
+    const int hd = c->m.head_dim;
+    size_t need = (size_t)c->nrows * c->pf_max_splits * c->n_heads * RQ_PSTRIDE(hd) * 4;
+    int rc = grow(c, (void **)&c->d_part, &c->part_bytes, need);
+    if (rc) return rc;
+    AttnPrefillArgs a;
+    a.work = c->d_work;
+    a.n_work = (int)c->h_work.size();
+    a.rows = c->d_rows;
+    a.maps = c->d_maps;
+    a.layer = layer;
+    a.n_kv = c->n_kv;
+    a.G = c->G;
+    a.q = q;
+    a.qh = c->qh;
+    a.n_heads = c->n_heads;
+    a.scale = 1.0f / sqrtf((float)hd);
+    a.max_splits = c->pf_max_splits;
+    a.part = c->d_part;
+    a.err = c->d_err;
+    const bool prof = c->prof_on && (size_t)(2 * c->prof_n + 2) <= c->prof_ev.size();
+    if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n], c->stream);
+    cudaError_t e = launch_attn_prefill(a, c->stream);
+    if (e != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "prefill attention launch: %s", cudaGetErrorString(e));
+    if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n++ + 1], c->stream);
+    c->launches++;
+    return launch_combine(c, q, out, c->d_part, PF_SPLIT, c->pf_max_splits);
 }
 
-int rq_cuda_attn_prefill(RqCuda *c, int layer, const float *q, float *out) { return rq_cuda_attn_decode(c, layer, q, out); }
+int rq_cuda_attn_prefill_dev(RqCuda *c, int layer, const float *q, float *out) {
+    int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_prefill");
+    if (rc) return rc;
+    if (!q || !out) return fail(c, RQ_CUDA_ERR_ARG, "attn_prefill: null rows");
+    CU(c, cudaSetDevice(c->device));
+    return launch_prefill(c, layer, q, out);
+}
+
+int rq_cuda_attn_prefill(RqCuda *c, int layer, const float *q, float *out) {
+    int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_prefill");
+    if (rc) return rc;
+    if (!q || !out) return fail(c, RQ_CUDA_ERR_ARG, "attn_prefill: null rows");
+    CU(c, cudaSetDevice(c->device));
+    size_t qb = (size_t)c->nrows * c->n_heads * c->qh * 4, ob = (size_t)c->nrows * c->n_heads * c->m.head_dim * 4;
+    if ((rc = stage_q(c, q, qb, ob))) return rc;
+    if ((rc = launch_prefill(c, layer, c->d_q, c->d_out))) return rc;
+    CU(c, cudaMemcpyAsync(out, c->d_out, ob, cudaMemcpyDeviceToHost, c->stream));
+    return rq_cuda_sync(c);
+}
 
 int rq_cuda_dn_rec_dev(RqCuda *c, int lin_layer, const float *rows, float *out) {
     int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_rec");

@@ -1,0 +1,86 @@
+"""Parity of the tensor-core prefill attention (through the C ABI) with the CPU checker.
+
+Q and the softmax weights are rounded to f16 for the tensor cores, so the comparison is by the acceptance bar
+(max-abs <= 2e-3, rel-L2 <= 1e-3; per row 4e-3), not bit for bit; the split-K decode kernels on the same rows
+(bit-exact with the CPU) serve as a second reference.
+"""
+import numpy as np
+import pytest
+
+from tests.helpers import assert_close, errors
+
+pytestmark = pytest.mark.gpu
+F16 = 2
+
+
+def fill_seq(c, n, n_kv, hd, seed):
+    from gwenedeg_b200 import synth
+    s = c.new_seq(n, F16)
+    k, v = synth.normal(seed, (n, n_kv, hd)), synth.normal(seed + 1, (n, n_kv, hd))
+    for lo in range(0, n, 512):
+        hi = min(n, lo + 512)
+        c.pass_begin([(s, lo, hi - lo)])
+        c.kv_store(0, k[lo:hi], v[lo:hi])
+        c.pass_end()
+    return s
+
+
+@pytest.mark.parametrize("n_heads,n_kv", [(16, 8), (32, 8), (8, 8), (16, 2)])
+def test_chunk_over_prefix_matches_cpu(checker, n_heads, n_kv):
+    """A chunk of rows over a cached prefix, crossing the 1024-position split edge and the tile edges."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    hd, n = 128, 1300
+    c = g.Context(0, n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd)
+    s = fill_seq(c, n, n_kv, hd, 40 + n_heads)
+    pos0, rows = 900, 300   # rows at positions 900..1199: np 901..1200
+    q = synth.normal(7, (rows, n_heads, hd))
+    c.pass_begin([(s, pos0, rows)])
+    got = c.attn_prefill(0, q)
+    ref_gpu = c.attn_decode(0, q)
+    c.pass_end(commit=False)
+    want = checker.attention(F16, s.read_kv(0, 0), s.read_kv(0, 1), n_kv, n_heads, hd, q, np.arange(pos0 + 1, pos0 + rows + 1, dtype=np.int32))
+    assert_close(ref_gpu, want, "split-K on the chunk")
+    assert_close(got, want, "tensor-core prefill")
+    print("prefill errors", errors(got, want))
+    c.close()
+
+
+def test_short_rows_and_mixed_segments(checker):
+    """Rows from position 0 (a single key, partial tiles), two chunks and decode rows of other sequences in one pass."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    n_heads, n_kv, hd = 16, 8, 128
+    c = g.Context(0, n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd)
+    a = fill_seq(c, 200, n_kv, hd, 1)
+    b = fill_seq(c, 2500, n_kv, hd, 3)
+    d = fill_seq(c, 1025, n_kv, hd, 5)
+    segs = [(a, 0, 70), (b, 2040, 100), (d, 1024, 1)]
+    q = synth.normal(9, (171, n_heads, hd))
+    c.pass_begin(segs)
+    got = c.attn_prefill(0, q)
+    c.pass_end(commit=False)
+    r = 0
+    for s, pos0, n in segs:
+        want = checker.attention(F16, s.read_kv(0, 0), s.read_kv(0, 1), n_kv, n_heads, hd, q[r:r + n], np.arange(pos0 + 1, pos0 + n + 1, dtype=np.int32))
+        assert_close(got[r:r + n], want, f"segment at {pos0}")
+        r += n
+    c.close()
+
+
+def test_config2_shape_one_layer(checker):
+    """Qwen3-0.6B-shaped chunked prefill: 512 rows at positions 3584..4095 over a 4096-position cache (one layer)."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    n_heads, n_kv, hd = 16, 8, 128
+    c = g.Context(0, n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd)
+    s = c.new_seq(4096, F16)
+    s.fill_synthetic(4096, 11)
+    q = synth.normal(13, (512, n_heads, hd))
+    c.pass_begin([(s, 3584, 512)])
+    got = c.attn_prefill(0, q)
+    c.pass_end(commit=False)
+    rows = [0, 1, 63, 64, 255, 511]  # the CPU checker on a few rows (the full chunk takes it a while)
+    want = checker.attention(F16, s.read_kv(0, 0), s.read_kv(0, 1), n_kv, n_heads, hd, q[rows], np.array([3585 + r for r in rows], np.int32))
+    assert_close(got[rows], want, "config-2 rows")
+    c.close()
