@@ -138,6 +138,55 @@ def cpu_leg(ctx_all, reps, sample_every):
     return info
 
 
+PF_LAYERS, PF_HEADS, PF_KV, PF_ROWS, PF_PREFIX = 28, 16, 8, 512, 3584
+
+
+def prefill_leg(device, steps, layers=None, warm=3):
+    """Qwen3-0.6B-shaped chunked prefill attention (512 new rows over a 3584-position f16 prefix, 28 layers, one
+    sequence): TFLOP/s of the tensor-core prefill path, flops = 4 x head_dim per causal (query, key) pair per query head."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    PF_LAYERS = layers or globals()["PF_LAYERS"]
+    c = g.Context(device, n_attn=PF_LAYERS, n_heads=PF_HEADS, n_kv_heads=PF_KV, head_dim=HD, max_rows=PF_ROWS)
+    s = c.new_seq(PF_PREFIX + PF_ROWS, g.KV_F16)
+    s.fill_synthetic(PF_PREFIX + PF_ROWS, 77)
+    qn = PF_ROWS * PF_HEADS * HD
+    q_host = c.pinned((PF_LAYERS, PF_ROWS, PF_HEADS, HD))
+    q_host[:] = synth.normal(5, (PF_LAYERS, PF_ROWS, PF_HEADS, HD))
+    q_dev, out_dev = c.malloc(q_host.nbytes), c.malloc(q_host.nbytes)
+    c.h2d(q_dev, q_host)
+    c.sync()
+
+    def step():
+        c.pass_begin([(s, PF_PREFIX, PF_ROWS)])
+        for l in range(PF_LAYERS):
+            c.attn_prefill_dev(l, q_dev + l * qn * 4, out_dev + l * qn * 4)
+        c.pass_end(commit=False)
+
+    for _ in range(warm):
+        step()
+    c.sync()
+    c.profile_begin(steps * PF_LAYERS)
+    c.timer_start()
+    for _ in range(steps):
+        step()
+    ms = c.timer_stop()
+    kern_ms, kern_n = c.profile_end()
+    pairs = sum(p + 1 for p in range(PF_PREFIX, PF_PREFIX + PF_ROWS))
+    flops_layer = 4.0 * HD * pairs * PF_HEADS
+    c.close()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, how = float(json.load(f)["bf16_tflops"]), "measured (burst)"
+    except Exception:
+        peak, how = 1590.0, "fallback"
+    tf_step = flops_layer * PF_LAYERS * steps / (ms * 1e-3) / 1e12
+    tf_kern = flops_layer * kern_n / (kern_ms * 1e-3) / 1e12
+    return {"workload": "qwen3-0.6b-prefill-512-over-3584", "tflops": tf_step, "ms_per_chunk_all_layers": ms / steps,
+            "roofline": {"bound": "tensor", "achieved": tf_kern, "peak": peak, "unit": "TFLOP/s", "frac": tf_kern / peak, "traffic": None,
+                         "peak_source": how, "kernel": "attn_prefill_kernel", "flops_per_launch": flops_layer, "launches_timed": kern_n}}
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -274,6 +323,13 @@ def run_ours(args, rank, local_rank, world):
     achieved = bytes_per_launch / (part_ms / max(part_n, 1) * 1e-3) / 1e9
     achieved = reduce_sum(achieved) / world  # mean over ranks of the per-GPU figure
 
+    c.close()
+    prefill = None
+    if rank == 0 and not args.small:
+        try:
+            prefill = prefill_leg(local_rank, max(2, min(args.steps, 5)))
+        except Exception as e:
+            prefill = {"error": repr(e)}
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu:
@@ -301,9 +357,9 @@ def run_ours(args, rank, local_rank, world):
                          "traffic": None, "peak_source": how, "kernel": "attn_part_kernel<f16,128,4>",
                          "algorithmic_bytes_per_launch_rank0": bytes_per_launch, "launches_timed": part_n},
             "cpu_baseline": cpu,
+            "prefill": prefill,
         }
         print(json.dumps(line), flush=True)
-    c.close()
     if dist is not None:
         dist.destroy_process_group()
 
@@ -315,6 +371,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: the headline batched-decode benchmark (default); prefill: only the chunked-prefill leg "
+                         "(512 rows over a 3584-position prefix), printed as its own line")
     ap.add_argument("--small", action="store_true",
                     help="profiling case for ncu captures: 8 sequences of 4096..8192 positions, 2 layers (about 0.4 GB of "
                          "KV per layer: larger than the L2, small enough for a multi-pass capture), no CPU / end-to-end legs")
@@ -328,6 +387,14 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "prefill":
+        if rank == 0:
+            r = prefill_leg(local_rank, args.steps, layers=2 if args.small else None, warm=args.warmup)
+            print(json.dumps({"metric": "Qwen3-0.6B attn: prefill TFLOP/s (512 rows over 3584)", "value": r["tflops"], "unit": "TFLOP/s",
+                              "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "f16",
+                              "data": "synthetic", "config": {"workload": r["workload"], "layers": 2 if args.small else PF_LAYERS},
+                              "roofline": r["roofline"]}), flush=True)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         # started without torchrun: re-launch one rank per GPU

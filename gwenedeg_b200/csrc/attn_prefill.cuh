@@ -117,12 +117,19 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+#ifdef RQ_PF_TRACE
+__device__ long long pf_trace[64];  // experiments only: event times of CTA (0, 0), in clock cycles from its start
+#define PF_T(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 64) pf_trace[i] = clock64() - pf_t0; } while (0)
+#else
+#define PF_T(i) do { } while (0)
+#endif
+
 constexpr int PF_SMEM = 3 * 32768 + 1024 + 128;  // Q | K | V (32 KB each), alignment slack, barriers
 
 // maps: per segment the tensor maps of its sequence's K cache ({16 positions, rows of 32 bytes}, 32-byte swizzle, box 16 x
 // 256) and V cache ({128 dims, rows of 256 bytes}, 128-byte swizzle, box 64 x 128).  k_rows_per_layer / v_rows_per_layer:
 // rows of those 2-D views per layer of each segment's sequence.
-__global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PfWork *__restrict__ work, const PassRow *__restrict__ rows,
+__global__ void __launch_bounds__(PF_THREADS, 2) attn_prefill_kernel(const PfWork *__restrict__ work, const PassRow *__restrict__ rows,
                                                                   const CUtensorMap *__restrict__ maps, int layer, int n_kv, int G,
                                                                   const float *__restrict__ q, int qh, int n_heads, float scale,
                                                                   int max_splits, float *__restrict__ part, int *err) {
@@ -135,6 +142,9 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PfWork *
     uint64_t *bar_k = bars, *bar_v = bars + 1, *bar_s = bars + 2, *bar_o = bars + 3, *bar_p = bars + 4;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef RQ_PF_TRACE
+    const long long pf_t0 = clock64();
+#endif
     const PfWork w = work[blockIdx.x];
     const int g = blockIdx.y;
     const PassRow r0 = rows[w.row0];
@@ -146,42 +156,6 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PfWork *
     // rows of the 2-D views: K rows are 32 bytes (one dim of a tile), V rows 256 bytes (one position)
     const long long k_layer_rows = (long long)(r0.lk / 32), v_layer_rows = (long long)(r0.lv / 256);
 
-    if (tid == 0) {
-        mbar_init(bar_k, 1);
-        mbar_init(bar_v, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
-        mbar_init(bar_p, 128);
-        mbar_fence_init();
-    }
-    if (warp == 4) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TM_COLS));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
-    }
-    // Q tile -> shared memory as f16, K-major with the 128-byte swizzle: vector t = row t / G, head g G + t % G;
-    // 16-byte chunk c of 16: k-block c / 8, physical chunk (c % 8) ^ (t % 8)
-    if (warp < 4) {
-        const int t = tid, rl = t / G, x = t % G;
-        const bool valid = rl < w.nrows;
-        const float *qv = q + ((size_t)(w.row0 + (valid ? rl : 0)) * n_heads + (size_t)g * G + x) * qh;
-#pragma unroll 4
-        for (int c = 0; c < 16; c++) {
-            float4 a = valid ? *reinterpret_cast<const float4 *>(qv + c * 8) : make_float4(0, 0, 0, 0);
-            float4 b = valid ? *reinterpret_cast<const float4 *>(qv + c * 8 + 4) : make_float4(0, 0, 0, 0);
-            __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w), h2 = __floats2half2_rn(b.x, b.y),
-                    h3 = __floats2half2_rn(b.z, b.w);
-            uint4 pk = make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1), *reinterpret_cast<uint32_t *>(&h2),
-                                  *reinterpret_cast<uint32_t *>(&h3));
-            *reinterpret_cast<uint4 *>(sQ + (c >> 3) * 16384 + t * 128 + (((c & 7) ^ (t & 7)) << 4)) = pk;
-        }
-    }
-    fence_proxy_async();  // Q was written by ordinary stores and will be read by the tensor core
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tbase = *tmem_slot;
-    bool ok = true;
-
     // first K / V row of key block j in the 2-D views
     auto k_row = [&](int j) {
         int t0 = s0 + j * PF_BN;
@@ -191,6 +165,53 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PfWork *
         int t0 = s0 + j * PF_BN;
         return (long long)layer * v_layer_rows + ((long long)(t0 / ATT_P) * n_kv + g) * ATT_P + (t0 % ATT_P);
     };
+
+    if (tid == 0) PF_T(44);  // work item and row fetched
+    if (tid == 0) {
+        mbar_init(bar_k, 1);
+        mbar_init(bar_v, 1);
+        mbar_init(bar_s, 1);
+        mbar_init(bar_o, 1);
+        mbar_init(bar_p, 128);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (warp == 4) {
+        if (lane == 0) {  // the first K / V blocks start loading while the other warps convert Q
+            mbar_expect_tx(bar_k, 32768);
+            for (int i = 0; i < 4; i++) tma_load_2d(sK + i * 8192, mk, 0, (int)k_row(0) + i * 256, bar_k);
+            mbar_expect_tx(bar_v, 32768);
+            for (int i = 0; i < 2; i++) tma_load_2d(sV + i * 16384, mv, i * 64, (int)v_row(0), bar_v);
+        }
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    // Q tile -> shared memory as f16, K-major with the 128-byte swizzle: vector t = row t / G, head g G + t % G;
+    // 16-byte chunk c of 16: k-block c / 8, physical chunk (c % 8) ^ (t % 8)
+    if (tid == 0) PF_T(45);  // barriers ready, first loads issued
+    if (warp < 4) {
+        // a warp converts 32 vectors, one per step: its lanes read the vector's 128 floats as one coalesced 512-byte
+        // row (lane L: dims 4L .. 4L + 3) and store 4 halves into chunk L / 2
+#pragma unroll
+        for (int rr = 0; rr < 32; rr++) {
+            const int t = warp * 32 + rr, rl = t / G, x = t % G;
+            float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (rl < w.nrows) a = *reinterpret_cast<const float4 *>(q + ((size_t)(w.row0 + rl) * n_heads + (size_t)g * G + x) * qh + 4 * lane);
+            __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
+            const int c = lane >> 1;
+            *reinterpret_cast<uint2 *>(sQ + (c >> 3) * 16384 + t * 128 + (((c & 7) ^ (t & 7)) << 4) + (lane & 1) * 8) =
+                make_uint2(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1));
+        }
+    }
+    if (tid == 0) PF_T(46);  // Q converted
+    fence_proxy_async();  // Q was written by ordinary stores and will be read by the tensor core
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tbase = *tmem_slot;
+    bool ok = true;
+    if (tid == 0) PF_T(0);  // prologue done (Q in shared memory, TMEM allocated)
 
     if (warp == 4) {
         // ---- TMA loads and MMA issue (one thread)
@@ -219,8 +240,6 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PfWork *
                     umma_ts(tbase + O_COL, tbase + S_COL + ks * 8, umma_desc(smem_u32(sV) + ks * 2048, 16384, 1024, 2), idesc, (j > 0) | (ks > 0));
                 umma_commit(bar_o);
             };
-            load_k(0);
-            load_v(0);
             ok = mbar_wait_bounded(bar_k, 0, err, 11) && ok;
             tc_fence_after();
             mma_qk();
@@ -231,12 +250,14 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PfWork *
                 ok = mbar_wait_bounded(bar_p, ph, err, 13) && ok;  // P(j) is in TMEM
                 ok = mbar_wait_bounded(bar_v, ph, err, 14) && ok;
                 tc_fence_after();
+                PF_T(3 + 4 * j);  // P V (j) issued (P and V ready)
                 mma_pv(j);
                 if (j + 1 < nblk) {
                     ok = mbar_wait_bounded(bar_k, ph ^ 1, err, 15) && ok;
                     tc_fence_after();
                     mma_qk();  // queued behind P V (j): it may overwrite the S / P columns only after they were read
                     ok = mbar_wait_bounded(bar_o, ph, err, 16) && ok;  // the V buffer is free
+                    PF_T(4 + 4 * j);  // P V (j) complete
                     load_v(j + 1);
                 }
             }
@@ -254,21 +275,26 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PfWork *
             const int t0 = s0 + j * PF_BN;
             ok = mbar_wait_bounded(bar_s, ph, err, 21) && ok;
             tc_fence_after();
-            const bool need_mask = t0 + PF_BN > np_min;  // (uniform over the CTA)
-            // pass 1: row max of the block
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; cc++) {
-                uint32_t r[32];
-                tmem_ld32(lane_addr + S_COL + cc * 32, r);
-                tmem_wait_ld();
+            if (tid == 0) PF_T(1 + 4 * j);  // S(j) ready
+            // the thread's whole row of S (128 scores) in registers: four loads in flight, one wait
+            uint32_t r[4][32];
 #pragma unroll
-                for (int x = 0; x < 32; x++) {
-                    float s = __uint_as_float(r[x]);
-                    if (need_mask && t0 + cc * 32 + x >= np) s = -INFINITY;
-                    mx = fmaxf(mx, s);
-                }
+            for (int cc = 0; cc < 4; cc++) tmem_ld32(lane_addr + S_COL + cc * 32, r[cc]);
+            tmem_wait_ld();
+            const bool need_mask = t0 + PF_BN > np_min;  // (uniform over the CTA: only the blocks on the diagonal)
+            if (need_mask) {
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++)
+#pragma unroll
+                    for (int x = 0; x < 32; x++)
+                        if (t0 + cc * 32 + x >= np) r[cc][x] = 0xff800000u;  // -inf
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++)
+#pragma unroll
+                for (int x = 0; x < 32; x++) mx4[x & 3] = fmaxf(mx4[x & 3], __uint_as_float(r[cc][x]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the running max moves only when it grows by more than 8 in the exponent (p stays below 2^8: exact enough
             // in f16, and O is rescaled rarely); the first block with a valid position sets it
             float alpha = 1.0f;
@@ -282,72 +308,71 @@ __global__ void __launch_bounds__(PF_THREADS) attn_prefill_kernel(const PfWork *
                 l *= alpha;
 #pragma unroll 1
                 for (int cc = 0; cc < 4; cc++) {
-                    uint32_t r[32];
-                    tmem_ld32(lane_addr + O_COL + cc * 32, r);
+                    uint32_t o[32];
+                    tmem_ld32(lane_addr + O_COL + cc * 32, o);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int x = 0; x < 32; x++) r[x] = __float_as_uint(__uint_as_float(r[x]) * alpha);
-                    tmem_st32(lane_addr + O_COL + cc * 32, r);
+                    for (int x = 0; x < 32; x++) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
+                    tmem_st32(lane_addr + O_COL + cc * 32, o);
                 }
                 tmem_wait_st();
             }
-            // pass 2: p = 2^((s - m) c) rounded to f16, row sum of the rounded values, P over the first 64 columns of S
+            // p = 2^((s - m) c) (a masked score is -inf: p = 0), row sum, P as f16 pairs over the first 64 columns of S
             const float mc = m_used == -INFINITY ? 0.0f : m_used * c;
-#pragma unroll 1
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
             for (int cc = 0; cc < 4; cc++) {
-                uint32_t r[32], pk[16];
-                tmem_ld32(lane_addr + S_COL + cc * 32, r);
-                tmem_wait_ld();
 #pragma unroll
                 for (int x = 0; x < 32; x += 2) {
-                    float s0v = __uint_as_float(r[x]), s1v = __uint_as_float(r[x + 1]);
-                    float p0 = ex2(fmaf(s0v, c, -mc)), p1 = ex2(fmaf(s1v, c, -mc));
-                    if ((need_mask && t0 + cc * 32 + x >= np) || m_used == -INFINITY) p0 = 0.0f;
-                    if ((need_mask && t0 + cc * 32 + x + 1 >= np) || m_used == -INFINITY) p1 = 0.0f;
+                    float p0 = ex2(fmaf(__uint_as_float(r[cc][x]), c, -mc)), p1 = ex2(fmaf(__uint_as_float(r[cc][x + 1]), c, -mc));
+                    l4[(x >> 1) & 3] += p0 + p1;
                     __half2 h = __floats2half2_rn(p0, p1);
-                    float2 back = __half22float2(h);
-                    l += back.x + back.y;
-                    pk[x >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                    r[cc >> 1][(cc & 1) * 16 + (x >> 1)] = *reinterpret_cast<uint32_t *>(&h);  // (slots already consumed)
                 }
-                // the 16 packed columns of this chunk: always behind the columns of S still to be read
-                asm volatile(
-                    "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
-                        lane_addr + S_COL + cc * 16),
-                    "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7]), "r"(pk[8]), "r"(pk[9]),
-                    "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]), "r"(pk[15])
-                    : "memory");
             }
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            tmem_st32(lane_addr + S_COL, r[0]);
+            tmem_st32(lane_addr + S_COL + 32, r[1]);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar_p);
+            if (tid == 0) PF_T(2 + 4 * j);  // softmax(j) done
         }
         // ---- epilogue: the partial result (o unnormalised, m in scaled-score units, l)
         ok = mbar_wait_bounded(bar_o, (nblk - 1) & 1, err, 22) && ok;
         tc_fence_after();
+        if (tid == 0) PF_T(40);  // last P V complete
         {
-            // (tcgen05.ld is warp-collective: padding vectors load too, only real ones store)
-            const bool valid = rl < w.nrows;
-            const int x = t % G;
-            float *p = part + (((size_t)(w.row0 + (valid ? rl : 0)) * max_splits + w.split) * n_heads + (size_t)g * G + x) * RQ_PSTRIDE(HD);
+            // every thread's row of O goes through shared memory (Q / K / V are no longer needed: all MMAs are
+            // complete) so that the global stores are coalesced: a warp then writes one 512-byte row per step
+            constexpr int OST = HD + 4;  // floats per staged row (the padding spreads the rows over the banks)
+            float *so = reinterpret_cast<float *>(sm);
 #pragma unroll 1
             for (int cc = 0; cc < 4; cc++) {
                 uint32_t r[32];
                 tmem_ld32(lane_addr + O_COL + cc * 32, r);
                 tmem_wait_ld();
-                if (valid) {
 #pragma unroll
-                    for (int y = 0; y < 32; y += 4)
-                        *reinterpret_cast<float4 *>(p + cc * 32 + y) =
-                            ok ? make_float4(__uint_as_float(r[y]), __uint_as_float(r[y + 1]), __uint_as_float(r[y + 2]), __uint_as_float(r[y + 3]))
-                               : make_float4(0, 0, 0, 0);
-                }
+                for (int y = 0; y < 32; y += 4)
+                    *reinterpret_cast<float4 *>(so + (size_t)t * OST + cc * 32 + y) =
+                        make_float4(__uint_as_float(r[y]), __uint_as_float(r[y + 1]), __uint_as_float(r[y + 2]), __uint_as_float(r[y + 3]));
             }
-            if (valid) {
-                p[HD] = m_used * scale;
-                p[HD + 1] = l;
+            so[(size_t)t * OST + HD] = m_used * scale;
+            so[(size_t)t * OST + HD + 1] = l;
+            if (tid == 0) PF_T(42);  // O staged
+            __syncwarp();  // (a warp stages and writes the same 32 rows)
+#pragma unroll 8
+            for (int rr = 0; rr < 32; rr++) {
+                const int tt = warp * 32 + rr, rl2 = tt / G, x = tt % G;
+                if (rl2 >= w.nrows) continue;
+                float *p = part + (((size_t)(w.row0 + rl2) * max_splits + w.split) * n_heads + (size_t)g * G + x) * RQ_PSTRIDE(HD);
+                float4 v4 = *reinterpret_cast<const float4 *>(so + (size_t)tt * OST + 4 * lane);
+                *reinterpret_cast<float4 *>(p + 4 * lane) = ok ? v4 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (lane < 2) p[HD + lane] = so[(size_t)tt * OST + HD + lane];
             }
         }
     }
+    if (tid == 0) PF_T(41);  // partial written
     tc_fence_before();
     __syncthreads();
     if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(TM_COLS));

@@ -57,6 +57,12 @@ struct RqCuda {
     std::vector<RqCudaSegment> segs;
     PassRow *h_rows, *d_rows;  // nrows + 1 entries (the last one holds the total block count)
     DnSeg *h_dseg, *d_dseg;
+    // the pinned tables are double-buffered: a pass fills the half the pass before the previous one used, after that
+    // half's upload (an event) is known to be complete, so opening a pass never waits for the device
+    PassRow *h_rows2[2];
+    DnSeg *h_dseg2[2];
+    cudaEvent_t up_ev[2];
+    int up_idx;
     // scratch, grown on demand
     float *d_part;  size_t part_bytes;
     float *d_q;     size_t q_bytes;     // staging of host q rows
@@ -197,9 +203,13 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
     c->err[0] = 0;
     bool okk = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) == cudaSuccess &&
                cudaEventCreate(&c->ev0) == cudaSuccess && cudaEventCreate(&c->ev1) == cudaSuccess &&
-               cudaMallocHost((void **)&c->h_rows, sizeof(PassRow) * (max_rows + 1)) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_rows2[0], sizeof(PassRow) * (max_rows + 1)) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_rows2[1], sizeof(PassRow) * (max_rows + 1)) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_dseg2[0], sizeof(DnSeg) * max_rows) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_dseg2[1], sizeof(DnSeg) * max_rows) == cudaSuccess &&
+               cudaEventCreateWithFlags(&c->up_ev[0], cudaEventDisableTiming) == cudaSuccess &&
+               cudaEventCreateWithFlags(&c->up_ev[1], cudaEventDisableTiming) == cudaSuccess &&
                cudaMalloc((void **)&c->d_rows, sizeof(PassRow) * (max_rows + 1)) == cudaSuccess &&
-               cudaMallocHost((void **)&c->h_dseg, sizeof(DnSeg) * max_rows) == cudaSuccess &&
                cudaMalloc((void **)&c->d_dseg, sizeof(DnSeg) * max_rows) == cudaSuccess &&
                cudaMalloc((void **)&c->d_err, sizeof(int)) == cudaSuccess &&
                cudaMallocHost((void **)&c->h_err, sizeof(int)) == cudaSuccess &&
@@ -223,8 +233,11 @@ void rq_cuda_free(RqCuda *c) {
     if (c->h_maps) cudaFreeHost(c->h_maps);
     for (void *p : dev)
         if (p) cudaFree(p);
-    if (c->h_rows) cudaFreeHost(c->h_rows);
-    if (c->h_dseg) cudaFreeHost(c->h_dseg);
+    for (int i = 0; i < 2; i++) {
+        if (c->h_rows2[i]) cudaFreeHost(c->h_rows2[i]);
+        if (c->h_dseg2[i]) cudaFreeHost(c->h_dseg2[i]);
+        if (c->up_ev[i]) cudaEventDestroy(c->up_ev[i]);
+    }
     if (c->h_err) cudaFreeHost(c->h_err);
     for (cudaEvent_t ev : c->prof_ev) cudaEventDestroy(ev);
     if (c->ev0) cudaEventDestroy(c->ev0);
@@ -447,9 +460,12 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
     }
     if (total > c->max_rows) return fail(c, RQ_CUDA_ERR_ARG, "%ld rows exceed the context's %d", total, c->max_rows);
     CU(c, cudaSetDevice(c->device));
-    // (the previous pass's table may still be read by kernels in flight: the copy below is stream-ordered behind
-    // them, and the pinned source is rewritten only after the stream drained it)
-    CU(c, cudaStreamSynchronize(c->stream));
+    // (the device table may still be read by kernels of the previous pass: the copy below is stream-ordered behind
+    // them; the pinned half written now was last uploaded two passes ago)
+    c->up_idx ^= 1;
+    CU(c, cudaEventSynchronize(c->up_ev[c->up_idx]));
+    c->h_rows = c->h_rows2[c->up_idx];
+    c->h_dseg = c->h_dseg2[c->up_idx];
     int r = 0, blk = 0, mx = 0;
     for (int i = 0; i < nseg; i++) {
         const RqCudaSegment &g = seg[i];
@@ -476,38 +492,10 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
     }
     memset(&c->h_rows[r], 0, sizeof(PassRow));
     c->h_rows[r].blk0 = blk;
-    // tensor-core prefill: the segments' tensor maps, and the work list (M tile of 128 / G rows, 1024-position split)
-    c->pf_ready = 0;
-    if (c->m.n_attn > 0 && c->m.head_dim == 128 && kvt == KV_F16) {
-        bool all = true;
-        for (int i = 0; i < nseg; i++) all = all && seg[i].seq->has_tm;
-        if (all) {
-            const int rpt = 128 / c->G;
-            c->h_work.clear();
-            for (int i = 0; i < nseg; i++) {
-                c->h_maps[2 * i] = seg[i].seq->tm_k;
-                c->h_maps[2 * i + 1] = seg[i].seq->tm_v;
-            }
-            int row = 0;
-            for (int i = 0; i < nseg; i++) {
-                for (int m0 = 0; m0 < seg[i].n; m0 += rpt) {
-                    int nr = std::min(rpt, seg[i].n - m0), np_max = seg[i].pos0 + m0 + nr;
-                    for (int k = 0; k * PF_SPLIT < np_max; k++) c->h_work.push_back(PfWork{i, row + m0, nr, k});
-                }
-                row += seg[i].n;
-            }
-            c->pf_max_splits = (mx + PF_SPLIT - 1) / PF_SPLIT;
-            size_t wb = c->h_work.size() * sizeof(PfWork);
-            int rc2 = grow(c, (void **)&c->d_work, &c->work_bytes, wb);
-            if (rc2) return rc2;
-            CU(c, cudaMemcpyAsync(c->d_maps, c->h_maps, sizeof(CUtensorMap) * 2 * nseg, cudaMemcpyHostToDevice, c->stream));
-            CU(c, cudaMemcpyAsync(c->d_work, c->h_work.data(), wb, cudaMemcpyHostToDevice, c->stream));
-            CU(c, cudaStreamSynchronize(c->stream));  // (the work list is pageable host memory)
-            c->pf_ready = 1;
-        }
-    }
+    c->pf_ready = 0;  // (the tensor-core prefill tables are made by the first prefill call of the pass)
     CU(c, cudaMemcpyAsync(c->d_rows, c->h_rows, sizeof(PassRow) * (r + 1), cudaMemcpyHostToDevice, c->stream));
     if (c->m.n_lin > 0) CU(c, cudaMemcpyAsync(c->d_dseg, c->h_dseg, sizeof(DnSeg) * nseg, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaEventRecord(c->up_ev[c->up_idx], c->stream));
     c->segs.assign(seg, seg + nseg);
     for (int i = 0; i < nseg; i++) seg[i].seq->in_pass = 1;
     c->nrows = r;
@@ -613,7 +601,7 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
 
 static int launch_combine(RqCuda *c, const float *q, float *out, const float *part, int split_len, int fixed_stride) {
     const int hd = c->m.head_dim;
-    dim3 grid(c->nrows, c->n_heads);
+    dim3 grid(c->nrows, (c->n_heads + COMBINE_HPB - 1) / COMBINE_HPB);
     const bool quant = kv_quant(c->pass_kvt);
 #define COMBINE(HD_)                                                                                                          \
     if (quant) attn_combine_kernel<HD_, true><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride); \
@@ -692,10 +680,44 @@ int rq_cuda_attn_decode_noalloc(RqCuda *c, int layer, const float *q, float *out
     return launch_decode_with(c, layer, q, out, g_noalloc_ptr[c->device]);
 }
 
+static int prefill_tables(RqCuda *c) {
+    // once per pass: the segments' tensor maps and the work list (M tile of 128 / G rows x 1024-position split) of the
+    // tensor-core prefill kernel; pf_ready 1: made, -1: the pass does not qualify (cache type, head_dim)
+    if (c->pf_ready) return RQ_CUDA_OK;
+    c->pf_ready = -1;
+    if (c->m.head_dim != 128 || c->pass_kvt != KV_F16) return RQ_CUDA_OK;
+    for (auto &g : c->segs)
+        if (!g.seq->has_tm) return RQ_CUDA_OK;
+    const int rpt = 128 / c->G, nseg = (int)c->segs.size();
+    c->h_work.clear();
+    int row = 0;
+    for (int i = 0; i < nseg; i++) {
+        const RqCudaSegment &g = c->segs[i];
+        c->h_maps[2 * i] = g.seq->tm_k;
+        c->h_maps[2 * i + 1] = g.seq->tm_v;
+        for (int m0 = 0; m0 < g.n; m0 += rpt) {
+            int nr = std::min(rpt, g.n - m0), np_max = g.pos0 + m0 + nr;
+            for (int k = 0; k * PF_SPLIT < np_max; k++) c->h_work.push_back(PfWork{i, row + m0, nr, k});
+        }
+        row += g.n;
+    }
+    c->pf_max_splits = (c->max_np + PF_SPLIT - 1) / PF_SPLIT;
+    size_t wb = c->h_work.size() * sizeof(PfWork);
+    int rc = grow(c, (void **)&c->d_work, &c->work_bytes, wb);
+    if (rc) return rc;
+    CU(c, cudaMemcpyAsync(c->d_maps, c->h_maps, sizeof(CUtensorMap) * 2 * nseg, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaMemcpyAsync(c->d_work, c->h_work.data(), wb, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaStreamSynchronize(c->stream));  // (the work list is pageable host memory, the maps are reused next pass)
+    c->pf_ready = 1;
+    return RQ_CUDA_OK;
+}
+
 static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     // tensor-core tiles where the pass qualifies (f16 cache, head_dim 128); other shapes take the split-K kernels,
     // which compute the same attention on the CUDA cores
-    if (!c->pf_ready) return launch_decode(c, layer, q, out);
+    int rc0 = prefill_tables(c);
+    if (rc0) return rc0;
+    if (c->pf_ready != 1) return launch_decode(c, layer, q, out);
     const int hd = c->m.head_dim;
     size_t need = (size_t)c->nrows * c->pf_max_splits * c->n_heads * RQ_PSTRIDE(hd) * 4;
     int rc = grow(c, (void **)&c->d_part, &c->part_bytes, need);

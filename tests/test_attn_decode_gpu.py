@@ -77,7 +77,9 @@ def test_prompt_chunk_rows_match_cpu(checker):
     from gwenedeg_b200 import synth
     n_heads, n_kv, hd, n = 4, 2, 128, 300
     c = make_ctx(n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd)
-    k, v = kv_rows(77, n, n_kv, hd)
+    # (no f16-range outliers here: the chunk goes through the tensor-core kernel, whose f16 rounding of the softmax
+    # weights is bounded relative to the output, and the absolute bar is stated for N(0,1)-sized values)
+    k, v = kv_rows(77, n, n_kv, hd, outlier=False)
     a, b = c.new_seq(n, F16), c.new_seq(n, F16)
     c.pass_begin([(a, 0, n)])
     c.kv_store(0, k, v)
