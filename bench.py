@@ -30,6 +30,7 @@ N_SEQ, N_LAYERS, N_HEADS, N_KV, HD = 64, 36, 32, 8, 128
 CTX_LO, CTX_HI, CTX_SEED = 512, 32768, 20250
 KV_BYTES_PER_POS = 2 * N_KV * HD * 2           # f16 K + V of one position of one layer: 4096 B (the algorithmic bytes)
 METRIC = "Qwen3-8B attn: decode rows/s (B=64 ragged ctx)"
+TRAFFIC_RATIO = (189.70 + 4.27) / 189.25  # measured DRAM bytes (read + written) over algorithmic K+V bytes, ncu capture of --small
 
 
 def contexts():
@@ -185,6 +186,117 @@ def prefill_leg(device, steps, layers=None, warm=3):
     return {"workload": "qwen3-0.6b-prefill-512-over-3584", "tflops": tf_step, "ms_per_chunk_all_layers": ms / steps,
             "roofline": {"bound": "tensor", "achieved": tf_kern, "peak": peak, "unit": "TFLOP/s", "frac": tf_kern / peak, "traffic": None,
                          "peak_source": how, "kernel": "attn_prefill_kernel", "flops_per_launch": flops_layer, "launches_timed": kern_n}}
+
+
+Q8_SEQ, Q8_CTX, Q8_BYTES_PER_POS = 32, 40960, 2 * N_KV * (HD + HD // 32 * 2)  # 2,176 B of q8 K + V per position per layer
+
+
+def q8_leg(args, rank, local_rank, world):
+    """Qwen3-8B-shaped q8 KV decode: 32 sequences at context 40,960, K and V int8 in blocks of 32 dims with bf16
+    scales (the reference's tile format), dequantisation fused into the kernel.  With N > 1 every rank holds a group
+    of KV heads of every sequence and the outputs are all-gathered (NCCL)."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    from gwenedeg_b200.sharded import HeadShardedContext
+    import torch
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    layers = 2 if args.small else N_LAYERS
+    nseq = 4 if args.small else Q8_SEQ
+    sh = HeadShardedContext(local_rank, rank, world, n_attn=layers, n_heads=N_HEADS, n_kv_heads=N_KV, head_dim=HD, max_rows=nseq)
+    c = sh.ctx
+    seqs = []
+    for i in range(nseq):
+        s = c.new_seq(Q8_CTX, g.KV_Q8)
+        s.fill_synthetic(Q8_CTX, 500 + i)
+        seqs.append(s)
+    c.sync()
+    q = torch.from_numpy(synth.normal(11, (layers, nseq, N_HEADS, HD))).cuda()
+    segs = [(s, Q8_CTX - 1, 1) for s in seqs]
+
+    def step():
+        c.pass_begin(segs)
+        outs = [sh.attn_decode(l, q[l]) for l in range(layers)]
+        c.pass_end(commit=False)
+        return outs
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    c.profile_begin(args.steps * layers)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    kern_ms, kern_n = c.profile_end()
+    if dist is not None:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    peak, how = peaks()
+    bytes_launch = nseq * Q8_CTX * Q8_BYTES_PER_POS / world
+    achieved = bytes_launch / (kern_ms / max(kern_n, 1) * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({"metric": "Qwen3-8B attn: q8 KV decode rows/s (B=32, ctx 40960)", "value": nseq * args.steps / (ms * 1e-3),
+                          "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+                          "higher_is_better": True, "scaling": "strong", "dtype": "f32", "data": "synthetic",
+                          "config": {"workload": "qwen3-8b-decode-q8-b32-ctx40960", "layers": layers, "sequences": nseq,
+                                     "parallelism": f"kv-head-sharded x{world} + all-gather"},
+                          "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                                       "traffic": None, "peak_source": how, "kernel": "attn_part_kernel<q8,128,4>",
+                                       "algorithmic_bytes_per_launch_rank0": bytes_launch, "launches_timed": kern_n}}), flush=True)
+    sh.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+DN_LAYERS, DN_SEQ, DN_TOKENS, DN_HEADS, DN_DK = 18, 4, 8192, 16, 128
+
+
+def deltanet_leg(args, local_rank):
+    """Qwen3.5-style Gated DeltaNet recurrence: 18 linear layers, 4 sequences x 8,192 tokens in chunks of 512 rows, 16 heads,
+    d_k = d_v = 128, post-prep rows resident on the device.  flops = 8 d_k d_v per (token, head)."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    layers = 2 if args.small else DN_LAYERS
+    tokens = 1024 if args.small else DN_TOKENS
+    chunk = 128  # rows per sequence per pass: 4 x 128 = 512 rows
+    c = g.Context(local_rank, n_lin=layers, dn_nk=DN_HEADS, dn_nv=DN_HEADS, dn_dk=DN_DK, dn_dv=DN_DK, max_rows=DN_SEQ * chunk)
+    seqs = [c.new_seq(tokens, g.KV_F16) for _ in range(DN_SEQ)]
+    rows = synth.deltanet_rows(3, DN_SEQ * chunk, DN_HEADS, DN_HEADS, DN_DK, DN_DK)  # one pass worth of rows, reused
+    rows_dev = c.to_device(rows)
+    out_dev = c.malloc(DN_SEQ * chunk * DN_HEADS * DN_DK * 4)
+
+    def run():
+        for pos in range(0, tokens, chunk):
+            c.pass_begin([(s, pos, chunk) for s in seqs])
+            for l in range(layers):
+                c.dn_rec_dev(l, rows_dev, out_dev)
+            c.pass_end()
+        for s in seqs:
+            s.truncate(0)
+
+    run()
+    c.sync()
+    c.timer_start()
+    for _ in range(args.steps):
+        run()
+    ms = c.timer_stop()
+    tok = DN_SEQ * tokens * args.steps
+    flops = 8.0 * DN_DK * DN_DK * DN_HEADS * layers * tok
+    print(json.dumps({"metric": "Qwen3.5 Gated DeltaNet recurrence: tokens/s (all linear layers)", "value": tok / (ms * 1e-3), "unit": "tokens/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": 1, "ms_per_step": ms / args.steps, "higher_is_better": True, "dtype": "f32",
+                      "data": "synthetic", "config": {"workload": "qwen3.5-deltanet-4x8192", "layers": layers, "tokens": tokens, "heads": DN_HEADS},
+                      "tflops": flops / (ms * 1e-3) / 1e12, "form": "exact token-by-token recurrence (bit-identical to the CPU code)"}), flush=True)
+    c.close()
 
 
 def run_reference(args, rank, world):
@@ -354,7 +466,7 @@ def run_ours(args, rank, local_rank, world):
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": how, "kernel": "attn_part_kernel<f16,128,4>",
+                         "traffic": bytes_per_launch * TRAFFIC_RATIO, "traffic_source": "ncu dram read+write of the small case, scaled by positions (profiles/attn_part_kernel_decode_b64_ragged.md)", "peak_source": how, "kernel": "attn_part_kernel<f16,128,4>",
                          "algorithmic_bytes_per_launch_rank0": bytes_per_launch, "launches_timed": part_n},
             "cpu_baseline": cpu,
             "prefill": prefill,
@@ -371,7 +483,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode-q8", "deltanet"],
                     help="decode: the headline batched-decode benchmark (default); prefill: only the chunked-prefill leg "
                          "(512 rows over a 3584-position prefix), printed as its own line")
     ap.add_argument("--small", action="store_true",
@@ -387,6 +499,13 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "decode-q8":
+        q8_leg(args, rank, local_rank, world)
+        return
+    if args.workload == "deltanet":
+        if rank == 0:
+            deltanet_leg(args, local_rank)
         return
     if args.workload == "prefill":
         if rank == 0:
