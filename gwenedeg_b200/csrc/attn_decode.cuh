@@ -58,6 +58,17 @@ __host__ __device__ constexpr size_t dec_smem_bytes(int buf, int hd, int nvt, bo
     return (size_t)buf + (size_t)ATT_P * nvt * 4 + (quant ? (size_t)nvt * hd * 4 : 0) + (size_t)4 * nvt * 4 + 16 + 32;
 }
 
+// int8 level in byte `sel` (0..3) of w_flipped (the packed levels with their sign bits flipped: n + 128 per byte) as an
+// exact float, without the slow integer-to-float conversion unit: the byte becomes the low mantissa bits of 2^23
+__device__ __forceinline__ float s8_to_f32(uint32_t w_flipped, int sel) {
+    // bytes of the result: [3] = 0x4B, [2] = [1] = 0x00 (from the constant), [0] = byte `sel` of the levels
+    return __uint_as_float(__byte_perm(w_flipped, 0x4B000000u, 0x7540 | sel)) - 8388736.0f;  // 2^23 + 128
+}
+// 4-bit level (stored + 8) at bit `sh` of w as an exact float: (nibble - 8)
+__device__ __forceinline__ float u4_to_f32(uint32_t w, int sh) {
+    return __uint_as_float(((w >> sh) & 15u) | 0x4B000000u) - 8388616.0f;  // 2^23 + 8
+}
+
 // dim i of PPT adjacent positions (first one: j0) of a K tile; d: the bf16 scales of those positions for dim i's
 // 32-dim chunk (quantised formats: value = level x scale, exact in fp32)
 template <int KF, int PPT>
@@ -77,13 +88,13 @@ __device__ __forceinline__ void load_k(const uint8_t *kt, int i, int j0, const f
             if constexpr (PPT == 4) w = *reinterpret_cast<const uint32_t *>(kt + (size_t)i * 16 + j0);
             else w = *reinterpret_cast<const uint16_t *>(kt + (size_t)i * 16 + j0);
 #pragma unroll
-            for (int p = 0; p < PPT; p++) k[p] = (float)(int)(int8_t)((w >> (8 * p)) & 0xff) * d[p];
+            for (int p = 0; p < PPT; p++) k[p] = s8_to_f32(w ^ 0x80808080u, p) * d[p];
         } else {  // q4: byte [dim pair][position], low nibble dim 2p, high nibble dim 2p + 1
             if constexpr (PPT == 4) w = *reinterpret_cast<const uint32_t *>(kt + (size_t)(i >> 1) * 16 + j0);
             else w = *reinterpret_cast<const uint16_t *>(kt + (size_t)(i >> 1) * 16 + j0);
             const int sh = 4 * (i & 1);
 #pragma unroll
-            for (int p = 0; p < PPT; p++) k[p] = (float)((int)((w >> (8 * p + sh)) & 15) - 8) * d[p];
+            for (int p = 0; p < PPT; p++) k[p] = u4_to_f32(w, 8 * p + sh) * d[p];
         }
     }
 }
@@ -122,21 +133,21 @@ __device__ __forceinline__ void load_v(const uint8_t *vt, int j, int i0, float *
         const float d = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(vt + 16 * HD + (j * (HD / 32) + (i0 >> 5)) * 2));
         const int8_t *p = reinterpret_cast<const int8_t *>(vt + (size_t)j * HD + i0);
         if constexpr (DPT == 1) {
-            vv[0] = (float)(int)p[0] * d;
+            vv[0] = s8_to_f32((uint32_t)(uint8_t)p[0] ^ 0x80u, 0) * d;
         } else if constexpr (DPT == 2) {
-            uint32_t w = *reinterpret_cast<const uint16_t *>(p);
-            vv[0] = (float)(int)(int8_t)(w & 0xff) * d; vv[1] = (float)(int)(int8_t)(w >> 8) * d;
+            uint32_t w = (uint32_t)*reinterpret_cast<const uint16_t *>(p) ^ 0x8080u;
+            vv[0] = s8_to_f32(w, 0) * d; vv[1] = s8_to_f32(w, 1) * d;
         } else {
-            uint32_t w = *reinterpret_cast<const uint32_t *>(p);
+            uint32_t w = *reinterpret_cast<const uint32_t *>(p) ^ 0x80808080u;
 #pragma unroll
-            for (int x = 0; x < 4; x++) vv[x] = (float)(int)(int8_t)((w >> (8 * x)) & 0xff) * d;
+            for (int x = 0; x < 4; x++) vv[x] = s8_to_f32(w, x) * d;
         }
     } else {  // q4: per position and group 16 bytes, byte l = dims 32c + l (low nibble), 32c + 16 + l (high)
         const float d = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(vt + 8 * HD + (j * (HD / 32) + (i0 >> 5)) * 2));
         const uint8_t *p = vt + (size_t)j * (HD / 2) + (i0 >> 5) * 16 + (i0 & 15);
         const int sh = 4 * ((i0 >> 4) & 1);
 #pragma unroll
-        for (int x = 0; x < DPT; x++) vv[x] = (float)((int)((p[x] >> sh) & 15) - 8) * d;
+        for (int x = 0; x < DPT; x++) vv[x] = u4_to_f32(p[x], sh) * d;
     }
 }
 
@@ -258,7 +269,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
             // thread's positions; a single vector (NV == 1) takes the scalar path.  The loads of step i + PF are issued
             // before the arithmetic of step i (software pipeline: few warps are resident, so the shared-memory latency
             // has to be hidden inside the thread).
-            constexpr int NVP = NV / 2, PF = 3;
+            constexpr int NVP = NV / 2, PF = KF == KV_F16 ? 3 : 4;
             const float *qg = qs + (size_t)grp * HD * NV;
             float2 a2[NVP > 0 ? NVP : 1][PPT], c2[NVP > 0 ? NVP : 1][PPT];
             float a1[PPT], c1[PPT];
@@ -284,7 +295,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
                 };
 #pragma unroll
                 for (int i = 0; i < PF; i++) fetch(i, i);
-#pragma unroll
+#pragma unroll(KF == KV_F16 ? HD : ATT_DC)  // (quantised formats: one chunk per trip keeps the code in the instruction cache)
                 for (int i = 0; i < HD; i++) {
                     const int slot = i % PF;
                     float kk[PPT];
