@@ -351,7 +351,7 @@ def run_ours(args, rank, local_rank, world):
         return float(t.item())
 
     ctx_all = contexts()
-    mine = shard(ctx_all, world)[rank]
+    mine = shard(ctx_all, args.shard_of)[0] if args.shard_of > 1 else shard(ctx_all, world)[rank]
     my_ctx = [int(ctx_all[i]) for i in mine]
     my_pos = sum(my_ctx)
 
@@ -449,7 +449,7 @@ def run_ours(args, rank, local_rank, world):
                 cpu = cpu_leg(ctx_all, reps=3, sample_every=8)
             except Exception as e:  # the baseline is reported, never required
                 cpu = {"value": None, "unit": "rows/s", "cores": 0, "kind": "unavailable", "sample": repr(e)}
-        value = N_SEQ * args.steps / (ms_max * 1e-3)
+        value = (len(mine) if args.shard_of > 1 else N_SEQ) * args.steps / (ms_max * 1e-3)
         line = {
             "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -486,6 +486,9 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode-q8", "deltanet"],
                     help="decode: the headline batched-decode benchmark (default); prefill: only the chunked-prefill leg "
                          "(512 rows over a 3584-position prefix), printed as its own line")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="profiling aid (one GPU): run only the sequences rank 0 of a W-rank job would own, to look at the "
+                         "per-GPU workload of a multi-GPU run under ncu")
     ap.add_argument("--small", action="store_true",
                     help="profiling case for ncu captures: 8 sequences of 4096..8192 positions, 2 layers (about 0.4 GB of "
                          "KV per layer: larger than the L2, small enough for a multi-pass capture), no CPU / end-to-end legs")

@@ -507,86 +507,88 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
 // :2291).  One CTA of HD threads per (row, query head).
 // split_len / fixed_stride: the partials of a row are one per `split_len` positions, the first one at record index
 // row.blk0 (fixed_stride 0: the decode kernel's 256-position blocks) or r * fixed_stride (the prefill kernel's splits).
-constexpr int COMBINE_HPB = 1;  // query heads one CTA of the merge kernel handles, one after the other
+constexpr int COMBINE_NG = 4;  // thread groups of the merge kernel: each fetches a quarter of the partials
 
+// One CTA of COMBINE_NG x HD threads per (row, query head).  The partial results are fetched into shared memory by all
+// the threads at once (group g takes the partials b = g mod COMBINE_NG: many loads in flight, the kernel is bound by
+// their latency), then the first HD threads run the two fma chains over them in partial order.
 template <int HD, bool QUANT>
-__global__ void __launch_bounds__(HD) attn_combine_kernel(const PassRow *__restrict__ rows, int n_heads, const float *__restrict__ part,
-                                                          const float *__restrict__ q, int qh, int gated, float *__restrict__ out,
-                                                          int split_len, int fixed_stride) {
-    const int r = blockIdx.x, i = threadIdx.x;
+__global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const PassRow *__restrict__ rows, int n_heads,
+                                                                      const float *__restrict__ part, const float *__restrict__ q, int qh,
+                                                                      int gated, float *__restrict__ out, int split_len, int fixed_stride) {
+    constexpr int CH = 8192 / HD;  // partials per chunk: 32 KB of shared memory
+    const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, i = tid % HD, grp = tid / HD;
     const PassRow row = rows[r];
     const int nb = (row.np + split_len - 1) / split_len;
     const size_t pst = RQ_PSTRIDE(HD);
     const size_t bstride = (size_t)n_heads * pst;
-    const float *prow = part + (size_t)(fixed_stride ? r * fixed_stride : row.blk0) * n_heads * pst;
+    const float *p0 = part + ((size_t)(fixed_stride ? r * fixed_stride : row.blk0) * n_heads + h) * pst;
+    __shared__ float tile[CH][HD];
+    __shared__ float cs[CH], ls[CH], red[COMBINE_NG * HD / 32];
     __shared__ float x[QUANT ? HD : 1];
-    __shared__ float cs[HD], ls[HD], red[HD / 32];  // per chunk of HD partials: c_b and l_b
-#pragma unroll 1
-    for (int hh = 0; hh < COMBINE_HPB; hh++) {
-        const int h = blockIdx.y * COMBINE_HPB + hh;
-        if (h >= n_heads) break;
-        const float *p0 = prow + (size_t)h * pst;
-        float res;
-        if (nb == 1) {
+    float res = 0.0f;
+    if (nb == 1) {
+        if (grp == 0) {
             float inv = 1.0f / p0[HD + 1];
             res = p0[i] * inv;
-        } else {
-            // M = max of the m_b (threads over partials, then a shuffle / shared-memory reduction: any order gives
-            // the same maximum)
-            float M = -INFINITY;
-            for (int b = i; b < nb; b += HD) M = fmaxf(M, p0[b * bstride + HD]);
+        }
+    } else {
+        // M = max of the m_b (any order gives the same maximum)
+        float M = -INFINITY;
+        for (int b = tid; b < nb; b += COMBINE_NG * HD) M = fmaxf(M, p0[b * bstride + HD]);
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-            __syncthreads();  // (red, cs, ls of the previous head have been read)
-            if ((i & 31) == 0) red[i >> 5] = M;
+        for (int o = 16; o >= 1; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        if ((tid & 31) == 0) red[tid >> 5] = M;
+        __syncthreads();
+        M = red[0];
+#pragma unroll
+        for (int wv = 1; wv < COMBINE_NG * HD / 32; wv++) M = fmaxf(M, red[wv]);
+        float L = 0.0f, acc = 0.0f;
+        for (int b0 = 0; b0 < nb; b0 += CH) {
+            const int cnt = min(CH, nb - b0);
+            __syncthreads();  // (the previous chunk has been consumed)
+            const float *pc = p0 + (size_t)b0 * bstride;
+#pragma unroll 8
+            for (int b = grp; b < cnt; b += COMBINE_NG) tile[b][i] = pc[(size_t)b * bstride + i];
+            if (tid < cnt) {
+                cs[tid] = exp_att(pc[(size_t)tid * bstride + HD] - M);  // c_b = exp_att(m_b - M)
+                ls[tid] = pc[(size_t)tid * bstride + HD + 1];
+            }
             __syncthreads();
-            M = red[0];
-#pragma unroll
-            for (int wv = 1; wv < HD / 32; wv++) M = fmaxf(M, red[wv]);
-            // partials in order, HD at a time: c_b = exp_att(m_b - M) by one thread per partial, then every thread runs
-            // the two fma chains (L over the l_b, its own output dim over the o_b) in partial order
-            float L = 0.0f, acc = 0.0f;
-            for (int b0 = 0; b0 < nb; b0 += HD) {
-                const int cnt = min(HD, nb - b0);
-                __syncthreads();
-                if (i < cnt) {
-                    const float *p = p0 + (size_t)(b0 + i) * bstride;
-                    cs[i] = exp_att(p[HD] - M);
-                    ls[i] = p[HD + 1];
-                }
-                __syncthreads();
-                const float *po = p0 + (size_t)b0 * bstride + i;
+            if (grp == 0) {
+                // L = fma chain over the l_b, out[i] = fma chain over the o_b[i], both in partial order
 #pragma unroll 8
                 for (int b = 0; b < cnt; b++) {
                     L = fmaf(cs[b], ls[b], L);
-                    acc = fmaf(cs[b], po[(size_t)b * bstride], acc);
+                    acc = fmaf(cs[b], tile[b][i], acc);
                 }
             }
-            float inv = 1.0f / L;
-            res = acc * inv;
         }
-        if constexpr (QUANT) {
-            __syncthreads();  // (the previous head's values have been read)
-            x[i] = res;
+        float inv = 1.0f / L;
+        res = acc * inv;
+    }
+    if constexpr (QUANT) {
+        if (grp == 0) x[i] = res;
+        __syncthreads();
+        for (int hs = 1; hs < HD; hs <<= 1) {
+            float a = 0.0f, bb = 0.0f;
+            int j = 0;
+            if (tid < HD / 2) {
+                j = (tid / hs) * 2 * hs + (tid % hs);
+                a = x[j];
+                bb = x[j + hs];
+            }
             __syncthreads();
-            for (int hs = 1; hs < HD; hs <<= 1) {
-                float a = 0.0f, bb = 0.0f;
-                int j = 0;
-                if (i < HD / 2) {
-                    j = (i / hs) * 2 * hs + (i % hs);
-                    a = x[j];
-                    bb = x[j + hs];
-                }
-                __syncthreads();
-                if (i < HD / 2) {
-                    x[j] = a + bb;
-                    x[j + hs] = a - bb;
-                }
-                __syncthreads();
+            if (tid < HD / 2) {
+                x[j] = a + bb;
+                x[j + hs] = a - bb;
             }
-            res = kvq_neg(i) ? -x[i] : x[i];
-            res = res * (1.0f / (float)HD);
+            __syncthreads();
         }
+        res = kvq_neg(i) ? -x[i] : x[i];
+        res = res * (1.0f / (float)HD);
+    }
+    if (grp == 0) {
         if (gated) res = res * sigmoid_att(q[((size_t)r * n_heads + h) * qh + HD + i]);
         out[((size_t)r * n_heads + h) * HD + i] = res;
     }

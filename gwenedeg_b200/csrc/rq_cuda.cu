@@ -601,11 +601,11 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
 
 static int launch_combine(RqCuda *c, const float *q, float *out, const float *part, int split_len, int fixed_stride) {
     const int hd = c->m.head_dim;
-    dim3 grid(c->nrows, (c->n_heads + COMBINE_HPB - 1) / COMBINE_HPB);
+    dim3 grid(c->nrows, c->n_heads);
     const bool quant = kv_quant(c->pass_kvt);
 #define COMBINE(HD_)                                                                                                          \
-    if (quant) attn_combine_kernel<HD_, true><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride); \
-    else attn_combine_kernel<HD_, false><<<grid, HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride);
+    if (quant) attn_combine_kernel<HD_, true><<<grid, COMBINE_NG * HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride); \
+    else attn_combine_kernel<HD_, false><<<grid, COMBINE_NG * HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride);
     switch (hd) {
         case 64: COMBINE(64) break;
         case 128: COMBINE(128) break;
