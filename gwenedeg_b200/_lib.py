@@ -53,6 +53,7 @@ PROTOTYPES = {
     "rq_cuda_pass_end": (_i, [_vp, _i]),
     "rq_cuda_kv_store": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_kv_store_dev": (_i, [_vp, _i, _vp, _vp]),
+    "rq_cuda_qk_norm_rope_store_dev": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, C.c_float]),
     "rq_cuda_attn_decode": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_attn_decode_dev": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_attn_decode_noalloc": (_i, [_vp, _i, _vp, _vp]),

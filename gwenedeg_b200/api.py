@@ -102,6 +102,10 @@ class Context:
                 raise ValueError("K / V rows must be [rows][kv_heads][head_dim]")
         self.check(self.L.rq_cuda_kv_store(self.h, layer, _ptr(k), _ptr(v)))
 
+    def qk_norm_rope_store_dev(self, layer, q_dev, k_dev, v_dev, qw_dev, kw_dev, rope_dim, rope_theta=1e6):
+        self.check(self.L.rq_cuda_qk_norm_rope_store_dev(self.h, layer, _ptr(q_dev), _ptr(k_dev), _ptr(v_dev), _ptr(qw_dev), _ptr(kw_dev),
+                                                        rope_dim, C.c_float(rope_theta)))
+
     def _attn(self, fn, layer, q):
         q = np.ascontiguousarray(q, np.float32)
         if q.size != self.nrows * self.n_heads * self.qh:

@@ -11,25 +11,16 @@
 
 namespace rq {
 
+// Element i of one row (x = the row's value for dim i; all HD threads of the CTA call this together) into position j
+// of its tile, in the format fmt of that half; xs: HD floats of shared memory (rotation scratch of q8 / q4).
 template <int HD>
-__global__ void __launch_bounds__(HD) kv_store_kernel(const PassRow *__restrict__ rows, int layer, int n_kv, int kvt,
-                                                      const float *__restrict__ k, const float *__restrict__ v) {
-    const int r = blockIdx.x, h = blockIdx.y, half = blockIdx.z, i = threadIdx.x;
-    const float *src = half ? v : k;
-    if (!src) return;
-    const PassRow row = rows[r];
-    const int pos = row.pos, j = pos % ATT_T;
-    const int fmt = kv_fmt(kvt, half);
-    const size_t tb = kv_tile_bytes(kvt, HD, half);
-    uint8_t *tile = const_cast<uint8_t *>(half ? row.v : row.k) + (size_t)layer * (half ? row.lv : row.lk) +
-                    kv_tile_index(pos, h, n_kv) * tb;
-    float x = src[((size_t)r * n_kv + h) * HD + i];
+__device__ __forceinline__ void kv_store_elem(uint8_t *tile, int fmt, int half, int j, int i, float x, float *xs) {
     if (fmt == KV_F16) {
         reinterpret_cast<uint16_t *>(tile)[half ? (size_t)j * HD + i : (size_t)i * ATT_T + j] = f32_to_f16_sat(x);
         return;
     }
     // rotation: signs, then butterflies h = 1, 2, 4, ... (each output one rounded add / subtract)
-    __shared__ float xs[HD];
+    __syncthreads();
     xs[i] = kvq_neg(i) ? -x : x;
     __syncthreads();
     for (int hh = 1; hh < HD; hh <<= 1) {
@@ -75,6 +66,73 @@ __global__ void __launch_bounds__(HD) kv_store_kernel(const PassRow *__restrict_
         int n1 = __shfl_sync(0xffffffffu, n, (lane + 16) & 31);
         if (lane < 16) tile[(size_t)j * (HD / 2) + 16 * c + lane] = (uint8_t)((n + 8) | (n1 + 8) << 4);
     }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(HD) kv_store_kernel(const PassRow *__restrict__ rows, int layer, int n_kv, int kvt,
+                                                      const float *__restrict__ k, const float *__restrict__ v) {
+    const int r = blockIdx.x, h = blockIdx.y, half = blockIdx.z, i = threadIdx.x;
+    const float *src = half ? v : k;
+    if (!src) return;
+    const PassRow row = rows[r];
+    const int pos = row.pos;
+    uint8_t *tile = const_cast<uint8_t *>(half ? row.v : row.k) + (size_t)layer * (half ? row.lv : row.lk) +
+                    kv_tile_index(pos, h, n_kv) * (size_t)kv_tile_bytes(kvt, HD, half);
+    __shared__ float xs[HD];
+    kv_store_elem<HD>(tile, kv_fmt(kvt, half), half, pos % ATT_T, i, src[((size_t)r * n_kv + h) * HD + i], xs);
+}
+
+// Fused producer of the attention's inputs, the step right before the path in the reference's workers: per row and head
+// the QK-norm (RMSNorm over the head, weight * (x / rms)) and the NeoX-style RoPE of the first `rd` dims for the row's
+// position (qk_norm_rope, reference src/forward.c:1266; rope_row :1248; rmsnorm :886), then K and V go straight into
+// the cache tiles (kv_store :1901) and q is left in place for the attention call.  The reference compiles this step
+// with -Ofast and its vectorised libm, so agreement with it is to rounding (~1e-6), not to the bit.
+// grid: (rows, n_heads + 2 n_kv): y < n_heads: a query head; next n_kv: a key head; last n_kv: a value head.
+template <int HD>
+__global__ void __launch_bounds__(HD) qk_norm_rope_store_kernel(const PassRow *__restrict__ rows, int layer, int n_kv, int n_heads, int kvt,
+                                                                float *__restrict__ q, int qh, const float *__restrict__ k,
+                                                                const float *__restrict__ v, const float *__restrict__ q_norm_w,
+                                                                const float *__restrict__ k_norm_w, int rd, float log_theta) {
+    const int r = blockIdx.x, y = blockIdx.y, i = threadIdx.x;
+    const PassRow row = rows[r];
+    const int pos = row.pos;
+    __shared__ float xs[HD];
+    __shared__ float red[HD / 32];
+    const int kind = y < n_heads ? 0 : y < n_heads + n_kv ? 1 : 2;  // q, k, v
+    const int h = kind == 0 ? y : kind == 1 ? y - n_heads : y - n_heads - n_kv;
+    float x;
+    if (kind == 0) x = q[((size_t)r * n_heads + h) * qh + i];
+    else x = (kind == 1 ? k : v)[((size_t)r * n_kv + h) * HD + i];
+    if (kind < 2) {
+        float ss = x * x;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((i & 31) == 0) red[i >> 5] = ss;
+        __syncthreads();
+        ss = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < HD / 32; wv++) ss += red[wv];
+        ss = 1.0f / sqrtf(ss * (1.0f / HD) + 1e-6f);
+        x = (kind == 0 ? q_norm_w : k_norm_w)[i] * (ss * x);
+        xs[i] = x;
+        __syncthreads();
+        if (i < rd) {
+            const int j = i < rd / 2 ? i : i - rd / 2;
+            const float freq = expf(log_theta * (-(float)j / (float)(rd / 2)));
+            float sn, cs;
+            sincosf((float)pos * freq, &sn, &cs);
+            const float a = xs[j], b = xs[j + rd / 2];
+            x = i < rd / 2 ? a * cs - b * sn : a * sn + b * cs;
+        }
+    }
+    if (kind == 0) {
+        q[((size_t)r * n_heads + h) * qh + i] = x;
+        return;
+    }
+    const int half = kind - 1;
+    uint8_t *tile = const_cast<uint8_t *>(half ? row.v : row.k) + (size_t)layer * (half ? row.lv : row.lk) +
+                    kv_tile_index(pos, h, n_kv) * (size_t)kv_tile_bytes(kvt, HD, half);
+    kv_store_elem<HD>(tile, kv_fmt(kvt, half), half, pos % ATT_T, i, x, xs);
 }
 
 // ---- synthetic fill -----------------------------------------------------------------------------------------------

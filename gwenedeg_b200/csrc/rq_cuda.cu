@@ -2,6 +2,7 @@
 // pass, and the launches of the kernels in this directory.  No PyTorch, no CPU fallback: every compute entry point
 // needs a CUDA device and fails with RQ_CUDA_ERR_DEVICE otherwise.
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -554,6 +555,31 @@ int rq_cuda_kv_store(RqCuda *c, int layer, const float *k, const float *v) {
     rc = rq_cuda_kv_store_dev(c, layer, k ? c->d_k : nullptr, v ? c->d_v : nullptr);
     if (rc) return rc;
     CU(c, cudaStreamSynchronize(c->stream));  // the host rows may be reused on return
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_qk_norm_rope_store_dev(RqCuda *c, int layer, float *q, const float *k, const float *v, const float *q_norm_w,
+                                   const float *k_norm_w, int rope_dim, float rope_theta) {
+    int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "qk_norm_rope_store");
+    if (rc) return rc;
+    if (!q || !k || !v || !q_norm_w || !k_norm_w) return fail(c, RQ_CUDA_ERR_ARG, "qk_norm_rope_store: null argument");
+    const int hd = c->m.head_dim;
+    if (rope_dim < 2 || rope_dim > hd || (rope_dim & 1) || !(rope_theta > 1.0f))
+        return fail(c, RQ_CUDA_ERR_ARG, "qk_norm_rope_store: %d rotated dims, base %g", rope_dim, (double)rope_theta);
+    CU(c, cudaSetDevice(c->device));
+    const float log_theta = (float)log((double)rope_theta);
+    dim3 grid(c->nrows, c->n_heads + 2 * c->n_kv);
+#define PRODUCER(HD_)                                                                                                          \
+    qk_norm_rope_store_kernel<HD_><<<grid, HD_, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->n_heads, c->pass_kvt, q, c->qh, k, v, \
+                                                                q_norm_w, k_norm_w, rope_dim, log_theta)
+    switch (hd) {
+        case 64: PRODUCER(64); break;
+        case 128: PRODUCER(128); break;
+        default: PRODUCER(256); break;
+    }
+#undef PRODUCER
+    c->launches++;
+    CU(c, cudaGetLastError());
     return RQ_CUDA_OK;
 }
 

@@ -118,6 +118,16 @@ int rq_cuda_pass_end(RqCuda *ctx, int commit);
 int rq_cuda_kv_store(RqCuda *ctx, int layer, const float *k, const float *v);
 int rq_cuda_kv_store_dev(RqCuda *ctx, int layer, const float *k_dev, const float *v_dev);
 
+/* The step right before the path, fused on the device (device pointers): per row of the pass, QK-norm (RMSNorm per head)
+ * and NeoX-style RoPE of q and k for the row's position, then K and V into the cache tiles, replacing qk_norm_rope
+ * (forward.c:1266), rope_row (:1248) and kv_store at the call sites :2679-2687, :3059-3085, :3568-3578.
+ * q: [rows][heads_local][qh] raw projections, normed + rotated in place (a gate half is left untouched);
+ * k, v: [rows][kv_heads_local][head_dim] raw projections; q_norm_w, k_norm_w: [head_dim] weights of the layer;
+ * rope_dim: rotated dims per head (head_dim for Qwen3, 64 for Qwen3.5); rope_theta: the RoPE base (1e6).
+ * The reference builds this step with -Ofast: results agree to rounding (~1e-6 relative), not bit for bit. */
+int rq_cuda_qk_norm_rope_store_dev(RqCuda *ctx, int layer, float *q_dev, const float *k_dev, const float *v_dev,
+                                   const float *q_norm_w_dev, const float *k_norm_w_dev, int rope_dim, float rope_theta);
+
 /* Attention of every row of the pass over its sequence's cache of layer `layer`: split-K flash-decode over the
  * reference's fixed 256-position blocks with the partial results merged in block order, replacing the attention
  * items of decode_worker (forward.c:2691-2715) and batch_decode_worker (:3582-3616): attention_part :1806 +

@@ -193,6 +193,24 @@ static void store_quant_row(int fmt, uint8_t *tile, int j, int hd, const float *
     }
 }
 
+GWO_API void gwo_qk_norm_rope(float *v, int n_heads, int stride, const float *norm_w, int hd, int rd, int pos, float log_theta) {
+    /* per head: x <- w (x / rms(x)) with rms over hd dims (eps 1e-6 inside the root), then the pairs (j, j + rd/2) of
+     * the first rd dims rotated by pos * theta^(-j / (rd/2)).  The reference compiles this part with -Ofast (its
+     * vectorised libm): agreement is to rounding, not to the bit */
+    for (int h = 0; h < n_heads; h++) {
+        float *q = v + (size_t)h * stride, ss = 0.0f;
+        for (int j = 0; j < hd; j++) ss += q[j] * q[j];
+        ss = 1.0f / sqrtf(ss * (1.0f / hd) + 1e-6f);
+        for (int j = 0; j < hd; j++) q[j] = norm_w[j] * (ss * q[j]);
+        for (int j = 0; j < rd / 2; j++) {
+            float freq = expf(log_theta * (-(float)j / (rd / 2)));
+            float c = cosf(pos * freq), sn = sinf(pos * freq), x = q[j], y = q[j + rd / 2];
+            q[j] = x * c - y * sn;
+            q[j + rd / 2] = x * sn + y * c;
+        }
+    }
+}
+
 GWO_API void gwo_kv_store(int kvt, void *kl, void *vl, int pos, int n_kv, int hd, const float *k, const float *v) {
     int j = pos % T;
     for (int h = 0; h < n_kv; h++) {

@@ -60,6 +60,8 @@ class Oracle:
         for n in ("gwo_f32_f16", "gwo_f16_f32", "gwo_exp_att", "gwo_sigmoid"):
             getattr(L, n).argtypes = [_vp, _vp, _sz]
             getattr(L, n).restype = None
+        L.gwo_qk_norm_rope.argtypes = [_vp, _i, _i, _vp, _i, _i, _i, _f]
+        L.gwo_qk_norm_rope.restype = None
         L.gwo_kv_store.argtypes = [_i, _vp, _vp, _i, _i, _i, _vp, _vp]
         L.gwo_kv_store.restype = None
         L.gwo_kv_block_f32.argtypes = [_i, _vp, _vp, _i, _i, _vp, _vp]
@@ -133,6 +135,16 @@ class Oracle:
         y = np.empty_like(x)
         self.L.gwo_sigmoid(self._p(x), self._p(y), x.size)
         return y
+
+    def qk_norm_rope(self, rows, norm_w, hd, positions, theta=1e6, rd=None, gated=False):
+        """rows [n][heads][hd (or 2 hd when gated)] -> normed + rotated copy (the gate half untouched)."""
+        rows = np.array(rows, np.float32, order="C")
+        n, nh, st = rows.shape
+        w = np.ascontiguousarray(norm_w, np.float32)
+        lt = np.float32(np.log(np.float64(theta)))
+        for r in range(n):
+            self.L.gwo_qk_norm_rope(rows[r].ctypes.data_as(_vp), nh, st, self._p(w), hd, rd or hd, int(positions[r]), lt)
+        return rows
 
     def new_cache(self, kvt, kv_len, n_kv, hd):
         """Zeroed K and V byte buffers of one layer (kv_len a multiple of 256)."""

@@ -59,6 +59,14 @@ DN_EXACT GWO_API void gwo_sigmoid(const float *x, float *y, size_t n) { RQ_FP_EX
     for (size_t i = 0; i < n; i++) y[i] = dn_sigmoid(x[i]);
 }
 
+/* QK-norm (RMSNorm per head) + NeoX RoPE of one row's heads, in place (rope_row :1248, qk_norm_rope :1266): v holds
+ * n_heads heads `stride` floats apart; the first rd dims of each head are rotated for position pos */
+GWO_API void gwo_qk_norm_rope(float *v, int n_heads, int stride, const float *norm_w, int hd, int rd, int pos, float log_theta) {
+    float cs[512];
+    rope_row(cs, rd, pos, log_theta);
+    qk_norm_rope(v, n_heads, stride, norm_w, hd, cs, rd);
+}
+
 /* K and / or V rows of all kv heads of one position (k, v: [n_kv][hd] floats, either may be NULL) */
 GWO_API void gwo_kv_store(int kvt, void *kl, void *vl, int pos, int n_kv, int hd, const float *k, const float *v) {
     for (int h = 0; h < n_kv; h++)
