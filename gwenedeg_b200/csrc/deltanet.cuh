@@ -94,22 +94,37 @@ __global__ void __launch_bounds__(32) dn_rec_kernel(const DnSeg *__restrict__ se
         const Stage &cur = ring[t % DN_STAGES], &nxt = ring[(t + 1) % DN_STAGES];
         u = (cur.val[lane] - u) * cur.beta;
         float o = 0.0f, un = 0.0f;
+        // (key / query values are read four at a time: one 16-byte broadcast load serves four steps of the chains)
+        const float4 *ck4 = reinterpret_cast<const float4 *>(cur.key), *cq4 = reinterpret_cast<const float4 *>(cur.qry);
+        const float4 *nk4 = reinterpret_cast<const float4 *>(nxt.key);
         if (t + 1 < sg.n) {
             const float egn = nxt.eg;
 #pragma unroll
-            for (int k = 0; k < DK; k++) {
-                float sv = fmaf(cur.key[k], u, S[k] * eg);
-                S[k] = sv;
-                o = fmaf(sv, cur.qry[k], o);
-                un = fmaf(sv * egn, nxt.key[k], un);
+            for (int k4 = 0; k4 < DK / 4; k4++) {
+                const float4 kk = ck4[k4], qq = cq4[k4], kn = nk4[k4];
+                const float kv[4] = {kk.x, kk.y, kk.z, kk.w}, qv[4] = {qq.x, qq.y, qq.z, qq.w}, nv4[4] = {kn.x, kn.y, kn.z, kn.w};
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
+                    const int k = 4 * k4 + x;
+                    float sv = fmaf(kv[x], u, S[k] * eg);
+                    S[k] = sv;
+                    o = fmaf(sv, qv[x], o);
+                    un = fmaf(sv * egn, nv4[x], un);
+                }
             }
             eg = egn;
         } else {
 #pragma unroll
-            for (int k = 0; k < DK; k++) {
-                float sv = fmaf(cur.key[k], u, S[k] * eg);
-                S[k] = sv;
-                o = fmaf(sv, cur.qry[k], o);
+            for (int k4 = 0; k4 < DK / 4; k4++) {
+                const float4 kk = ck4[k4], qq = cq4[k4];
+                const float kv[4] = {kk.x, kk.y, kk.z, kk.w}, qv[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
+                    const int k = 4 * k4 + x;
+                    float sv = fmaf(kv[x], u, S[k] * eg);
+                    S[k] = sv;
+                    o = fmaf(sv, qv[x], o);
+                }
             }
         }
         out[(size_t)(sg.row0 + t) * vdim + (size_t)h * dv + (size_t)jb * DN_BW + lane] = o;
