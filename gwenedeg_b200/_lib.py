@@ -62,6 +62,9 @@ PROTOTYPES = {
     "rq_cuda_attn_prefill_dev": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_dn_rec": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_dn_rec_dev": (_i, [_vp, _i, _vp, _vp]),
+    "rq_cuda_dn_set_weights": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
+    "rq_cuda_dn_prep_dev": (_i, [_vp, _i, _vp]),
+    "rq_cuda_dn_out_dev": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_malloc": (_i, [_vp, _sz, _pp]),
     "rq_cuda_mfree": (_i, [_vp, _vp]),
     "rq_cuda_malloc_host": (_i, [_vp, _sz, _pp]),

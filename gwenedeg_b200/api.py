@@ -134,6 +134,16 @@ class Context:
         self.check(self.L.rq_cuda_dn_rec(self.h, lin_layer, _ptr(rows), _ptr(out)))
         return out
 
+    def dn_set_weights(self, lin_layer, conv, a, dt, norm):
+        arrs = [np.ascontiguousarray(x, np.float32) for x in (conv, a, dt, norm)]
+        self.check(self.L.rq_cuda_dn_set_weights(self.h, lin_layer, *[_ptr(x) for x in arrs]))
+
+    def dn_prep_dev(self, lin_layer, rows_dev):
+        self.check(self.L.rq_cuda_dn_prep_dev(self.h, lin_layer, _ptr(rows_dev)))
+
+    def dn_out_dev(self, lin_layer, rows_dev, out_dev):
+        self.check(self.L.rq_cuda_dn_out_dev(self.h, lin_layer, _ptr(rows_dev), _ptr(out_dev)))
+
     def dn_rec_dev(self, lin_layer, rows_dev, out_dev):
         self.check(self.L.rq_cuda_dn_rec_dev(self.h, lin_layer, _ptr(rows_dev), _ptr(out_dev)))
 

@@ -136,4 +136,106 @@ __global__ void __launch_bounds__(32) dn_rec_kernel(const DnSeg *__restrict__ se
     for (int k = 0; k < DK; k++) Sg[(size_t)k * DN_BW] = S[k];
 }
 
+// ---- the steps around the recurrence (dn_prep_part, reference src/forward.c:2104; dn_out :2280) ----------------------
+// sum of x[i] y[i] over n = 16 m values held in shared memory, in the reference's order (dn_dot16 :2018): lane j of 16
+// adds i = j, j + 16, ... as an fma chain, then the tree (j + 8, + 4, + 2, + 1).  Called by the whole CTA (>= 32
+// threads); the result comes back to every thread through res_smem.
+__device__ __forceinline__ float dn_dot16_cta(const float *x, const float *y, int n, float *res_smem) {
+    const int tid = threadIdx.x;
+    if (tid < 32) {
+        const int j = tid & 15;
+        float a = 0.0f;
+        for (int i = j; i < n; i += 16) a = fmaf(x[i], y[i], a);
+        a = a + __shfl_down_sync(0xffffffffu, a, 8, 16);
+        a = a + __shfl_down_sync(0xffffffffu, a, 4, 16);
+        a = a + __shfl_down_sync(0xffffffffu, a, 2, 16);
+        a = a + __shfl_down_sync(0xffffffffu, a, 1, 16);
+        if (tid == 0) *res_smem = a;
+    }
+    __syncthreads();
+    return *res_smem;
+}
+
+// Step 1 of a linear-attention layer for the rows of the pass, in place (rows: [q | k | v | z | alpha | beta] raw
+// projections -> q, k, v = SiLU(causal conv over the last `conv` inputs), q / k L2-normalised, q also x 1/sqrt(dk),
+// exp(g) and beta in place of alpha / beta).  One CTA of 128 threads per (segment, channel group: q or k of a key head,
+// v of a value head); thread i owns channel i and walks the segment's rows in order with the last conv - 1 raw
+// inputs in registers, so the conv state is read once and written once.  dk = dv = 128, conv <= 8.
+// Everything except the two libm calls of the gate (expf, log1pf) repeats the reference's operations in order.
+__global__ void __launch_bounds__(128) dn_prep_kernel(const DnSeg *__restrict__ segs, int lin_layer, int nk, int nv, int K,
+                                                      const float *__restrict__ w_conv, const float *__restrict__ w_a,
+                                                      const float *__restrict__ w_dt, float *__restrict__ rows, int lw) {
+    constexpr int CN = 128;
+    const int i = threadIdx.x, grp = blockIdx.x;
+    const DnSeg sg = segs[blockIdx.y];
+    const int kind = grp < nk ? 0 : grp < 2 * nk ? 1 : 2, h = kind == 0 ? grp : kind == 1 ? grp - nk : grp - 2 * nk;
+    const int conv_dim = 2 * nk * CN + nv * CN, vdim = nv * CN;
+    const size_t c0 = kind == 0 ? (size_t)h * CN : kind == 1 ? (size_t)nk * CN + (size_t)h * CN : (size_t)2 * nk * CN + (size_t)h * CN;
+    float *st = sg.state + (size_t)lin_layer * sg.lstride + (size_t)(K - 1) * c0;  // [K - 1][CN], oldest first
+    const float *w = w_conv + (size_t)K * c0;                                      // [K][CN] taps
+    __shared__ float buf[CN];
+    __shared__ float dot;
+    float win[8], wt[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        wt[j] = j < K ? w[(size_t)j * CN + i] : 0.0f;
+        win[j] = (j < K - 1 && !sg.first) ? st[(size_t)j * CN + i] : 0.0f;
+    }
+    for (int t = 0; t < sg.n; t++) {
+        float *row = rows + (size_t)(sg.row0 + t) * lw;
+        const float x = row[c0 + i];
+        float o = wt[0] * win[0];
+#pragma unroll
+        for (int j = 1; j < 7; j++)
+            if (j < K - 1) o = fmaf(wt[j], win[j], o);
+        float wl = wt[0];
+#pragma unroll
+        for (int j = 1; j < 8; j++)
+            if (j == K - 1) wl = wt[j];
+        o = fmaf(wl, x, o);
+#pragma unroll
+        for (int j = 0; j < 7; j++)  // the window moves on: win[K - 2] = this row's input
+            win[j] = j < K - 2 ? win[j + 1] : (j == K - 2 ? x : win[j]);
+        o = o * sigmoid_att(o);
+        if (kind < 2) {
+            __syncthreads();  // (buf and dot of the previous row have been read)
+            buf[i] = o;
+            __syncthreads();
+            const float inv = 1.0f / sqrtf(dn_dot16_cta(buf, buf, CN, &dot) + 1e-6f);
+            if (kind == 0) {
+                const float sc = 1.0f / sqrtf((float)CN);
+                o = o * inv * sc;
+            } else {
+                o = o * inv;
+            }
+        } else if (i == 0) {
+            float *ab = row + conv_dim + vdim + h;
+            const float xg = ab[0] + w_dt[h];
+            const float sp = xg > 20.0f ? xg : log1pf(expf(xg));
+            ab[0] = expf(w_a[h] * sp);
+            ab[nv] = sigmoid_att(ab[nv]);
+        }
+        row[c0 + i] = o;
+    }
+#pragma unroll
+    for (int j = 0; j < 7; j++)
+        if (j < K - 1) st[(size_t)j * CN + i] = win[j];
+}
+
+// Step 3: the gated RMSNorm of a head's outputs times SiLU(z), in place on out [rows][nv * 128] (dn_out :2280)
+__global__ void __launch_bounds__(128) dn_out_kernel(int nk, int nv, const float *__restrict__ w_norm, const float *__restrict__ rows, int lw,
+                                                     float *__restrict__ out) {
+    constexpr int DV = 128;
+    const int r = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+    __shared__ float buf[DV];
+    __shared__ float dot;
+    float *o = out + (size_t)r * nv * DV + (size_t)h * DV;
+    const float z = rows[(size_t)r * lw + (size_t)2 * nk * DV + (size_t)nv * DV + (size_t)h * DV + j];
+    const float x = o[j];
+    buf[j] = x;
+    __syncthreads();
+    const float ss = 1.0f / sqrtf(dn_dot16_cta(buf, buf, DV, &dot) * (1.0f / DV) + 1e-6f);
+    o[j] = w_norm[j] * (ss * x) * (z * sigmoid_att(z));
+}
+
 }  // namespace rq

@@ -78,6 +78,10 @@ struct RqCuda {
     PfWork *d_work; size_t work_bytes;
     std::vector<PfWork> h_work;
     int pf_ready, pf_max_splits;
+    // DeltaNet weights of the steps around the recurrence (rq_cuda_dn_set_weights): per linear layer conv taps, A, dt
+    // bias, norm weight
+    float *d_dnw; size_t dnw_layer_floats;
+    std::vector<char> dnw_set;
     // optional per-launch timing of the dominant kernel (rq_cuda_profile_begin / _end)
     std::vector<cudaEvent_t> prof_ev;
     int prof_on, prof_n;
@@ -230,6 +234,7 @@ void rq_cuda_free(RqCuda *c) {
     if (!c) return;
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->d_dnw) cudaFree(c->d_dnw);
     void *dev[] = {c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->flush, c->d_maps, c->d_work};
     if (c->h_maps) cudaFreeHost(c->h_maps);
     for (void *p : dev)
@@ -821,6 +826,72 @@ int rq_cuda_dn_rec(RqCuda *c, int lin_layer, const float *rows, float *out) {
     if ((rc = rq_cuda_dn_rec_dev(c, lin_layer, d_rows, d_out))) return rc;
     CU(c, cudaMemcpyAsync(out, d_out, ob, cudaMemcpyDeviceToHost, c->stream));
     return rq_cuda_sync(c);
+}
+
+int rq_cuda_dn_set_weights(RqCuda *c, int lin_layer, const float *conv, const float *a, const float *dt, const float *norm) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    const RqCudaModel &m = c->m;
+    if (lin_layer < 0 || lin_layer >= m.n_lin || !conv || !a || !dt || !norm) return fail(c, RQ_CUDA_ERR_ARG, "dn_set_weights: layer %d", lin_layer);
+    if (m.dn_dk != 128 || m.dn_dv != 128 || m.dn_conv > 8)
+        return fail(c, RQ_CUDA_ERR_ARG, "dn_prep / dn_out are built for dk = dv = 128 and at most 8 conv taps");
+    CU(c, cudaSetDevice(c->device));
+    const size_t cd = (size_t)2 * m.dn_nk * m.dn_dk + (size_t)m.dn_nv * m.dn_dv;
+    const size_t nconv = cd * m.dn_conv, per = nconv + 2 * m.dn_nv + m.dn_dv;
+    if (!c->d_dnw) {
+        CU(c, cudaMalloc((void **)&c->d_dnw, per * m.n_lin * 4));
+        c->dnw_layer_floats = per;
+        c->dnw_set.assign(m.n_lin, 0);
+    }
+    float *base = c->d_dnw + (size_t)lin_layer * per;
+    CU(c, cudaMemcpyAsync(base, conv, nconv * 4, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaMemcpyAsync(base + nconv, a, m.dn_nv * 4, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaMemcpyAsync(base + nconv + m.dn_nv, dt, m.dn_nv * 4, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaMemcpyAsync(base + nconv + 2 * m.dn_nv, norm, m.dn_dv * 4, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaStreamSynchronize(c->stream));
+    c->dnw_set[lin_layer] = 1;
+    return RQ_CUDA_OK;
+}
+
+static int dn_weights(RqCuda *c, int lin_layer, const char *what, const float **conv, const float **a, const float **dt, const float **norm) {
+    if (!c->d_dnw || !c->dnw_set[lin_layer]) return fail(c, RQ_CUDA_ERR_STATE, "%s: rq_cuda_dn_set_weights was not called for layer %d", what, lin_layer);
+    const RqCudaModel &m = c->m;
+    const size_t nconv = ((size_t)2 * m.dn_nk * m.dn_dk + (size_t)m.dn_nv * m.dn_dv) * m.dn_conv;
+    const float *base = c->d_dnw + (size_t)lin_layer * c->dnw_layer_floats;
+    *conv = base;
+    *a = base + nconv;
+    *dt = *a + m.dn_nv;
+    *norm = *dt + m.dn_nv;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_dn_prep_dev(RqCuda *c, int lin_layer, float *rows) {
+    int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_prep");
+    if (rc) return rc;
+    if (!rows) return fail(c, RQ_CUDA_ERR_ARG, "dn_prep: null rows");
+    const float *conv, *a, *dt, *norm;
+    if ((rc = dn_weights(c, lin_layer, "dn_prep", &conv, &a, &dt, &norm))) return rc;
+    CU(c, cudaSetDevice(c->device));
+    const RqCudaModel &m = c->m;
+    const int lw = 2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
+    dn_prep_kernel<<<dim3(2 * m.dn_nk + m.dn_nv, c->nseg), 128, 0, c->stream>>>(c->d_dseg, lin_layer, m.dn_nk, m.dn_nv, m.dn_conv, conv, a, dt, rows, lw);
+    c->launches++;
+    CU(c, cudaGetLastError());
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_dn_out_dev(RqCuda *c, int lin_layer, const float *rows, float *out) {
+    int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_out");
+    if (rc) return rc;
+    if (!rows || !out) return fail(c, RQ_CUDA_ERR_ARG, "dn_out: null rows");
+    const float *conv, *a, *dt, *norm;
+    if ((rc = dn_weights(c, lin_layer, "dn_out", &conv, &a, &dt, &norm))) return rc;
+    CU(c, cudaSetDevice(c->device));
+    const RqCudaModel &m = c->m;
+    const int lw = 2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
+    dn_out_kernel<<<dim3(c->nrows, m.dn_nv), 128, 0, c->stream>>>(m.dn_nk, m.dn_nv, norm, rows, lw, out);
+    c->launches++;
+    CU(c, cudaGetLastError());
+    return RQ_CUDA_OK;
 }
 
 // ---------------------------------------------------------------------------------------------------- helpers

@@ -163,6 +163,17 @@ int rq_cuda_attn_prefill_dev(RqCuda *ctx, int layer, const float *q_dev, float *
 int rq_cuda_dn_rec(RqCuda *ctx, int lin_layer, const float *rows, float *out);
 int rq_cuda_dn_rec_dev(RqCuda *ctx, int lin_layer, const float *rows_dev, float *out_dev);
 
+/* The steps around the recurrence, on the device (dk = dv = 128): the layer's weights once (host pointers: conv taps in the
+ * reference's per-channel-group order [conv][channels of the group] at conv * first_channel, conv * (2 nk dk + nv dv) floats;
+ * ssm_a = -exp(A_log) [nv]; the dt bias [nv]; the gated RMSNorm weight [dv]; src/internal.h:166-169), then per pass
+ * rq_cuda_dn_prep_dev (dn_prep_part, forward.c:2104: causal conv + SiLU, L2 norm of q / k, exp(g) and beta; raw projection
+ * rows -> recurrence inputs, in place; the conv part of the state is advanced) and rq_cuda_dn_out_dev (dn_out :2280: gated
+ * RMSNorm x SiLU(z), in place on the recurrence's outputs).  Same operations in the same order as the reference, except
+ * the two libm calls of the gate (expf, log1pf), which agree to the last bits only. */
+int rq_cuda_dn_set_weights(RqCuda *ctx, int lin_layer, const float *conv, const float *ssm_a, const float *ssm_dt, const float *ssm_norm);
+int rq_cuda_dn_prep_dev(RqCuda *ctx, int lin_layer, float *rows_dev);
+int rq_cuda_dn_out_dev(RqCuda *ctx, int lin_layer, const float *rows_dev, float *out_dev);
+
 /* ---- device memory and timing helpers for hosts without a CUDA runtime of their own (ctypes, cgo, JNI) ---- */
 int rq_cuda_malloc(RqCuda *ctx, size_t bytes, void **dev);
 int rq_cuda_mfree(RqCuda *ctx, void *dev);

@@ -40,3 +40,56 @@ def test_recurrence_matches_cpu(checker, nk, nv):
     assert bit_equal(sa.read_state(1)[d.conv_floats:], st_a[d.conv_floats:])
     assert not sa.read_state(0).any()  # the other layer's state is untouched
     c.close()
+
+
+def test_prep_rec_out_pipeline_matches_cpu(checker):
+    """dn_prep -> dn_rec -> dn_out on the device over two consecutive passes (the conv state carries over): q, k, v and beta
+    equal the CPU code's bits, exp(g) agrees to the last bits (libm expf / log1pf), and from the device's own prepared rows
+    the recurrence and the output stage equal the CPU code bit for bit."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    from oracle import gwo
+    nk, nv, dk, dv, K = 2, 4, 128, 128, 4
+    cd = 2 * nk * dk + nv * dv
+    w_conv = synth.normal(21, (cd * K,)) * np.float32(0.5)
+    w_a = (-np.abs(synth.normal(22, (nv,))) - np.float32(0.1)).astype(np.float32)
+    w_dt, w_norm = synth.normal(23, (nv,)), synth.normal(24, (dv,))
+    d = gwo.DeltaNet(checker, nk, nv, dk, dv, K, w_conv, w_a, w_dt, w_norm)
+    c = g.Context(0, n_lin=1, dn_nk=nk, dn_nv=nv, dn_dk=dk, dn_dv=dv, dn_conv=K, max_rows=128)
+    c.dn_set_weights(0, w_conv, w_a, w_dt, w_norm)
+    s = c.new_seq(256, 2)
+    st = d.new_state()
+    raw = synth.normal(25, (70, d.lw))
+    rows_dev = c.malloc(64 * d.lw * 4)
+    out_dev = c.malloc(64 * nv * dv * 4)
+    for lo, hi in ((0, 3), (3, 64), (64, 70)):   # a pass shorter than the conv window, a long one, a continuation
+        n = hi - lo
+        c.h2d(rows_dev, np.ascontiguousarray(raw[lo:hi]))
+        c.pass_begin([(s, lo, n)])
+        c.dn_prep_dev(0, rows_dev)
+        prep_gpu = np.empty((n, d.lw), np.float32)
+        c.d2h(prep_gpu, rows_dev)
+        c.dn_rec_dev(0, rows_dev, out_dev)
+        rec_gpu = np.empty((n, nv * dv), np.float32)
+        c.d2h(rec_gpu, out_dev)
+        c.dn_out_dev(0, rows_dev, out_dev)
+        fin_gpu = np.empty((n, nv * dv), np.float32)
+        c.d2h(fin_gpu, out_dev)
+        c.sync()
+        c.pass_end()
+        st_before = st.copy()
+        prep_cpu = d.prep(st, raw[lo:hi], lo == 0)
+        eg0 = cd + nv * dv
+        assert bit_equal(prep_gpu[:, :eg0], prep_cpu[:, :eg0])                    # q, k, v (and z untouched)
+        assert bit_equal(prep_gpu[:, eg0 + nv:], prep_cpu[:, eg0 + nv:])          # beta
+        assert np.abs(prep_gpu[:, eg0:eg0 + nv] / prep_cpu[:, eg0:eg0 + nv] - 1).max() < 1e-6   # exp(g)
+        # from the device's prepared rows on, bits again
+        st_rec = st_before.copy()
+        st_rec[:d.conv_floats] = st[:d.conv_floats]
+        rec_cpu = d.rec(st_rec, prep_gpu, lo == 0)
+        assert bit_equal(rec_gpu, rec_cpu)
+        assert bit_equal(fin_gpu, d.out(prep_gpu, rec_cpu))
+        st[:] = st_rec
+        got_state = s.read_state(0)
+        assert bit_equal(got_state[:d.conv_floats], st[:d.conv_floats]) and bit_equal(got_state[d.conv_floats:], st[d.conv_floats:])
+    c.close()
