@@ -594,6 +594,51 @@ __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const Pass
     }
 }
 
+// The same merge for rows with few partials each (the tensor-core prefill path: head_dim 128, 16-bit cache, one
+// partial per 1024-position split): one warp per (row, query head), lane L holds dims 4L .. 4L + 3, so a launch is a
+// few hundred CTAs instead of one per output row.  Arithmetic as attn_combine_kernel: M = max of the m_b,
+// c_b = exp_att(m_b - M), L and out as fma chains in partial order, out * (1 / L), gate.
+constexpr int COMBINE_ROWS_WARPS = 8;
+template <int HD>
+__global__ void __launch_bounds__(32 * COMBINE_ROWS_WARPS) attn_combine_rows_kernel(const PassRow *__restrict__ rows, int nrows, int n_heads,
+                                                                                 const float *__restrict__ part, const float *__restrict__ q,
+                                                                                 int qh, int gated, float *__restrict__ out, int split_len,
+                                                                                 int fixed_stride) {
+    static_assert(HD == 128, "a lane holds 4 of the row's 128 dims");
+    const int wi = blockIdx.x * COMBINE_ROWS_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (wi >= nrows * n_heads) return;
+    const int r = wi / n_heads, h = wi % n_heads;
+    const int nb = (rows[r].np + split_len - 1) / split_len;
+    const size_t pst = RQ_PSTRIDE(HD), bstride = (size_t)n_heads * pst;
+    const float *p0 = part + ((size_t)r * fixed_stride * n_heads + h) * pst;
+    float4 res;
+    if (nb == 1) {
+        const float inv = 1.0f / p0[HD + 1];
+        const float4 o = *reinterpret_cast<const float4 *>(p0 + 4 * lane);
+        res = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+    } else {
+        float M = -INFINITY;
+        for (int b = 0; b < nb; b++) M = fmaxf(M, p0[b * bstride + HD]);
+        float L = 0.0f;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+        for (int b = 0; b < nb; b++) {
+            const float *pb = p0 + b * bstride;
+            const float4 o = *reinterpret_cast<const float4 *>(pb + 4 * lane);
+            const float cb = exp_att(pb[HD] - M);
+            L = fmaf(cb, pb[HD + 1], L);
+            acc.x = fmaf(cb, o.x, acc.x), acc.y = fmaf(cb, o.y, acc.y), acc.z = fmaf(cb, o.z, acc.z), acc.w = fmaf(cb, o.w, acc.w);
+        }
+        const float inv = 1.0f / L;
+        res = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    }
+    if (gated) {
+        const float4 gq = *reinterpret_cast<const float4 *>(q + ((size_t)r * n_heads + h) * qh + HD + 4 * lane);
+        res.x = res.x * sigmoid_att(gq.x), res.y = res.y * sigmoid_att(gq.y), res.z = res.z * sigmoid_att(gq.z), res.w = res.w * sigmoid_att(gq.w);
+    }
+    *reinterpret_cast<float4 *>(out + ((size_t)r * n_heads + h) * HD + 4 * lane) = res;
+}
+
 }  // namespace rq
 
 namespace rq {

@@ -28,9 +28,12 @@
 
 namespace rq {
 
-constexpr int PF_SPLIT = 1024;   // key positions per partial result (a multiple of the 128-position key block)
+#ifndef RQ_PF_SPLIT
+#define RQ_PF_SPLIT 1024
+#endif
+constexpr int PF_SPLIT = RQ_PF_SPLIT;  // key positions per partial result (a multiple of the 128-position key block)
 constexpr int PF_BN = 128;       // key positions per MMA block
-constexpr int PF_THREADS = 160;  // 4 softmax warps + 1 TMA / MMA warp
+constexpr int PF_THREADS = 352;  // 2 streams x 4 softmax warps + the P V, S and TMA warps
 
 struct PfWork {
     int seg;     // segment index (its tensor maps)
@@ -84,6 +87,12 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// true in exactly one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
@@ -119,31 +128,44 @@ __device__ __forceinline__ float ex2(float x) {
 
 #ifdef RQ_PF_TRACE
 __device__ long long pf_trace[64];  // experiments only: event times of CTA (0, 0), in clock cycles from its start
+__device__ unsigned long long pf_span[3 * 2048];  // per CTA: start and end (globaltimer, ns), SM id
 #define PF_T(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 64) pf_trace[i] = clock64() - pf_t0; } while (0)
+__device__ __forceinline__ unsigned long long pf_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 #else
 #define PF_T(i) do { } while (0)
 #endif
 
-constexpr int PF_SMEM = 3 * 32768 + 1024 + 128;  // Q | K | V (32 KB each), alignment slack, barriers
+constexpr int PF_SMEM = 6 * 32768 + 1024 + 256 + 2048;  // Q | K x 3 stages | V x 2 stages (32 KB each), slack, barriers, (m, l) exchange
 
 // maps: per segment the tensor maps of its sequence's K cache ({16 positions, rows of 32 bytes}, 32-byte swizzle, box 16 x
-// 256) and V cache ({128 dims, rows of 256 bytes}, 128-byte swizzle, box 64 x 128).  k_rows_per_layer / v_rows_per_layer:
-// rows of those 2-D views per layer of each segment's sequence.
-__global__ void __launch_bounds__(PF_THREADS, 2) attn_prefill_kernel(const PfWork *__restrict__ work, const PassRow *__restrict__ rows,
+// 256) and V cache ({128 dims, rows of 256 bytes}, 128-byte swizzle, box 64 x 128).
+__global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWork *__restrict__ work, const PassRow *__restrict__ rows,
                                                                   const CUtensorMap *__restrict__ maps, int layer, int n_kv, int G,
                                                                   const float *__restrict__ q, int qh, int n_heads, float scale,
                                                                   int max_splits, float *__restrict__ part, int *err) {
-    constexpr int HD = 128, S_COL = 0, O_COL = 128, TM_COLS = 256;
+    // TMEM columns: S at 0 (128); P (f16 pairs) of key block j, stream h (the block's keys 64 h .. 64 h + 63) at
+    // 128 + 64 (j % 2) + 32 h; O of stream h at 256 + 128 h
+    constexpr int HD = 128, TM_COLS = 512, P_COL = 128, O_COL = 256;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *sQ = sm, *sK = sm + 32768, *sV = sm + 65536;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 98304);  // 0: K loaded, 1: V loaded, 2: S done, 3: O done, 4: P stored
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + 98304 + 64);
-    uint64_t *bar_k = bars, *bar_v = bars + 1, *bar_s = bars + 2, *bar_o = bars + 3, *bar_p = bars + 4;
+    uint8_t *sQ = sm, *sK = sm + 32768, *sV = sm + 131072;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 196608);
+    // K stage loaded (3), V stage loaded (2), S written (1), S read by every softmax thread (1), K stage free (3),
+    // P V of block j complete (2: j % 2), P (j) of stream h stored (4: 2 h + j % 2).  Every barrier's next phase depends
+    // on each of its waiters having seen the current one, so a parity wait is never ambiguous
+    uint64_t *bar_k = bars, *bar_v = bars + 3, *bar_s = bars + 5, *bar_sfree = bars + 6, *bar_kfree = bars + 7, *bar_o = bars + 10,
+             *bar_p = bars + 12;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + 196608 + 192);
+    float *sml = reinterpret_cast<float *>(sm + 196608 + 256);  // [stream][vector][m, l]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef RQ_PF_TRACE
     const long long pf_t0 = clock64();
+    const unsigned long long pf_g0 = pf_now();
 #endif
     const PfWork w = work[blockIdx.x];
     const int g = blockIdx.y;
@@ -165,37 +187,48 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attn_prefill_kernel(const PfWor
         int t0 = s0 + j * PF_BN;
         return (long long)layer * v_layer_rows + ((long long)(t0 / ATT_P) * n_kv + g) * ATT_P + (t0 % ATT_P);
     };
+    auto load_k = [&](int j) {  // key block j -> stage j % 3
+        uint64_t *bar = bar_k + j % 3;
+        uint8_t *dst = sK + (j % 3) * 32768;
+        mbar_expect_tx(bar, 32768);
+        const int y = (int)k_row(j);
+        for (int i = 0; i < 4; i++) tma_load_2d(dst + i * 8192, mk, 0, y + i * 256, bar);
+    };
+    auto load_v = [&](int j) {  // -> stage j % 2
+        uint64_t *bar = bar_v + (j & 1);
+        uint8_t *dst = sV + (j & 1) * 32768;
+        mbar_expect_tx(bar, 32768);
+        const int y = (int)v_row(j);
+        for (int i = 0; i < 2; i++) tma_load_2d(dst + i * 16384, mv, i * 64, y, bar);
+    };
 
-    if (tid == 0) PF_T(44);  // work item and row fetched
+    if (tid == 0) PF_T(60);  // work item and row fetched
     if (tid == 0) {
-        mbar_init(bar_k, 1);
-        mbar_init(bar_v, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
-        mbar_init(bar_p, 128);
+        for (int i = 0; i < 12; i++) mbar_init(bars + i, i == 6 ? 256 : 1);
+        for (int i = 0; i < 4; i++) mbar_init(bar_p + i, 128);
         mbar_fence_init();
     }
     __syncthreads();
-    if (warp == 4) {
+    if (tid == 0) PF_T(61);  // barriers ready
+    if (warp == 10) {
         if (lane == 0) {  // the first K / V blocks start loading while the other warps convert Q
-            mbar_expect_tx(bar_k, 32768);
-            for (int i = 0; i < 4; i++) tma_load_2d(sK + i * 8192, mk, 0, (int)k_row(0) + i * 256, bar_k);
-            mbar_expect_tx(bar_v, 32768);
-            for (int i = 0; i < 2; i++) tma_load_2d(sV + i * 16384, mv, i * 64, (int)v_row(0), bar_v);
+            load_k(0);
+            if (nblk > 1) load_k(1);
+            load_v(0);
+            if (nblk > 2) load_k(2);
+            if (nblk > 1) load_v(1);
         }
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
-    }
-    // Q tile -> shared memory as f16, K-major with the 128-byte swizzle: vector t = row t / G, head g G + t % G;
-    // 16-byte chunk c of 16: k-block c / 8, physical chunk (c % 8) ^ (t % 8)
-    if (tid == 0) PF_T(45);  // barriers ready, first loads issued
-    if (warp < 4) {
-        // a warp converts 32 vectors, one per step: its lanes read the vector's 128 floats as one coalesced 512-byte
+    } else if (warp < 8) {
+        // Q tile -> shared memory as f16, K-major with the 128-byte swizzle: vector t = row t / G, head g G + t % G;
+        // 16-byte chunk c of 16: k-block c / 8, physical chunk (c % 8) ^ (t % 8).
+        // A warp converts 16 vectors, one per step: its lanes read the vector's 128 floats as one coalesced 512-byte
         // row (lane L: dims 4L .. 4L + 3) and store 4 halves into chunk L / 2
 #pragma unroll
-        for (int rr = 0; rr < 32; rr++) {
-            const int t = warp * 32 + rr, rl = t / G, x = t % G;
+        for (int rr = 0; rr < 16; rr++) {
+            const int t = warp * 16 + rr, rl = t / G, x = t % G;
             float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (rl < w.nrows) a = *reinterpret_cast<const float4 *>(q + ((size_t)(w.row0 + rl) * n_heads + (size_t)g * G + x) * qh + 4 * lane);
             __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
@@ -204,7 +237,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attn_prefill_kernel(const PfWor
                 make_uint2(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1));
         }
     }
-    if (tid == 0) PF_T(46);  // Q converted
+    if (tid == 0) PF_T(62);  // Q converted
     fence_proxy_async();  // Q was written by ordinary stores and will be read by the tensor core
     tc_fence_before();
     __syncthreads();
@@ -213,161 +246,218 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attn_prefill_kernel(const PfWor
     bool ok = true;
     if (tid == 0) PF_T(0);  // prologue done (Q in shared memory, TMEM allocated)
 
-    if (warp == 4) {
-        // ---- TMA loads and MMA issue (one thread)
-        if (lane == 0) {
-            auto load_k = [&](int j) {
-                mbar_expect_tx(bar_k, 32768);
-                int y = (int)k_row(j);
-                for (int i = 0; i < 4; i++) tma_load_2d(sK + i * 8192, mk, 0, y + i * 256, bar_k);
-            };
-            auto load_v = [&](int j) {
-                mbar_expect_tx(bar_v, 32768);
-                int y = (int)v_row(j);
-                for (int i = 0; i < 2; i++) tma_load_2d(sV + i * 16384, mv, i * 64, y, bar_v);
-            };
-            constexpr uint32_t idesc = umma_idesc(128, 128);
-            auto mma_qk = [&]() {
-#pragma unroll
-                for (int ks = 0; ks < 8; ks++)
-                    umma_ss(tbase + S_COL, umma_desc(smem_u32(sQ) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, 2),
-                            umma_desc(smem_u32(sK) + ks * 512, 4096, 256, 6), idesc, ks > 0);
-                umma_commit(bar_s);
-            };
-            auto mma_pv = [&](int j) {
-#pragma unroll
-                for (int ks = 0; ks < 8; ks++)
-                    umma_ts(tbase + O_COL, tbase + S_COL + ks * 8, umma_desc(smem_u32(sV) + ks * 2048, 16384, 1024, 2), idesc, (j > 0) | (ks > 0));
-                umma_commit(bar_o);
-            };
-            ok = mbar_wait_bounded(bar_k, 0, err, 11) && ok;
-            tc_fence_after();
-            mma_qk();
+    if (warp >= 8) {
+        // ---- three warps: P V issue, S issue, TMA loads.  The softmax threads free S as soon as they hold their scores
+        // in registers, so S (j + 1) is computed while they work on block j and they never wait for the tensor cores;
+        // P is double-buffered, so P V (j) runs under the softmax of block j + 1.  Each of the three warps runs its loop
+        // converged (all lanes wait, descriptors stay warp-uniform) and one elected lane issues
+        constexpr uint32_t idesc = umma_idesc(128, 128);
+        // (a descriptor's address field counts 16-byte units from bit 0: adding bytes / 16 moves the start)
+        if (warp == 8) {
+            // O (stream h) += P (j, h) V (j, h): keys 64 h .. 64 h + 63 of block j, 4 k-steps of 16 keys each
+            const uint64_t dv = umma_desc(smem_u32(sV), 16384, 1024, 2);
             for (int j = 0; j < nblk; j++) {
-                const uint32_t ph = j & 1;
-                ok = mbar_wait_bounded(bar_s, ph, err, 12) && ok;  // S(j) done: the K buffer is free
-                if (j + 1 < nblk) load_k(j + 1);
-                ok = mbar_wait_bounded(bar_p, ph, err, 13) && ok;  // P(j) is in TMEM
-                ok = mbar_wait_bounded(bar_v, ph, err, 14) && ok;
+                const uint32_t ph = j & 1, ph2 = (j >> 1) & 1;
+                const uint64_t b0 = dv + (uint64_t)(ph * (32768 >> 4));
+                const uint32_t pa = tbase + P_COL + ph * 64;
+                ok = mbar_wait_bounded(bar_v + ph, ph2, err, 14) && ok;
+                ok = mbar_wait_bounded(bar_p + ph, ph2, err, 13) && ok;  // P(j) of stream 0 is in TMEM
                 tc_fence_after();
-                PF_T(3 + 4 * j);  // P V (j) issued (P and V ready)
-                mma_pv(j);
-                if (j + 1 < nblk) {
-                    ok = mbar_wait_bounded(bar_k, ph ^ 1, err, 15) && ok;
-                    tc_fence_after();
-                    mma_qk();  // queued behind P V (j): it may overwrite the S / P columns only after they were read
-                    ok = mbar_wait_bounded(bar_o, ph, err, 16) && ok;  // the V buffer is free
-                    PF_T(4 + 4 * j);  // P V (j) complete
-                    load_v(j + 1);
+                if (lane == 0 && j < 8) PF_T(3 + 4 * j);
+                if (elect_one()) {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) umma_ts(tbase + O_COL, pa + ks * 8, b0 + (uint64_t)(ks * 128), idesc, (j > 0) | (ks > 0));
                 }
+                __syncwarp();
+                ok = mbar_wait_bounded(bar_p + 2 + ph, ph2, err, 13) && ok;
+                tc_fence_after();
+                if (elect_one()) {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++)
+                        umma_ts(tbase + O_COL + 128, pa + 32 + ks * 8, b0 + (uint64_t)(512 + ks * 128), idesc, (j > 0) | (ks > 0));
+                    umma_commit(bar_o + ph);  // both streams' P (j) were read, V (j) too
+                }
+                __syncwarp();
+                if (lane == 0 && j < 8) PF_T(4 + 4 * j);
+            }
+        } else if (warp == 9) {
+            // S (j) = Q K (j)^T, once every softmax thread has read S (j - 1)
+            const uint64_t dq = umma_desc(smem_u32(sQ), 16, 1024, 2), dk = umma_desc(smem_u32(sK), 4096, 256, 6);
+            for (int j = 0; j < nblk; j++) {
+                const uint64_t b0 = dk + (uint64_t)((j % 3) * (32768 >> 4));
+                ok = mbar_wait_bounded(bar_k + j % 3, (j / 3) & 1, err, 11) && ok;
+                if (j >= 1) ok = mbar_wait_bounded(bar_sfree, (j - 1) & 1, err, 12) && ok;
+                tc_fence_after();
+                if (elect_one()) {
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++)
+                        umma_ss(tbase, dq + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), b0 + (uint64_t)(ks * 32), idesc,
+                                ks > 0);
+                    umma_commit(bar_s);
+                    umma_commit(bar_kfree + j % 3);
+                }
+                __syncwarp();
+            }
+        } else if (warp == 10) {
+            // K (j + 3) into the stage of K (j) once S (j) is complete; V (j + 2) into the stage of V (j) once P V (j) is
+            for (int j = 0; j < nblk; j++) {
+                if (j + 3 < nblk) {
+                    ok = mbar_wait_bounded(bar_kfree + j % 3, (j / 3) & 1, err, 15) && ok;
+                    if (lane == 0) load_k(j + 3);
+                }
+                if (j + 2 < nblk) {
+                    ok = mbar_wait_bounded(bar_o + (j & 1), (j >> 1) & 1, err, 16) && ok;
+                    if (lane == 0) load_v(j + 2);
+                }
+                __syncwarp();
             }
         }
-        __syncwarp();
     } else {
-        // ---- softmax: thread t owns query vector t (TMEM lane t)
-        const int t = tid, rl = t / G;
+        // ---- softmax: warps 0-3 are stream 0, warps 4-7 stream 1; thread t of a stream owns query vector t (TMEM lane t)
+        // and, of every key block, the 64 keys of its stream, with its own running max, row sum and O accumulator:
+        // the two streams are independent until the epilogue merges them
+        const int h = warp >> 2, t = tid & 127, rl = t / G;
         const int np = rl < w.nrows ? np_min + rl : 0;  // positions this vector attends (0: a padding vector)
-        const uint32_t lane_addr = tbase + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_addr = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t o_col = O_COL + h * 128;
         const float c = scale * 1.44269504088896341f;
         float m_used = -INFINITY, l = 0.0f;
+        // The waits of the loop are polled once well before their result is needed (a poll of a completed barrier
+        // still takes ~150 cycles to answer), and only a poll that failed is followed by a real wait
+        bool s_seen = false;
+#ifdef RQ_PF_STAGGER
+        if (h == 1) {  // the second stream starts half a block late, so that the two warps of a scheduler alternate
+            const long long c0 = clock64();
+            while (clock64() - c0 < RQ_PF_STAGGER) {
+            }
+        }
+#endif
         for (int j = 0; j < nblk; j++) {
-            const uint32_t ph = j & 1;
-            const int t0 = s0 + j * PF_BN;
-            ok = mbar_wait_bounded(bar_s, ph, err, 21) && ok;
+            const int t0 = s0 + j * PF_BN + h * 64;  // first key of this thread's half of the block
+            if (!s_seen) ok = mbar_wait_bounded(bar_s, j & 1, err, 21) && ok;
             tc_fence_after();
-            if (tid == 0) PF_T(1 + 4 * j);  // S(j) ready
-            // the thread's whole row of S (128 scores) in registers: four loads in flight, one wait
-            uint32_t r[4][32];
-#pragma unroll
-            for (int cc = 0; cc < 4; cc++) tmem_ld32(lane_addr + S_COL + cc * 32, r[cc]);
+            if (t == 0 && j < 8 && h == 0) PF_T(1 + 4 * j);  // S(j) ready
+            uint32_t r[2][32], pk[32];
+            tmem_ld32(lane_addr + h * 64, r[0]);
+            tmem_ld32(lane_addr + h * 64 + 32, r[1]);
+            // P V (j - 2) was the last reader of the P buffer this block will store to
+            const bool o_seen = j < 2 || mbar_try_wait(bar_o + (j & 1), ((j - 2) >> 1) & 1);
             tmem_wait_ld();
-            const bool need_mask = t0 + PF_BN > np_min;  // (uniform over the CTA: only the blocks on the diagonal)
+            tc_fence_before();
+            mbar_arrive(bar_sfree);  // the scores are in registers: S (j + 1) may be computed
+            if (t == 0 && j == 3) PF_T(48 + 8 * h);
+            const bool need_mask = s0 + (j + 1) * PF_BN > np_min;  // (uniform over the CTA: only the blocks on the diagonal)
             if (need_mask) {
 #pragma unroll
-                for (int cc = 0; cc < 4; cc++)
+                for (int cc = 0; cc < 2; cc++)
 #pragma unroll
                     for (int x = 0; x < 32; x++)
                         if (t0 + cc * 32 + x >= np) r[cc][x] = 0xff800000u;  // -inf
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            // p = 2^((s - m) c) (a masked score is -inf: p = 0) as f16 pairs, the row sum, and the row maximum in the
+            // same sweep, so that its comparisons fill the issue slots the exponential unit leaves
+            float mx, lsum;
+            auto sweep = [&](float mc) {
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int cc = 0; cc < 4; cc++)
+                for (int cc = 0; cc < 2; cc++) {
 #pragma unroll
-                for (int x = 0; x < 32; x++) mx4[x & 3] = fmaxf(mx4[x & 3], __uint_as_float(r[cc][x]));
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // the running max moves only when it grows by more than 8 in the exponent (p stays below 2^8: exact enough
-            // in f16, and O is rescaled rarely); the first block with a valid position sets it
-            float alpha = 1.0f;
+                    for (int x = 0; x < 32; x += 2) {
+                        const float a0 = __uint_as_float(r[cc][x]), a1 = __uint_as_float(r[cc][x + 1]);
+                        const float p0 = ex2(fmaf(a0, c, -mc)), p1 = ex2(fmaf(a1, c, -mc));
+                        mx4[(x >> 1) & 3] = fmaxf(mx4[(x >> 1) & 3], fmaxf(a0, a1));
+                        l4[(x >> 1) & 3] += p0 + p1;
+                        __half2 hh = __floats2half2_rn(p0, p1);
+                        pk[cc * 16 + (x >> 1)] = *reinterpret_cast<uint32_t *>(&hh);
+                    }
+                }
+                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                lsum = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            };
+            // The running max moves only when the block's maximum exceeds it by more than 8 in the exponent (p stays
+            // below 2^8: exact enough in f16, and O is rescaled rarely).  So the sweep runs with the running max as it
+            // stands; in the rare block where some row's max has to move (the first block with a valid key always),
+            // O and l of the warp's rows are rescaled and the sweep is repeated with the new max
+            sweep(m_used == -INFINITY ? 0.0f : m_used * c);
             const bool move = mx > -INFINITY && (m_used == -INFINITY || (mx - m_used) * c > 8.0f);
-            if (move) {
-                alpha = m_used == -INFINITY ? 0.0f : ex2((m_used - mx) * c);
-                m_used = mx;
-            }
-            if (j > 0 && __any_sync(0xffffffffu, move)) {
-                // O and l of this warp's rows are rescaled (P V (j - 1) has completed: S (j) was queued behind it)
-                l *= alpha;
+            if (__any_sync(0xffffffffu, move)) {
+                float alpha = 1.0f;
+                if (move) {
+                    alpha = m_used == -INFINITY ? 0.0f : ex2((m_used - mx) * c);
+                    m_used = mx;
+                }
+                if (j > 0) {
+                    // (P V (j - 1) must have completed; P V (j - 3), the barrier's phase before, was seen complete
+                    // before P (j - 1) was stored)
+                    ok = mbar_wait_bounded(bar_o + ((j - 1) & 1), ((j - 1) >> 1) & 1, err, 23) && ok;
+                    tc_fence_after();
+                    l *= alpha;
 #pragma unroll 1
-                for (int cc = 0; cc < 4; cc++) {
-                    uint32_t o[32];
-                    tmem_ld32(lane_addr + O_COL + cc * 32, o);
-                    tmem_wait_ld();
+                    for (int cc = 0; cc < 4; cc++) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_addr + o_col + cc * 32, o);
+                        tmem_wait_ld();
 #pragma unroll
-                    for (int x = 0; x < 32; x++) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
-                    tmem_st32(lane_addr + O_COL + cc * 32, o);
+                        for (int x = 0; x < 32; x++) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
+                        tmem_st32(lane_addr + o_col + cc * 32, o);
+                    }
+                    tmem_wait_st();
                 }
-                tmem_wait_st();
+                sweep(m_used == -INFINITY ? 0.0f : m_used * c);
             }
-            // p = 2^((s - m) c) (a masked score is -inf: p = 0), row sum, P as f16 pairs over the first 64 columns of S
-            const float mc = m_used == -INFINITY ? 0.0f : m_used * c;
-            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int cc = 0; cc < 4; cc++) {
-#pragma unroll
-                for (int x = 0; x < 32; x += 2) {
-                    float p0 = ex2(fmaf(__uint_as_float(r[cc][x]), c, -mc)), p1 = ex2(fmaf(__uint_as_float(r[cc][x + 1]), c, -mc));
-                    l4[(x >> 1) & 3] += p0 + p1;
-                    __half2 h = __floats2half2_rn(p0, p1);
-                    r[cc >> 1][(cc & 1) * 16 + (x >> 1)] = *reinterpret_cast<uint32_t *>(&h);  // (slots already consumed)
-                }
-            }
-            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-            tmem_st32(lane_addr + S_COL, r[0]);
-            tmem_st32(lane_addr + S_COL + 32, r[1]);
+            l += lsum;
+            if (t == 0 && j == 3) PF_T(50 + 8 * h);
+            if (!o_seen) ok = mbar_wait_bounded(bar_o + (j & 1), ((j - 2) >> 1) & 1, err, 24) && ok;
+            tc_fence_after();
+            tmem_st32(lane_addr + P_COL + (j & 1) * 64 + h * 32, pk);
+            s_seen = j + 1 < nblk && mbar_try_wait(bar_s, (j + 1) & 1);  // (answered while the store completes)
             tmem_wait_st();
+            if (t == 0 && j == 3) PF_T(51 + 8 * h);
             tc_fence_before();
-            mbar_arrive(bar_p);
-            if (tid == 0) PF_T(2 + 4 * j);  // softmax(j) done
+            mbar_arrive(bar_p + 2 * h + (j & 1));
+            if (lane == 0 && j == 3 && h == 0) PF_T(52 + warp);
+            if (t == 0 && j < 8 && h == 0) PF_T(2 + 4 * j);  // softmax(j) done
         }
-        // ---- epilogue: the partial result (o unnormalised, m in scaled-score units, l)
-        ok = mbar_wait_bounded(bar_o, (nblk - 1) & 1, err, 22) && ok;
+        // ---- epilogue: the two streams merge into the partial result (o unnormalised, m in scaled-score units, l)
+        sml[(h * 128 + t) * 2] = m_used;
+        sml[(h * 128 + t) * 2 + 1] = l;
+        ok = mbar_wait_bounded(bar_o + ((nblk - 1) & 1), ((nblk - 1) >> 1) & 1, err, 22) && ok;
         tc_fence_after();
-        if (tid == 0) PF_T(40);  // last P V complete
+        if (t == 0) PF_T(40 + 4 * h);
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // (the softmax warps only) every MMA of the CTA is complete
+        const float m_other = sml[((h ^ 1) * 128 + t) * 2], l_other = sml[((h ^ 1) * 128 + t) * 2 + 1];
+        const float M = fmaxf(m_used, m_other);
+        const float c_own = m_used == -INFINITY ? 0.0f : ex2((m_used - M) * c), c_other = m_other == -INFINITY ? 0.0f : ex2((m_other - M) * c);
         {
-            // every thread's row of O goes through shared memory (Q / K / V are no longer needed: all MMAs are
-            // complete) so that the global stores are coalesced: a warp then writes one 512-byte row per step
+            // every thread's row of c O goes through shared memory (Q, K and V are no longer needed) so that the global
+            // stores are coalesced: a warp then sums the two streams' rows and writes one 512-byte row per step
             constexpr int OST = HD + 4;  // floats per staged row (the padding spreads the rows over the banks)
-            float *so = reinterpret_cast<float *>(sm);
+            float *so = reinterpret_cast<float *>(sm), *so_own = so + (size_t)h * 128 * OST;
 #pragma unroll 1
             for (int cc = 0; cc < 4; cc++) {
                 uint32_t r[32];
-                tmem_ld32(lane_addr + O_COL + cc * 32, r);
+                tmem_ld32(lane_addr + o_col + cc * 32, r);
                 tmem_wait_ld();
 #pragma unroll
                 for (int y = 0; y < 32; y += 4)
-                    *reinterpret_cast<float4 *>(so + (size_t)t * OST + cc * 32 + y) =
-                        make_float4(__uint_as_float(r[y]), __uint_as_float(r[y + 1]), __uint_as_float(r[y + 2]), __uint_as_float(r[y + 3]));
+                    *reinterpret_cast<float4 *>(so_own + (size_t)t * OST + cc * 32 + y) =
+                        make_float4(__uint_as_float(r[y]) * c_own, __uint_as_float(r[y + 1]) * c_own, __uint_as_float(r[y + 2]) * c_own,
+                                    __uint_as_float(r[y + 3]) * c_own);
             }
-            so[(size_t)t * OST + HD] = m_used * scale;
-            so[(size_t)t * OST + HD + 1] = l;
-            if (tid == 0) PF_T(42);  // O staged
-            __syncwarp();  // (a warp stages and writes the same 32 rows)
+            if (h == 0) {
+                so[(size_t)t * OST + HD] = M * scale;
+                so[(size_t)t * OST + HD + 1] = c_own * l + c_other * l_other;
+            }
+            if (t == 0) PF_T(42 + 4 * h);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
 #pragma unroll 8
-            for (int rr = 0; rr < 32; rr++) {
-                const int tt = warp * 32 + rr, rl2 = tt / G, x = tt % G;
+            for (int rr = 0; rr < 16; rr++) {
+                const int tt = warp * 16 + rr, rl2 = tt / G, x = tt % G;
                 if (rl2 >= w.nrows) continue;
                 float *p = part + (((size_t)(w.row0 + rl2) * max_splits + w.split) * n_heads + (size_t)g * G + x) * RQ_PSTRIDE(HD);
-                float4 v4 = *reinterpret_cast<const float4 *>(so + (size_t)tt * OST + 4 * lane);
-                *reinterpret_cast<float4 *>(p + 4 * lane) = ok ? v4 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                const float4 a = *reinterpret_cast<const float4 *>(so + (size_t)tt * OST + 4 * lane);
+                const float4 b = *reinterpret_cast<const float4 *>(so + (size_t)(128 + tt) * OST + 4 * lane);
+                *reinterpret_cast<float4 *>(p + 4 * lane) = ok ? make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 if (lane < 2) p[HD + lane] = so[(size_t)tt * OST + HD + lane];
             }
         }
@@ -375,7 +465,17 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attn_prefill_kernel(const PfWor
     if (tid == 0) PF_T(41);  // partial written
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(TM_COLS));
+#ifdef RQ_PF_TRACE
+    if (tid == 0) {
+        const int ci = blockIdx.y * gridDim.x + blockIdx.x;
+        if (ci < 2048) {
+            unsigned smid;
+            asm("mov.u32 %0, %smid;" : "=r"(smid));
+            pf_span[3 * ci] = pf_g0, pf_span[3 * ci + 1] = pf_now(), pf_span[3 * ci + 2] = smid;
+        }
+    }
+#endif
+    if (warp == 10) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(TM_COLS));
 }
 
 cudaError_t launch_attn_prefill(const AttnPrefillArgs &a, cudaStream_t stream) {

@@ -92,12 +92,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Wait for a phase of the barrier with an iteration limit: on expiry the kernel records `code` in *err and the caller
-// carries on to its exit (results are then invalid and the host reports RQ_CUDA_ERR_STATE).  try_wait itself blocks
-// for a hardware-defined slice, so the limit below is many orders of magnitude beyond any healthy copy.
+// Wait for a phase of the barrier with a time limit (0.2 s, far beyond any healthy copy or MMA): on expiry the kernel
+// records `code` in *err and the caller carries on to its exit (results are then invalid and the host reports
+// RQ_CUDA_ERR_STATE).  Once any thread has recorded an expiry the other waits give up quickly as well.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *err, int code) {
-    for (int it = 0; it < (1 << 22); it++)
+    unsigned long long t0 = 0;
+    for (int it = 0; it < (1 << 26); it++) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63) == 63) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            if (*reinterpret_cast<volatile int *>(err) != 0) return false;
+            if (now - t0 > 200000000ull) break;
+        }
+    }
     atomicExch(err, code);
     return false;
 }

@@ -774,7 +774,13 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     if (e != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "prefill attention launch: %s", cudaGetErrorString(e));
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n++ + 1], c->stream);
     c->launches++;
-    return launch_combine(c, q, out, c->d_part, PF_SPLIT, c->pf_max_splits);
+    // (this path is head_dim 128 over a 16-bit cache: a warp per output row merges its few partials)
+    const int nout = c->nrows * c->n_heads;
+    attn_combine_rows_kernel<128><<<(nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS, 32 * COMBINE_ROWS_WARPS, 0, c->stream>>>(
+        c->d_rows, c->nrows, c->n_heads, c->d_part, q, c->qh, c->m.gated, out, PF_SPLIT, c->pf_max_splits);
+    c->launches++;
+    CU(c, cudaGetLastError());
+    return RQ_CUDA_OK;
 }
 
 int rq_cuda_attn_prefill_dev(RqCuda *c, int layer, const float *q, float *out) {
