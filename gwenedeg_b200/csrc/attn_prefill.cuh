@@ -5,22 +5,27 @@
 // plus the chunk's earlier rows.
 //
 // Work item = (M tile of 128 query vectors = 128 / G consecutive rows x the G query heads of one KV head, KV head, split of
-// 1024 key positions).  The split length is a constant of the kernel, so what a row computes depends on its own position
+// 2048 key positions).  The split length is a constant of the kernel, so what a row computes depends on its own position
 // only; every work item leaves a partial result (o, m, l) in the format of the split-K decode kernel and
-// attn_combine_kernel merges a row's partials in split order.  Arithmetic: Q and P are rounded to f16 for the tensor
+// attn_combine_rows_kernel merges a row's partials in split order.  Arithmetic: Q and P are rounded to f16 for the tensor
 // cores (fp32 accumulation), so results agree with the CPU code to ~3e-4 relative, not bit for bit.
 //
-// One CTA = 4 softmax warps (thread t owns TMEM lane t = query vector t) + 1 warp whose lane 0 issues the TMA loads and
-// the MMAs.  Per 128-position key block:
-//   K block: 8 cache tiles [dim][16 pos] -> shared memory by 2-D TMA with the 32-byte swizzle = the MN-major canonical
-//            layout of an MMA B operand (positions contiguous), no transposition needed;
-//   S = Q K^T: 8 x tcgen05.mma (M 128, N 128, K 16), Q from shared memory (K-major, 128-byte swizzle), S in TMEM;
-//   softmax: two passes of tcgen05.ld over the thread's row (max; then p = 2^((s - m) c), row sum), causal mask by
-//            position, the running max only moves when it grows by more than 2^8 (then O and l are rescaled);
-//   P (f16) overwrites the first 64 columns of S in TMEM and is the A operand of O += P V (8 x tcgen05.mma, V rows
-//            [pos][dim] by TMA with the 128-byte swizzle, MN-major B operand), O accumulates in TMEM.
-// TMEM: 256 columns per CTA (S / P 128, O 128); 96 KB of shared memory: two CTAs per SM overlap one's softmax with
-// the other's MMAs.
+// One CTA (one per SM: all 512 TMEM columns, 193 KB of shared memory) = 8 softmax warps + 3 issue warps.  Per
+// 128-position key block j:
+//   TMA warp:   K block (8 cache tiles [dim][16 pos]) -> shared memory by 2-D TMA with the 32-byte swizzle = the MN-major
+//               canonical layout of an MMA B operand (positions contiguous), no transposition needed; V rows [pos][dim]
+//               with the 128-byte swizzle, MN-major B operand as well.  3 K stages, 2 V stages.
+//   S warp:     S = Q K^T: 8 x tcgen05.mma (M 128, N 128, K 16), Q from shared memory (K-major, 128-byte swizzle), S in TMEM.
+//   softmax:    thread t of stream h (warps 4h .. 4h + 3) owns query vector t and the block's keys 64 h .. 64 h + 63: it
+//               loads its 64 scores into registers and at once releases S, so S (j + 1) is computed under the softmax of
+//               block j and the softmax threads never wait for the tensor cores.  One sweep does p = 2^((s - m) c), the
+//               row sum and the block maximum; the running max moves only when the block's exceeds it by more than 2^8
+//               (then O and l are rescaled and the sweep repeated), the causal mask goes by position.  P (f16) goes to
+//               the block's P buffer in TMEM (double-buffered).
+//   P V warp:   O_h += P_h V_h, 4 x tcgen05.mma per stream with P as the A operand from TMEM; the two streams keep their
+//               own (m, l, O) and the epilogue merges them, so no thread ever needs another's row maximum.
+// TMEM: S 128 columns, P 2 x 64, O 2 x 128.  The loop is bound by the softmax warps' issue slots (~1,750 cycles per
+// block against 1,024 of MMA time), prologue (Q conversion, first TMA) and epilogue (partial write) cost ~13k cycles.
 #pragma once
 #include <cuda.h>
 
@@ -29,7 +34,7 @@
 namespace rq {
 
 #ifndef RQ_PF_SPLIT
-#define RQ_PF_SPLIT 1024
+#define RQ_PF_SPLIT 2048
 #endif
 constexpr int PF_SPLIT = RQ_PF_SPLIT;  // key positions per partial result (a multiple of the 128-position key block)
 constexpr int PF_BN = 128;       // key positions per MMA block
@@ -92,6 +97,26 @@ __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
     asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}" : "=r"(pred));
     return pred != 0;
+}
+// The issue warps' waits: as mbar_wait_bounded, but each poll may sleep in hardware until the phase completes (up to
+// the hint, in ns), so that a waiting warp does not take issue slots from the softmax warps of its scheduler
+__device__ __forceinline__ bool mbar_wait_sleepy(uint64_t *bar, uint32_t parity, int *err, int code) {
+    unsigned long long t0 = 0;
+    for (int it = 0; it < (1 << 26); it++) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done)
+                     : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
+                     : "memory");
+        if (done) return true;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        if (*reinterpret_cast<volatile int *>(err) != 0) return false;
+        if (now - t0 > 200000000ull) break;
+    }
+    atomicExch(err, code);
+    return false;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -226,12 +251,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
         // 16-byte chunk c of 16: k-block c / 8, physical chunk (c % 8) ^ (t % 8).
         // A warp converts 16 vectors, one per step: its lanes read the vector's 128 floats as one coalesced 512-byte
         // row (lane L: dims 4L .. 4L + 3) and store 4 halves into chunk L / 2
+        // (all 16 loads are issued before the first conversion, so that their latencies overlap)
+        float4 a[16];
+        int rl = (warp * 16) / G, x = (warp * 16) % G;
 #pragma unroll
         for (int rr = 0; rr < 16; rr++) {
-            const int t = warp * 16 + rr, rl = t / G, x = t % G;
-            float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (rl < w.nrows) a = *reinterpret_cast<const float4 *>(q + ((size_t)(w.row0 + rl) * n_heads + (size_t)g * G + x) * qh + 4 * lane);
-            __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
+            a[rr] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (rl < w.nrows) a[rr] = __ldg(reinterpret_cast<const float4 *>(q + ((size_t)(w.row0 + rl) * n_heads + (size_t)g * G + x) * qh) + lane);
+            if (++x == G) x = 0, rl++;
+        }
+#pragma unroll
+        for (int rr = 0; rr < 16; rr++) {
+            const int t = warp * 16 + rr;
+            __half2 h0 = __floats2half2_rn(a[rr].x, a[rr].y), h1 = __floats2half2_rn(a[rr].z, a[rr].w);
             const int c = lane >> 1;
             *reinterpret_cast<uint2 *>(sQ + (c >> 3) * 16384 + t * 128 + (((c & 7) ^ (t & 7)) << 4) + (lane & 1) * 8) =
                 make_uint2(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1));
@@ -260,8 +292,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
                 const uint32_t ph = j & 1, ph2 = (j >> 1) & 1;
                 const uint64_t b0 = dv + (uint64_t)(ph * (32768 >> 4));
                 const uint32_t pa = tbase + P_COL + ph * 64;
-                ok = mbar_wait_bounded(bar_v + ph, ph2, err, 14) && ok;
-                ok = mbar_wait_bounded(bar_p + ph, ph2, err, 13) && ok;  // P(j) of stream 0 is in TMEM
+                ok = mbar_wait_sleepy(bar_v + ph, ph2, err, 14) && ok;
+                ok = mbar_wait_sleepy(bar_p + ph, ph2, err, 13) && ok;  // P(j) of stream 0 is in TMEM
                 tc_fence_after();
                 if (lane == 0 && j < 8) PF_T(3 + 4 * j);
                 if (elect_one()) {
@@ -269,7 +301,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
                     for (int ks = 0; ks < 4; ks++) umma_ts(tbase + O_COL, pa + ks * 8, b0 + (uint64_t)(ks * 128), idesc, (j > 0) | (ks > 0));
                 }
                 __syncwarp();
-                ok = mbar_wait_bounded(bar_p + 2 + ph, ph2, err, 13) && ok;
+                ok = mbar_wait_sleepy(bar_p + 2 + ph, ph2, err, 13) && ok;
                 tc_fence_after();
                 if (elect_one()) {
 #pragma unroll
@@ -285,8 +317,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
             const uint64_t dq = umma_desc(smem_u32(sQ), 16, 1024, 2), dk = umma_desc(smem_u32(sK), 4096, 256, 6);
             for (int j = 0; j < nblk; j++) {
                 const uint64_t b0 = dk + (uint64_t)((j % 3) * (32768 >> 4));
-                ok = mbar_wait_bounded(bar_k + j % 3, (j / 3) & 1, err, 11) && ok;
-                if (j >= 1) ok = mbar_wait_bounded(bar_sfree, (j - 1) & 1, err, 12) && ok;
+                ok = mbar_wait_sleepy(bar_k + j % 3, (j / 3) & 1, err, 11) && ok;
+                if (lane == 0 && j == 0) PF_T(63);
+                if (j >= 1) ok = mbar_wait_sleepy(bar_sfree, (j - 1) & 1, err, 12) && ok;
                 tc_fence_after();
                 if (elect_one()) {
 #pragma unroll
@@ -302,11 +335,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
             // K (j + 3) into the stage of K (j) once S (j) is complete; V (j + 2) into the stage of V (j) once P V (j) is
             for (int j = 0; j < nblk; j++) {
                 if (j + 3 < nblk) {
-                    ok = mbar_wait_bounded(bar_kfree + j % 3, (j / 3) & 1, err, 15) && ok;
+                    ok = mbar_wait_sleepy(bar_kfree + j % 3, (j / 3) & 1, err, 15) && ok;
                     if (lane == 0) load_k(j + 3);
                 }
                 if (j + 2 < nblk) {
-                    ok = mbar_wait_bounded(bar_o + (j & 1), (j >> 1) & 1, err, 16) && ok;
+                    ok = mbar_wait_sleepy(bar_o + (j & 1), (j >> 1) & 1, err, 16) && ok;
                     if (lane == 0) load_v(j + 2);
                 }
                 __syncwarp();
@@ -325,13 +358,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
         // The waits of the loop are polled once well before their result is needed (a poll of a completed barrier
         // still takes ~150 cycles to answer), and only a poll that failed is followed by a real wait
         bool s_seen = false;
-#ifdef RQ_PF_STAGGER
-        if (h == 1) {  // the second stream starts half a block late, so that the two warps of a scheduler alternate
-            const long long c0 = clock64();
-            while (clock64() - c0 < RQ_PF_STAGGER) {
-            }
-        }
-#endif
         for (int j = 0; j < nblk; j++) {
             const int t0 = s0 + j * PF_BN + h * 64;  // first key of this thread's half of the block
             if (!s_seen) ok = mbar_wait_bounded(bar_s, j & 1, err, 21) && ok;
@@ -358,17 +384,20 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
             // same sweep, so that its comparisons fill the issue slots the exponential unit leaves
             float mx, lsum;
             auto sweep = [&](float mc) {
+                // (scalar FMA / add on purpose: measured on this kernel's mix, the packed f32x2 forms and a polynomial
+                // 2^x on the FMA pipe are both slower: the sweep is bound by issue slots, not by the exponential unit)
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int cc = 0; cc < 2; cc++) {
 #pragma unroll
                     for (int x = 0; x < 32; x += 2) {
+                        const int i = cc * 16 + (x >> 1);  // pair index
                         const float a0 = __uint_as_float(r[cc][x]), a1 = __uint_as_float(r[cc][x + 1]);
                         const float p0 = ex2(fmaf(a0, c, -mc)), p1 = ex2(fmaf(a1, c, -mc));
-                        mx4[(x >> 1) & 3] = fmaxf(mx4[(x >> 1) & 3], fmaxf(a0, a1));
-                        l4[(x >> 1) & 3] += p0 + p1;
+                        mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(a0, a1));
+                        l4[i & 3] += p0 + p1;
                         __half2 hh = __floats2half2_rn(p0, p1);
-                        pk[cc * 16 + (x >> 1)] = *reinterpret_cast<uint32_t *>(&hh);
+                        pk[i] = *reinterpret_cast<uint32_t *>(&hh);
                     }
                 }
                 mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
@@ -378,15 +407,26 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
             // below 2^8: exact enough in f16, and O is rescaled rarely).  So the sweep runs with the running max as it
             // stands; in the rare block where some row's max has to move (the first block with a valid key always),
             // O and l of the warp's rows are rescaled and the sweep is repeated with the new max
-            sweep(m_used == -INFINITY ? 0.0f : m_used * c);
+            const bool fresh = __any_sync(0xffffffffu, m_used == -INFINITY);  // (the first block; rows without a valid key so far)
+            if (fresh) {  // no running max to sweep with yet: the block's maximum first
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int cc = 0; cc < 2; cc++)
+#pragma unroll
+                    for (int x = 0; x < 32; x++) mx4[x & 3] = fmaxf(mx4[x & 3], __uint_as_float(r[cc][x]));
+                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            } else {
+                sweep(m_used * c);
+            }
             const bool move = mx > -INFINITY && (m_used == -INFINITY || (mx - m_used) * c > 8.0f);
-            if (__any_sync(0xffffffffu, move)) {
+            const bool any_move = __any_sync(0xffffffffu, move);
+            if (fresh || any_move) {
                 float alpha = 1.0f;
                 if (move) {
                     alpha = m_used == -INFINITY ? 0.0f : ex2((m_used - mx) * c);
                     m_used = mx;
                 }
-                if (j > 0) {
+                if (j > 0 && any_move) {
                     // (P V (j - 1) must have completed; P V (j - 3), the barrier's phase before, was seen complete
                     // before P (j - 1) was stored)
                     ok = mbar_wait_bounded(bar_o + ((j - 1) & 1), ((j - 1) >> 1) & 1, err, 23) && ok;
@@ -450,9 +490,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
             }
             if (t == 0) PF_T(42 + 4 * h);
             asm volatile("bar.sync 1, 256;" ::: "memory");
+            int rl2 = (warp * 16) / G, x = (warp * 16) % G - 1;
 #pragma unroll 8
             for (int rr = 0; rr < 16; rr++) {
-                const int tt = warp * 16 + rr, rl2 = tt / G, x = tt % G;
+                const int tt = warp * 16 + rr;
+                if (++x == G) x = 0, rl2++;
                 if (rl2 >= w.nrows) continue;
                 float *p = part + (((size_t)(w.row0 + rl2) * max_splits + w.split) * n_heads + (size_t)g * G + x) * RQ_PSTRIDE(HD);
                 const float4 a = *reinterpret_cast<const float4 *>(so + (size_t)tt * OST + 4 * lane);
