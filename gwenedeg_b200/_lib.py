@@ -62,6 +62,8 @@ PROTOTYPES = {
     "rq_cuda_attn_prefill_dev": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_dn_rec": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_dn_rec_dev": (_i, [_vp, _i, _vp, _vp]),
+    "rq_cuda_dn_chunk": (_i, [_vp, _i, _vp, _vp]),
+    "rq_cuda_dn_chunk_dev": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_dn_set_weights": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
     "rq_cuda_dn_prep_dev": (_i, [_vp, _i, _vp]),
     "rq_cuda_dn_out_dev": (_i, [_vp, _i, _vp, _vp]),

@@ -134,6 +134,18 @@ class Context:
         self.check(self.L.rq_cuda_dn_rec(self.h, lin_layer, _ptr(rows), _ptr(out)))
         return out
 
+    def dn_chunk(self, lin_layer, rows):
+        """The recurrence in its chunked tensor-core form (prompt chunks): same rows, output and state as dn_rec."""
+        rows = np.ascontiguousarray(rows, np.float32)
+        if rows.size != self.nrows * self.lw:
+            raise ValueError("DeltaNet rows must be [rows][lw]")
+        out = np.empty((self.nrows, self.vdim), np.float32)
+        self.check(self.L.rq_cuda_dn_chunk(self.h, lin_layer, _ptr(rows), _ptr(out)))
+        return out
+
+    def dn_chunk_dev(self, lin_layer, rows_dev, out_dev):
+        self.check(self.L.rq_cuda_dn_chunk_dev(self.h, lin_layer, _ptr(rows_dev), _ptr(out_dev)))
+
     def dn_set_weights(self, lin_layer, conv, a, dt, norm):
         arrs = [np.ascontiguousarray(x, np.float32) for x in (conv, a, dt, norm)]
         self.check(self.L.rq_cuda_dn_set_weights(self.h, lin_layer, *[_ptr(x) for x in arrs]))

@@ -120,4 +120,13 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
                  : "memory");
 }
 
+// One segment of the open pass as the DeltaNet kernels see it.
+struct DnSeg {
+    float *state;   // the segment's sequence: state of linear layer 0 (conv part included)
+    size_t lstride; // floats from one linear layer's state to the next
+    int row0, n;    // rows of the pass: row0 .. row0 + n - 1
+    int first;      // the segment starts at position 0: S is cleared first
+    int pad;
+};
+
 }  // namespace rq

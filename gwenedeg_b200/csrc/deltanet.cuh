@@ -19,14 +19,6 @@
 
 namespace rq {
 
-struct DnSeg {
-    float *state;   // the segment's sequence: state of linear layer 0 (conv part included)
-    size_t lstride; // floats from one linear layer's state to the next
-    int row0, n;    // rows of the pass: row0 .. row0 + n - 1
-    int first;      // the segment starts at position 0: S is cleared first
-    int pad;
-};
-
 constexpr int DN_BW = 32;
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {

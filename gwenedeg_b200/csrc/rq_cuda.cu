@@ -16,6 +16,7 @@
 #include "attn_decode.cuh"
 #include "attn_prefill.cuh"
 #include "deltanet.cuh"
+#include "deltanet_chunk.cuh"
 #include "kv_store.cuh"
 
 using namespace rq;
@@ -175,7 +176,7 @@ int rq_cuda_device_count(void) {
 int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ctx) {
     if (!ctx) return RQ_CUDA_ERR_ARG;
     *ctx = nullptr;
-    if (!model || max_rows < 1 || max_rows > 512) return RQ_CUDA_ERR_ARG;
+    if (!model || max_rows < 1 || max_rows > 16384) return RQ_CUDA_ERR_ARG;
     const RqCudaModel &m = *model;
     int nkv_local = m.kv_heads_local > 0 ? m.kv_heads_local : m.n_kv_heads;
     if (m.n_attn < 0 || m.n_lin < 0 || (m.n_attn == 0 && m.n_lin == 0)) return RQ_CUDA_ERR_ARG;
@@ -818,20 +819,57 @@ int rq_cuda_dn_rec_dev(RqCuda *c, int lin_layer, const float *rows, float *out) 
     return RQ_CUDA_OK;
 }
 
+int rq_cuda_dn_chunk_dev(RqCuda *c, int lin_layer, const float *rows, float *out) {
+    int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_chunk");
+    if (rc) return rc;
+    if (!rows || !out) return fail(c, RQ_CUDA_ERR_ARG, "dn_chunk: null rows");
+    const RqCudaModel &m = c->m;
+    if (m.dn_dk != 128 || m.dn_dv != 128) return fail(c, RQ_CUDA_ERR_ARG, "dn_chunk is built for dk = dv = 128");
+    CU(c, cudaSetDevice(c->device));
+    DnChunkArgs a;
+    a.segs = c->d_dseg;
+    a.nseg = c->nseg;
+    a.lin_layer = lin_layer;
+    a.nk = m.dn_nk;
+    a.nv = m.dn_nv;
+    a.conv_floats = ((size_t)(m.dn_conv - 1) * (2 * m.dn_nk * m.dn_dk + m.dn_nv * m.dn_dv) + 15) / 16 * 16;
+    a.rows = rows;
+    a.lw = 2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
+    a.out = out;
+    a.err = c->d_err;
+    cudaError_t e = launch_dn_chunk(a, c->stream);
+    if (e != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "dn_chunk launch: %s", cudaGetErrorString(e));
+    c->launches++;
+    return RQ_CUDA_OK;
+}
+
+static int dn_host(RqCuda *c, int lin_layer, const float *rows, float *out, bool chunked) {
+    const RqCudaModel &m = c->m;
+    const int lw = 2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
+    size_t rb = (size_t)c->nrows * lw * 4, ob = (size_t)c->nrows * m.dn_nv * m.dn_dv * 4;
+    int rc;
+    if ((rc = grow(c, (void **)&c->d_dn, &c->dn_bytes, rb + ob))) return rc;
+    float *d_rows = c->d_dn, *d_out = c->d_dn + (size_t)c->nrows * lw;
+    CU(c, cudaMemcpyAsync(d_rows, rows, rb, cudaMemcpyHostToDevice, c->stream));
+    if ((rc = chunked ? rq_cuda_dn_chunk_dev(c, lin_layer, d_rows, d_out) : rq_cuda_dn_rec_dev(c, lin_layer, d_rows, d_out))) return rc;
+    CU(c, cudaMemcpyAsync(out, d_out, ob, cudaMemcpyDeviceToHost, c->stream));
+    return rq_cuda_sync(c);
+}
+
+int rq_cuda_dn_chunk(RqCuda *c, int lin_layer, const float *rows, float *out) {
+    int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_chunk");
+    if (rc) return rc;
+    if (!rows || !out) return fail(c, RQ_CUDA_ERR_ARG, "dn_chunk: null rows");
+    CU(c, cudaSetDevice(c->device));
+    return dn_host(c, lin_layer, rows, out, true);
+}
+
 int rq_cuda_dn_rec(RqCuda *c, int lin_layer, const float *rows, float *out) {
     int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_rec");
     if (rc) return rc;
     if (!rows || !out) return fail(c, RQ_CUDA_ERR_ARG, "dn_rec: null rows");
     CU(c, cudaSetDevice(c->device));
-    const RqCudaModel &m = c->m;
-    const int lw = 2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
-    size_t rb = (size_t)c->nrows * lw * 4, ob = (size_t)c->nrows * m.dn_nv * m.dn_dv * 4;
-    if ((rc = grow(c, (void **)&c->d_dn, &c->dn_bytes, rb + ob))) return rc;
-    float *d_rows = c->d_dn, *d_out = c->d_dn + (size_t)c->nrows * lw;
-    CU(c, cudaMemcpyAsync(d_rows, rows, rb, cudaMemcpyHostToDevice, c->stream));
-    if ((rc = rq_cuda_dn_rec_dev(c, lin_layer, d_rows, d_out))) return rc;
-    CU(c, cudaMemcpyAsync(out, d_out, ob, cudaMemcpyDeviceToHost, c->stream));
-    return rq_cuda_sync(c);
+    return dn_host(c, lin_layer, rows, out, false);
 }
 
 int rq_cuda_dn_set_weights(RqCuda *c, int lin_layer, const float *conv, const float *a, const float *dt, const float *norm) {

@@ -163,6 +163,14 @@ int rq_cuda_attn_prefill_dev(RqCuda *ctx, int layer, const float *q_dev, float *
 int rq_cuda_dn_rec(RqCuda *ctx, int lin_layer, const float *rows, float *out);
 int rq_cuda_dn_rec_dev(RqCuda *ctx, int lin_layer, const float *rows_dev, float *out_dev);
 
+/* The same recurrence for passes with many rows per sequence (prompt chunks: the dn_rec_run items of prefill_worker,
+ * forward.c:3018-3027), re-associated per chunk of 64 tokens (WY / UT form) so that the work runs as dense products on
+ * the tensor cores.  Same arguments, layouts and state as rq_cuda_dn_rec; operands are rounded to f16 (fp32
+ * accumulation and state), so results agree with the token recurrence to ~5e-4 relative instead of bit for bit.
+ * dk = dv = 128 only (RQ_CUDA_ERR_ARG otherwise). */
+int rq_cuda_dn_chunk(RqCuda *ctx, int lin_layer, const float *rows, float *out);
+int rq_cuda_dn_chunk_dev(RqCuda *ctx, int lin_layer, const float *rows_dev, float *out_dev);
+
 /* The steps around the recurrence, on the device (dk = dv = 128): the layer's weights once (host pointers: conv taps in the
  * reference's per-channel-group order [conv][channels of the group] at conv * first_channel, conv * (2 nk dk + nv dv) floats;
  * ssm_a = -exp(A_log) [nv]; the dt bias [nv]; the gated RMSNorm weight [dv]; src/internal.h:166-169), then per pass
