@@ -126,7 +126,7 @@ struct DnSeg {
     size_t lstride; // floats from one linear layer's state to the next
     int row0, n;    // rows of the pass: row0 .. row0 + n - 1
     int first;      // the segment starts at position 0: S is cleared first
-    int pad;
+    int chunk0;     // 64-token chunks of all earlier segments of the pass (the chunked DeltaNet's work records)
 };
 
 }  // namespace rq

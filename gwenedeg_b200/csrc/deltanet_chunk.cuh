@@ -10,19 +10,19 @@
 //  => U    = T' R,   R = B V - (B G K) S0,   T' = (I + A)^-1,  A_ij = beta_i (g_i / g_j)(k_i . k_j) for j < i
 //     O    = (G Q) S0 + M U,                 M_ij = (g_i / g_j)(q_i . k_j) for j <= i
 //     S    = g_63 S0 + Kt^T U,               Kt_j = (g_63 / g_j) k_j
-// One CTA per (segment, value head, half of the dv columns): the two halves of a head are independent given K and Q, so
-// they run on two SMs (each repeats the small K / Q products).  256 threads; warps w and w + 4 own TMEM lanes
-// 32 (w % 4) .. + 31 and split the columns.  Steps of a chunk:
-//   0  rows -> f16 operands in shared memory (the scaled copies above), gates -> log2 prefix sums; the next chunk's rows
-//      are prefetched into L2; S (TMEM, fp32) -> f16 copy in shared memory, and S *= g_63 in place
-//   1  MMA: K K^T and Q K^T (N = 64) | -(B G K) S0 and (G Q) S0, which need nothing of this chunk but the operands
-//   2  A (fp32) and M (f16) from the first two products, masked and decayed
-//   3  T' by blocks of 16 (forward substitution on the diagonal blocks, block products below them) -> f16;
-//      R = B V - (B G K) S0 -> f16
-//   4  MMA: U = T' R
-//   5  U -> f16 in shared memory
-//   6  MMA: O += M U;  S += Kt^T U
-//   7  O -> global memory through shared memory (coalesced rows)
+// Two kernels per layer and pass:
+//   dn_chunk_prep_kernel   everything of a chunk that does not depend on the state, one CTA per (chunk, value head), all
+//                          chunks of the pass in parallel: rows -> the scaled f16 operands G Q, -(B G K), Kt and B V; the
+//                          products K K^T and Q K^T on the tensor cores; A and M from them (masked, decayed); T' =
+//                          (I + A)^-1 by blocks of 32 (forward substitution on the two diagonal blocks, two products for the
+//                          block below).  Everything goes to a work buffer in the operand layout of the second kernel.
+//   dn_chunk_state_kernel  the walk over a segment's chunks in order, one CTA per (segment, value head, half of the dv
+//                          columns: the halves are independent given T' and M).  Per chunk, operands arrive by bulk
+//                          copies (TMA), two chunks deep:
+//                            S (TMEM, fp32) -> f16 copy in shared memory, and S *= g_63 in place
+//                            MMA: -(B G K) S0 and (G Q) S0;   R = B V - (B G K) S0 -> f16
+//                            MMA: U = T' R;                    U -> f16
+//                            MMA: O += M U;  S += Kt^T U;      O -> global memory through shared memory
 // All MMAs are M = 128 (rows 64 .. 127 of the token-indexed products are never read).  Every operand buffer has the
 // same physical layout, [64-column half][row][128 bytes] with the 128-byte swizzle, which serves as a K-major operand
 // (row = M or N index) and as an MN-major one (row = K index) alike.
@@ -33,41 +33,48 @@ namespace rq {
 
 constexpr int DNC_C = 64;  // tokens per chunk
 constexpr int DNC_THREADS = 256;
+// the work buffer's record per (chunk, value head): the state kernel's operands, in its shared-memory layout
+constexpr int DNC_GQ = 0, DNC_NBGK = 16384, DNC_KT = 32768, DNC_T = 49152, DNC_M = 57344, DNC_BV = 65536, DNC_LG = 98304, DNC_ITEM = 98560;
 
 struct DnChunkArgs {
-    const DnSeg *segs;
-    int nseg, lin_layer, nk, nv;
+    const DnSeg *segs;  // (DnSeg::chunk0: chunks of all earlier segments = the segment's first record in `work`)
+    int nseg, max_chunks, lin_layer, nk, nv;
     size_t conv_floats;
     const float *rows;
     int lw;
     float *out;
+    uint8_t *work;  // [chunks of the pass][nv] records of DNC_ITEM bytes
     int *err;
 };
-// launches dn_chunk_kernel (grid: 2 x value heads, segments) on `stream`; dk = dv = 128 only
+// launches the two kernels on `stream`; dk = dv = 128 only
 cudaError_t launch_dn_chunk(const DnChunkArgs &a, cudaStream_t stream);
 
 #ifdef RQ_DN_CHUNK_INSTANTIATE
 namespace dnc {
-// shared-memory map (bytes from a 1024-byte aligned base)
-constexpr int K16 = 0, Q16 = 16384, GQ16 = 32768, NBGK16 = 49152, KT16 = 65536, T16 = 81920, M16 = 90112, BV32 = 98304, R16 = 114688,
-              U16 = 122880, S16 = 131072, AF = 147456, AST = 68, XF = AF + 64 * AST * 4, PF = XF + 64 * AST * 4, LG = PF + 16 * AST * 4, BETA = LG + 256, BAR = BETA + 256, SLOT = BAR + 16,
-              END = SLOT + 16;
-constexpr int SMEM = END + 1024;  // (BAR holds two barriers)
-constexpr int HV = 64;  // dv columns per CTA
-constexpr int S_COL = 0, Y_COL = 64, Z_COL = 128, X_COL = 256;
+constexpr int AST = 68;  // floats per row of the fp32 64 x 64 matrices in shared memory
+// ---- prep kernel: shared memory (bytes from a 1024-byte aligned base); TMEM: K K^T | Q K^T (128 columns)
+constexpr int P_K16 = 0, P_Q16 = 16384, P_SLACK = 32768, P_AF = 49152, P_XF = P_AF + 64 * AST * 4, P_PF = P_XF + 64 * AST * 4,
+              P_LG = P_PF + 32 * AST * 4, P_BETA = P_LG + 256, P_BAR = P_BETA + 256, P_SLOT = P_BAR + 16, P_SMEM = P_SLOT + 16 + 1024;
+// (P_SLACK: 16 KB that the M = 128 products read past the 64 rows of Q16; never used otherwise)
+// ---- state kernel: two stages of operands (the record's first 64 KB, then the CTA's half of B V, then the gates)
+constexpr int ST_BV = 65536, ST_LG = 81920, ST_BYTES = 82944;
+constexpr int S_S16 = 2 * ST_BYTES, S_R16 = S_S16 + 16384, S_U16 = S_R16 + 8192, S_OUT = S_U16 + 8192, S_BAR = S_OUT + 64 * AST * 4,
+              S_SLOT = S_BAR + 32, S_SMEM = S_SLOT + 16 + 1024;
+constexpr int HV = 64;  // dv columns per CTA of the state kernel
+constexpr int S_COL = 0, Y_COL = 64, Z_COL = 128;
 }  // namespace dnc
 
-// 4 adjacent values (dims 4 lane .. 4 lane + 3 of row `row`) -> the swizzled f16 operand layout of a 64-row buffer
-__device__ __forceinline__ void dnc_store4(uint8_t *buf, int row, int lane, float a, float b, float c, float d) {
-    __half2 h0 = __floats2half2_rn(a, b), h1 = __floats2half2_rn(c, d);
+// byte offset of 4 adjacent values (dims 4 lane .. 4 lane + 3 of row `row`) in the swizzled f16 layout of a 64-row,
+// 128-column buffer
+__device__ __forceinline__ int dnc_off4(int row, int lane) {
     const int ch = lane >> 1;
-    *reinterpret_cast<uint2 *>(buf + (ch >> 3) * 8192 + row * 128 + (((ch & 7) ^ (row & 7)) << 4) + (lane & 1) * 8) =
-        make_uint2(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1));
+    return (ch >> 3) * 8192 + row * 128 + (((ch & 7) ^ (row & 7)) << 4) + (lane & 1) * 8;
 }
 __device__ __forceinline__ uint32_t dnc_pack(float a, float b) {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&h);
 }
+__device__ __forceinline__ uint2 dnc_pack4(float a, float b, float c, float d) { return make_uint2(dnc_pack(a, b), dnc_pack(c, d)); }
 // 32 adjacent fp32 values r (columns 32 cb .. 32 cb + 31 of row `row`) -> f16 in a buffer of 128-byte rows
 __device__ __forceinline__ void dnc_store_row32(uint8_t *buf, int row, int cb, const float *r) {
 #pragma unroll
@@ -80,34 +87,233 @@ __device__ __forceinline__ void dnc_store_row32(uint8_t *buf, int row, int cb, c
     }
 }
 
-__global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_kernel(const DnSeg *__restrict__ segs, int lin_layer, int nk, int nv, size_t conv_floats,
-                                                               const float *__restrict__ rows, int lw, float *__restrict__ out, int *err) {
+// grid: (chunk of the segment, value head, segment)
+__global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg *__restrict__ segs, int nk, int nv, const float *__restrict__ rows,
+                                                                  int lw, uint8_t *__restrict__ work, int *err) {
+    using namespace dnc;
+    constexpr int DK = 128, DV = 128, C = DNC_C;
+    const DnSeg sg = segs[blockIdx.z];
+    const int c0 = blockIdx.x * C;
+    if (c0 >= sg.n) return;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    float *s_a = reinterpret_cast<float *>(sm + P_AF), *s_x = reinterpret_cast<float *>(sm + P_XF), *s_p = reinterpret_cast<float *>(sm + P_PF);
+    float *s_lg = reinterpret_cast<float *>(sm + P_LG), *s_beta = reinterpret_cast<float *>(sm + P_BETA);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(sm + P_BAR);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + P_SLOT);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.y, cnt = min(C, sg.n - c0);
+    const int trow = (warp & 3) * 32 + lane, cb = warp >> 2;
+    const int conv_dim = 2 * nk * DK + nv * DV, vdim = nv * DV;
+    const size_t oq = (size_t)(h % nk) * DK, okk = (size_t)nk * DK + oq, ov = (size_t)2 * nk * DK + (size_t)h * DV;
+    const size_t oe = (size_t)conv_dim + vdim + h, ob = oe + nv;
+    uint8_t *rec = work + ((size_t)(sg.chunk0 + blockIdx.x) * nv + h) * DNC_ITEM;
+
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        mbar_fence_init();
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    // gates -> inclusive log2 prefix sums (tokens past the end: eg 1, beta 0)
+    if (warp == 0) {
+        const float *r0 = rows + (size_t)(sg.row0 + c0 + lane) * lw, *r1 = r0 + (size_t)32 * lw;
+        float a0 = lane < cnt ? fmaxf(log2f(r0[oe]), -1.0e4f) : 0.0f, a1 = lane + 32 < cnt ? fmaxf(log2f(r1[oe]), -1.0e4f) : 0.0f;
+        s_beta[lane] = lane < cnt ? r0[ob] : 0.0f;
+        s_beta[lane + 32] = lane + 32 < cnt ? r1[ob] : 0.0f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float b0 = __shfl_up_sync(0xffffffffu, a0, o), b1 = __shfl_up_sync(0xffffffffu, a1, o);
+            if (lane >= o) a0 += b0, a1 += b1;
+        }
+        a1 += __shfl_sync(0xffffffffu, a0, 31);
+        s_lg[lane] = a0;
+        s_lg[lane + 32] = a1;
+        reinterpret_cast<float *>(rec + DNC_LG)[lane] = a0;
+        reinterpret_cast<float *>(rec + DNC_LG)[lane + 32] = a1;
+    }
+    float4 qv[8], kv[8], vv[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int j = warp * 8 + i;
+        qv[i] = kv[i] = vv[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (j < cnt) {
+            const float *r = rows + (size_t)(sg.row0 + c0 + j) * lw;
+            qv[i] = __ldg(reinterpret_cast<const float4 *>(r + oq) + lane);
+            kv[i] = __ldg(reinterpret_cast<const float4 *>(r + okk) + lane);
+            vv[i] = __ldg(reinterpret_cast<const float4 *>(r + ov) + lane);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tbase = *tmem_slot;
+    const uint32_t lane_addr = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+    bool ok = true;
+    // rows -> f16: K and Q for the two products here, the scaled copies straight into the record
+    const float lgc = s_lg[C - 1];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int j = warp * 8 + i, off = dnc_off4(j, lane);
+        const float gam = ex2(s_lg[j]), bet = s_beta[j], nbg = -bet * gam, kt = ex2(lgc - s_lg[j]);
+        *reinterpret_cast<uint2 *>(sm + P_K16 + off) = dnc_pack4(kv[i].x, kv[i].y, kv[i].z, kv[i].w);
+        *reinterpret_cast<uint2 *>(sm + P_Q16 + off) = dnc_pack4(qv[i].x, qv[i].y, qv[i].z, qv[i].w);
+        *reinterpret_cast<uint2 *>(rec + DNC_GQ + off) = dnc_pack4(qv[i].x * gam, qv[i].y * gam, qv[i].z * gam, qv[i].w * gam);
+        *reinterpret_cast<uint2 *>(rec + DNC_NBGK + off) = dnc_pack4(kv[i].x * nbg, kv[i].y * nbg, kv[i].z * nbg, kv[i].w * nbg);
+        *reinterpret_cast<uint2 *>(rec + DNC_KT + off) = dnc_pack4(kv[i].x * kt, kv[i].y * kt, kv[i].z * kt, kv[i].w * kt);
+        // beta v, fp32, per half of the dv columns: [half][token][64]
+        *reinterpret_cast<float4 *>(rec + DNC_BV + (lane >> 4) * 16384 + (j * 64 + 4 * (lane & 15)) * 4) =
+            make_float4(vv[i].x * bet, vv[i].y * bet, vv[i].z * bet, vv[i].w * bet);
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    // K K^T and Q K^T (M 128, N 64, K 128)
+    if (warp == 4 && (tc_fence_after(), elect_one())) {
+        const uint32_t sbase = smem_u32(sm);
+        constexpr uint32_t id_kk = umma_idesc(128, 64, 0, 0);
+        auto d_k128 = [&](int buf, int ks) { return umma_desc(sbase + buf + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024, 2); };
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) umma_ss(tbase, d_k128(P_K16, ks), d_k128(P_K16, ks), id_kk, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) umma_ss(tbase + 64, d_k128(P_Q16, ks), d_k128(P_K16, ks), id_kk, ks > 0);
+        umma_commit(bar);
+    }
+    ok = mbar_wait_bounded(bar, 0, err, 31) && ok;
+    tc_fence_after();
+    // A (fp32, strictly lower) and M (f16, lower with the diagonal): row i, columns 32 cb .. + 31 per thread
+    if ((warp & 3) < 2) {
+        uint32_t g[32], mq[32];
+        tmem_ld32(lane_addr + cb * 32, g);
+        tmem_ld32(lane_addr + 64 + cb * 32, mq);
+        tmem_wait_ld();
+        const int i = trow;
+        const float lgi = s_lg[i], bi = s_beta[i];
+        float mv[32], av[32];
+#pragma unroll
+        for (int x = 0; x < 32; x++) {
+            const int j = 32 * cb + x;
+            const float ratio = j <= i ? ex2(lgi - s_lg[j]) : 0.0f;
+            av[x] = j < i ? bi * ratio * __uint_as_float(g[x]) : 0.0f;
+            mv[x] = j <= i ? ratio * __uint_as_float(mq[x]) : 0.0f;
+        }
+#pragma unroll
+        for (int x = 0; x < 32; x += 4) *reinterpret_cast<float4 *>(s_a + i * AST + 32 * cb + x) = make_float4(av[x], av[x + 1], av[x + 2], av[x + 3]);
+        dnc_store_row32(rec + DNC_M, i, cb, mv);
+    }
+    tc_fence_before();
+    __syncthreads();
+    // T' = (I + A)^-1 = [[X11, 0], [-X22 A21 X11, X22]] with 32 x 32 blocks: the two diagonal blocks by forward
+    // substitution (a column per thread: x_r = [r == c] - sum_{q<r} A_rq x_q), then the two products on all threads
+    if (tid < 64) {
+        const int b = tid >> 5;
+        float x[32];
+#pragma unroll
+        for (int r = 0; r < 32; r++) {
+            float acc[4] = {r == lane ? 1.0f : 0.0f, 0.0f, 0.0f, 0.0f};
+            const float *arow = s_a + (32 * b + r) * AST + 32 * b;
+#pragma unroll
+            for (int q4 = 0; q4 < (r + 3) / 4; q4++) {
+                const float4 a4 = *reinterpret_cast<const float4 *>(arow + 4 * q4);  // (entries q >= r are zero)
+                const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                for (int y = 0; y < 4; y++)
+                    if (4 * q4 + y < r) acc[y] = fmaf(-av[y], x[4 * q4 + y], acc[y]);
+            }
+            x[r] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+            s_x[(32 * b + r) * AST + 32 * b + lane] = x[r];
+        }
+    }
+    __syncthreads();
+    {
+        const int r = tid >> 3, c4 = (tid & 7) * 4;
+        {  // P = A21 X11
+            float4 p = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float *arow = s_a + (32 + r) * AST;
+#pragma unroll
+            for (int q4 = 0; q4 < 8; q4++) {
+                const float4 a4 = *reinterpret_cast<const float4 *>(arow + 4 * q4);
+                const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                for (int y = 0; y < 4; y++) {
+                    const float4 x4 = *reinterpret_cast<const float4 *>(s_x + (4 * q4 + y) * AST + c4);
+                    p.x = fmaf(av[y], x4.x, p.x), p.y = fmaf(av[y], x4.y, p.y), p.z = fmaf(av[y], x4.z, p.z), p.w = fmaf(av[y], x4.w, p.w);
+                }
+            }
+            *reinterpret_cast<float4 *>(s_p + r * AST + c4) = p;
+        }
+        __syncthreads();
+        {  // X21 = -X22 P
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float *xrow = s_x + (32 + r) * AST + 32;
+#pragma unroll
+            for (int q4 = 0; q4 < 8; q4++) {
+                const float4 a4 = *reinterpret_cast<const float4 *>(xrow + 4 * q4);
+                const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                for (int y = 0; y < 4; y++) {
+                    const float4 p4 = *reinterpret_cast<const float4 *>(s_p + (4 * q4 + y) * AST + c4);
+                    v.x = fmaf(-av[y], p4.x, v.x), v.y = fmaf(-av[y], p4.y, v.y), v.z = fmaf(-av[y], p4.z, v.z), v.w = fmaf(-av[y], p4.w, v.w);
+                }
+            }
+            *reinterpret_cast<float4 *>(s_x + (32 + r) * AST + c4) = v;
+        }
+        __syncthreads();
+        // -> f16, K-major rows of 64: thread (row, 16-column block); the upper right block is zero
+        const int row = tid >> 2, jb = tid & 3;
+        float f[16];
+#pragma unroll
+        for (int q = 0; q < 16; q++) f[q] = ((row >= 32 || jb < 2) && ok) ? s_x[row * AST + 16 * jb + q] : 0.0f;
+#pragma unroll
+        for (int q = 0; q < 2; q++) {
+            uint4 w;
+            w.x = dnc_pack(f[8 * q], f[8 * q + 1]), w.y = dnc_pack(f[8 * q + 2], f[8 * q + 3]);
+            w.z = dnc_pack(f[8 * q + 4], f[8 * q + 5]), w.w = dnc_pack(f[8 * q + 6], f[8 * q + 7]);
+            *reinterpret_cast<uint4 *>(rec + DNC_T + row * 128 + (((2 * jb + q) ^ (row & 7)) << 4)) = w;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(128));
+}
+
+#ifdef RQ_DNC_TRACE
+__device__ long long dnc_trace[32];  // experiments only: event times of CTA (0, 0), third chunk, in clock cycles
+#define DNC_T(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && n == 2 && tid == 0) dnc_trace[i] = clock64() - dnc_t0; } while (0)
+#else
+#define DNC_T(i) do { } while (0)
+#endif
+
+// grid: (2 x value heads, segments)
+__global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const DnSeg *__restrict__ segs, int lin_layer, int nv, size_t conv_floats,
+                                                                     const uint8_t *__restrict__ work, float *__restrict__ out, int *err) {
     using namespace dnc;
     constexpr int DK = 128, DV = 128, C = DNC_C;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    float *s_a = reinterpret_cast<float *>(sm + AF), *s_lg = reinterpret_cast<float *>(sm + LG), *s_beta = reinterpret_cast<float *>(sm + BETA);
-    float *s_bv = reinterpret_cast<float *>(sm + BV32);  // [token][HV] beta v
-    uint64_t *bar = reinterpret_cast<uint64_t *>(sm + BAR);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + SLOT);
+    uint64_t *bar_full = reinterpret_cast<uint64_t *>(sm + S_BAR), *bar = bar_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + S_SLOT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x >> 1, hv = blockIdx.x & 1;  // value head, which half of its dv columns
     const int trow = (warp & 3) * 32 + lane, cb = warp >> 2;  // this thread's TMEM lane and its 32-column block of a 64-column tile
     const DnSeg sg = segs[blockIdx.y];
-    const int conv_dim = 2 * nk * DK + nv * DV, vdim = nv * DV;
-    const size_t oq = (size_t)(h % nk) * DK, okk = (size_t)nk * DK + oq, ov = (size_t)2 * nk * DK + (size_t)h * DV + (size_t)hv * HV;
-    const size_t oe = (size_t)conv_dim + vdim + h, ob = oe + nv;
+    const int vdim = nv * DV, nch = (sg.n + C - 1) / C;
     // the CTA's part of the state: blocks 2 hv, 2 hv + 1 of [dv / 32][dk][32]
     float *Sg = sg.state + (size_t)lin_layer * sg.lstride + conv_floats + (size_t)h * DK * DV + (size_t)hv * 2 * DK * 32;
+    const uint8_t *rec0 = work + ((size_t)sg.chunk0 * nv + h) * DNC_ITEM;
 
     if (tid == 0) {
-        mbar_init(bar, 1);      // the chunk's products 1a, 4 and 6, each waited for by every thread before the next is issued
-        mbar_init(bar + 1, 1);  // product 1b (issued right behind 1a: a barrier of its own keeps the parity waits unambiguous)
+        mbar_init(bar_full, 1);
+        mbar_init(bar_full + 1, 1);
+        mbar_init(bar, 1);
         mbar_fence_init();
     }
     if (warp == 4) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     tc_fence_before();
@@ -116,7 +322,17 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_kernel(const DnSeg *_
     const uint32_t tbase = *tmem_slot;
     const uint32_t lane_addr = tbase + ((uint32_t)((warp & 3) * 32) << 16);
     bool ok = true;
-    uint32_t phase = 0, phase_b = 0;
+    uint32_t phase = 0;
+    // chunk n's operands -> stage n % 2 (one thread): the record's first 64 KB, the CTA's half of B V, the gates
+    auto load_chunk = [&](int n) {
+        uint8_t *st = sm + (n & 1) * ST_BYTES;
+        const uint8_t *rec = rec0 + (size_t)n * nv * DNC_ITEM;
+        mbar_expect_tx(bar_full + (n & 1), 65536 + 16384 + 256);
+        bulk_g2s(st, rec, 65536, bar_full + (n & 1));
+        bulk_g2s(st + ST_BV, rec + DNC_BV + hv * 16384, 16384, bar_full + (n & 1));
+        bulk_g2s(st + ST_LG, rec + DNC_LG, 256, bar_full + (n & 1));
+    };
+    if (tid == 0 && nch > 0) load_chunk(0);
 
     // the state -> TMEM: thread (trow, cb) holds columns 32 cb .. + 31 of row trow of S ([dk][HV])
     {
@@ -135,7 +351,7 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_kernel(const DnSeg *_
     tc_fence_after();
 
     const uint32_t sbase = smem_u32(sm);
-    constexpr uint32_t id_kk = umma_idesc(128, 64, 0, 0), id_kmn = umma_idesc(128, 64, 0, 1), id_mnmn = umma_idesc(128, 64, 1, 1);
+    constexpr uint32_t id_kmn = umma_idesc(128, 64, 0, 1), id_mnmn = umma_idesc(128, 64, 1, 1);
     // K-major operand of a 64-row, 128-column buffer, k-step ks of 16 columns
     auto d_k128 = [&](int buf, int ks) { return umma_desc(sbase + buf + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024, 2); };
     // K-major operand of a 64-column buffer (one 128-byte row per M index)
@@ -148,43 +364,16 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_kernel(const DnSeg *_
         tc_fence_after();
     };
 
-    for (int c0 = 0; c0 < sg.n; c0 += C) {
-        const int cnt = min(C, sg.n - c0);
-        // ---- 0: gates -> inclusive log2 prefix sums; rows -> f16 operands; the state's f16 copy and its decay
-        if (warp == 0) {
-            const float *r0 = rows + (size_t)(sg.row0 + c0 + lane) * lw, *r1 = r0 + (size_t)32 * lw;
-            float a0 = lane < cnt ? fmaxf(log2f(r0[oe]), -1.0e4f) : 0.0f, a1 = lane + 32 < cnt ? fmaxf(log2f(r1[oe]), -1.0e4f) : 0.0f;
-            s_beta[lane] = lane < cnt ? r0[ob] : 0.0f;
-            s_beta[lane + 32] = lane + 32 < cnt ? r1[ob] : 0.0f;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const float b0 = __shfl_up_sync(0xffffffffu, a0, o), b1 = __shfl_up_sync(0xffffffffu, a1, o);
-                if (lane >= o) a0 += b0, a1 += b1;
-            }
-            a1 += __shfl_sync(0xffffffffu, a0, 31);
-            s_lg[lane] = a0;
-            s_lg[lane + 32] = a1;
-        }
-        float4 qv[8], kv[8], vv[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int j = warp * 8 + i;
-            qv[i] = kv[i] = vv[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (j < cnt) {
-                const float *r = rows + (size_t)(sg.row0 + c0 + j) * lw;
-                qv[i] = __ldg(reinterpret_cast<const float4 *>(r + oq) + lane);
-                kv[i] = __ldg(reinterpret_cast<const float4 *>(r + okk) + lane);
-                if (lane < HV / 4) vv[i] = __ldg(reinterpret_cast<const float4 *>(r + ov) + lane);
-            }
-            if (j + C < sg.n - c0 && (lane & 7) == 0) {  // the same row of the next chunk -> L2
-                const float *rn = rows + (size_t)(sg.row0 + c0 + C + j) * lw;
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(rn + oq + 4 * lane));
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(rn + okk + 4 * lane));
-                if (lane < HV / 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(rn + ov + 4 * lane));
-            }
-        }
-        __syncthreads();  // (the gates; and every thread is past the previous chunk's output staging)
-        const float lgc = s_lg[C - 1];
+    for (int n = 0; n < nch; n++) {
+        const int c0 = n * C, cnt = min(C, sg.n - c0), sb = (n & 1) * ST_BYTES;
+#ifdef RQ_DNC_TRACE
+        const long long dnc_t0 = clock64();
+#endif
+        // the next chunk's operands start loading (its stage was last read by chunk n - 1, whose products are complete
+        // and whose B V rows and gates every thread read before the barrier at the end of that chunk)
+        if (tid == 0 && n + 1 < nch) load_chunk(n + 1);
+        ok = mbar_wait_bounded(bar_full + (n & 1), (n >> 1) & 1, err, 33) && ok;
+        DNC_T(0);
         {
             // S (the previous chunk's result) -> its f16 copy, the B operand of this chunk's S0 products; S *= g_63
             uint32_t r[32];
@@ -193,135 +382,33 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_kernel(const DnSeg *_
             float f[32];
 #pragma unroll
             for (int x = 0; x < 32; x++) f[x] = __uint_as_float(r[x]);
-            dnc_store_row32(sm + S16, trow, cb, f);
-            const float gc = ex2(lgc);
+            dnc_store_row32(sm + S_S16, trow, cb, f);
+            const float gc = ex2(reinterpret_cast<const float *>(sm + sb + ST_LG)[C - 1]);
 #pragma unroll
             for (int x = 0; x < 32; x++) r[x] = __float_as_uint(f[x] * gc);
             tmem_st32(lane_addr + S_COL + cb * 32, r);
+            tmem_wait_st();
         }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int j = warp * 8 + i;
-            const float gam = ex2(s_lg[j]), bet = s_beta[j], nbg = -bet * gam, kt = ex2(lgc - s_lg[j]);
-            dnc_store4(sm + K16, j, lane, kv[i].x, kv[i].y, kv[i].z, kv[i].w);
-            dnc_store4(sm + Q16, j, lane, qv[i].x, qv[i].y, qv[i].z, qv[i].w);
-            dnc_store4(sm + GQ16, j, lane, qv[i].x * gam, qv[i].y * gam, qv[i].z * gam, qv[i].w * gam);
-            dnc_store4(sm + NBGK16, j, lane, kv[i].x * nbg, kv[i].y * nbg, kv[i].z * nbg, kv[i].w * nbg);
-            dnc_store4(sm + KT16, j, lane, kv[i].x * kt, kv[i].y * kt, kv[i].z * kt, kv[i].w * kt);
-            if (lane < HV / 4)
-                *reinterpret_cast<float4 *>(s_bv + j * HV + 4 * lane) = make_float4(vv[i].x * bet, vv[i].y * bet, vv[i].z * bet, vv[i].w * bet);
-        }
-        tmem_wait_st();
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        // ---- 1: K K^T and Q K^T -> X; -(B G K) S0 -> Y and (G Q) S0 -> Z
-        if (tid == 128) {
-            tc_fence_after();
+        DNC_T(1);
+        // ---- -(B G K) S0 -> Y and (G Q) S0 -> Z
+        if (warp == 4 && (tc_fence_after(), elect_one())) {
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) umma_ss(tbase + X_COL, d_k128(K16, ks), d_k128(K16, ks), id_kk, ks > 0);
+            for (int ks = 0; ks < 8; ks++) umma_ss(tbase + Y_COL, d_k128(sb + DNC_NBGK, ks), d_mn(S_S16, ks, 0), id_kmn, ks > 0);
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) umma_ss(tbase + X_COL + 64, d_k128(Q16, ks), d_k128(K16, ks), id_kk, ks > 0);
+            for (int ks = 0; ks < 8; ks++) umma_ss(tbase + Z_COL, d_k128(sb + DNC_GQ, ks), d_mn(S_S16, ks, 0), id_kmn, ks > 0);
             umma_commit(bar);
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) umma_ss(tbase + Y_COL, d_k128(NBGK16, ks), d_mn(S16, ks, 0), id_kmn, ks > 0);
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) umma_ss(tbase + Z_COL, d_k128(GQ16, ks), d_mn(S16, ks, 0), id_kmn, ks > 0);
-            umma_commit(bar + 1);
         }
         wait_mma();
-        // ---- 2: A (fp32, strictly lower) and M (f16, lower with the diagonal): row i, columns 32 cb .. + 31 per thread
-        if ((warp & 3) < 2) {
-            uint32_t g[32], mq[32];
-            tmem_ld32(lane_addr + X_COL + cb * 32, g);
-            tmem_ld32(lane_addr + X_COL + 64 + cb * 32, mq);
-            tmem_wait_ld();
-            const int i = trow;
-            const float lgi = s_lg[i], bi = s_beta[i];
-            float mv[32];
-#pragma unroll
-            for (int x = 0; x < 32; x++) {
-                const int j = 32 * cb + x;
-                const float ratio = j <= i ? ex2(lgi - s_lg[j]) : 0.0f;
-                s_a[i * AST + j] = j < i ? bi * ratio * __uint_as_float(g[x]) : 0.0f;
-                mv[x] = j <= i ? ratio * __uint_as_float(mq[x]) : 0.0f;
-            }
-            dnc_store_row32(sm + M16, i, cb, mv);
-        }
-        tc_fence_before();
-        __syncthreads();
-        // ---- 3: T' = (I + A)^-1 by blocks of 16: the four diagonal blocks by forward substitution (a column per thread),
-        // then block row by block row T'_ij = -T'_ii (sum_{k=j}^{i-1} A_ik T'_kj), 256 threads on a 16 x 16 block each time
-        {
-            float *s_x = reinterpret_cast<float *>(sm + XF), *s_p = reinterpret_cast<float *>(sm + PF);
-            if (tid < 64) {
-                const int b = tid >> 4, c = tid & 15;
-                float x[16];
-#pragma unroll
-                for (int r = 0; r < 16; r++) {
-                    float acc = r == c ? 1.0f : 0.0f;
-#pragma unroll
-                    for (int q = 0; q < r; q++) acc = fmaf(-s_a[(16 * b + r) * AST + 16 * b + q], x[q], acc);
-                    x[r] = acc;
-                    s_x[(16 * b + r) * AST + 16 * b + c] = acc;
-                }
-            }
-            __syncthreads();
-            const int r = tid >> 4, c = tid & 15;
-#pragma unroll
-            for (int i = 1; i < 4; i++) {
-                const float *arow = s_a + (16 * i + r) * AST;
-#pragma unroll
-                for (int j = 0; j < i; j++) {
-                    float p = 0.0f;
-#pragma unroll
-                    for (int k4 = 4 * j; k4 < 4 * i; k4++) {
-                        const float4 a4 = *reinterpret_cast<const float4 *>(arow + 4 * k4);
-                        p = fmaf(a4.x, s_x[(4 * k4) * AST + 16 * j + c], p);
-                        p = fmaf(a4.y, s_x[(4 * k4 + 1) * AST + 16 * j + c], p);
-                        p = fmaf(a4.z, s_x[(4 * k4 + 2) * AST + 16 * j + c], p);
-                        p = fmaf(a4.w, s_x[(4 * k4 + 3) * AST + 16 * j + c], p);
-                    }
-                    s_p[r * AST + 16 * j + c] = p;
-                }
-                __syncthreads();
-                const float *drow = s_x + (16 * i + r) * AST + 16 * i;  // row r of T'_ii
-#pragma unroll
-                for (int j = 0; j < i; j++) {
-                    float x = 0.0f;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; q4++) {
-                        const float4 d4 = *reinterpret_cast<const float4 *>(drow + 4 * q4);
-                        x = fmaf(-d4.x, s_p[(4 * q4) * AST + 16 * j + c], x);
-                        x = fmaf(-d4.y, s_p[(4 * q4 + 1) * AST + 16 * j + c], x);
-                        x = fmaf(-d4.z, s_p[(4 * q4 + 2) * AST + 16 * j + c], x);
-                        x = fmaf(-d4.w, s_p[(4 * q4 + 3) * AST + 16 * j + c], x);
-                    }
-                    s_x[(16 * i + r) * AST + 16 * j + c] = x;
-                }
-                __syncthreads();
-            }
-            // -> f16, K-major rows of 64: thread (row, 16-column block), zero above the diagonal blocks
-            const int row = tid >> 2, jb = tid & 3;
-            float f[16];
-#pragma unroll
-            for (int q = 0; q < 16; q++) f[q] = jb <= (row >> 4) ? s_x[row * AST + 16 * jb + q] : 0.0f;
-#pragma unroll
-            for (int q = 0; q < 2; q++) {
-                uint4 w;
-                w.x = dnc_pack(f[8 * q], f[8 * q + 1]), w.y = dnc_pack(f[8 * q + 2], f[8 * q + 3]);
-                w.z = dnc_pack(f[8 * q + 4], f[8 * q + 5]), w.w = dnc_pack(f[8 * q + 6], f[8 * q + 7]);
-                *reinterpret_cast<uint4 *>(sm + T16 + row * 128 + (((2 * jb + q) ^ (row & 7)) << 4)) = w;
-            }
-        }
-        ok = mbar_wait_bounded(bar + 1, phase_b, err, 32) && ok;  // (the S0 products)
-        phase_b ^= 1;
-        tc_fence_after();
-        // R = B V - (B G K) S0 -> f16: row j, columns 32 cb .. + 31 per thread
+        DNC_T(2);
+        // ---- R = B V - (B G K) S0 -> f16: row j, columns 32 cb .. + 31 per thread
         if ((warp & 3) < 2) {
             uint32_t r[32];
             tmem_ld32(lane_addr + Y_COL + cb * 32, r);
             tmem_wait_ld();
+            const float *s_bv = reinterpret_cast<const float *>(sm + sb + ST_BV);
             float f[32];
 #pragma unroll
             for (int x = 0; x < 32; x += 4) {
@@ -329,20 +416,21 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_kernel(const DnSeg *_
                 f[x] = b.x + __uint_as_float(r[x]), f[x + 1] = b.y + __uint_as_float(r[x + 1]);
                 f[x + 2] = b.z + __uint_as_float(r[x + 2]), f[x + 3] = b.w + __uint_as_float(r[x + 3]);
             }
-            dnc_store_row32(sm + R16, trow, cb, f);
+            dnc_store_row32(sm + S_R16, trow, cb, f);
         }
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        // ---- 4: U = T' R -> Y
-        if (tid == 128) {
-            tc_fence_after();
+        DNC_T(3);
+        // ---- U = T' R -> Y
+        if (warp == 4 && (tc_fence_after(), elect_one())) {
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++) umma_ss(tbase + Y_COL, d_k64(T16, ks), d_mn(R16, ks, 0), id_kmn, ks > 0);
+            for (int ks = 0; ks < 4; ks++) umma_ss(tbase + Y_COL, d_k64(sb + DNC_T, ks), d_mn(S_R16, ks, 0), id_kmn, ks > 0);
             umma_commit(bar);
         }
         wait_mma();
-        // ---- 5: U -> f16
+        DNC_T(4);
+        // ---- U -> f16
         if ((warp & 3) < 2) {
             uint32_t r[32];
             tmem_ld32(lane_addr + Y_COL + cb * 32, r);
@@ -350,44 +438,48 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_kernel(const DnSeg *_
             float f[32];
 #pragma unroll
             for (int x = 0; x < 32; x++) f[x] = __uint_as_float(r[x]);
-            dnc_store_row32(sm + U16, trow, cb, f);
+            dnc_store_row32(sm + S_U16, trow, cb, f);
         }
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        // ---- 6: O += M U -> Z;  S += Kt^T U
-        if (tid == 128) {
-            tc_fence_after();
+        DNC_T(5);
+        // ---- O += M U -> Z;  S += Kt^T U
+        if (warp == 4 && (tc_fence_after(), elect_one())) {
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++) umma_ss(tbase + Z_COL, d_k64(M16, ks), d_mn(U16, ks, 0), id_kmn, 1);
+            for (int ks = 0; ks < 4; ks++) umma_ss(tbase + Z_COL, d_k64(sb + DNC_M, ks), d_mn(S_U16, ks, 0), id_kmn, 1);
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++) umma_ss(tbase + S_COL, d_mn(KT16, ks, 8192), d_mn(U16, ks, 0), id_mnmn, 1);
+            for (int ks = 0; ks < 4; ks++) umma_ss(tbase + S_COL, d_mn(sb + DNC_KT, ks, 8192), d_mn(S_U16, ks, 0), id_mnmn, 1);
             umma_commit(bar);
         }
         wait_mma();
-        // ---- 7: O rows -> global memory, staged through shared memory (over K16, which no MMA reads any more)
+        DNC_T(6);
+        // ---- O rows -> global memory, staged through shared memory
         {
-            constexpr int OST = HV + 4;
-            float *so = reinterpret_cast<float *>(sm);
+            float *so = reinterpret_cast<float *>(sm + S_OUT);
             if ((warp & 3) < 2) {
                 uint32_t r[32];
                 tmem_ld32(lane_addr + Z_COL + cb * 32, r);
                 tmem_wait_ld();
 #pragma unroll
                 for (int y = 0; y < 32; y += 4)
-                    *reinterpret_cast<float4 *>(so + (size_t)trow * OST + cb * 32 + y) =
+                    *reinterpret_cast<float4 *>(so + (size_t)trow * AST + cb * 32 + y) =
                         make_float4(__uint_as_float(r[y]), __uint_as_float(r[y + 1]), __uint_as_float(r[y + 2]), __uint_as_float(r[y + 3]));
             }
             tc_fence_before();
             __syncthreads();
+            DNC_T(7);
             // a warp writes two rows of 256 bytes per step
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int j = warp * 8 + 2 * i + (lane >> 4), l16 = lane & 15;
                 if (j < cnt)
                     *reinterpret_cast<float4 *>(out + (size_t)(sg.row0 + c0 + j) * vdim + (size_t)h * DV + (size_t)hv * HV + 4 * l16) =
-                        ok ? *reinterpret_cast<const float4 *>(so + (size_t)j * OST + 4 * l16) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        ok ? *reinterpret_cast<const float4 *>(so + (size_t)j * AST + 4 * l16) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
+            fence_proxy_async();  // (this chunk's stage is overwritten by bulk copies next)
+            __syncthreads();      // (the staging area and this chunk's stage are free again)
+            DNC_T(8);
         }
     }
     // the state back to global memory
@@ -403,7 +495,7 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_kernel(const DnSeg *_
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(512));
+    if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(256));
 }
 
 cudaError_t launch_dn_chunk(const DnChunkArgs &a, cudaStream_t stream) {
@@ -411,11 +503,13 @@ cudaError_t launch_dn_chunk(const DnChunkArgs &a, cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(dn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dnc::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(dn_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dnc::P_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(dn_chunk_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dnc::S_SMEM);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    dn_chunk_kernel<<<dim3(2 * a.nv, a.nseg), DNC_THREADS, dnc::SMEM, stream>>>(a.segs, a.lin_layer, a.nk, a.nv, a.conv_floats, a.rows, a.lw, a.out, a.err);
+    dn_chunk_prep_kernel<<<dim3(a.max_chunks, a.nv, a.nseg), DNC_THREADS, dnc::P_SMEM, stream>>>(a.segs, a.nk, a.nv, a.rows, a.lw, a.work, a.err);
+    dn_chunk_state_kernel<<<dim3(2 * a.nv, a.nseg), DNC_THREADS, dnc::S_SMEM, stream>>>(a.segs, a.lin_layer, a.nv, a.conv_floats, a.work, a.out, a.err);
     return cudaGetLastError();
 }
 #endif  // RQ_DN_CHUNK_INSTANTIATE

@@ -82,6 +82,8 @@ struct RqCuda {
     // DeltaNet weights of the steps around the recurrence (rq_cuda_dn_set_weights): per linear layer conv taps, A, dt
     // bias, norm weight
     float *d_dnw; size_t dnw_layer_floats;
+    int dn_chunks, dn_max_chunks;          // 64-token chunks of the open pass: all segments, the longest one
+    uint8_t *d_dnwork; size_t dnwork_bytes;  // the chunked DeltaNet's work records
     std::vector<char> dnw_set;
     // optional per-launch timing of the dominant kernel (rq_cuda_profile_begin / _end)
     std::vector<cudaEvent_t> prof_ev;
@@ -236,7 +238,7 @@ void rq_cuda_free(RqCuda *c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->d_dnw) cudaFree(c->d_dnw);
-    void *dev[] = {c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->flush, c->d_maps, c->d_work};
+    void *dev[] = {c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->flush, c->d_maps, c->d_work, c->d_dnwork};
     if (c->h_maps) cudaFreeHost(c->h_maps);
     for (void *p : dev)
         if (p) cudaFree(p);
@@ -473,7 +475,7 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
     CU(c, cudaEventSynchronize(c->up_ev[c->up_idx]));
     c->h_rows = c->h_rows2[c->up_idx];
     c->h_dseg = c->h_dseg2[c->up_idx];
-    int r = 0, blk = 0, mx = 0;
+    int r = 0, blk = 0, mx = 0, dn_chunks = 0, dn_max_chunks = 0;
     for (int i = 0; i < nseg; i++) {
         const RqCudaSegment &g = seg[i];
         for (int j = 0; j < g.n; j++, r++) {
@@ -495,10 +497,14 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
         d.row0 = r - g.n;
         d.n = g.n;
         d.first = g.pos0 == 0;
-        d.pad = 0;
+        d.chunk0 = dn_chunks;
+        dn_chunks += (g.n + 63) / 64;
+        dn_max_chunks = std::max(dn_max_chunks, (g.n + 63) / 64);
     }
     memset(&c->h_rows[r], 0, sizeof(PassRow));
     c->h_rows[r].blk0 = blk;
+    c->dn_chunks = dn_chunks;
+    c->dn_max_chunks = dn_max_chunks;
     c->pf_ready = 0;  // (the tensor-core prefill tables are made by the first prefill call of the pass)
     CU(c, cudaMemcpyAsync(c->d_rows, c->h_rows, sizeof(PassRow) * (r + 1), cudaMemcpyHostToDevice, c->stream));
     if (c->m.n_lin > 0) CU(c, cudaMemcpyAsync(c->d_dseg, c->h_dseg, sizeof(DnSeg) * nseg, cudaMemcpyHostToDevice, c->stream));
@@ -826,9 +832,13 @@ int rq_cuda_dn_chunk_dev(RqCuda *c, int lin_layer, const float *rows, float *out
     const RqCudaModel &m = c->m;
     if (m.dn_dk != 128 || m.dn_dv != 128) return fail(c, RQ_CUDA_ERR_ARG, "dn_chunk is built for dk = dv = 128");
     CU(c, cudaSetDevice(c->device));
+    int rcg = grow(c, (void **)&c->d_dnwork, &c->dnwork_bytes, (size_t)c->dn_chunks * m.dn_nv * DNC_ITEM);
+    if (rcg) return rcg;
     DnChunkArgs a;
     a.segs = c->d_dseg;
     a.nseg = c->nseg;
+    a.max_chunks = c->dn_max_chunks;
+    a.work = c->d_dnwork;
     a.lin_layer = lin_layer;
     a.nk = m.dn_nk;
     a.nv = m.dn_nv;
@@ -839,7 +849,7 @@ int rq_cuda_dn_chunk_dev(RqCuda *c, int lin_layer, const float *rows, float *out
     a.err = c->d_err;
     cudaError_t e = launch_dn_chunk(a, c->stream);
     if (e != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "dn_chunk launch: %s", cudaGetErrorString(e));
-    c->launches++;
+    c->launches += 2;
     return RQ_CUDA_OK;
 }
 
