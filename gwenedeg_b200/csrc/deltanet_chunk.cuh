@@ -34,7 +34,8 @@ namespace rq {
 constexpr int DNC_C = 64;  // tokens per chunk
 constexpr int DNC_THREADS = 256;
 // the work buffer's record per (chunk, value head): the state kernel's operands, in its shared-memory layout
-constexpr int DNC_GQ = 0, DNC_NBGK = 16384, DNC_KT = 32768, DNC_T = 49152, DNC_M = 57344, DNC_BV = 65536, DNC_LG = 98304, DNC_ITEM = 98560;
+constexpr int DNC_GQ = 0, DNC_NBGK = 16384, DNC_KT = 32768, DNC_T = 49152, DNC_M = 57344, DNC_BV = 65536, DNC_BVH = 64 * 68 * 4, DNC_LG = DNC_BV + 2 * DNC_BVH,
+              DNC_ITEM = DNC_LG + 256;  // (B V: fp32 [half of dv][token][64 of 68]: the row padding keeps the state kernel's row reads conflict-free)
 
 struct DnChunkArgs {
     const DnSeg *segs;  // (DnSeg::chunk0: chunks of all earlier segments = the segment's first record in `work`)
@@ -57,8 +58,8 @@ constexpr int P_K16 = 0, P_Q16 = 16384, P_SLACK = 32768, P_AF = 49152, P_XF = P_
               P_LG = P_PF + 32 * AST * 4, P_BETA = P_LG + 256, P_BAR = P_BETA + 256, P_SLOT = P_BAR + 16, P_SMEM = P_SLOT + 16 + 1024;
 // (P_SLACK: 16 KB that the M = 128 products read past the 64 rows of Q16; never used otherwise)
 // ---- state kernel: two stages of operands (the record's first 64 KB, then the CTA's half of B V, then the gates)
-constexpr int ST_BV = 65536, ST_LG = 81920, ST_BYTES = 82944;
-constexpr int S_S16 = 2 * ST_BYTES, S_R16 = S_S16 + 16384, S_U16 = S_R16 + 8192, S_OUT = S_U16 + 8192, S_BAR = S_OUT + 64 * AST * 4,
+constexpr int ST_BV = 65536, ST_LG = ST_BV + DNC_BVH, ST_BYTES = 83968;
+constexpr int S_S16 = 2 * ST_BYTES, S_R16 = S_S16 + 16384, S_U16 = S_R16 + 8192, S_BAR = S_U16 + 8192,
               S_SLOT = S_BAR + 32, S_SMEM = S_SLOT + 16 + 1024;
 constexpr int HV = 64;  // dv columns per CTA of the state kernel
 constexpr int S_COL = 0, Y_COL = 64, Z_COL = 128;
@@ -87,6 +88,15 @@ __device__ __forceinline__ void dnc_store_row32(uint8_t *buf, int row, int cb, c
     }
 }
 
+#ifdef RQ_DNC_TRACE
+__device__ long long dnc_trace[32];  // experiments only: event times of CTA (0, 0), third chunk, in clock cycles
+#define DNC_T(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && n == 2 && tid == 0) dnc_trace[i] = clock64() - dnc_t0; } while (0)
+#define DNP_T(i) do { if (blockIdx.x == 2 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) dnc_trace[16 + i] = clock64() - dnp_t0; } while (0)
+#else
+#define DNC_T(i) do { } while (0)
+#define DNP_T(i) do { } while (0)
+#endif
+
 // grid: (chunk of the segment, value head, segment)
 __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg *__restrict__ segs, int nk, int nv, const float *__restrict__ rows,
                                                                   int lw, uint8_t *__restrict__ work, int *err) {
@@ -103,6 +113,9 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + P_SLOT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef RQ_DNC_TRACE
+    const long long dnp_t0 = clock64();
+#endif
     const int h = blockIdx.y, cnt = min(C, sg.n - c0);
     const int trow = (warp & 3) * 32 + lane, cb = warp >> 2;
     const int conv_dim = 2 * nk * DK + nv * DV, vdim = nv * DV;
@@ -147,9 +160,11 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
             vv[i] = __ldg(reinterpret_cast<const float4 *>(r + ov) + lane);
         }
     }
+    DNP_T(0);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    DNP_T(1);
     const uint32_t tbase = *tmem_slot;
     const uint32_t lane_addr = tbase + ((uint32_t)((warp & 3) * 32) << 16);
     bool ok = true;
@@ -165,12 +180,14 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
         *reinterpret_cast<uint2 *>(rec + DNC_NBGK + off) = dnc_pack4(kv[i].x * nbg, kv[i].y * nbg, kv[i].z * nbg, kv[i].w * nbg);
         *reinterpret_cast<uint2 *>(rec + DNC_KT + off) = dnc_pack4(kv[i].x * kt, kv[i].y * kt, kv[i].z * kt, kv[i].w * kt);
         // beta v, fp32, per half of the dv columns: [half][token][64]
-        *reinterpret_cast<float4 *>(rec + DNC_BV + (lane >> 4) * 16384 + (j * 64 + 4 * (lane & 15)) * 4) =
+        *reinterpret_cast<float4 *>(rec + DNC_BV + (lane >> 4) * DNC_BVH + (j * AST + 4 * (lane & 15)) * 4) =
             make_float4(vv[i].x * bet, vv[i].y * bet, vv[i].z * bet, vv[i].w * bet);
     }
+    DNP_T(2);
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
+    DNP_T(3);
     // K K^T and Q K^T (M 128, N 64, K 128)
     if (warp == 4 && (tc_fence_after(), elect_one())) {
         const uint32_t sbase = smem_u32(sm);
@@ -184,6 +201,7 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
     }
     ok = mbar_wait_bounded(bar, 0, err, 31) && ok;
     tc_fence_after();
+    DNP_T(4);
     // A (fp32, strictly lower) and M (f16, lower with the diagonal): row i, columns 32 cb .. + 31 per thread
     if ((warp & 3) < 2) {
         uint32_t g[32], mq[32];
@@ -204,8 +222,10 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
         for (int x = 0; x < 32; x += 4) *reinterpret_cast<float4 *>(s_a + i * AST + 32 * cb + x) = make_float4(av[x], av[x + 1], av[x + 2], av[x + 3]);
         dnc_store_row32(rec + DNC_M, i, cb, mv);
     }
+    DNP_T(5);
     tc_fence_before();
     __syncthreads();
+    DNP_T(6);
     // T' = (I + A)^-1 = [[X11, 0], [-X22 A21 X11, X22]] with 32 x 32 blocks: the two diagonal blocks by forward
     // substitution (a column per thread: x_r = [r == c] - sum_{q<r} A_rq x_q), then the two products on all threads
     if (tid < 64) {
@@ -227,7 +247,9 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
             s_x[(32 * b + r) * AST + 32 * b + lane] = x[r];
         }
     }
+    DNP_T(7);
     __syncthreads();
+    DNP_T(8);
     {
         const int r = tid >> 3, c4 = (tid & 7) * 4;
         {  // P = A21 X11
@@ -246,6 +268,7 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
             *reinterpret_cast<float4 *>(s_p + r * AST + c4) = p;
         }
         __syncthreads();
+        DNP_T(9);
         {  // X21 = -X22 P
             float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             const float *xrow = s_x + (32 + r) * AST + 32;
@@ -262,6 +285,7 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
             *reinterpret_cast<float4 *>(s_x + (32 + r) * AST + c4) = v;
         }
         __syncthreads();
+        DNP_T(10);
         // -> f16, K-major rows of 64: thread (row, 16-column block); the upper right block is zero
         const int row = tid >> 2, jb = tid & 3;
         float f[16];
@@ -275,17 +299,11 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
             *reinterpret_cast<uint4 *>(rec + DNC_T + row * 128 + (((2 * jb + q) ^ (row & 7)) << 4)) = w;
         }
     }
+    DNP_T(11);
     tc_fence_before();
     __syncthreads();
     if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(128));
 }
-
-#ifdef RQ_DNC_TRACE
-__device__ long long dnc_trace[32];  // experiments only: event times of CTA (0, 0), third chunk, in clock cycles
-#define DNC_T(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && n == 2 && tid == 0) dnc_trace[i] = clock64() - dnc_t0; } while (0)
-#else
-#define DNC_T(i) do { } while (0)
-#endif
 
 // grid: (2 x value heads, segments)
 __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const DnSeg *__restrict__ segs, int lin_layer, int nv, size_t conv_floats,
@@ -327,9 +345,9 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
     auto load_chunk = [&](int n) {
         uint8_t *st = sm + (n & 1) * ST_BYTES;
         const uint8_t *rec = rec0 + (size_t)n * nv * DNC_ITEM;
-        mbar_expect_tx(bar_full + (n & 1), 65536 + 16384 + 256);
+        mbar_expect_tx(bar_full + (n & 1), 65536 + DNC_BVH + 256);
         bulk_g2s(st, rec, 65536, bar_full + (n & 1));
-        bulk_g2s(st + ST_BV, rec + DNC_BV + hv * 16384, 16384, bar_full + (n & 1));
+        bulk_g2s(st + ST_BV, rec + DNC_BV + hv * DNC_BVH, DNC_BVH, bar_full + (n & 1));
         bulk_g2s(st + ST_LG, rec + DNC_LG, 256, bar_full + (n & 1));
     };
     if (tid == 0 && nch > 0) load_chunk(0);
@@ -412,7 +430,7 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
             float f[32];
 #pragma unroll
             for (int x = 0; x < 32; x += 4) {
-                const float4 b = *reinterpret_cast<const float4 *>(s_bv + trow * HV + 32 * cb + x);
+                const float4 b = *reinterpret_cast<const float4 *>(s_bv + trow * AST + 32 * cb + x);
                 f[x] = b.x + __uint_as_float(r[x]), f[x + 1] = b.y + __uint_as_float(r[x + 1]);
                 f[x + 2] = b.z + __uint_as_float(r[x + 2]), f[x + 3] = b.w + __uint_as_float(r[x + 3]);
             }
@@ -454,33 +472,24 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
         }
         wait_mma();
         DNC_T(6);
-        // ---- O rows -> global memory, staged through shared memory
-        {
-            float *so = reinterpret_cast<float *>(sm + S_OUT);
-            if ((warp & 3) < 2) {
-                uint32_t r[32];
-                tmem_ld32(lane_addr + Z_COL + cb * 32, r);
-                tmem_wait_ld();
+        // ---- O rows -> global memory: thread (row, 32-column block) writes its 128 bytes
+        if ((warp & 3) < 2) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + Z_COL + cb * 32, r);
+            tmem_wait_ld();
+            if (trow < cnt) {
+                float4 *dst = reinterpret_cast<float4 *>(out + (size_t)(sg.row0 + c0 + trow) * vdim + (size_t)h * DV + (size_t)hv * HV + 32 * cb);
 #pragma unroll
-                for (int y = 0; y < 32; y += 4)
-                    *reinterpret_cast<float4 *>(so + (size_t)trow * AST + cb * 32 + y) =
-                        make_float4(__uint_as_float(r[y]), __uint_as_float(r[y + 1]), __uint_as_float(r[y + 2]), __uint_as_float(r[y + 3]));
+                for (int y = 0; y < 8; y++)
+                    dst[y] = ok ? make_float4(__uint_as_float(r[4 * y]), __uint_as_float(r[4 * y + 1]), __uint_as_float(r[4 * y + 2]), __uint_as_float(r[4 * y + 3]))
+                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
-            tc_fence_before();
-            __syncthreads();
-            DNC_T(7);
-            // a warp writes two rows of 256 bytes per step
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int j = warp * 8 + 2 * i + (lane >> 4), l16 = lane & 15;
-                if (j < cnt)
-                    *reinterpret_cast<float4 *>(out + (size_t)(sg.row0 + c0 + j) * vdim + (size_t)h * DV + (size_t)hv * HV + 4 * l16) =
-                        ok ? *reinterpret_cast<const float4 *>(so + (size_t)j * AST + 4 * l16) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            }
-            fence_proxy_async();  // (this chunk's stage is overwritten by bulk copies next)
-            __syncthreads();      // (the staging area and this chunk's stage are free again)
-            DNC_T(8);
         }
+        DNC_T(7);
+        fence_proxy_async();  // (this chunk's stage is overwritten by bulk copies next)
+        tc_fence_before();
+        __syncthreads();      // (this chunk's stage and the O columns are free again)
+        DNC_T(8);
     }
     // the state back to global memory
     tc_fence_after();
