@@ -12,17 +12,20 @@
 //     S    = g_63 S0 + Kt^T U,               Kt_j = (g_63 / g_j) k_j
 // Two kernels per layer and pass:
 //   dn_chunk_prep_kernel   everything of a chunk that does not depend on the state, one CTA per (chunk, value head), all
-//                          chunks of the pass in parallel: rows -> the scaled f16 operands G Q, -(B G K), Kt and B V; the
-//                          products K K^T and Q K^T on the tensor cores; A and M from them (masked, decayed); T' =
-//                          (I + A)^-1 by blocks of 32 (forward substitution on the two diagonal blocks, two products for the
-//                          block below).  Everything goes to a work buffer in the operand layout of the second kernel.
+//                          chunks of the pass in parallel: rows -> K and Q as f16 operands, beta v, the gates' log2 prefix
+//                          sums; the products K K^T and Q K^T on the tensor cores; A and M from them (masked, decayed);
+//                          T' = (I + A)^-1 by blocks of 32 (forward substitution on the two diagonal blocks, two products
+//                          for the block below).  Everything goes to a work buffer in the operand layout of the second
+//                          kernel.
 //   dn_chunk_state_kernel  the walk over a segment's chunks in order, one CTA per (segment, value head, half of the dv
 //                          columns: the halves are independent given T' and M).  Per chunk, operands arrive by bulk
 //                          copies (TMA), two chunks deep:
 //                            S (TMEM, fp32) -> f16 copy in shared memory, and S *= g_63 in place
-//                            MMA: -(B G K) S0 and (G Q) S0;   R = B V - (B G K) S0 -> f16
-//                            MMA: U = T' R;                    U -> f16
-//                            MMA: O += M U;  S += Kt^T U;      O -> global memory through shared memory
+//                            MMA: K S0 and Q S0;               R_j = beta_j v_j - beta_j g_j (K S0)_j -> f16
+//                            MMA: U = T' R;                    U and (g_63 / g_j) U -> f16
+//                            MMA: M U;  S += K^T (scaled U);   O_i = g_i (Q S0)_i + (M U)_i -> global memory
+//                          (the per-token scalings sit on the output side of each product, so K and Q are the only
+//                          row operands and a record is 83 KB)
 // All MMAs are M = 128 (rows 64 .. 127 of the token-indexed products are never read).  Every operand buffer has the
 // same physical layout, [64-column half][row][128 bytes] with the 128-byte swizzle, which serves as a K-major operand
 // (row = M or N index) and as an MN-major one (row = K index) alike.
@@ -34,8 +37,10 @@ namespace rq {
 constexpr int DNC_C = 64;  // tokens per chunk
 constexpr int DNC_THREADS = 256;
 // the work buffer's record per (chunk, value head): the state kernel's operands, in its shared-memory layout
-constexpr int DNC_GQ = 0, DNC_NBGK = 16384, DNC_KT = 32768, DNC_T = 49152, DNC_M = 57344, DNC_BV = 65536, DNC_BVH = 64 * 68 * 4, DNC_LG = DNC_BV + 2 * DNC_BVH,
-              DNC_ITEM = DNC_LG + 256;  // (B V: fp32 [half of dv][token][64 of 68]: the row padding keeps the state kernel's row reads conflict-free)
+// K, Q (f16, operand layout) | T' | M | beta v (fp32 [half of dv][token][64 of 68]: the row padding keeps the state kernel's
+// row reads conflict-free) | log2 decay prefix sums [64], beta [64]
+constexpr int DNC_K = 0, DNC_Q = 16384, DNC_T = 32768, DNC_M = 40960, DNC_BV = 49152, DNC_BVH = 64 * 68 * 4, DNC_SC = DNC_BV + 2 * DNC_BVH,
+              DNC_ITEM = DNC_SC + 512;
 
 struct DnChunkArgs {
     const DnSeg *segs;  // (DnSeg::chunk0: chunks of all earlier segments = the segment's first record in `work`)
@@ -58,11 +63,11 @@ constexpr int P_K16 = 0, P_Q16 = 16384, P_SLACK = 32768, P_AF = 49152, P_XF = P_
               P_LG = P_PF + 32 * AST * 4, P_BETA = P_LG + 256, P_BAR = P_BETA + 256, P_SLOT = P_BAR + 16, P_SMEM = P_SLOT + 16 + 1024;
 // (P_SLACK: 16 KB that the M = 128 products read past the 64 rows of Q16; never used otherwise)
 // ---- state kernel: two stages of operands (the record's first 64 KB, then the CTA's half of B V, then the gates)
-constexpr int ST_BV = 65536, ST_LG = ST_BV + DNC_BVH, ST_BYTES = 83968;
-constexpr int S_S16 = 2 * ST_BYTES, S_R16 = S_S16 + 16384, S_U16 = S_R16 + 8192, S_BAR = S_U16 + 8192,
+constexpr int ST_BV = 49152, ST_SC = ST_BV + DNC_BVH, ST_BYTES = 67584;
+constexpr int S_S16 = 2 * ST_BYTES, S_R16 = S_S16 + 16384, S_U16 = S_R16 + 8192, S_UK16 = S_U16 + 8192, S_BAR = S_UK16 + 8192,
               S_SLOT = S_BAR + 32, S_SMEM = S_SLOT + 16 + 1024;
 constexpr int HV = 64;  // dv columns per CTA of the state kernel
-constexpr int S_COL = 0, Y_COL = 64, Z_COL = 128;
+constexpr int S_COL = 0, Y_COL = 64, Z1_COL = 128, Z2_COL = 192;
 }  // namespace dnc
 
 // byte offset of 4 adjacent values (dims 4 lane .. 4 lane + 3 of row `row`) in the swizzled f16 layout of a 64-row,
@@ -145,8 +150,9 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
         a1 += __shfl_sync(0xffffffffu, a0, 31);
         s_lg[lane] = a0;
         s_lg[lane + 32] = a1;
-        reinterpret_cast<float *>(rec + DNC_LG)[lane] = a0;
-        reinterpret_cast<float *>(rec + DNC_LG)[lane + 32] = a1;
+        float *sc = reinterpret_cast<float *>(rec + DNC_SC);
+        sc[lane] = a0, sc[lane + 32] = a1;
+        sc[64 + lane] = s_beta[lane], sc[96 + lane] = s_beta[lane + 32];
     }
     float4 qv[8], kv[8], vv[8];
 #pragma unroll
@@ -168,17 +174,17 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
     const uint32_t tbase = *tmem_slot;
     const uint32_t lane_addr = tbase + ((uint32_t)((warp & 3) * 32) << 16);
     bool ok = true;
-    // rows -> f16: K and Q for the two products here, the scaled copies straight into the record
-    const float lgc = s_lg[C - 1];
+    // rows -> f16: K and Q for the two products here and into the record (the state kernel applies the per-token
+    // scalings g_j, beta_j g_j, g_63 / g_j on the other side of its products)
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const int j = warp * 8 + i, off = dnc_off4(j, lane);
-        const float gam = ex2(s_lg[j]), bet = s_beta[j], nbg = -bet * gam, kt = ex2(lgc - s_lg[j]);
-        *reinterpret_cast<uint2 *>(sm + P_K16 + off) = dnc_pack4(kv[i].x, kv[i].y, kv[i].z, kv[i].w);
-        *reinterpret_cast<uint2 *>(sm + P_Q16 + off) = dnc_pack4(qv[i].x, qv[i].y, qv[i].z, qv[i].w);
-        *reinterpret_cast<uint2 *>(rec + DNC_GQ + off) = dnc_pack4(qv[i].x * gam, qv[i].y * gam, qv[i].z * gam, qv[i].w * gam);
-        *reinterpret_cast<uint2 *>(rec + DNC_NBGK + off) = dnc_pack4(kv[i].x * nbg, kv[i].y * nbg, kv[i].z * nbg, kv[i].w * nbg);
-        *reinterpret_cast<uint2 *>(rec + DNC_KT + off) = dnc_pack4(kv[i].x * kt, kv[i].y * kt, kv[i].z * kt, kv[i].w * kt);
+        const float bet = s_beta[j];
+        const uint2 k2 = dnc_pack4(kv[i].x, kv[i].y, kv[i].z, kv[i].w), q2 = dnc_pack4(qv[i].x, qv[i].y, qv[i].z, qv[i].w);
+        *reinterpret_cast<uint2 *>(sm + P_K16 + off) = k2;
+        *reinterpret_cast<uint2 *>(sm + P_Q16 + off) = q2;
+        *reinterpret_cast<uint2 *>(rec + DNC_K + off) = k2;
+        *reinterpret_cast<uint2 *>(rec + DNC_Q + off) = q2;
         // beta v, fp32, per half of the dv columns: [half][token][64]
         *reinterpret_cast<float4 *>(rec + DNC_BV + (lane >> 4) * DNC_BVH + (j * AST + 4 * (lane & 15)) * 4) =
             make_float4(vv[i].x * bet, vv[i].y * bet, vv[i].z * bet, vv[i].w * bet);
@@ -341,14 +347,14 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
     const uint32_t lane_addr = tbase + ((uint32_t)((warp & 3) * 32) << 16);
     bool ok = true;
     uint32_t phase = 0;
-    // chunk n's operands -> stage n % 2 (one thread): the record's first 64 KB, the CTA's half of B V, the gates
+    // chunk n's operands -> stage n % 2 (one thread): K, Q, T', M (48 KB), the CTA's half of beta v, the gates
     auto load_chunk = [&](int n) {
         uint8_t *st = sm + (n & 1) * ST_BYTES;
         const uint8_t *rec = rec0 + (size_t)n * nv * DNC_ITEM;
-        mbar_expect_tx(bar_full + (n & 1), 65536 + DNC_BVH + 256);
-        bulk_g2s(st, rec, 65536, bar_full + (n & 1));
+        mbar_expect_tx(bar_full + (n & 1), 49152 + DNC_BVH + 512);
+        bulk_g2s(st, rec, 49152, bar_full + (n & 1));
         bulk_g2s(st + ST_BV, rec + DNC_BV + hv * DNC_BVH, DNC_BVH, bar_full + (n & 1));
-        bulk_g2s(st + ST_LG, rec + DNC_LG, 256, bar_full + (n & 1));
+        bulk_g2s(st + ST_SC, rec + DNC_SC, 512, bar_full + (n & 1));
     };
     if (tid == 0 && nch > 0) load_chunk(0);
 
@@ -401,7 +407,7 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
 #pragma unroll
             for (int x = 0; x < 32; x++) f[x] = __uint_as_float(r[x]);
             dnc_store_row32(sm + S_S16, trow, cb, f);
-            const float gc = ex2(reinterpret_cast<const float *>(sm + sb + ST_LG)[C - 1]);
+            const float gc = ex2(reinterpret_cast<const float *>(sm + sb + ST_SC)[C - 1]);
 #pragma unroll
             for (int x = 0; x < 32; x++) r[x] = __float_as_uint(f[x] * gc);
             tmem_st32(lane_addr + S_COL + cb * 32, r);
@@ -411,17 +417,19 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
         tc_fence_before();
         __syncthreads();
         DNC_T(1);
-        // ---- -(B G K) S0 -> Y and (G Q) S0 -> Z
+        // ---- K S0 -> Y and Q S0 -> Z1
         if (warp == 4 && (tc_fence_after(), elect_one())) {
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) umma_ss(tbase + Y_COL, d_k128(sb + DNC_NBGK, ks), d_mn(S_S16, ks, 0), id_kmn, ks > 0);
+            for (int ks = 0; ks < 8; ks++) umma_ss(tbase + Y_COL, d_k128(sb + DNC_K, ks), d_mn(S_S16, ks, 0), id_kmn, ks > 0);
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) umma_ss(tbase + Z_COL, d_k128(sb + DNC_GQ, ks), d_mn(S_S16, ks, 0), id_kmn, ks > 0);
+            for (int ks = 0; ks < 8; ks++) umma_ss(tbase + Z1_COL, d_k128(sb + DNC_Q, ks), d_mn(S_S16, ks, 0), id_kmn, ks > 0);
             umma_commit(bar);
         }
         wait_mma();
         DNC_T(2);
-        // ---- R = B V - (B G K) S0 -> f16: row j, columns 32 cb .. + 31 per thread
+        // ---- R = beta v - beta_j g_j (k_j S0) -> f16: row j, columns 32 cb .. + 31 per thread
+        const float *s_sc = reinterpret_cast<const float *>(sm + sb + ST_SC);
+        const float lgj = s_sc[trow & 63], nbg = -s_sc[64 + (trow & 63)] * ex2(lgj);
         if ((warp & 3) < 2) {
             uint32_t r[32];
             tmem_ld32(lane_addr + Y_COL + cb * 32, r);
@@ -431,8 +439,8 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
 #pragma unroll
             for (int x = 0; x < 32; x += 4) {
                 const float4 b = *reinterpret_cast<const float4 *>(s_bv + trow * AST + 32 * cb + x);
-                f[x] = b.x + __uint_as_float(r[x]), f[x + 1] = b.y + __uint_as_float(r[x + 1]);
-                f[x + 2] = b.z + __uint_as_float(r[x + 2]), f[x + 3] = b.w + __uint_as_float(r[x + 3]);
+                f[x] = fmaf(nbg, __uint_as_float(r[x]), b.x), f[x + 1] = fmaf(nbg, __uint_as_float(r[x + 1]), b.y);
+                f[x + 2] = fmaf(nbg, __uint_as_float(r[x + 2]), b.z), f[x + 3] = fmaf(nbg, __uint_as_float(r[x + 3]), b.w);
             }
             dnc_store_row32(sm + S_R16, trow, cb, f);
         }
@@ -448,7 +456,7 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
         }
         wait_mma();
         DNC_T(4);
-        // ---- U -> f16
+        // ---- U -> f16, plain (for M U) and with rows scaled by g_63 / g_j (for the state update)
         if ((warp & 3) < 2) {
             uint32_t r[32];
             tmem_ld32(lane_addr + Y_COL + cb * 32, r);
@@ -457,31 +465,40 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
 #pragma unroll
             for (int x = 0; x < 32; x++) f[x] = __uint_as_float(r[x]);
             dnc_store_row32(sm + S_U16, trow, cb, f);
+            const float kt = ex2(s_sc[C - 1] - lgj);
+#pragma unroll
+            for (int x = 0; x < 32; x++) f[x] *= kt;
+            dnc_store_row32(sm + S_UK16, trow, cb, f);
         }
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
         DNC_T(5);
-        // ---- O += M U -> Z;  S += Kt^T U
+        // ---- M U -> Z2;  S += K^T (scaled U)
         if (warp == 4 && (tc_fence_after(), elect_one())) {
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++) umma_ss(tbase + Z_COL, d_k64(sb + DNC_M, ks), d_mn(S_U16, ks, 0), id_kmn, 1);
+            for (int ks = 0; ks < 4; ks++) umma_ss(tbase + Z2_COL, d_k64(sb + DNC_M, ks), d_mn(S_U16, ks, 0), id_kmn, ks > 0);
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++) umma_ss(tbase + S_COL, d_mn(sb + DNC_KT, ks, 8192), d_mn(S_U16, ks, 0), id_mnmn, 1);
+            for (int ks = 0; ks < 4; ks++) umma_ss(tbase + S_COL, d_mn(sb + DNC_K, ks, 8192), d_mn(S_UK16, ks, 0), id_mnmn, 1);
             umma_commit(bar);
         }
         wait_mma();
         DNC_T(6);
-        // ---- O rows -> global memory: thread (row, 32-column block) writes its 128 bytes
+        // ---- O = g_i (q_i S0) + (M U)_i -> global memory: thread (row, 32-column block) writes its 128 bytes
         if ((warp & 3) < 2) {
-            uint32_t r[32];
-            tmem_ld32(lane_addr + Z_COL + cb * 32, r);
+            uint32_t r1[32], r2[32];
+            tmem_ld32(lane_addr + Z1_COL + cb * 32, r1);
+            tmem_ld32(lane_addr + Z2_COL + cb * 32, r2);
             tmem_wait_ld();
             if (trow < cnt) {
+                const float gi = ex2(lgj);
                 float4 *dst = reinterpret_cast<float4 *>(out + (size_t)(sg.row0 + c0 + trow) * vdim + (size_t)h * DV + (size_t)hv * HV + 32 * cb);
 #pragma unroll
                 for (int y = 0; y < 8; y++)
-                    dst[y] = ok ? make_float4(__uint_as_float(r[4 * y]), __uint_as_float(r[4 * y + 1]), __uint_as_float(r[4 * y + 2]), __uint_as_float(r[4 * y + 3]))
+                    dst[y] = ok ? make_float4(fmaf(gi, __uint_as_float(r1[4 * y]), __uint_as_float(r2[4 * y])),
+                                              fmaf(gi, __uint_as_float(r1[4 * y + 1]), __uint_as_float(r2[4 * y + 1])),
+                                              fmaf(gi, __uint_as_float(r1[4 * y + 2]), __uint_as_float(r2[4 * y + 2])),
+                                              fmaf(gi, __uint_as_float(r1[4 * y + 3]), __uint_as_float(r2[4 * y + 3])))
                                 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
         }
