@@ -261,15 +261,15 @@ def q8_leg(args, rank, local_rank, world):
 DN_LAYERS, DN_SEQ, DN_TOKENS, DN_HEADS, DN_DK = 18, 4, 8192, 16, 128
 
 
-def deltanet_leg(args, local_rank):
+def deltanet_leg(local_rank, steps, small=False):
     """Qwen3.5-style Gated DeltaNet: 18 linear layers, 4 sequences x 8,192 tokens, 16 heads, d_k = d_v = 128, post-prep rows
     resident on the device, prompt passes of 512 rows per sequence.  Reported: the chunked tensor-core form (the prefill
     path) as `value`, and the exact token recurrence (the decode path, bit-identical to the CPU code) beside it.
     flops = 8 d_k d_v per (token, head)."""
     import gwenedeg_b200 as g
     from gwenedeg_b200 import synth
-    layers = 2 if args.small else DN_LAYERS
-    tokens = 1024 if args.small else DN_TOKENS
+    layers = 2 if small else DN_LAYERS
+    tokens = 1024 if small else DN_TOKENS
     chunk = 512  # rows per sequence per pass
     c = g.Context(local_rank, n_lin=layers, dn_nk=DN_HEADS, dn_nv=DN_HEADS, dn_dk=DN_DK, dn_dv=DN_DK, max_rows=DN_SEQ * chunk)
     seqs = [c.new_seq(tokens, g.KV_F16) for _ in range(DN_SEQ)]
@@ -287,15 +287,15 @@ def deltanet_leg(args, local_rank):
             s.truncate(0)
 
     res = {}
-    for name, fn, steps in (("chunked", c.dn_chunk_dev, args.steps), ("exact", c.dn_rec_dev, max(1, min(args.steps, 2)))):
+    for name, fn, nst in (("chunked", c.dn_chunk_dev, steps), ("exact", c.dn_rec_dev, max(1, min(steps, 2)))):
         run(fn)
         c.sync()
         n0 = c.launch_count()
         c.timer_start()
-        for _ in range(steps):
+        for _ in range(nst):
             run(fn)
         ms = c.timer_stop()
-        res[name] = (DN_SEQ * tokens * steps / (ms * 1e-3), ms / steps, (c.launch_count() - n0) // steps)
+        res[name] = (DN_SEQ * tokens * nst / (ms * 1e-3), ms / nst, (c.launch_count() - n0) // nst)
     tok_s, ms_step, launches = res["chunked"]
     flops_tok = 8.0 * DN_DK * DN_DK * DN_HEADS * layers
     try:
@@ -304,16 +304,16 @@ def deltanet_leg(args, local_rank):
     except Exception:
         peak, how = 1590.0, "fallback"
     tf = flops_tok * tok_s / 1e12
-    print(json.dumps({"metric": "Qwen3.5 Gated DeltaNet: tokens/s (all linear layers, prompt passes)", "value": tok_s, "unit": "tokens/s",
-                      "n_gpus": 1, "steps": args.steps, "warmup": 1, "ms_per_step": ms_step, "higher_is_better": True, "dtype": "f16 operands, f32 state",
+    c.close()
+    return {"metric": "Qwen3.5 Gated DeltaNet: tokens/s (all linear layers, prompt passes)", "value": tok_s, "unit": "tokens/s",
+                      "n_gpus": 1, "steps": steps, "warmup": 1, "ms_per_step": ms_step, "higher_is_better": True, "dtype": "f16 operands, f32 state",
                       "data": "synthetic", "gpu_launches": launches,
                       "config": {"workload": "qwen3.5-deltanet-4x8192", "layers": layers, "tokens": tokens, "heads": DN_HEADS, "rows_per_pass": DN_SEQ * chunk},
                       "form": "chunked (64-token WY / UT) on tcgen05", "tflops": tf,
                       "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
                                    "peak_source": how, "kernel": "dn_chunk_kernel", "flops": "8 dk dv per (token, head): the recurrence's count"},
                       "exact_recurrence": {"tokens_per_s": res["exact"][0], "ms_per_step": res["exact"][1], "tflops": flops_tok * res["exact"][0] / 1e12,
-                                           "form": "token by token, bit-identical to the CPU code"}}), flush=True)
-    c.close()
+                                           "form": "token by token, bit-identical to the CPU code"}}
 
 
 def run_reference(args, rank, world):
@@ -453,12 +453,17 @@ def run_ours(args, rank, local_rank, world):
     achieved = reduce_sum(achieved) / world  # mean over ranks of the per-GPU figure
 
     c.close()
-    prefill = None
+    prefill = deltanet = None
     if rank == 0 and not args.small:
         try:
             prefill = prefill_leg(local_rank, max(2, min(args.steps, 5)))
         except Exception as e:
             prefill = {"error": repr(e)}
+        try:
+            d = deltanet_leg(local_rank, 1)
+            deltanet = {k: d[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "form", "tflops", "roofline", "exact_recurrence")}
+        except Exception as e:
+            deltanet = {"error": repr(e)}
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu:
@@ -487,6 +492,7 @@ def run_ours(args, rank, local_rank, world):
                          "algorithmic_bytes_per_launch_rank0": bytes_per_launch, "launches_timed": part_n},
             "cpu_baseline": cpu,
             "prefill": prefill,
+            "deltanet": deltanet,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -525,7 +531,7 @@ def main():
         return
     if args.workload == "deltanet":
         if rank == 0:
-            deltanet_leg(args, local_rank)
+            print(json.dumps(deltanet_leg(local_rank, args.steps, small=args.small)), flush=True)
         return
     if args.workload == "prefill":
         if rank == 0:

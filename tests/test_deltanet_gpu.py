@@ -133,3 +133,34 @@ def test_chunked_form_matches_cpu(checker, nk, nv):
     assert_close(got3, d.rec(st_a, nxt, False), "decode row after chunked prefill")
     assert not sa.read_state(0).any()
     c.close()
+
+
+def test_chunked_form_ragged_segments(checker):
+    """Segments of 1, 63, 64, 65 and 129 rows in one pass (chunks that are one token, one short, exact, one over), each
+    from position 0, then all of them continued by 7 more rows: outputs and states against the token recurrence."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    from oracle import gwo
+    nk, nv, dk, dv = 2, 4, 128, 128
+    lens = [1, 63, 64, 65, 129]
+    c = g.Context(0, n_lin=1, dn_nk=nk, dn_nv=nv, dn_dk=dk, dn_dv=dv, max_rows=512)
+    d = gwo.DeltaNet(checker, nk, nv, dk, dv)
+    seqs = [c.new_seq(512, 2) for _ in lens]
+    states = [d.new_state() for _ in lens]
+    rows = [synth.deltanet_rows(20 + i, n + 7, nk, nv, dk, dv) for i, n in enumerate(lens)]
+    c.pass_begin([(s, 0, n) for s, n in zip(seqs, lens)])
+    got = c.dn_chunk(0, np.concatenate([r[:n] for r, n in zip(rows, lens)]))
+    c.pass_end()
+    at = 0
+    for i, n in enumerate(lens):
+        want = d.rec(states[i], rows[i][:n], True)
+        assert_close(got[at:at + n], want, f"segment of {n} rows")
+        at += n
+    c.pass_begin([(s, n, 7) for s, n in zip(seqs, lens)])
+    got = c.dn_chunk(0, np.concatenate([r[n:] for r, n in zip(rows, lens)]))
+    c.pass_end()
+    for i, n in enumerate(lens):
+        want = d.rec(states[i], rows[i][n:], False)
+        assert_close(got[7 * i:7 * i + 7], want, f"segment of {n} rows, continued")
+        assert_close(seqs[i].read_state(0)[d.conv_floats:].reshape(-1, 128), states[i][d.conv_floats:].reshape(-1, 128), f"state after {n} + 7 rows")
+    c.close()
