@@ -162,6 +162,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
     constexpr bool QUANT = kv_quant(KVT);
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_wait();
+    pdl_launch_dependents();
 
     uint8_t *buf = smem;
     float *qs = reinterpret_cast<float *>(smem + C::BUF);  // q [NGRP][HD][NV] while scoring ...
@@ -518,6 +520,8 @@ __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const Pass
                                                                       int gated, float *__restrict__ out, int split_len, int fixed_stride) {
     constexpr int CH = 8192 / HD;  // partials per chunk: 32 KB of shared memory
     const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, i = tid % HD, grp = tid / HD;
+    pdl_wait();
+    pdl_launch_dependents();
     const PassRow row = rows[r];
     const int nb = (row.np + split_len - 1) / split_len;
     const size_t pst = RQ_PSTRIDE(HD);
@@ -606,6 +610,8 @@ __global__ void __launch_bounds__(32 * COMBINE_ROWS_WARPS) attn_combine_rows_ker
                                                                                  int fixed_stride) {
     static_assert(HD == 128, "a lane holds 4 of the row's 128 dims");
     const int wi = blockIdx.x * COMBINE_ROWS_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_launch_dependents();
     if (wi >= nrows * n_heads) return;
     const int r = wi / n_heads, h = wi % n_heads;
     const int nb = (rows[r].np + split_len - 1) / split_len;
@@ -675,9 +681,8 @@ static cudaError_t launch_one(const AttnPartArgs &a, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    kern<<<dim3(a.total_blocks, a.n_kv), DEC_THREADS, smem, stream>>>(a.rows, a.nrows, a.layer, a.n_kv, a.G, a.q, a.qh, a.n_heads,
-                                                                   a.scale, a.part, a.err);
-    return cudaGetLastError();
+    return launch_pdl(kern, dim3(a.total_blocks, a.n_kv), dim3(DEC_THREADS), smem, stream, a.rows, a.nrows, a.layer, a.n_kv, a.G, a.q, a.qh, a.n_heads,
+                      a.scale, a.part, a.err);
 }
 
 template <int KVT, int HD>

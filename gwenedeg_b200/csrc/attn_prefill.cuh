@@ -106,6 +106,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
     const long long pf_t0 = clock64();
     const unsigned long long pf_g0 = pf_now();
 #endif
+    pdl_wait();
+    pdl_launch_dependents();
     const PfWork w = work[blockIdx.x];
     const int g = blockIdx.y;
     const PassRow r0 = rows[w.row0];
@@ -443,9 +445,8 @@ cudaError_t launch_attn_prefill(const AttnPrefillArgs &a, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    attn_prefill_kernel<<<dim3(a.n_work, a.n_kv), PF_THREADS, PF_SMEM, stream>>>(a.work, a.rows, a.maps, a.layer, a.n_kv, a.G, a.q, a.qh,
-                                                                               a.n_heads, a.scale, a.max_splits, a.part, a.err);
-    return cudaGetLastError();
+    return launch_pdl(attn_prefill_kernel, dim3(a.n_work, a.n_kv), dim3(PF_THREADS), PF_SMEM, stream, a.work, a.rows, a.maps, a.layer, a.n_kv, a.G, a.q,
+                      a.qh, a.n_heads, a.scale, a.max_splits, a.part, a.err);
 }
 #endif  // RQ_ATTN_PREFILL_INSTANTIATE
 

@@ -120,6 +120,28 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
                  : "memory");
 }
 
+// ---- programmatic dependent launch: a kernel launched with launch_pdl may be scheduled while the kernel before it in
+// the stream still runs; it must call pdl_wait() before it touches global memory (the wait returns once the earlier
+// kernel has completed and its writes are visible; in a normal launch it returns at once).  pdl_launch_dependents() lets
+// the next such kernel be scheduled as soon as every CTA of this one has started.  What is saved is the launch latency
+// between the kernels of one layer, a few microseconds each.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // One segment of the open pass as the DeltaNet kernels see it.
 struct DnSeg {
     float *state;   // the segment's sequence: state of linear layer 0 (conv part included)

@@ -107,6 +107,8 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
                                                                   int lw, uint8_t *__restrict__ work, int *err) {
     using namespace dnc;
     constexpr int DK = 128, DV = 128, C = DNC_C;
+    pdl_wait();
+    pdl_launch_dependents();
     const DnSeg sg = segs[blockIdx.z];
     const int c0 = blockIdx.x * C;
     if (c0 >= sg.n) return;
@@ -322,6 +324,8 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + S_SLOT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_wait();
+    pdl_launch_dependents();
     const int h = blockIdx.x >> 1, hv = blockIdx.x & 1;  // value head, which half of its dv columns
     const int trow = (warp & 3) * 32 + lane, cb = warp >> 2;  // this thread's TMEM lane and its 32-column block of a 64-column tile
     const DnSeg sg = segs[blockIdx.y];
@@ -534,9 +538,11 @@ cudaError_t launch_dn_chunk(const DnChunkArgs &a, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    dn_chunk_prep_kernel<<<dim3(a.max_chunks, a.nv, a.nseg), DNC_THREADS, dnc::P_SMEM, stream>>>(a.segs, a.nk, a.nv, a.rows, a.lw, a.work, a.err);
-    dn_chunk_state_kernel<<<dim3(2 * a.nv, a.nseg), DNC_THREADS, dnc::S_SMEM, stream>>>(a.segs, a.lin_layer, a.nv, a.conv_floats, a.work, a.out, a.err);
-    return cudaGetLastError();
+    cudaError_t e = launch_pdl(dn_chunk_prep_kernel, dim3(a.max_chunks, a.nv, a.nseg), dim3(DNC_THREADS), dnc::P_SMEM, stream, a.segs, a.nk, a.nv, a.rows,
+                               a.lw, a.work, a.err);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(dn_chunk_state_kernel, dim3(2 * a.nv, a.nseg), dim3(DNC_THREADS), dnc::S_SMEM, stream, a.segs, a.lin_layer, a.nv, a.conv_floats,
+                      a.work, a.out, a.err);
 }
 #endif  // RQ_DN_CHUNK_INSTANTIATE
 

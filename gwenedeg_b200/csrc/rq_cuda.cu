@@ -641,9 +641,10 @@ static int launch_combine(RqCuda *c, const float *q, float *out, const float *pa
     const int hd = c->m.head_dim;
     dim3 grid(c->nrows, c->n_heads);
     const bool quant = kv_quant(c->pass_kvt);
+    cudaError_t ce = cudaSuccess;
 #define COMBINE(HD_)                                                                                                          \
-    if (quant) attn_combine_kernel<HD_, true><<<grid, COMBINE_NG * HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride); \
-    else attn_combine_kernel<HD_, false><<<grid, COMBINE_NG * HD_, 0, c->stream>>>(c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride);
+    if (quant) ce = launch_pdl(attn_combine_kernel<HD_, true>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride); \
+    else ce = launch_pdl(attn_combine_kernel<HD_, false>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride);
     switch (hd) {
         case 64: COMBINE(64) break;
         case 128: COMBINE(128) break;
@@ -651,7 +652,7 @@ static int launch_combine(RqCuda *c, const float *q, float *out, const float *pa
     }
 #undef COMBINE
     c->launches++;
-    CU(c, cudaGetLastError());
+    CU(c, ce);
     return RQ_CUDA_OK;
 }
 
@@ -783,10 +784,9 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     c->launches++;
     // (this path is head_dim 128 over a 16-bit cache: a warp per output row merges its few partials)
     const int nout = c->nrows * c->n_heads;
-    attn_combine_rows_kernel<128><<<(nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS, 32 * COMBINE_ROWS_WARPS, 0, c->stream>>>(
-        c->d_rows, c->nrows, c->n_heads, c->d_part, q, c->qh, c->m.gated, out, PF_SPLIT, c->pf_max_splits);
+    CU(c, launch_pdl(attn_combine_rows_kernel<128>, dim3((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), dim3(32 * COMBINE_ROWS_WARPS), 0, c->stream,
+                     c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh, c->m.gated, out, PF_SPLIT, c->pf_max_splits));
     c->launches++;
-    CU(c, cudaGetLastError());
     return RQ_CUDA_OK;
 }
 
