@@ -87,8 +87,14 @@ __device__ __forceinline__ void load_k(const uint8_t *kt, int i, int j0, const f
         if constexpr (KF == KV_Q8) {
             if constexpr (PPT == 4) w = *reinterpret_cast<const uint32_t *>(kt + (size_t)i * 16 + j0);
             else w = *reinterpret_cast<const uint16_t *>(kt + (size_t)i * 16 + j0);
+            // (packed fp32x2 subtract and multiply: two levels per instruction, each lane rounded as the scalar form)
+            w ^= 0x80808080u;
 #pragma unroll
-            for (int p = 0; p < PPT; p++) k[p] = s8_to_f32(w ^ 0x80808080u, p) * d[p];
+            for (int p = 0; p < PPT; p += 2) {
+                float2 f = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 | p)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 | (p + 1))));
+                f = __fmul2_rn(__fadd2_rn(f, make_float2(-8388736.0f, -8388736.0f)), make_float2(d[p], d[p + 1]));
+                k[p] = f.x, k[p + 1] = f.y;
+            }
         } else {  // q4: byte [dim pair][position], low nibble dim 2p, high nibble dim 2p + 1
             if constexpr (PPT == 4) w = *reinterpret_cast<const uint32_t *>(kt + (size_t)(i >> 1) * 16 + j0);
             else w = *reinterpret_cast<const uint16_t *>(kt + (size_t)(i >> 1) * 16 + j0);
@@ -136,7 +142,9 @@ __device__ __forceinline__ void load_v(const uint8_t *vt, int j, int i0, float *
             vv[0] = s8_to_f32((uint32_t)(uint8_t)p[0] ^ 0x80u, 0) * d;
         } else if constexpr (DPT == 2) {
             uint32_t w = (uint32_t)*reinterpret_cast<const uint16_t *>(p) ^ 0x8080u;
-            vv[0] = s8_to_f32(w, 0) * d; vv[1] = s8_to_f32(w, 1) * d;
+            float2 f = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7541)));
+            f = __fmul2_rn(__fadd2_rn(f, make_float2(-8388736.0f, -8388736.0f)), make_float2(d, d));
+            vv[0] = f.x, vv[1] = f.y;
         } else {
             uint32_t w = *reinterpret_cast<const uint32_t *>(p) ^ 0x80808080u;
 #pragma unroll
