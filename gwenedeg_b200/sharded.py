@@ -47,8 +47,11 @@ class HeadShardedContext:
         self.ctx = Context(device, n_attn=n_attn, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, gated=gated,
                            kv_head0=self.kv0, kv_heads_local=self.kv_local, max_rows=max_rows)
         self.device = torch.device("cuda", device)
-        # the library's kernels and NCCL's run on one stream, in order
-        self.ctx.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+        # the library's kernels, the torch copies around them and NCCL's collectives are ordered on one stream of this
+        # object (torch's default stream has the null handle, which the library reads as "my own stream": passing it
+        # would leave the two unordered)
+        self.stream = torch.cuda.Stream(device=self.device)
+        self.ctx.set_stream(self.stream.cuda_stream)
 
     def local_q(self, q_full):
         """The query heads of this rank's KV heads: q_full [rows][n_heads][qh] (torch, on this device)."""
@@ -63,15 +66,23 @@ class HeadShardedContext:
         torch = self.torch
         import torch.distributed as dist
         rows = q_full.shape[0]
-        ql = self.local_q(q_full)
-        out_l = torch.empty((rows, self.heads_local, self.hd), dtype=torch.float32, device=self.device)
-        self.ctx.attn_decode_dev(layer, ql.data_ptr(), out_l.data_ptr())
-        if self.world == 1:
-            return out_l
-        gathered = torch.empty((self.world, rows, self.heads_local, self.hd), dtype=torch.float32, device=self.device)
-        dist.all_gather_into_tensor(gathered, out_l, group=self.group)
-        # rank-major -> head order (contiguous groups: a plain transpose)
-        return gathered.permute(1, 0, 2, 3).reshape(rows, self.n_heads, self.hd)
+        caller = torch.cuda.current_stream(self.device)
+        self.stream.wait_stream(caller)  # q_full was produced on the caller's stream
+        with torch.cuda.stream(self.stream):
+            ql = self.local_q(q_full)
+            out_l = torch.empty((rows, self.heads_local, self.hd), dtype=torch.float32, device=self.device)
+            self.ctx.attn_decode_dev(layer, ql.data_ptr(), out_l.data_ptr())
+            if self.world == 1:
+                res = out_l
+            else:
+                gathered = torch.empty((self.world, rows, self.heads_local, self.hd), dtype=torch.float32, device=self.device)
+                dist.all_gather_into_tensor(gathered, out_l, group=self.group)
+                # rank-major -> head order (contiguous groups: a plain transpose)
+                res = gathered.permute(1, 0, 2, 3).reshape(rows, self.n_heads, self.hd)
+            for t in (q_full, ql, out_l, res):
+                t.record_stream(self.stream)
+        caller.wait_stream(self.stream)  # the result is used on the caller's stream
+        return res
 
     def close(self):
         self.ctx.close()
