@@ -65,18 +65,6 @@ struct AttnPrefillArgs {
 cudaError_t launch_attn_prefill(const AttnPrefillArgs &a, cudaStream_t stream);
 
 #ifdef RQ_ATTN_PREFILL_INSTANTIATE
-#ifdef RQ_PF_TRACE
-__device__ long long pf_trace[64];  // experiments only: event times of CTA (0, 0), in clock cycles from its start
-__device__ unsigned long long pf_span[3 * 2048];  // per CTA: start and end (globaltimer, ns), SM id
-#define PF_T(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 64) pf_trace[i] = clock64() - pf_t0; } while (0)
-__device__ __forceinline__ unsigned long long pf_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#else
-#define PF_T(i) do { } while (0)
-#endif
 
 constexpr int PF_SMEM = 6 * 32768 + 1024 + 256 + 2048;  // Q | K x 3 stages | V x 2 stages (32 KB each), slack, barriers, (m, l) exchange
 
@@ -102,10 +90,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
     float *sml = reinterpret_cast<float *>(sm + 196608 + 256);  // [stream][vector][m, l]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef RQ_PF_TRACE
-    const long long pf_t0 = clock64();
-    const unsigned long long pf_g0 = pf_now();
-#endif
     pdl_wait();
     pdl_launch_dependents();
     const PfWork w = work[blockIdx.x];
@@ -143,14 +127,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
         for (int i = 0; i < 2; i++) tma_load_2d(dst + i * 16384, mv, i * 64, y, bar);
     };
 
-    if (tid == 0) PF_T(60);  // work item and row fetched
     if (tid == 0) {
         for (int i = 0; i < 12; i++) mbar_init(bars + i, i == 6 ? 256 : 1);
         for (int i = 0; i < 4; i++) mbar_init(bar_p + i, 128);
         mbar_fence_init();
     }
     __syncthreads();
-    if (tid == 0) PF_T(61);  // barriers ready
     if (warp == 10) {
         if (lane == 0) {  // the first K / V blocks start loading while the other warps convert Q
             load_k(0);
@@ -185,14 +167,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
                 make_uint2(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1));
         }
     }
-    if (tid == 0) PF_T(62);  // Q converted
     fence_proxy_async();  // Q was written by ordinary stores and will be read by the tensor core
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tbase = *tmem_slot;
     bool ok = true;
-    if (tid == 0) PF_T(0);  // prologue done (Q in shared memory, TMEM allocated)
 
     if (warp >= 8) {
         // ---- three warps: P V issue, S issue, TMA loads.  The softmax threads free S as soon as they hold their scores
@@ -211,7 +191,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
                 ok = mbar_wait_sleepy(bar_v + ph, ph2, err, 14) && ok;
                 ok = mbar_wait_sleepy(bar_p + ph, ph2, err, 13) && ok;  // P(j) of stream 0 is in TMEM
                 tc_fence_after();
-                if (lane == 0 && j < 8) PF_T(3 + 4 * j);
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++) umma_ts(tbase + O_COL, pa + ks * 8, b0 + (uint64_t)(ks * 128), idesc, (j > 0) | (ks > 0));
@@ -226,7 +205,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
                     umma_commit(bar_o + ph);  // both streams' P (j) were read, V (j) too
                 }
                 __syncwarp();
-                if (lane == 0 && j < 8) PF_T(4 + 4 * j);
             }
         } else if (warp == 9) {
             // S (j) = Q K (j)^T, once every softmax thread has read S (j - 1)
@@ -234,7 +212,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
             for (int j = 0; j < nblk; j++) {
                 const uint64_t b0 = dk + (uint64_t)((j % 3) * (32768 >> 4));
                 ok = mbar_wait_sleepy(bar_k + j % 3, (j / 3) & 1, err, 11) && ok;
-                if (lane == 0 && j == 0) PF_T(63);
                 if (j >= 1) ok = mbar_wait_sleepy(bar_sfree, (j - 1) & 1, err, 12) && ok;
                 tc_fence_after();
                 if (elect_one()) {
@@ -278,7 +255,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
             const int t0 = s0 + j * PF_BN + h * 64;  // first key of this thread's half of the block
             if (!s_seen) ok = mbar_wait_bounded(bar_s, j & 1, err, 21) && ok;
             tc_fence_after();
-            if (t == 0 && j < 8 && h == 0) PF_T(1 + 4 * j);  // S(j) ready
             uint32_t r[2][32], pk[32];
             tmem_ld32(lane_addr + h * 64, r[0]);
             tmem_ld32(lane_addr + h * 64 + 32, r[1]);
@@ -287,7 +263,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(bar_sfree);  // the scores are in registers: S (j + 1) may be computed
-            if (t == 0 && j == 3) PF_T(48 + 8 * h);
             const bool need_mask = s0 + (j + 1) * PF_BN > np_min;  // (uniform over the CTA: only the blocks on the diagonal)
             if (need_mask) {
 #pragma unroll
@@ -362,24 +337,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
                 sweep(m_used == -INFINITY ? 0.0f : m_used * c);
             }
             l += lsum;
-            if (t == 0 && j == 3) PF_T(50 + 8 * h);
             if (!o_seen) ok = mbar_wait_bounded(bar_o + (j & 1), ((j - 2) >> 1) & 1, err, 24) && ok;
             tc_fence_after();
             tmem_st32(lane_addr + P_COL + (j & 1) * 64 + h * 32, pk);
             s_seen = j + 1 < nblk && mbar_try_wait(bar_s, (j + 1) & 1);  // (answered while the store completes)
             tmem_wait_st();
-            if (t == 0 && j == 3) PF_T(51 + 8 * h);
             tc_fence_before();
             mbar_arrive(bar_p + 2 * h + (j & 1));
-            if (lane == 0 && j == 3 && h == 0) PF_T(52 + warp);
-            if (t == 0 && j < 8 && h == 0) PF_T(2 + 4 * j);  // softmax(j) done
         }
         // ---- epilogue: the two streams merge into the partial result (o unnormalised, m in scaled-score units, l)
         sml[(h * 128 + t) * 2] = m_used;
         sml[(h * 128 + t) * 2 + 1] = l;
         ok = mbar_wait_bounded(bar_o + ((nblk - 1) & 1), ((nblk - 1) >> 1) & 1, err, 22) && ok;
         tc_fence_after();
-        if (t == 0) PF_T(40 + 4 * h);
         asm volatile("bar.sync 1, 256;" ::: "memory");  // (the softmax warps only) every MMA of the CTA is complete
         const float m_other = sml[((h ^ 1) * 128 + t) * 2], l_other = sml[((h ^ 1) * 128 + t) * 2 + 1];
         const float M = fmaxf(m_used, m_other);
@@ -404,7 +374,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
                 so[(size_t)t * OST + HD] = M * scale;
                 so[(size_t)t * OST + HD + 1] = c_own * l + c_other * l_other;
             }
-            if (t == 0) PF_T(42 + 4 * h);
             asm volatile("bar.sync 1, 256;" ::: "memory");
             int rl2 = (warp * 16) / G, x = (warp * 16) % G - 1;
 #pragma unroll 8
@@ -420,19 +389,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
             }
         }
     }
-    if (tid == 0) PF_T(41);  // partial written
     tc_fence_before();
     __syncthreads();
-#ifdef RQ_PF_TRACE
-    if (tid == 0) {
-        const int ci = blockIdx.y * gridDim.x + blockIdx.x;
-        if (ci < 2048) {
-            unsigned smid;
-            asm("mov.u32 %0, %smid;" : "=r"(smid));
-            pf_span[3 * ci] = pf_g0, pf_span[3 * ci + 1] = pf_now(), pf_span[3 * ci + 2] = smid;
-        }
-    }
-#endif
     if (warp == 10) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(TM_COLS));
 }
 

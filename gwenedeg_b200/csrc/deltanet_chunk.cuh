@@ -93,14 +93,6 @@ __device__ __forceinline__ void dnc_store_row32(uint8_t *buf, int row, int cb, c
     }
 }
 
-#ifdef RQ_DNC_TRACE
-__device__ long long dnc_trace[32];  // experiments only: event times of CTA (0, 0), third chunk, in clock cycles
-#define DNC_T(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && n == 2 && tid == 0) dnc_trace[i] = clock64() - dnc_t0; } while (0)
-#define DNP_T(i) do { if (blockIdx.x == 2 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) dnc_trace[16 + i] = clock64() - dnp_t0; } while (0)
-#else
-#define DNC_T(i) do { } while (0)
-#define DNP_T(i) do { } while (0)
-#endif
 
 // grid: (chunk of the segment, value head, segment)
 __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg *__restrict__ segs, int nk, int nv, const float *__restrict__ rows,
@@ -120,9 +112,6 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + P_SLOT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef RQ_DNC_TRACE
-    const long long dnp_t0 = clock64();
-#endif
     const int h = blockIdx.y, cnt = min(C, sg.n - c0);
     const int trow = (warp & 3) * 32 + lane, cb = warp >> 2;
     const int conv_dim = 2 * nk * DK + nv * DV, vdim = nv * DV;
@@ -168,11 +157,9 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
             vv[i] = __ldg(reinterpret_cast<const float4 *>(r + ov) + lane);
         }
     }
-    DNP_T(0);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    DNP_T(1);
     const uint32_t tbase = *tmem_slot;
     const uint32_t lane_addr = tbase + ((uint32_t)((warp & 3) * 32) << 16);
     bool ok = true;
@@ -191,11 +178,9 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
         *reinterpret_cast<float4 *>(rec + DNC_BV + (lane >> 4) * DNC_BVH + (j * AST + 4 * (lane & 15)) * 4) =
             make_float4(vv[i].x * bet, vv[i].y * bet, vv[i].z * bet, vv[i].w * bet);
     }
-    DNP_T(2);
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
-    DNP_T(3);
     // K K^T and Q K^T (M 128, N 64, K 128)
     if (warp == 4 && (tc_fence_after(), elect_one())) {
         const uint32_t sbase = smem_u32(sm);
@@ -209,7 +194,6 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
     }
     ok = mbar_wait_bounded(bar, 0, err, 31) && ok;
     tc_fence_after();
-    DNP_T(4);
     // A (fp32, strictly lower) and M (f16, lower with the diagonal): row i, columns 32 cb .. + 31 per thread
     if ((warp & 3) < 2) {
         uint32_t g[32], mq[32];
@@ -230,10 +214,8 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
         for (int x = 0; x < 32; x += 4) *reinterpret_cast<float4 *>(s_a + i * AST + 32 * cb + x) = make_float4(av[x], av[x + 1], av[x + 2], av[x + 3]);
         dnc_store_row32(rec + DNC_M, i, cb, mv);
     }
-    DNP_T(5);
     tc_fence_before();
     __syncthreads();
-    DNP_T(6);
     // T' = (I + A)^-1 = [[X11, 0], [-X22 A21 X11, X22]] with 32 x 32 blocks: the two diagonal blocks by forward
     // substitution (a column per thread: x_r = [r == c] - sum_{q<r} A_rq x_q), then the two products on all threads
     if (tid < 64) {
@@ -255,9 +237,7 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
             s_x[(32 * b + r) * AST + 32 * b + lane] = x[r];
         }
     }
-    DNP_T(7);
     __syncthreads();
-    DNP_T(8);
     {
         const int r = tid >> 3, c4 = (tid & 7) * 4;
         {  // P = A21 X11
@@ -276,7 +256,6 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
             *reinterpret_cast<float4 *>(s_p + r * AST + c4) = p;
         }
         __syncthreads();
-        DNP_T(9);
         {  // X21 = -X22 P
             float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             const float *xrow = s_x + (32 + r) * AST + 32;
@@ -293,7 +272,6 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
             *reinterpret_cast<float4 *>(s_x + (32 + r) * AST + c4) = v;
         }
         __syncthreads();
-        DNP_T(10);
         // -> f16, K-major rows of 64: thread (row, 16-column block); the upper right block is zero
         const int row = tid >> 2, jb = tid & 3;
         float f[16];
@@ -307,7 +285,6 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
             *reinterpret_cast<uint4 *>(rec + DNC_T + row * 128 + (((2 * jb + q) ^ (row & 7)) << 4)) = w;
         }
     }
-    DNP_T(11);
     tc_fence_before();
     __syncthreads();
     if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(128));
@@ -394,14 +371,10 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
 
     for (int n = 0; n < nch; n++) {
         const int c0 = n * C, cnt = min(C, sg.n - c0), sb = (n & 1) * ST_BYTES;
-#ifdef RQ_DNC_TRACE
-        const long long dnc_t0 = clock64();
-#endif
         // the next chunk's operands start loading (its stage was last read by chunk n - 1, whose products are complete
         // and whose B V rows and gates every thread read before the barrier at the end of that chunk)
         if (tid == 0 && n + 1 < nch) load_chunk(n + 1);
         ok = mbar_wait_bounded(bar_full + (n & 1), (n >> 1) & 1, err, 33) && ok;
-        DNC_T(0);
         {
             // S (the previous chunk's result) -> its f16 copy, the B operand of this chunk's S0 products; S *= g_63
             uint32_t r[32];
@@ -420,7 +393,6 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        DNC_T(1);
         // ---- K S0 -> Y and Q S0 -> Z1
         if (warp == 4 && (tc_fence_after(), elect_one())) {
 #pragma unroll
@@ -430,7 +402,6 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
             umma_commit(bar);
         }
         wait_mma();
-        DNC_T(2);
         // ---- R = beta v - beta_j g_j (k_j S0) -> f16: row j, columns 32 cb .. + 31 per thread
         const float *s_sc = reinterpret_cast<const float *>(sm + sb + ST_SC);
         const float lgj = s_sc[trow & 63], nbg = -s_sc[64 + (trow & 63)] * ex2(lgj);
@@ -451,7 +422,6 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        DNC_T(3);
         // ---- U = T' R -> Y
         if (warp == 4 && (tc_fence_after(), elect_one())) {
 #pragma unroll
@@ -459,7 +429,6 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
             umma_commit(bar);
         }
         wait_mma();
-        DNC_T(4);
         // ---- U -> f16, plain (for M U) and with rows scaled by g_63 / g_j (for the state update)
         if ((warp & 3) < 2) {
             uint32_t r[32];
@@ -477,7 +446,6 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        DNC_T(5);
         // ---- M U -> Z2;  S += K^T (scaled U)
         if (warp == 4 && (tc_fence_after(), elect_one())) {
 #pragma unroll
@@ -487,7 +455,6 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
             umma_commit(bar);
         }
         wait_mma();
-        DNC_T(6);
         // ---- O = g_i (q_i S0) + (M U)_i -> global memory: thread (row, 32-column block) writes its 128 bytes
         if ((warp & 3) < 2) {
             uint32_t r1[32], r2[32];
@@ -506,11 +473,9 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
                                 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
         }
-        DNC_T(7);
         fence_proxy_async();  // (this chunk's stage is overwritten by bulk copies next)
         tc_fence_before();
         __syncthreads();      // (this chunk's stage and the O columns are free again)
-        DNC_T(8);
     }
     // the state back to global memory
     tc_fence_after();

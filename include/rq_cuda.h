@@ -68,13 +68,17 @@ typedef struct {
 } RqCudaSegment;
 
 /* ---- context (rq_ctx_new / rq_ctx_free / rq_ctx_error, runq.h:317-335) ------------------------------------ */
+/* max_rows: the most rows (and segments) a pass may hold, 1 .. 16384 (the reference's RQ_BATCH_MAX is 512) */
 int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ctx);
 void rq_cuda_free(RqCuda *ctx);
 const char *rq_cuda_error(const RqCuda *ctx);
 int rq_cuda_device_count(void);
 /* block until everything this context launched is complete; reports a device-side wait that expired as RQ_CUDA_ERR_STATE */
 int rq_cuda_sync(RqCuda *ctx);
-/* run this context's work on a caller-owned stream (a cudaStream_t; NULL: back to the context's own) */
+/* run this context's work on a caller-owned stream (a cudaStream_t; NULL: back to the context's own, a non-blocking stream:
+ * it is not ordered with the legacy default stream, whose handle is NULL as well).  The attention and DeltaNet kernels are
+ * launched with programmatic stream serialization: each waits for the kernel before it in the stream before it touches
+ * global memory, so ordinary stream order is all a caller needs. */
 int rq_cuda_set_stream(RqCuda *ctx, void *cuda_stream);
 
 /* ---- sequences (rq_seq_new :148, rq_seq_free :192, rq_seq_truncate :409, rq_seq_copy :553 of forward.c) ---- */
