@@ -57,7 +57,7 @@ def main():
         k, v, q = attn_inputs(seed, n_heads, n_kv, hd, gated)
         port = gwo.load("port")
         kl, vl = port.new_cache(kvt, 512, n_kv, hd)
-        port.kv_store(kvt, kl, vl, 0, k, v, n_kv, hd)  # the definition's bytes (IEEE division)
+        port.kv_store(kvt, kl, vl, 0, k, v, n_kv, hd)  # the definition's bytes (IEEE division: the reference's -Ofast builds round exact ties differently)
         out = ref.attention(kvt, kl, vl, n_kv, n_heads, hd, q, CONTEXTS, gated=gated, split=0)
         for o in (nat.attention(kvt, kl, vl, n_kv, n_heads, hd, q, CONTEXTS, gated=gated, split=1),
                   ref.attention(kvt, kl, vl, n_kv, n_heads, hd, q, CONTEXTS, gated=gated, split=1)):
