@@ -3,7 +3,7 @@ order), the chunked tensor-core form within the tolerance (max-abs 2e-3, relativ
 import numpy as np
 import pytest
 
-from tests.helpers import assert_close, bit_equal
+from tests.helpers import MAX_ABS, REL_L2, assert_close, bit_equal, errors
 
 pytestmark = pytest.mark.gpu
 
@@ -163,4 +163,45 @@ def test_chunked_form_ragged_segments(checker):
         want = d.rec(states[i], rows[i][n:], False)
         assert_close(got[7 * i:7 * i + 7], want, f"segment of {n} rows, continued")
         assert_close(seqs[i].read_state(0)[d.conv_floats:].reshape(-1, 128), states[i][d.conv_floats:].reshape(-1, 128), f"state after {n} + 7 rows")
+    c.close()
+
+
+def test_prep_chunk_out_pipeline_matches_cpu(checker):
+    """The prompt-pass pipeline on the device, back to back on one stream with no host synchronisation in between:
+    dn_prep -> dn_chunk (tensor cores) -> dn_out over a 200-row pass and a 100-row continuation, against the CPU code's
+    prep -> token recurrence -> out (tolerance: the chunked form rounds its operands to f16)."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    from oracle import gwo
+    nk, nv, dk, dv, K = 2, 4, 128, 128, 4
+    cd = 2 * nk * dk + nv * dv
+    w_conv = synth.normal(31, (cd * K,)) * np.float32(0.5)
+    w_a = (-np.abs(synth.normal(32, (nv,))) - np.float32(0.1)).astype(np.float32)
+    w_dt, w_norm = synth.normal(33, (nv,)), synth.normal(34, (dv,))
+    d = gwo.DeltaNet(checker, nk, nv, dk, dv, K, w_conv, w_a, w_dt, w_norm)
+    c = g.Context(0, n_lin=1, dn_nk=nk, dn_nv=nv, dn_dk=dk, dn_dv=dv, dn_conv=K, max_rows=256)
+    c.dn_set_weights(0, w_conv, w_a, w_dt, w_norm)
+    s = c.new_seq(512, 2)
+    st = d.new_state()
+    raw = synth.normal(35, (300, d.lw))
+    rows_dev = c.malloc(200 * d.lw * 4)
+    out_dev = c.malloc(200 * nv * dv * 4)
+    for lo, hi in ((0, 200), (200, 300)):
+        n = hi - lo
+        c.h2d(rows_dev, np.ascontiguousarray(raw[lo:hi]))
+        c.pass_begin([(s, lo, n)])
+        c.dn_prep_dev(0, rows_dev)
+        c.dn_chunk_dev(0, rows_dev, out_dev)
+        c.dn_out_dev(0, rows_dev, out_dev)
+        fin_gpu = np.empty((n, nv * dv), np.float32)
+        c.d2h(fin_gpu, out_dev)
+        c.sync()
+        c.pass_end()
+        prep_cpu = d.prep(st, raw[lo:hi], lo == 0)
+        fin_cpu = d.out(prep_cpu, d.rec(st, prep_cpu, lo == 0))
+        # dn_out divides each head by its RMS (values of order 1 to 10 from recurrence outputs of order 1e-2), so the
+        # absolute bar is scaled with the outputs' magnitude here; the relative one stands as it is
+        ma, rl = errors(fin_gpu, fin_cpu)
+        assert rl <= REL_L2 and ma <= MAX_ABS * max(1.0, float(np.abs(fin_cpu).max())), f"rows {lo}..{hi}: max-abs {ma:.3g}, rel-L2 {rl:.3g}"
+    assert_close(s.read_state(0)[d.conv_floats:].reshape(-1, 128), st[d.conv_floats:].reshape(-1, 128), "state after the pipeline")
     c.close()
