@@ -267,21 +267,31 @@ def q8_leg(args, rank, local_rank, world):
 DN_LAYERS, DN_SEQ, DN_TOKENS, DN_HEADS, DN_DK = 18, 4, 8192, 16, 128
 
 
-def deltanet_leg(local_rank, steps, small=False):
+def deltanet_leg(local_rank, steps, small=False, rank=0, world=1):
     """Qwen3.5-style Gated DeltaNet: 18 linear layers, 4 sequences x 8,192 tokens, 16 heads, d_k = d_v = 128, post-prep rows
     resident on the device, prompt passes of 512 rows per sequence.  Reported: the chunked tensor-core form (the prefill
     path) as `value`, and the exact token recurrence (the decode path, bit-identical to the CPU code) beside it.
-    flops = 8 d_k d_v per (token, head)."""
+    flops = 8 d_k d_v per (token, head).  On N GPUs (N = 2 or 4) the sequences are dealt to the ranks (the state is per
+    sequence: no collective on the data path), the time is the slowest rank's and the value the whole job's."""
     import gwenedeg_b200 as g
     from gwenedeg_b200 import synth
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        if DN_SEQ % world:
+            raise SystemExit(f"the DeltaNet workload has {DN_SEQ} sequences: run it on 1, 2 or 4 GPUs")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    nseq = DN_SEQ // world
     layers = 2 if small else DN_LAYERS
     tokens = 1024 if small else DN_TOKENS
     chunk = 512  # rows per sequence per pass
-    c = g.Context(local_rank, n_lin=layers, dn_nk=DN_HEADS, dn_nv=DN_HEADS, dn_dk=DN_DK, dn_dv=DN_DK, max_rows=DN_SEQ * chunk)
-    seqs = [c.new_seq(tokens, g.KV_F16) for _ in range(DN_SEQ)]
-    rows = synth.deltanet_rows(3, DN_SEQ * chunk, DN_HEADS, DN_HEADS, DN_DK, DN_DK)  # one pass worth of rows, reused
+    c = g.Context(local_rank, n_lin=layers, dn_nk=DN_HEADS, dn_nv=DN_HEADS, dn_dk=DN_DK, dn_dv=DN_DK, max_rows=nseq * chunk)
+    seqs = [c.new_seq(tokens, g.KV_F16) for _ in range(nseq)]
+    rows = synth.deltanet_rows(3 + rank, nseq * chunk, DN_HEADS, DN_HEADS, DN_DK, DN_DK)  # one pass worth of rows, reused
     rows_dev = c.to_device(rows)
-    out_dev = c.malloc(DN_SEQ * chunk * DN_HEADS * DN_DK * 4)
+    out_dev = c.malloc(nseq * chunk * DN_HEADS * DN_DK * 4)
 
     def run(fn):
         for pos in range(0, tokens, chunk):
@@ -296,12 +306,23 @@ def deltanet_leg(local_rank, steps, small=False):
     for name, fn, nst in (("chunked", c.dn_chunk_dev, steps), ("exact", c.dn_rec_dev, max(1, min(steps, 2)))):
         run(fn)
         c.sync()
+        if dist is not None:
+            dist.barrier()
         n0 = c.launch_count()
         c.timer_start()
         for _ in range(nst):
             run(fn)
         ms = c.timer_stop()
-        res[name] = (DN_SEQ * tokens * nst / (ms * 1e-3), ms / nst, (c.launch_count() - n0) // nst)
+        nl = c.launch_count() - n0
+        if dist is not None:
+            import torch
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)  # the slowest rank's time
+            ms = float(t[0].item())
+            t2 = torch.tensor([float(nl)], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t2, op=dist.ReduceOp.SUM)
+            nl = int(t2.item())
+        res[name] = (DN_SEQ * tokens * nst / (ms * 1e-3), ms / nst, nl // nst)
     tok_s, ms_step, launches = res["chunked"]
     flops_tok = 8.0 * DN_DK * DN_DK * DN_HEADS * layers
     try:
@@ -311,12 +332,15 @@ def deltanet_leg(local_rank, steps, small=False):
         peak, how = 1590.0, "fallback"
     tf = flops_tok * tok_s / 1e12
     c.close()
+    if dist is not None:
+        dist.destroy_process_group()
     return {"metric": "Qwen3.5 Gated DeltaNet: tokens/s (all linear layers, prompt passes)", "value": tok_s, "unit": "tokens/s",
-                      "n_gpus": 1, "steps": steps, "warmup": 1, "ms_per_step": ms_step, "higher_is_better": True, "dtype": "f16 operands, f32 state",
+                      "n_gpus": world, "scaling": "strong", "steps": steps, "warmup": 1, "ms_per_step": ms_step, "higher_is_better": True, "dtype": "f16 operands, f32 state",
                       "data": "synthetic", "gpu_launches": launches,
-                      "config": {"workload": "qwen3.5-deltanet-4x8192", "layers": layers, "tokens": tokens, "heads": DN_HEADS, "rows_per_pass": DN_SEQ * chunk},
+                      "config": {"workload": "qwen3.5-deltanet-4x8192", "layers": layers, "tokens": tokens, "heads": DN_HEADS, "rows_per_pass": nseq * chunk,
+                                 "parallelism": f"sequence-sharded x{world}"},
                       "form": "chunked (64-token WY / UT) on tcgen05", "tflops": tf,
-                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None,
+                      "roofline": {"bound": "tensor", "achieved": tf / world, "peak": peak, "unit": "TFLOP/s", "frac": tf / world / peak, "traffic": None,
                                    "peak_source": how, "kernel": "dn_chunk_kernel", "flops": "8 dk dv per (token, head): the recurrence's count"},
                       "exact_recurrence": {"tokens_per_s": res["exact"][0], "ms_per_step": res["exact"][1], "tflops": flops_tok * res["exact"][0] / 1e12,
                                            "form": "token by token, bit-identical to the CPU code"}}
@@ -541,8 +565,9 @@ def main():
         q8_leg(args, rank, local_rank, world)
         return
     if args.workload == "deltanet":
+        line = deltanet_leg(local_rank, args.steps, small=args.small, rank=rank, world=world)
         if rank == 0:
-            print(json.dumps(deltanet_leg(local_rank, args.steps, small=args.small)), flush=True)
+            print(json.dumps(line), flush=True)
         return
     if args.workload == "prefill":
         if rank == 0:
