@@ -34,8 +34,9 @@ enum {
     RQ_CUDA_ERR_DEVICE = -16  /* no usable CUDA device, or a CUDA call failed (text in rq_cuda_error) */
 };
 
-/* KV cache element types: the values of RQ_KV_* (src/runq.h:214-215) for the types this library implements
- * (the fp32-arithmetic attention over f32 / f16 / q8 / q4 / q4k4 caches; src/kvtype.h:12-29) */
+/* KV cache element types: the values of RQ_KV_* (src/runq.h:214-215; src/kvtype.h:12-29).  The device holds f16, q8, q4 and
+ * q4k4 caches (attention arithmetic in fp32, as the reference's); RQ_CUDA_KV_F32 is listed for the numbering only:
+ * rq_cuda_seq_new refuses it with RQ_CUDA_ERR_ARG. */
 enum { RQ_CUDA_KV_F32 = 0, RQ_CUDA_KV_F16 = 2, RQ_CUDA_KV_Q8 = 3, RQ_CUDA_KV_Q4 = 8, RQ_CUDA_KV_Q4K4 = 9 };
 
 typedef struct RqCuda RqCuda;       /* a compute context on one device: stream, scratch, the open pass (RqCtx, forward.c:32) */
