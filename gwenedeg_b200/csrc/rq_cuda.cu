@@ -832,7 +832,13 @@ int rq_cuda_dn_chunk_dev(RqCuda *c, int lin_layer, const float *rows, float *out
     const RqCudaModel &m = c->m;
     if (m.dn_dk != 128 || m.dn_dv != 128) return fail(c, RQ_CUDA_ERR_ARG, "dn_chunk is built for dk = dv = 128");
     CU(c, cudaSetDevice(c->device));
-    int rcg = grow(c, (void **)&c->d_dnwork, &c->dnwork_bytes, (size_t)c->dn_chunks * m.dn_nv * DNC_ITEM);
+    // one work record per (64-token chunk, value head): a pass of many short segments (decode rows) would ask for a
+    // record per row and belongs to rq_cuda_dn_rec
+    const size_t work_need = (size_t)c->dn_chunks * m.dn_nv * DNC_ITEM;
+    if (work_need > ((size_t)8 << 30))
+        return fail(c, RQ_CUDA_ERR_ARG, "dn_chunk: %d chunks x %d heads need %zu MB of work records; use dn_rec for passes of short segments",
+                    c->dn_chunks, m.dn_nv, work_need >> 20);
+    int rcg = grow(c, (void **)&c->d_dnwork, &c->dnwork_bytes, work_need);
     if (rcg) return rcg;
     DnChunkArgs a;
     a.segs = c->d_dseg;
