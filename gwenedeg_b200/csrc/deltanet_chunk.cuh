@@ -369,6 +369,17 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
         tc_fence_after();
     };
 
+    // a chunk's output row stays in registers and is stored under the next chunk's first products, off the chain of
+    // dependent steps
+    float ov[32];
+    float4 *ov_dst = nullptr;
+    auto flush_out = [&]() {
+        if (ov_dst) {
+#pragma unroll
+            for (int y = 0; y < 8; y++) ov_dst[y] = ok ? make_float4(ov[4 * y], ov[4 * y + 1], ov[4 * y + 2], ov[4 * y + 3]) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            ov_dst = nullptr;
+        }
+    };
     for (int n = 0; n < nch; n++) {
         const int c0 = n * C, cnt = min(C, sg.n - c0), sb = (n & 1) * ST_BYTES;
         // the next chunk's operands start loading (its stage was last read by chunk n - 1, whose products are complete
@@ -401,6 +412,7 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
             for (int ks = 0; ks < 8; ks++) umma_ss(tbase + Z1_COL, d_k128(sb + DNC_Q, ks), d_mn(S_S16, ks, 0), id_kmn, ks > 0);
             umma_commit(bar);
         }
+        flush_out();  // (the previous chunk's rows)
         wait_mma();
         // ---- R = beta v - beta_j g_j (k_j S0) -> f16: row j, columns 32 cb .. + 31 per thread
         const float *s_sc = reinterpret_cast<const float *>(sm + sb + ST_SC);
@@ -455,7 +467,8 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
             umma_commit(bar);
         }
         wait_mma();
-        // ---- O = g_i (q_i S0) + (M U)_i -> global memory: thread (row, 32-column block) writes its 128 bytes
+        // ---- O = g_i (q_i S0) + (M U)_i: thread (row, 32-column block) takes its 32 values; they go to global memory
+        // (128 bytes per thread) under the next chunk's first products
         if ((warp & 3) < 2) {
             uint32_t r1[32], r2[32];
             tmem_ld32(lane_addr + Z1_COL + cb * 32, r1);
@@ -463,20 +476,16 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
             tmem_wait_ld();
             if (trow < cnt) {
                 const float gi = ex2(lgj);
-                float4 *dst = reinterpret_cast<float4 *>(out + (size_t)(sg.row0 + c0 + trow) * vdim + (size_t)h * DV + (size_t)hv * HV + 32 * cb);
 #pragma unroll
-                for (int y = 0; y < 8; y++)
-                    dst[y] = ok ? make_float4(fmaf(gi, __uint_as_float(r1[4 * y]), __uint_as_float(r2[4 * y])),
-                                              fmaf(gi, __uint_as_float(r1[4 * y + 1]), __uint_as_float(r2[4 * y + 1])),
-                                              fmaf(gi, __uint_as_float(r1[4 * y + 2]), __uint_as_float(r2[4 * y + 2])),
-                                              fmaf(gi, __uint_as_float(r1[4 * y + 3]), __uint_as_float(r2[4 * y + 3])))
-                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int y = 0; y < 32; y++) ov[y] = fmaf(gi, __uint_as_float(r1[y]), __uint_as_float(r2[y]));
+                ov_dst = reinterpret_cast<float4 *>(out + (size_t)(sg.row0 + c0 + trow) * vdim + (size_t)h * DV + (size_t)hv * HV + 32 * cb);
             }
         }
         fence_proxy_async();  // (this chunk's stage is overwritten by bulk copies next)
         tc_fence_before();
         __syncthreads();      // (this chunk's stage and the O columns are free again)
     }
+    flush_out();  // (the last chunk's rows)
     // the state back to global memory
     tc_fence_after();
     {
