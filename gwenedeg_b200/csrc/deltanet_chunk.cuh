@@ -14,8 +14,8 @@
 //   dn_chunk_prep_kernel   everything of a chunk that does not depend on the state, one CTA per (chunk, value head), all
 //                          chunks of the pass in parallel: rows -> K and Q as f16 operands, beta v, the gates' log2 prefix
 //                          sums; the products K K^T and Q K^T on the tensor cores; A and M from them (masked, decayed);
-//                          T' = (I + A)^-1 by blocks of 32 (forward substitution on the two diagonal blocks, two products
-//                          for the block below).  Everything goes to a work buffer in the operand layout of the second
+//                          T' = (I + A)^-1 by two levels of blocks (forward substitution on the four 16 x 16 diagonal
+//                          blocks, two products for each block below them).  Everything goes to a work buffer in the operand layout of the second
 //                          kernel.
 //   dn_chunk_state_kernel  the walk over a segment's chunks in order, one CTA per (segment, value head, half of the dv
 //                          columns: the halves are independent given T' and M).  Per chunk, operands arrive by bulk
@@ -216,15 +216,16 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
     }
     tc_fence_before();
     __syncthreads();
-    // T' = (I + A)^-1 = [[X11, 0], [-X22 A21 X11, X22]] with 32 x 32 blocks: the two diagonal blocks by forward
-    // substitution (a column per thread: x_r = [r == c] - sum_{q<r} A_rq x_q), then the two products on all threads
+    // T' = (I + A)^-1 by two levels of the block formula  inv [[L11, 0], [A21, L22]] = [[X11, 0], [-X22 A21 X11, X22]]:
+    // the four 16 x 16 diagonal blocks by forward substitution (a column per thread: x_r = [r == c] - sum_{q<r} A_rq x_q),
+    // from them the two 32 x 32 diagonal blocks, from those the whole; the products run on all threads
     if (tid < 64) {
-        const int b = tid >> 5;
-        float x[32];
+        const int b = tid >> 4, cc = tid & 15;
+        float x[16];
 #pragma unroll
-        for (int r = 0; r < 32; r++) {
-            float acc[4] = {r == lane ? 1.0f : 0.0f, 0.0f, 0.0f, 0.0f};
-            const float *arow = s_a + (32 * b + r) * AST + 32 * b;
+        for (int r = 0; r < 16; r++) {
+            float acc[4] = {r == cc ? 1.0f : 0.0f, 0.0f, 0.0f, 0.0f};
+            const float *arow = s_a + (16 * b + r) * AST + 16 * b;
 #pragma unroll
             for (int q4 = 0; q4 < (r + 3) / 4; q4++) {
                 const float4 a4 = *reinterpret_cast<const float4 *>(arow + 4 * q4);  // (entries q >= r are zero)
@@ -234,7 +235,44 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
                     if (4 * q4 + y < r) acc[y] = fmaf(-av[y], x[4 * q4 + y], acc[y]);
             }
             x[r] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-            s_x[(32 * b + r) * AST + 32 * b + lane] = x[r];
+            s_x[(16 * b + r) * AST + 16 * b + cc] = x[r];
+        }
+    }
+    __syncthreads();
+    {
+        // inside 32-block B: the lower left 16 x 16 block, thread = (B, row r, two columns c2, c2 + 1)
+        const int B = tid >> 7, r = (tid >> 3) & 15, c2 = (tid & 7) * 2;
+        {  // P = A21 X11
+            float p0 = 0.0f, p1 = 0.0f;
+            const float *arow = s_a + (32 * B + 16 + r) * AST + 32 * B;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+                const float4 a4 = *reinterpret_cast<const float4 *>(arow + 4 * q4);
+                const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                for (int y = 0; y < 4; y++) {
+                    const float2 x2 = *reinterpret_cast<const float2 *>(s_x + (32 * B + 4 * q4 + y) * AST + 32 * B + c2);
+                    p0 = fmaf(av[y], x2.x, p0), p1 = fmaf(av[y], x2.y, p1);
+                }
+            }
+            *reinterpret_cast<float2 *>(s_p + (16 * B + r) * AST + c2) = make_float2(p0, p1);
+        }
+        __syncthreads();
+        {  // X21 = -X22 P; the block above the diagonal is zero
+            float v0 = 0.0f, v1 = 0.0f;
+            const float *xrow = s_x + (32 * B + 16 + r) * AST + 32 * B + 16;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+                const float4 a4 = *reinterpret_cast<const float4 *>(xrow + 4 * q4);
+                const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                for (int y = 0; y < 4; y++) {
+                    const float2 p2 = *reinterpret_cast<const float2 *>(s_p + (16 * B + 4 * q4 + y) * AST + c2);
+                    v0 = fmaf(-av[y], p2.x, v0), v1 = fmaf(-av[y], p2.y, v1);
+                }
+            }
+            *reinterpret_cast<float2 *>(s_x + (32 * B + 16 + r) * AST + 32 * B + c2) = make_float2(v0, v1);
+            *reinterpret_cast<float2 *>(s_x + (32 * B + r) * AST + 32 * B + 16 + c2) = make_float2(0.0f, 0.0f);
         }
     }
     __syncthreads();
