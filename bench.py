@@ -489,7 +489,7 @@ def run_ours(args, rank, local_rank, world):
 
     c.close()
     prefill = deltanet = None
-    if rank == 0 and not args.small:
+    if world == 1 and not args.small:  # the other workloads ride on the one-GPU line only (each has its own --workload for N > 1)
         try:
             prefill = prefill_leg(local_rank, max(2, min(args.steps, 5)))
         except Exception as e:
