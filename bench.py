@@ -191,12 +191,16 @@ def prefill_leg(device, steps, layers=None, warm=3):
                          "peak_source": how, "kernel": "attn_prefill_kernel", "flops_per_launch": flops_layer, "launches_timed": kern_n}}
 
 
-Q8_SEQ, Q8_CTX, Q8_BYTES_PER_POS = 32, 40960, 2 * N_KV * (HD + HD // 32 * 2)  # 2,176 B of q8 K + V per position per layer
+Q8_SEQ, Q8_CTX = 32, 40960
+# bytes of K + V per position per layer: 8-bit half = int8 levels + a bf16 scale per 32 dims, 4-bit half = nibbles + the same
+# scales; q8 = both halves 8-bit (2,176 B), q4 = K 8-bit, V 4-bit (1,664 B), q4k4 = both 4-bit (1,152 B)
+_H8, _H4 = N_KV * (HD + HD // 32 * 2), N_KV * (HD // 2 + HD // 32 * 2)
+Q_BYTES_PER_POS = {"q8": 2 * _H8, "q4": _H8 + _H4, "q4k4": 2 * _H4}
 
 
-def q8_leg(args, rank, local_rank, world):
-    """Qwen3-8B-shaped q8 KV decode: 32 sequences at context 40,960, K and V int8 in blocks of 32 dims with bf16
-    scales (the reference's tile format), dequantisation fused into the kernel.  With N > 1 every rank holds a group
+def q8_leg(args, rank, local_rank, world, kv="q8"):
+    """Qwen3-8B-shaped quantised-KV decode: 32 sequences at context 40,960, K and V as int8 (q8), 4-bit V (q4) or 4-bit K and V (q4k4) levels in
+    blocks of 32 dims with bf16 scales (the reference's tile format), dequantisation fused into the kernel.  With N > 1 every rank holds a group
     of KV heads of every sequence and the outputs are all-gathered (NCCL)."""
     import gwenedeg_b200 as g
     from gwenedeg_b200 import synth
@@ -213,7 +217,7 @@ def q8_leg(args, rank, local_rank, world):
     c = sh.ctx
     seqs = []
     for i in range(nseq):
-        s = c.new_seq(Q8_CTX, g.KV_Q8)
+        s = c.new_seq(Q8_CTX, {"q8": g.KV_Q8, "q4": g.KV_Q4, "q4k4": g.KV_Q4K4}[kv])
         s.fill_synthetic(Q8_CTX, 500 + i)
         seqs.append(s)
     c.sync()
@@ -248,16 +252,16 @@ def q8_leg(args, rank, local_rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     peak, how = peaks()
-    bytes_launch = nseq * Q8_CTX * Q8_BYTES_PER_POS / world
+    bytes_launch = nseq * Q8_CTX * Q_BYTES_PER_POS[kv] / world
     achieved = bytes_launch / (kern_ms / max(kern_n, 1) * 1e-3) / 1e9
     if rank == 0:
-        print(json.dumps({"metric": "Qwen3-8B attn: q8 KV decode rows/s (B=32, ctx 40960)", "value": nseq * args.steps / (ms * 1e-3),
+        print(json.dumps({"metric": f"Qwen3-8B attn: {kv} KV decode rows/s (B=32, ctx 40960)", "value": nseq * args.steps / (ms * 1e-3),
                           "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
                           "higher_is_better": True, "scaling": "strong", "dtype": "f32", "data": "synthetic",
-                          "config": {"workload": "qwen3-8b-decode-q8-b32-ctx40960", "layers": layers, "sequences": nseq,
+                          "config": {"workload": f"qwen3-8b-decode-{kv}-b32-ctx40960", "layers": layers, "sequences": nseq,
                                      "parallelism": f"kv-head-sharded x{world} + all-gather"},
                           "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                                       "traffic": None, "peak_source": how, "kernel": "attn_part_kernel<q8,128,4>",
+                                       "traffic": None, "peak_source": how, "kernel": f"attn_part_kernel<{kv},128,4>",
                                        "algorithmic_bytes_per_launch_rank0": bytes_launch, "launches_timed": kern_n}}), flush=True)
     sh.close()
     if dist is not None:
@@ -541,7 +545,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode-q8", "deltanet"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode-q8", "decode-q4", "decode-q4k4", "deltanet"],
                     help="decode: the headline batched-decode benchmark (default); prefill: only the chunked-prefill leg "
                          "(512 rows over a 3584-position prefix), printed as its own line")
     ap.add_argument("--shard-of", type=int, default=1,
@@ -561,8 +565,8 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
-    if args.workload == "decode-q8":
-        q8_leg(args, rank, local_rank, world)
+    if args.workload in ("decode-q8", "decode-q4", "decode-q4k4"):
+        q8_leg(args, rank, local_rank, world, kv=args.workload[7:])
         return
     if args.workload == "deltanet":
         line = deltanet_leg(local_rank, args.steps, small=args.small, rank=rank, world=world)

@@ -98,9 +98,15 @@ __device__ __forceinline__ void load_k(const uint8_t *kt, int i, int j0, const f
         } else {  // q4: byte [dim pair][position], low nibble dim 2p, high nibble dim 2p + 1
             if constexpr (PPT == 4) w = *reinterpret_cast<const uint32_t *>(kt + (size_t)(i >> 1) * 16 + j0);
             else w = *reinterpret_cast<const uint16_t *>(kt + (size_t)(i >> 1) * 16 + j0);
-            const int sh = 4 * (i & 1);
+            // the dim's nibble of every position moved to the low half of its byte, then as the q8 path: a level + 8
+            // becomes the low mantissa bits of 2^23 and the subtract and multiply run two positions per instruction
+            w = (w >> (4 * (i & 1))) & 0x0F0F0F0Fu;
 #pragma unroll
-            for (int p = 0; p < PPT; p++) k[p] = u4_to_f32(w, 8 * p + sh) * d[p];
+            for (int p = 0; p < PPT; p += 2) {
+                float2 f = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 | p)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 | (p + 1))));
+                f = __fmul2_rn(__fadd2_rn(f, make_float2(-8388616.0f, -8388616.0f)), make_float2(d[p], d[p + 1]));  // 2^23 + 8
+                k[p] = f.x, k[p + 1] = f.y;
+            }
         }
     }
 }
@@ -154,8 +160,15 @@ __device__ __forceinline__ void load_v(const uint8_t *vt, int j, int i0, float *
         const float d = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(vt + 8 * HD + (j * (HD / 32) + (i0 >> 5)) * 2));
         const uint8_t *p = vt + (size_t)j * (HD / 2) + (i0 >> 5) * 16 + (i0 & 15);
         const int sh = 4 * ((i0 >> 4) & 1);
+        if constexpr (DPT == 2) {  // two adjacent bytes at once, packed subtract and multiply (each lane rounds as the scalar form)
+            const uint32_t w = ((uint32_t)*reinterpret_cast<const uint16_t *>(p) >> sh) & 0x0F0Fu;
+            float2 f = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540)), __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7541)));
+            f = __fmul2_rn(__fadd2_rn(f, make_float2(-8388616.0f, -8388616.0f)), make_float2(d, d));
+            vv[0] = f.x, vv[1] = f.y;
+        } else {
 #pragma unroll
-        for (int x = 0; x < DPT; x++) vv[x] = u4_to_f32(p[x], sh) * d;
+            for (int x = 0; x < DPT; x++) vv[x] = u4_to_f32(p[x], sh) * d;
+        }
     }
 }
 
