@@ -38,8 +38,9 @@ template <int KVT, int HD>
 struct DecCfg {
     static constexpr int KF = kv_fmt(KVT, 0), VF = kv_fmt(KVT, 1);
     static constexpr int KTB = kv_tile_bytes(KVT, HD, 0), VTB = kv_tile_bytes(KVT, HD, 1);
-    // positions per stage: a 16-bit cache at head_dim 256 is streamed in two halves of 128 positions
-    static constexpr int STAGES = (KF == KV_F16 && HD >= 128) ? 2 : 1;
+    // positions per stage: 16-bit and all-8-bit caches at head_dim >= 128 are streamed in two halves of 128 positions
+    // (smaller buffer, more CTAs per SM); with 4-bit levels the whole block at once measured faster
+    static constexpr int STAGES = ((KF == KV_F16 || VF == KV_Q8) && HD >= 128) ? 2 : 1;
     static constexpr int ST_TILES = ATT_PT / STAGES;
     static constexpr int ST_POS = ATT_P / STAGES;
     static constexpr int PPT = ST_POS / DEC_THREADS;  // adjacent positions a thread scores per stage: 4 or 2
