@@ -672,6 +672,18 @@ static int stage_q(RqCuda *c, const float *q, size_t qbytes, size_t obytes) {
     return RQ_CUDA_OK;
 }
 
+// The device-side address of a host buffer the GPU can write directly (page-locked and mapped: rq_cuda_malloc_host,
+// cudaMallocHost, cudaHostRegister), or null for ordinary host memory.  The merge kernel then stores its rows straight
+// into the caller's buffer and the separate device-to-host copy (and its latency after the last kernel) goes away.
+static float *mapped_host(void *p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return a.type == cudaMemoryTypeHost ? (float *)a.devicePointer : nullptr;
+}
+
 int rq_cuda_attn_decode(RqCuda *c, int layer, const float *q, float *out) {
     int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_decode");
     if (rc) return rc;
@@ -679,8 +691,9 @@ int rq_cuda_attn_decode(RqCuda *c, int layer, const float *q, float *out) {
     CU(c, cudaSetDevice(c->device));
     size_t qb = (size_t)c->nrows * c->n_heads * c->qh * 4, ob = (size_t)c->nrows * c->n_heads * c->m.head_dim * 4;
     if ((rc = stage_q(c, q, qb, ob))) return rc;
-    if ((rc = launch_decode(c, layer, c->d_q, c->d_out))) return rc;
-    CU(c, cudaMemcpyAsync(out, c->d_out, ob, cudaMemcpyDeviceToHost, c->stream));
+    float *od = mapped_host(out);
+    if ((rc = launch_decode(c, layer, c->d_q, od ? od : c->d_out))) return rc;
+    if (!od) CU(c, cudaMemcpyAsync(out, c->d_out, ob, cudaMemcpyDeviceToHost, c->stream));
     return rq_cuda_sync(c);
 }
 
@@ -805,8 +818,9 @@ int rq_cuda_attn_prefill(RqCuda *c, int layer, const float *q, float *out) {
     CU(c, cudaSetDevice(c->device));
     size_t qb = (size_t)c->nrows * c->n_heads * c->qh * 4, ob = (size_t)c->nrows * c->n_heads * c->m.head_dim * 4;
     if ((rc = stage_q(c, q, qb, ob))) return rc;
-    if ((rc = launch_prefill(c, layer, c->d_q, c->d_out))) return rc;
-    CU(c, cudaMemcpyAsync(out, c->d_out, ob, cudaMemcpyDeviceToHost, c->stream));
+    float *od = mapped_host(out);
+    if ((rc = launch_prefill(c, layer, c->d_q, od ? od : c->d_out))) return rc;
+    if (!od) CU(c, cudaMemcpyAsync(out, c->d_out, ob, cudaMemcpyDeviceToHost, c->stream));
     return rq_cuda_sync(c);
 }
 

@@ -144,3 +144,29 @@ def test_argument_errors_leave_state_untouched():
     with pytest.raises(g.RqCudaError):
         c.new_seq(10, 1)                     # bf16 caches are not implemented on the device
     c.close()
+
+
+@pytest.mark.parametrize("kvt", [F16, Q8])
+def test_page_locked_result_buffer_is_written_in_place(kvt):
+    """rq_cuda_attn_decode / _prefill store straight into a page-locked (mapped) host buffer and copy into an ordinary one:
+    the rows are the same bit for bit, and nothing outside them is touched."""
+    import ctypes as C
+    from gwenedeg_b200 import synth
+    n_heads, n_kv, hd, rows = 8, 2, 128, 5
+    c = make_ctx(n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, max_rows=512)
+    seqs = []
+    for i in range(rows):
+        s = c.new_seq(1200, kvt)
+        s.fill_synthetic(300 + 211 * i, 40 + i)
+        seqs.append(s)
+    q = synth.normal(91, (rows, n_heads, hd))
+    pinned = c.pinned((rows + 1, n_heads, hd))
+    for fn, name in ((c.L.rq_cuda_attn_decode, "decode"), (c.L.rq_cuda_attn_prefill, "prefill")):
+        c.pass_begin([(s, s.len - 1, 1) for s in seqs])
+        plain = c._attn(fn, 0, q)  # an ordinary numpy array: staged on the device, then copied
+        pinned[:] = 7.0
+        c.check(fn(c.h, 0, q.ctypes.data_as(C.c_void_p), pinned.ctypes.data_as(C.c_void_p)))
+        c.pass_end(commit=False)
+        assert bit_equal(plain, pinned[:rows]), name
+        assert np.all(pinned[rows] == 7.0), name
+    c.close()
