@@ -138,7 +138,9 @@ int rq_cuda_qk_norm_rope_store_dev(RqCuda *ctx, int layer, float *q_dev, const f
  * items of decode_worker (forward.c:2691-2715) and batch_decode_worker (:3582-3616): attention_part :1806 +
  * att_combine :1405, with att_q_rot :1662 before and att_o_unrot :1672 / attn_gate :2291 after.
  * q: host fp32 [rows][heads_local][qh] (qh = head_dim, or 2 head_dim when gated), out: host fp32
- * [rows][heads_local][head_dim].  Softmax scale 1/sqrt(head_dim). */
+ * [rows][heads_local][head_dim].  Softmax scale 1/sqrt(head_dim).  The call returns when `out` is complete.  If `out`
+ * is page-locked memory the GPU can address (rq_cuda_malloc_host, cudaMallocHost, cudaHostRegister) the last kernel
+ * stores into it directly; ordinary memory takes a staged copy.  The same holds for rq_cuda_attn_prefill. */
 int rq_cuda_attn_decode(RqCuda *ctx, int layer, const float *q, float *out);
 int rq_cuda_attn_decode_dev(RqCuda *ctx, int layer, const float *q_dev, float *out_dev);
 
