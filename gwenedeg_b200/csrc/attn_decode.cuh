@@ -539,11 +539,15 @@ constexpr int COMBINE_NG = 4;  // thread groups of the merge kernel: each fetche
 template <int HD, bool QUANT>
 __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const PassRow *__restrict__ rows, int n_heads,
                                                                       const float *__restrict__ part, const float *__restrict__ q, int qh,
-                                                                      int gated, float *__restrict__ out, int split_len, int fixed_stride) {
+                                                                      int gated, float *__restrict__ out, int split_len, int fixed_stride,
+                                                                      const int *err_src, int *err_dst) {
     constexpr int CH = 8192 / HD;  // partials per chunk: 32 KB of shared memory
     const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, i = tid % HD, grp = tid / HD;
     pdl_wait();
     pdl_launch_dependents();
+    // err_dst (a mapped host word, or null): the status word of the kernels before this one, complete after the wait
+    // above, goes to the host with the results instead of by a copy of its own
+    if (err_dst && r == 0 && h == 0 && tid == 0) *err_dst = *err_src;
     const PassRow row = rows[r];
     const int nb = (row.np + split_len - 1) / split_len;
     const size_t pst = RQ_PSTRIDE(HD);
@@ -629,11 +633,12 @@ template <int HD>
 __global__ void __launch_bounds__(32 * COMBINE_ROWS_WARPS) attn_combine_rows_kernel(const PassRow *__restrict__ rows, int nrows, int n_heads,
                                                                                  const float *__restrict__ part, const float *__restrict__ q,
                                                                                  int qh, int gated, float *__restrict__ out, int split_len,
-                                                                                 int fixed_stride) {
+                                                                                 int fixed_stride, const int *err_src, int *err_dst) {
     static_assert(HD == 128, "a lane holds 4 of the row's 128 dims");
     const int wi = blockIdx.x * COMBINE_ROWS_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     pdl_wait();
     pdl_launch_dependents();
+    if (err_dst && blockIdx.x == 0 && threadIdx.x == 0) *err_dst = *err_src;  // (as in attn_combine_kernel)
     if (wi >= nrows * n_heads) return;
     const int r = wi / n_heads, h = wi % n_heads;
     const int nb = (rows[r].np + split_len - 1) / split_len;

@@ -73,6 +73,7 @@ struct RqCuda {
     float *d_dn;    size_t dn_bytes;    // staging of DeltaNet rows
     int *d_err;
     int *h_err;  // pinned
+    int *err_fwd = nullptr;  // set around a launch whose merge kernel should store the status word to h_err itself
     void *flush; size_t flush_bytes;
     // tensor-core prefill: the segments' tensor maps and the work list of the open pass
     CUtensorMap *h_maps, *d_maps;  // [max_rows][2]
@@ -643,8 +644,8 @@ static int launch_combine(RqCuda *c, const float *q, float *out, const float *pa
     const bool quant = kv_quant(c->pass_kvt);
     cudaError_t ce = cudaSuccess;
 #define COMBINE(HD_)                                                                                                          \
-    if (quant) ce = launch_pdl(attn_combine_kernel<HD_, true>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride); \
-    else ce = launch_pdl(attn_combine_kernel<HD_, false>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride);
+    if (quant) ce = launch_pdl(attn_combine_kernel<HD_, true>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd); \
+    else ce = launch_pdl(attn_combine_kernel<HD_, false>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd);
     switch (hd) {
         case 64: COMBINE(64) break;
         case 128: COMBINE(128) break;
@@ -684,6 +685,18 @@ static float *mapped_host(void *p) {
     return a.type == cudaMemoryTypeHost ? (float *)a.devicePointer : nullptr;
 }
 
+// End of a host-buffer call whose merge kernel stored the status word to h_err itself (err_fwd): only the wait is left.
+static int sync_forwarded(RqCuda *c) {
+    CU(c, cudaStreamSynchronize(c->stream));
+    if (*c->h_err) {
+        int code = *c->h_err;
+        *c->h_err = 0;
+        cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream);
+        return fail(c, RQ_CUDA_ERR_STATE, "a device-side wait expired (code %d): results of the last pass are invalid", code);
+    }
+    return RQ_CUDA_OK;
+}
+
 int rq_cuda_attn_decode(RqCuda *c, int layer, const float *q, float *out) {
     int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_decode");
     if (rc) return rc;
@@ -692,9 +705,13 @@ int rq_cuda_attn_decode(RqCuda *c, int layer, const float *q, float *out) {
     size_t qb = (size_t)c->nrows * c->n_heads * c->qh * 4, ob = (size_t)c->nrows * c->n_heads * c->m.head_dim * 4;
     if ((rc = stage_q(c, q, qb, ob))) return rc;
     float *od = mapped_host(out);
-    if ((rc = launch_decode(c, layer, c->d_q, od ? od : c->d_out))) return rc;
+    c->err_fwd = (int *)mapped_host(c->h_err);
+    rc = launch_decode(c, layer, c->d_q, od ? od : c->d_out);
+    const bool fwd = c->err_fwd != nullptr;
+    c->err_fwd = nullptr;
+    if (rc) return rc;
     if (!od) CU(c, cudaMemcpyAsync(out, c->d_out, ob, cudaMemcpyDeviceToHost, c->stream));
-    return rq_cuda_sync(c);
+    return fwd ? sync_forwarded(c) : rq_cuda_sync(c);
 }
 
 // ---- decode attention without any allocation -------------------------------------------------------------------------
@@ -798,7 +815,7 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     // (this path is head_dim 128 over a 16-bit cache: a warp per output row merges its few partials)
     const int nout = c->nrows * c->n_heads;
     CU(c, launch_pdl(attn_combine_rows_kernel<128>, dim3((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), dim3(32 * COMBINE_ROWS_WARPS), 0, c->stream,
-                     c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh, c->m.gated, out, PF_SPLIT, c->pf_max_splits));
+                     c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh, c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd));
     c->launches++;
     return RQ_CUDA_OK;
 }
@@ -819,9 +836,13 @@ int rq_cuda_attn_prefill(RqCuda *c, int layer, const float *q, float *out) {
     size_t qb = (size_t)c->nrows * c->n_heads * c->qh * 4, ob = (size_t)c->nrows * c->n_heads * c->m.head_dim * 4;
     if ((rc = stage_q(c, q, qb, ob))) return rc;
     float *od = mapped_host(out);
-    if ((rc = launch_prefill(c, layer, c->d_q, od ? od : c->d_out))) return rc;
+    c->err_fwd = (int *)mapped_host(c->h_err);
+    rc = launch_prefill(c, layer, c->d_q, od ? od : c->d_out);
+    const bool fwd = c->err_fwd != nullptr;
+    c->err_fwd = nullptr;
+    if (rc) return rc;
     if (!od) CU(c, cudaMemcpyAsync(out, c->d_out, ob, cudaMemcpyDeviceToHost, c->stream));
-    return rq_cuda_sync(c);
+    return fwd ? sync_forwarded(c) : rq_cuda_sync(c);
 }
 
 int rq_cuda_dn_rec_dev(RqCuda *c, int lin_layer, const float *rows, float *out) {
