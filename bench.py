@@ -33,9 +33,27 @@ METRIC = "Qwen3-8B attn: decode rows/s (B=64 ragged ctx)"
 TRAFFIC_RATIO = (189.70 + 4.27) / 189.25  # measured DRAM bytes (read + written) over algorithmic K+V bytes, ncu capture of --small
 
 
+def _synth():
+    """gwenedeg_b200/synth.py (numpy only) loaded by path: the reference arm needs the workload's seeded context lengths
+    without importing the package, whose import loads the CUDA library."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("rq_bench_synth", os.path.join(ROOT, "gwenedeg_b200", "synth.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def contexts():
-    from gwenedeg_b200 import synth
-    return synth.ragged_contexts(CTX_SEED, N_SEQ, CTX_LO, CTX_HI)
+    return _synth().ragged_contexts(CTX_SEED, N_SEQ, CTX_LO, CTX_HI)
+
+
+def workload_config(ctx_all, small=False):
+    """The `config` object of the headline line: the workload only, the same in both arms."""
+    return {"workload": "qwen3-8b-decode-small-profile-case" if small else "qwen3-8b-decode-b64-ragged",
+            "sequences": N_SEQ, "layers": N_LAYERS, "heads": N_HEADS, "kv_heads": N_KV, "head_dim": HD, "kv_type": "f16",
+            "ctx": f"U[{CTX_LO},{CTX_HI}] seed {CTX_SEED}", "positions_total": int(np.sum(ctx_all)),
+            "l2": "inputs larger than L2: a layer pass streams 4,096 B per cached position, "
+                  f"{int(np.sum(ctx_all)) * KV_BYTES_PER_POS / 1e9:.2f} GB over the batch"}
 
 
 def shard(ctx, world):
@@ -133,6 +151,7 @@ def cpu_leg(ctx_all, reps, sample_every):
     # linear in positions: scale the sample's layer time to the full batch, all layers
     t_step_full = t_layer_sample * (float(np.sum(ctx_all)) / float(sum(ctx))) * N_LAYERS
     info = {"value": N_SEQ / t_step_full, "unit": "rows/s", "cores": cores, "kind": "reference" if orc.kind == "ref" else "port",
+            "isa": orc.isa, "library": orc.library,
             "sample": f"{len(idx)} of {N_SEQ} sequences (every {sample_every}th), 1 of {N_LAYERS} layers, {reps} reps, "
                       f"mean {t_layer_sample * 1e3:.1f} ms per layer pass (best {best * 1e3:.1f}), "
                       f"{sum(ctx) * KV_BYTES_PER_POS / t_layer_sample / 1e9:.1f} GB/s of KV; scaled by positions and layers"}
@@ -360,8 +379,7 @@ def run_reference(args, rank, world):
     line = {"metric": METRIC, "value": info["value"], "unit": "rows/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 * N_SEQ / info["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "impl": "reference",
-            "config": {"workload": "qwen3-8b-decode-b64-ragged", "sequences": N_SEQ, "layers": N_LAYERS, "heads": N_HEADS,
-                       "kv_heads": N_KV, "head_dim": HD, "kv_type": "f16", "ctx": f"U[{CTX_LO},{CTX_HI}] seed {CTX_SEED}"},
+            "config": workload_config(ctx_all),
             "cpu_baseline": info,
             "e2e": {"value": info["value"], "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "wall_s": time.time() - t0}
@@ -520,19 +538,16 @@ def run_ours(args, rank, local_rank, world):
             "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "qwen3-8b-decode-small-profile-case" if args.small else "qwen3-8b-decode-b64-ragged",
-                       "sequences": N_SEQ, "layers": N_LAYERS, "heads": N_HEADS,
-                       "kv_heads": N_KV, "head_dim": HD, "kv_type": "f16", "ctx": f"U[{CTX_LO},{CTX_HI}] seed {CTX_SEED}",
-                       "positions_total": int(np.sum(ctx_all)), "parallelism": f"sequence-sharded x{world}",
-                       "distinct_layer_caches_rank0": n_distinct, "l2": "inputs larger than L2 (each layer pass streams "
-                       f"{per_layer / 1e9:.2f} GB on rank 0)"},
+            "config": workload_config(ctx_all, args.small),
+            "run": {"parallelism": f"sequence-sharded x{world}", "distinct_layer_caches_rank0": n_distinct,
+                    "bytes_streamed_per_layer_pass_rank0": per_layer},
             "layer_rows_per_s": value * N_LAYERS,
             "e2e": {"value": N_SEQ * args.steps / (ms_e2e * 1e-3), "unit": "rows/s",
                     "h2d_bytes_per_step": N_LAYERS * N_SEQ * N_HEADS * HD * 4, "d2h_bytes_per_step": N_LAYERS * N_SEQ * N_HEADS * HD * 4},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": bytes_per_launch * TRAFFIC_RATIO, "traffic_source": "ncu dram read+write of the small case, scaled by positions (profiles/attn_part_kernel_decode_b64_ragged.md)", "peak_source": how, "kernel": "attn_part_kernel<f16,128,4>",
+                         "traffic": bytes_per_launch * TRAFFIC_RATIO, "traffic_source": "ncu dram read + write of the small case of the same kernel, scaled by positions", "peak_source": how, "kernel": "attn_part_kernel<f16,128,4>",
                          "algorithmic_bytes_per_launch_rank0": bytes_per_launch, "launches_timed": part_n},
             "cpu_baseline": cpu,
             "prefill": prefill,

@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "librq_cuda.so")
+# RQ_CUDA_LIB selects another build of the same library (the debug build with index checks: librq_cuda_debug.so)
+LIB_PATH = os.environ.get("RQ_CUDA_LIB") or os.path.join(HERE, "librq_cuda.so")
 
 OK, ERR_ARG, ERR_NOMEM, ERR_CONTEXT, ERR_STATE, ERR_DEVICE = 0, -1, -2, -3, -4, -16
 KV_F32, KV_F16, KV_Q8, KV_Q4, KV_Q4K4 = 0, 2, 3, 8, 9
@@ -34,7 +35,10 @@ PROTOTYPES = {
     "rq_cuda_free": (None, [_vp]),
     "rq_cuda_error": (C.c_char_p, [_vp]),
     "rq_cuda_device_count": (_i, []),
+    "rq_cuda_debug_build": (_i, []),
     "rq_cuda_sync": (_i, [_vp]),
+    "rq_cuda_reserve": (_i, [_vp, _i, C.c_longlong, _i]),
+    "rq_cuda_selftest_wait_expiry": (_i, [_vp, C.c_uint]),
     "rq_cuda_set_stream": (_i, [_vp, _vp]),
     "rq_cuda_seq_new": (_i, [_vp, _i, _i, _pp]),
     "rq_cuda_seq_free": (None, [_vp]),
@@ -79,7 +83,6 @@ PROTOTYPES = {
     "rq_cuda_launch_count": (_ull, [_vp]),
     "rq_cuda_profile_begin": (_i, [_vp, _i]),
     "rq_cuda_profile_end": (_i, [_vp, C.POINTER(C.c_float), C.POINTER(_i)]),
-    "rq_cuda_flush_l2": (_i, [_vp]),
 }
 
 _lib = None

@@ -75,6 +75,10 @@ class Context:
     def sync(self):
         self.check(self.L.rq_cuda_sync(self.h))
 
+    def reserve(self, rows, positions_total, max_ctx):
+        """Size the scratch for passes of up to `rows` rows over `positions_total` cached positions (no allocation later)."""
+        self.check(self.L.rq_cuda_reserve(self.h, rows, positions_total, max_ctx))
+
     def set_stream(self, stream_ptr):
         self.check(self.L.rq_cuda_set_stream(self.h, C.c_void_p(stream_ptr)))
 
@@ -223,9 +227,6 @@ class Context:
         ms, n = C.c_float(), C.c_int()
         self.check(self.L.rq_cuda_profile_end(self.h, C.byref(ms), C.byref(n)))
         return ms.value, n.value
-
-    def flush_l2(self):
-        self.check(self.L.rq_cuda_flush_l2(self.h))
 
 
 class Sequence:

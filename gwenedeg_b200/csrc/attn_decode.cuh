@@ -208,6 +208,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
     const size_t tile0 = ((size_t)b * n_kv + g) * ATT_PT;
     const uint8_t *kg = row.k + (size_t)layer * row.lk + tile0 * C::KTB;
     const uint8_t *vg = row.v + (size_t)layer * row.lv + tile0 * C::VTB;
+    // (debug build) the block lies inside the row and its tiles inside one layer of the cache
+    RQ_CHECK(lo >= 0 && lo < nrows && b >= 0 && n >= 1 && g < n_kv && (tile0 + ntl) * C::KTB <= row.lk && (tile0 + ntl) * C::VTB <= row.lv, err, 41);
 
     if (tid == 0) {
         mbar_init(bar, 1);
@@ -507,6 +509,9 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
     }
 
     // ---- the partial result of (row, head, block): o[hd], m, l
+    // ls[v] was written by lane 16 (v % 4) of warp v / 2 and is read by thread 0 below: the only barriers since are the
+    // conditional ones between V stages (none when the block has a single stage), so one more is needed here
+    __syncthreads();
 #pragma unroll
     for (int v = 0; v < NVT; v++) {
         if (v < G) {
@@ -550,6 +555,7 @@ __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const Pass
     if (err_dst && r == 0 && h == 0 && tid == 0) *err_dst = *err_src;
     const PassRow row = rows[r];
     const int nb = (row.np + split_len - 1) / split_len;
+    RQ_CHECK(nb >= 1 && h < n_heads, const_cast<int *>(err_src), 42);
     const size_t pst = RQ_PSTRIDE(HD);
     const size_t bstride = (size_t)n_heads * pst;
     const float *p0 = part + ((size_t)(fixed_stride ? r * fixed_stride : row.blk0) * n_heads + h) * pst;
@@ -625,7 +631,7 @@ __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const Pass
 }
 
 // The same merge for rows with few partials each (the tensor-core prefill path: head_dim 128, 16-bit cache, one
-// partial per 1024-position split): one warp per (row, query head), lane L holds dims 4L .. 4L + 3, so a launch is a
+// partial per split of PF_SPLIT = 2,048 positions): one warp per (row, query head), lane L holds dims 4L .. 4L + 3, so a launch is a
 // few hundred CTAs instead of one per output row.  Arithmetic as attn_combine_kernel: M = max of the m_b,
 // c_b = exp_att(m_b - M), L and out as fma chains in partial order, out * (1 / L), gate.
 constexpr int COMBINE_ROWS_WARPS = 8;

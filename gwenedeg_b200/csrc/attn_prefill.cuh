@@ -45,7 +45,7 @@ struct PfWork {
     int seg;     // segment index (its tensor maps)
     int row0;    // first row of the tile (index in the pass)
     int nrows;   // rows of the tile (<= 128 / G)
-    int split;   // which 1024-position split of the keys
+    int split;   // which split of PF_SPLIT key positions
 };
 
 struct AttnPrefillArgs {
@@ -99,6 +99,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
     const int s0 = w.split * PF_SPLIT;                        // first key position of this split
     const int s1 = min(s0 + PF_SPLIT, np_max);                // one past the last key position any row needs
     const int nblk = (s1 - s0 + PF_BN - 1) / PF_BN;          // >= 1 by construction of the work list
+    // (debug build) the split starts inside the tile's keys, the tile is one of at most 128 vectors, the KV head exists
+    RQ_CHECK(w.nrows >= 1 && w.nrows * G <= 128 && s0 >= 0 && s0 < np_max && nblk >= 1 && nblk <= PF_SPLIT / PF_BN && g < n_kv && w.split < max_splits, err, 43);
     const CUtensorMap *mk = maps + 2 * w.seg, *mv = mk + 1;
     // rows of the 2-D views: K rows are 32 bytes (one dim of a tile), V rows 256 bytes (one position)
     const long long k_layer_rows = (long long)(r0.lk / 32), v_layer_rows = (long long)(r0.lv / 256);

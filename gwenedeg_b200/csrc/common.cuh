@@ -95,7 +95,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Wait for a phase of the barrier with a time limit (0.2 s, far beyond any healthy copy or MMA): on expiry the kernel
 // records `code` in *err and the caller carries on to its exit (results are then invalid and the host reports
 // RQ_CUDA_ERR_STATE).  Once any thread has recorded an expiry the other waits give up quickly as well.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *err, int code) {
+__device__ __forceinline__ bool mbar_wait_bounded_ns(uint64_t *bar, uint32_t parity, int *err, int code, unsigned long long limit_ns) {
     unsigned long long t0 = 0;
     for (int it = 0; it < (1 << 26); it++) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -104,11 +104,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
             if (t0 == 0) t0 = now;
             if (*reinterpret_cast<volatile int *>(err) != 0) return false;
-            if (now - t0 > 200000000ull) break;
+            if (now - t0 > limit_ns) break;
         }
     }
     atomicExch(err, code);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *err, int code) {
+    return mbar_wait_bounded_ns(bar, parity, err, code, 200000000ull);
 }
 // order earlier generic-proxy accesses of shared memory before later async-proxy (bulk copy) writes to it
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -119,6 +122,24 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+
+// ---- index checks of the debug build (make debug: -DRQ_DEBUG, librq_cuda_debug.so).  The conditions are uniform over
+// the CTA and sit before its first barrier: a CTA whose work item does not fit its row or cache records `code` in the
+// status word and returns (no trap, nothing is read or written out of range); the host then reports RQ_CUDA_ERR_STATE.
+// The release build compiles them away.
+#ifdef RQ_DEBUG
+#define RQ_CHECK(cond, err, code)                    \
+    do {                                             \
+        if (!(cond)) {                               \
+            if (threadIdx.x == 0) atomicExch(err, code); \
+            return;                                  \
+        }                                            \
+    } while (0)
+#else
+#define RQ_CHECK(cond, err, code) \
+    do {                          \
+    } while (0)
+#endif
 
 // ---- programmatic dependent launch: a kernel launched with launch_pdl may be scheduled while the kernel before it in
 // the stream still runs; it must call pdl_wait() before it touches global memory (the wait returns once the earlier

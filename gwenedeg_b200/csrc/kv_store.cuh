@@ -70,12 +70,14 @@ __device__ __forceinline__ void kv_store_elem(uint8_t *tile, int fmt, int half, 
 
 template <int HD>
 __global__ void __launch_bounds__(HD) kv_store_kernel(const PassRow *__restrict__ rows, int layer, int n_kv, int kvt,
-                                                      const float *__restrict__ k, const float *__restrict__ v) {
+                                                      const float *__restrict__ k, const float *__restrict__ v, int *err) {
     const int r = blockIdx.x, h = blockIdx.y, half = blockIdx.z, i = threadIdx.x;
     const float *src = half ? v : k;
     if (!src) return;
     const PassRow row = rows[r];
     const int pos = row.pos;
+    // (debug build) the position's tile lies inside one layer of the cache
+    RQ_CHECK(pos >= 0 && (kv_tile_index(pos, h, n_kv) + 1) * (size_t)kv_tile_bytes(kvt, HD, half) <= (half ? row.lv : row.lk), err, 44);
     uint8_t *tile = const_cast<uint8_t *>(half ? row.v : row.k) + (size_t)layer * (half ? row.lv : row.lk) +
                     kv_tile_index(pos, h, n_kv) * (size_t)kv_tile_bytes(kvt, HD, half);
     __shared__ float xs[HD];
@@ -92,10 +94,11 @@ template <int HD>
 __global__ void __launch_bounds__(HD) qk_norm_rope_store_kernel(const PassRow *__restrict__ rows, int layer, int n_kv, int n_heads, int kvt,
                                                                 float *__restrict__ q, int qh, const float *__restrict__ k,
                                                                 const float *__restrict__ v, const float *__restrict__ q_norm_w,
-                                                                const float *__restrict__ k_norm_w, int rd, float log_theta) {
+                                                                const float *__restrict__ k_norm_w, int rd, float log_theta, int *err) {
     const int r = blockIdx.x, y = blockIdx.y, i = threadIdx.x;
     const PassRow row = rows[r];
     const int pos = row.pos;
+    RQ_CHECK(pos >= 0 && (kv_tile_index(pos, 0, n_kv) + 1) * (size_t)kv_tile_bytes(kvt, HD, 0) <= row.lk, err, 45);
     __shared__ float xs[HD];
     __shared__ float red[HD / 32];
     const int kind = y < n_heads ? 0 : y < n_heads + n_kv ? 1 : 2;  // q, k, v

@@ -9,6 +9,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
 #include <new>
 #include <vector>
 
@@ -40,6 +41,8 @@ struct RqCudaSeq {
     float *ssm;            // [n_lin] layers of ssm_floats
     size_t ssm_floats;
     int in_pass;
+    unsigned long long stamp;  // number of the last pass_begin that listed this sequence (duplicate check)
+    bool dead;                 // rq_cuda_seq_free was called while the sequence belonged to the open pass: freed at pass_end
     // 2-D views of the K and V caches for the tensor-core prefill kernel (f16, head_dim 128)
     CUtensorMap tm_k, tm_v;
     bool has_tm;
@@ -56,6 +59,7 @@ struct RqCuda {
     unsigned long long launches;
     // the open pass
     int pass_open, nrows, nseg, total_blocks, pass_kvt, max_np;
+    unsigned long long pass_no;  // counts pass_begin calls (RqCudaSeq::stamp)
     std::vector<RqCudaSegment> segs;
     PassRow *h_rows, *d_rows;  // nrows + 1 entries (the last one holds the total block count)
     DnSeg *h_dseg, *d_dseg;
@@ -74,7 +78,6 @@ struct RqCuda {
     int *d_err;
     int *h_err;  // pinned
     int *err_fwd = nullptr;  // set around a launch whose merge kernel should store the status word to h_err itself
-    void *flush; size_t flush_bytes;
     // tensor-core prefill: the segments' tensor maps and the work list of the open pass
     CUtensorMap *h_maps, *d_maps;  // [max_rows][2]
     PfWork *d_work; size_t work_bytes;
@@ -168,7 +171,27 @@ static int grow(RqCuda *c, void **p, size_t *have, size_t need) {
     return RQ_CUDA_OK;
 }
 
+// A one-CTA kernel whose only work is a bounded wait on an mbarrier that nothing ever arrives at: the wait runs out after
+// `limit_ns`, records `code` in the status word and the kernel returns by itself (rq_cuda_selftest_wait_expiry).
+__global__ void wait_expiry_kernel(int *err, unsigned long long limit_ns, int code) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    mbar_wait_bounded_ns(&bar, 0, err, code, limit_ns);
+}
+
 extern "C" {
+
+int rq_cuda_debug_build(void) {
+#ifdef RQ_DEBUG
+    return 1;
+#else
+    return 0;
+#endif
+}
 
 int rq_cuda_device_count(void) {
     int n = 0;
@@ -193,6 +216,9 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
         if (m.dn_nk < 1 || m.dn_nv < 1 || m.dn_nv % m.dn_nk || m.dn_dk != 128 || m.dn_dv < 32 || m.dn_dv % 32 ||
             m.dn_conv < 2)
             return RQ_CUDA_ERR_ARG;
+        // the DeltaNet kernels read rows with 16-byte loads: a row of 2 nk dk + 2 nv dv + 2 nv floats has to be a multiple
+        // of 4 floats (an even number of value heads)
+        if ((2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv) % 4) return RQ_CUDA_ERR_ARG;
     }
     int ndev = rq_cuda_device_count();
     if (ndev < 1 || device < 0 || device >= ndev) return RQ_CUDA_ERR_DEVICE;
@@ -239,7 +265,7 @@ void rq_cuda_free(RqCuda *c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->d_dnw) cudaFree(c->d_dnw);
-    void *dev[] = {c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->flush, c->d_maps, c->d_work, c->d_dnwork};
+    void *dev[] = {c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
     if (c->h_maps) cudaFreeHost(c->h_maps);
     for (void *p : dev)
         if (p) cudaFree(p);
@@ -271,8 +297,45 @@ int rq_cuda_sync(RqCuda *c) {
     return RQ_CUDA_OK;
 }
 
+int rq_cuda_selftest_wait_expiry(RqCuda *c, unsigned int limit_us) {
+    if (!c || limit_us < 1 || limit_us > 1000000) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    wait_expiry_kernel<<<1, 32, 0, c->stream>>>(c->d_err, (unsigned long long)limit_us * 1000ull, 99);
+    c->launches++;
+    CU(c, cudaGetLastError());
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_reserve(RqCuda *c, int rows, long long positions_total, int max_ctx) {
+    if (!c || rows < 1 || rows > c->max_rows || positions_total < rows || max_ctx < 1) return c ? fail(c, RQ_CUDA_ERR_ARG, "reserve: %d rows", rows) : RQ_CUDA_ERR_ARG;
+    if (c->pass_open) return fail(c, RQ_CUDA_ERR_STATE, "reserve: a pass is open");
+    CU(c, cudaSetDevice(c->device));
+    int rc = RQ_CUDA_OK;
+    if (c->m.n_attn > 0) {
+        const size_t rec = (size_t)c->n_heads * RQ_PSTRIDE(c->m.head_dim) * 4;
+        const size_t blocks = (size_t)(positions_total / ATT_P) + rows;                       // decode: a record per 256-position block
+        const size_t splits = (size_t)rows * ((max_ctx + PF_SPLIT - 1) / PF_SPLIT);           // prefill: a record per (row, split)
+        const size_t need = std::max(blocks, splits) * rec;
+        if (need > ((size_t)8 << 30)) return fail(c, RQ_CUDA_ERR_ARG, "reserve: %zu MB of partial results", need >> 20);
+        const size_t qb = (size_t)rows * c->n_heads * c->qh * 4, ob = (size_t)rows * c->n_heads * c->m.head_dim * 4;
+        const size_t kb = (size_t)rows * c->n_kv * c->m.head_dim * 4;
+        if ((rc = grow(c, (void **)&c->d_part, &c->part_bytes, need))) return rc;
+        if ((rc = grow(c, (void **)&c->d_q, &c->q_bytes, qb))) return rc;
+        if ((rc = grow(c, (void **)&c->d_out, &c->out_bytes, ob))) return rc;
+        if ((rc = grow(c, (void **)&c->d_k, &c->k_bytes, kb))) return rc;
+        if ((rc = grow(c, (void **)&c->d_v, &c->v_bytes, kb))) return rc;
+    }
+    if (c->m.n_lin > 0) {
+        const RqCudaModel &m = c->m;
+        const size_t lw = (size_t)2 * m.dn_nk * m.dn_dk + (size_t)2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
+        if ((rc = grow(c, (void **)&c->d_dn, &c->dn_bytes, (size_t)rows * (lw + (size_t)m.dn_nv * m.dn_dv) * 4))) return rc;
+    }
+    return RQ_CUDA_OK;
+}
+
 int rq_cuda_set_stream(RqCuda *c, void *s) {
     if (!c) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
     CU(c, cudaStreamSynchronize(c->stream));
     c->stream = s ? (cudaStream_t)s : c->own_stream;
     return RQ_CUDA_OK;
@@ -329,6 +392,12 @@ int rq_cuda_seq_new(RqCuda *c, int capacity, int kv_type, RqCudaSeq **seq) {
 
 void rq_cuda_seq_free(RqCudaSeq *s) {
     if (!s) return;
+    if (s->in_pass) {
+        // the open pass still refers to the sequence (its row table points at the caches, pass_end updates its length):
+        // the memory goes when the pass is closed
+        s->dead = true;
+        return;
+    }
     cudaSetDevice(s->ctx->device);
     cudaStreamSynchronize(s->ctx->stream);
     if (s->k) cudaFree(s->k);
@@ -452,6 +521,7 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
     if (!seg || nseg < 1 || nseg > c->max_rows) return fail(c, RQ_CUDA_ERR_ARG, "%d segments", nseg);
     long total = 0;
     int kvt = -1;
+    const unsigned long long stamp = ++c->pass_no;  // (a refused call leaves its stamp behind: the next call uses a new one)
     for (int i = 0; i < nseg; i++) {
         const RqCudaSegment &g = seg[i];
         if (!g.seq || g.seq->ctx != c) return fail(c, RQ_CUDA_ERR_ARG, "segment %d: not a sequence of this context", i);
@@ -462,8 +532,8 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
         if (g.pos0 > g.seq->len)
             return fail(c, RQ_CUDA_ERR_ARG, "segment %d: position %d leaves a gap after the sequence's %d positions", i, g.pos0,
                         g.seq->len);
-        for (int j = 0; j < i; j++)
-            if (seg[j].seq == g.seq) return fail(c, RQ_CUDA_ERR_ARG, "segment %d: its sequence appears twice", i);
+        if (g.seq->stamp == stamp) return fail(c, RQ_CUDA_ERR_ARG, "segment %d: its sequence appears twice", i);
+        g.seq->stamp = stamp;
         if (kvt < 0) kvt = g.seq->kvt;
         else if (kvt != g.seq->kvt) return fail(c, RQ_CUDA_ERR_ARG, "segment %d: all sequences of a pass share one KV type", i);
         total += g.n;
@@ -527,10 +597,21 @@ int rq_cuda_pass_end(RqCuda *c, int commit) {
     for (auto &g : c->segs) {
         g.seq->in_pass = 0;
         if (commit) g.seq->len = std::max(g.seq->len, g.pos0 + g.n);
+        if (g.seq->dead) rq_cuda_seq_free(g.seq);  // freed by the host while the pass was open
     }
+    c->segs.clear();
     c->pass_open = 0;
     return RQ_CUDA_OK;
 }
+
+// The kernels read and write the callers' device rows with 16-byte accesses.
+static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+#define NEED_ALIGNED(c, what, ...)                                                                                   \
+    do {                                                                                                             \
+        const void *ps_[] = {__VA_ARGS__};                                                                           \
+        for (const void *p_ : ps_)                                                                                   \
+            if (!aligned16(p_)) return fail(c, RQ_CUDA_ERR_ARG, "%s: device pointers must be 16-byte aligned", what); \
+    } while (0)
 
 static int need_pass(RqCuda *c, int layer, int nlayers, const char *what) {
     if (!c) return RQ_CUDA_ERR_ARG;
@@ -543,12 +624,13 @@ int rq_cuda_kv_store_dev(RqCuda *c, int layer, const float *k, const float *v) {
     int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "kv_store");
     if (rc) return rc;
     if (!k && !v) return fail(c, RQ_CUDA_ERR_ARG, "kv_store: no rows");
+    NEED_ALIGNED(c, "kv_store", k, v);
     CU(c, cudaSetDevice(c->device));
     dim3 grid(c->nrows, c->n_kv, 2);
     switch (c->m.head_dim) {
-        case 64: kv_store_kernel<64><<<grid, 64, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->pass_kvt, k, v); break;
-        case 128: kv_store_kernel<128><<<grid, 128, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->pass_kvt, k, v); break;
-        default: kv_store_kernel<256><<<grid, 256, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->pass_kvt, k, v); break;
+        case 64: kv_store_kernel<64><<<grid, 64, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->pass_kvt, k, v, c->d_err); break;
+        case 128: kv_store_kernel<128><<<grid, 128, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->pass_kvt, k, v, c->d_err); break;
+        default: kv_store_kernel<256><<<grid, 256, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->pass_kvt, k, v, c->d_err); break;
     }
     c->launches++;
     CU(c, cudaGetLastError());
@@ -576,6 +658,7 @@ int rq_cuda_qk_norm_rope_store_dev(RqCuda *c, int layer, float *q, const float *
     int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "qk_norm_rope_store");
     if (rc) return rc;
     if (!q || !k || !v || !q_norm_w || !k_norm_w) return fail(c, RQ_CUDA_ERR_ARG, "qk_norm_rope_store: null argument");
+    NEED_ALIGNED(c, "qk_norm_rope_store", q, k, v, q_norm_w, k_norm_w);
     const int hd = c->m.head_dim;
     if (rope_dim < 2 || rope_dim > hd || (rope_dim & 1) || !(rope_theta > 1.0f))
         return fail(c, RQ_CUDA_ERR_ARG, "qk_norm_rope_store: %d rotated dims, base %g", rope_dim, (double)rope_theta);
@@ -584,7 +667,7 @@ int rq_cuda_qk_norm_rope_store_dev(RqCuda *c, int layer, float *q, const float *
     dim3 grid(c->nrows, c->n_heads + 2 * c->n_kv);
 #define PRODUCER(HD_)                                                                                                          \
     qk_norm_rope_store_kernel<HD_><<<grid, HD_, 0, c->stream>>>(c->d_rows, layer, c->n_kv, c->n_heads, c->pass_kvt, q, c->qh, k, v, \
-                                                                q_norm_w, k_norm_w, rope_dim, log_theta)
+                                                                q_norm_w, k_norm_w, rope_dim, log_theta, c->d_err)
     switch (hd) {
         case 64: PRODUCER(64); break;
         case 128: PRODUCER(128); break;
@@ -661,6 +744,7 @@ int rq_cuda_attn_decode_dev(RqCuda *c, int layer, const float *q, float *out) {
     int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_decode");
     if (rc) return rc;
     if (!q || !out) return fail(c, RQ_CUDA_ERR_ARG, "attn_decode: null rows");
+    NEED_ALIGNED(c, "attn_decode", q, out);
     CU(c, cudaSetDevice(c->device));
     return launch_decode(c, layer, q, out);
 }
@@ -722,7 +806,9 @@ int rq_cuda_attn_decode(RqCuda *c, int layer, const float *q, float *out) {
 // entry point sit in the fixed array below, part of the library's image on every GPU that loads it, until exit.
 #define RQ_NOALLOC_PART_BYTES ((size_t)32 << 20)
 static __device__ __align__(256) unsigned char g_noalloc_part[RQ_NOALLOC_PART_BYTES];
-static float *g_noalloc_ptr[64];  // per device: the array's device address (not the host-side symbol)
+// per device: the array's device address (not the host-side symbol).  Atomic: contexts of one device may be driven by
+// different host threads; two of them racing through the first call both store the same address.
+static std::atomic<float *> g_noalloc_ptr[64];
 
 size_t rq_cuda_attn_decode_noalloc_max_bytes(void) { return RQ_NOALLOC_PART_BYTES; }
 
@@ -730,6 +816,7 @@ int rq_cuda_attn_decode_noalloc(RqCuda *c, int layer, const float *q, float *out
     int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_decode_noalloc");
     if (rc) return rc;
     if (!q || !out) return fail(c, RQ_CUDA_ERR_ARG, "attn_decode_noalloc: null rows");
+    NEED_ALIGNED(c, "attn_decode_noalloc", q, out);
     size_t need = (size_t)c->total_blocks * c->n_heads * RQ_PSTRIDE(c->m.head_dim) * 4;
     if (need > RQ_NOALLOC_PART_BYTES)
         return fail(c, RQ_CUDA_ERR_ARG,
@@ -738,19 +825,21 @@ int rq_cuda_attn_decode_noalloc(RqCuda *c, int layer, const float *q, float *out
                     need, c->total_blocks, c->n_heads, (size_t)RQ_NOALLOC_PART_BYTES);
     if (c->device < 0 || c->device >= 64) return fail(c, RQ_CUDA_ERR_ARG, "attn_decode_noalloc: device %d", c->device);
     CU(c, cudaSetDevice(c->device));
-    if (!g_noalloc_ptr[c->device]) {
+    float *part = g_noalloc_ptr[c->device].load(std::memory_order_acquire);
+    if (!part) {
         // once per device, with that device current: the address the kernels can use (the name g_noalloc_part in
         // host code is only a handle for this query)
         void *p = nullptr;
         CU(c, cudaGetSymbolAddress(&p, g_noalloc_part));
-        g_noalloc_ptr[c->device] = (float *)p;
+        part = (float *)p;
+        g_noalloc_ptr[c->device].store(part, std::memory_order_release);
     }
     // nothing in the array has to start at zero: every record the merge reads was written by this call's first kernel
-    return launch_decode_with(c, layer, q, out, g_noalloc_ptr[c->device]);
+    return launch_decode_with(c, layer, q, out, part);
 }
 
 static int prefill_tables(RqCuda *c) {
-    // once per pass: the segments' tensor maps and the work list (M tile of 128 / G rows x 1024-position split) of the
+    // once per pass: the segments' tensor maps and the work list (M tile of 128 / G rows x PF_SPLIT-position split) of the
     // tensor-core prefill kernel; pf_ready 1: made, -1: the pass does not qualify (cache type, head_dim)
     if (c->pf_ready) return RQ_CUDA_OK;
     c->pf_ready = -1;
@@ -789,6 +878,10 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     if (c->pf_ready != 1) return launch_decode(c, layer, q, out);
     const int hd = c->m.head_dim;
     size_t need = (size_t)c->nrows * c->pf_max_splits * c->n_heads * RQ_PSTRIDE(hd) * 4;
+    if (need > ((size_t)8 << 30))
+        return fail(c, RQ_CUDA_ERR_ARG,
+                    "attn_prefill: %d rows x %d splits of %d positions x %d heads need %zu MB of partial results; pass fewer rows at once",
+                    c->nrows, c->pf_max_splits, PF_SPLIT, c->n_heads, need >> 20);
     int rc = grow(c, (void **)&c->d_part, &c->part_bytes, need);
     if (rc) return rc;
     AttnPrefillArgs a;
@@ -824,6 +917,7 @@ int rq_cuda_attn_prefill_dev(RqCuda *c, int layer, const float *q, float *out) {
     int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_prefill");
     if (rc) return rc;
     if (!q || !out) return fail(c, RQ_CUDA_ERR_ARG, "attn_prefill: null rows");
+    NEED_ALIGNED(c, "attn_prefill", q, out);
     CU(c, cudaSetDevice(c->device));
     return launch_prefill(c, layer, q, out);
 }
@@ -849,6 +943,7 @@ int rq_cuda_dn_rec_dev(RqCuda *c, int lin_layer, const float *rows, float *out) 
     int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_rec");
     if (rc) return rc;
     if (!rows || !out) return fail(c, RQ_CUDA_ERR_ARG, "dn_rec: null rows");
+    NEED_ALIGNED(c, "dn_rec", rows, out);
     CU(c, cudaSetDevice(c->device));
     const RqCudaModel &m = c->m;
     const int lw = 2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
@@ -864,6 +959,7 @@ int rq_cuda_dn_chunk_dev(RqCuda *c, int lin_layer, const float *rows, float *out
     int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_chunk");
     if (rc) return rc;
     if (!rows || !out) return fail(c, RQ_CUDA_ERR_ARG, "dn_chunk: null rows");
+    NEED_ALIGNED(c, "dn_chunk", rows, out);
     const RqCudaModel &m = c->m;
     if (m.dn_dk != 128 || m.dn_dv != 128) return fail(c, RQ_CUDA_ERR_ARG, "dn_chunk is built for dk = dv = 128");
     CU(c, cudaSetDevice(c->device));
@@ -963,6 +1059,7 @@ int rq_cuda_dn_prep_dev(RqCuda *c, int lin_layer, float *rows) {
     int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_prep");
     if (rc) return rc;
     if (!rows) return fail(c, RQ_CUDA_ERR_ARG, "dn_prep: null rows");
+    NEED_ALIGNED(c, "dn_prep", rows);
     const float *conv, *a, *dt, *norm;
     if ((rc = dn_weights(c, lin_layer, "dn_prep", &conv, &a, &dt, &norm))) return rc;
     CU(c, cudaSetDevice(c->device));
@@ -978,6 +1075,7 @@ int rq_cuda_dn_out_dev(RqCuda *c, int lin_layer, const float *rows, float *out) 
     int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_out");
     if (rc) return rc;
     if (!rows || !out) return fail(c, RQ_CUDA_ERR_ARG, "dn_out: null rows");
+    NEED_ALIGNED(c, "dn_out", rows, out);
     const float *conv, *a, *dt, *norm;
     if ((rc = dn_weights(c, lin_layer, "dn_out", &conv, &a, &dt, &norm))) return rc;
     CU(c, cudaSetDevice(c->device));
@@ -1011,6 +1109,7 @@ int rq_cuda_malloc_host(RqCuda *c, size_t bytes, void **host) {
 }
 int rq_cuda_mfree_host(RqCuda *c, void *host) {
     if (!c) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
     CU(c, cudaFreeHost(host));
     return RQ_CUDA_OK;
 }
@@ -1074,18 +1173,6 @@ int rq_cuda_profile_end(RqCuda *c, float *total_ms, int *launches) {
     }
     *total_ms = tot;
     *launches = c->prof_n;
-    return RQ_CUDA_OK;
-}
-
-int rq_cuda_flush_l2(RqCuda *c) {
-    if (!c) return RQ_CUDA_ERR_ARG;
-    CU(c, cudaSetDevice(c->device));
-    const size_t bytes = (size_t)256 << 20;  // twice the 126 MB L2
-    if (!c->flush) {
-        CU(c, cudaMalloc(&c->flush, bytes));
-        c->flush_bytes = bytes;
-    }
-    CU(c, cudaMemsetAsync(c->flush, 0x5a, c->flush_bytes, c->stream));
     return RQ_CUDA_OK;
 }
 

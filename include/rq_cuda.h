@@ -74,8 +74,22 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
 void rq_cuda_free(RqCuda *ctx);
 const char *rq_cuda_error(const RqCuda *ctx);
 int rq_cuda_device_count(void);
+/* 1 when the library was built with the kernels' index checks compiled in (make debug: librq_cuda_debug.so; a work item
+ * that does not fit its row or cache sets the status word instead of touching memory), 0 for the release build */
+int rq_cuda_debug_build(void);
 /* block until everything this context launched is complete; reports a device-side wait that expired as RQ_CUDA_ERR_STATE */
 int rq_cuda_sync(RqCuda *ctx);
+/* Sizes the context's scratch ahead of time, so that no pass up to the given size allocates or synchronises on its first
+ * use (the reference's scratch is sized for max_ctx when the context is made and grown on demand, ctx_check_seq
+ * forward.c:628-634; this is the same with the demand stated up front): passes of at most `rows` rows attending at most
+ * `positions_total` cached positions in all, no row beyond `max_ctx` positions.  Not inside an open pass. */
+int rq_cuda_reserve(RqCuda *ctx, int rows, long long positions_total, int max_ctx);
+/* Error-path self test (no counterpart in the reference; the reference checks everything before it starts work,
+ * forward.c:3773-3801, and has no device to wait for): launches one small kernel that waits, with a limit of `limit_us`
+ * microseconds, on a barrier nothing completes.  The kernel gives up by itself, records code 99 in the context's status
+ * word and returns; the next rq_cuda_sync then reports RQ_CUDA_ERR_STATE exactly as it would after an expired wait inside
+ * an attention kernel, and the context stays usable. */
+int rq_cuda_selftest_wait_expiry(RqCuda *ctx, unsigned int limit_us);
 /* run this context's work on a caller-owned stream (a cudaStream_t; NULL: back to the context's own, a non-blocking stream:
  * it is not ordered with the legacy default stream, whose handle is NULL as well).  The attention and DeltaNet kernels are
  * launched with programmatic stream serialization: each waits for the kernel before it in the stream before it touches
@@ -207,8 +221,6 @@ unsigned long long rq_cuda_launch_count(const RqCuda *ctx);
  * stream and returns the summed milliseconds and the number of launches timed (at most max_launches) */
 int rq_cuda_profile_begin(RqCuda *ctx, int max_launches);
 int rq_cuda_profile_end(RqCuda *ctx, float *total_ms, int *launches);
-/* write `bytes` of device scratch (evicts the L2 between timed iterations of small workloads) */
-int rq_cuda_flush_l2(RqCuda *ctx);
 
 #ifdef __cplusplus
 }

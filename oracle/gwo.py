@@ -1,8 +1,9 @@
 """ctypes binding of the two CPU checkers (test infrastructure; never imported by the product package).
 
 `load("port")` gives this repository's plain-C restatement (oracle/liboracle.so, built from gw_oracle.c);
-`load("ref")` gives the reference's own C code behind the same `gwo_*` ABI (oracle/_ref/libgwref.so, or the
-portable `-DRUNQ_GENERIC` build when the host CPU lacks an ISA flag the native build was compiled for).
+`load("ref")` gives the reference's own C code behind the same `gwo_*` ABI: the widest build under oracle/_ref
+that the host CPU can run (libgwref.so: the build host's -march=native; libgwref_v4.so: x86-64-v4, the AVX-512
+attention kernels on any AVX-512 host; libgwref_generic.so: the portable `-DRUNQ_GENERIC` kernels).
 Both are numpy-in / numpy-out.
 """
 import ctypes as C
@@ -19,15 +20,34 @@ T, P = 16, 256
 _vp, _i, _sz, _f, _d = C.c_void_p, C.c_int, C.c_size_t, C.c_float, C.c_double
 
 
-def _host_has_flags(path):
+def _host_flags():
     try:
-        want = set(open(path).read().split())
         for line in open("/proc/cpuinfo"):
             if line.startswith("flags"):
-                return want <= set(line.split(":", 1)[1].split())
+                return set(line.split(":", 1)[1].split())
     except OSError:
         pass
-    return False
+    return set()
+
+
+# /proc/cpuinfo flags a build at each ISA level may use (the x86-64 psABI levels)
+_V3 = {"avx", "avx2", "bmi1", "bmi2", "f16c", "fma", "abm", "movbe", "xsave"}
+_V4 = _V3 | {"avx512f", "avx512bw", "avx512cd", "avx512dq", "avx512vl"}
+
+
+def ref_variants():
+    """The reference builds under oracle/_ref, widest ISA first: (path, the host flags it needs)."""
+    d = os.path.join(HERE, "_ref")
+    try:
+        native = set(open(os.path.join(d, "cpuflags.txt")).read().split())  # everything the build host had
+    except OSError:
+        native = None
+    out = []
+    if native is not None:
+        out.append((os.path.join(d, "libgwref.so"), native))
+    out.append((os.path.join(d, "libgwref_v4.so"), _V4))
+    out.append((os.path.join(d, "libgwref_generic.so"), _V3))
+    return [(p, f) for p, f in out if os.path.exists(p)]
 
 
 def build_port():
@@ -35,13 +55,12 @@ def build_port():
 
 
 def ref_path():
-    """Path of the loadable reference build, or None."""
-    native = os.path.join(HERE, "_ref", "libgwref.so")
-    generic = os.path.join(HERE, "_ref", "libgwref_generic.so")
-    if os.path.exists(native) and _host_has_flags(os.path.join(HERE, "_ref", "cpuflags.txt")):
-        return native
-    if os.path.exists(generic):
-        return generic
+    """Path of the widest reference build this host can run (native build, then the AVX-512 baseline x86-64-v4, then
+    the portable -DRUNQ_GENERIC one), or None."""
+    have = _host_flags()
+    for path, need in ref_variants():
+        if need <= have:
+            return path
     return None
 
 
@@ -97,6 +116,11 @@ class Oracle:
         L.gwo_bench_dn.argtypes = [_vp, _i, _vp, _vp, _sz, _vp, _sz, _i, _i, _vp]
         L.gwo_bench_dn.restype = _d
         self.kind = "ref" if L.gwo_kind() == 1 else "port"
+        isa = L.gwo_isa()
+        # which attention kernels the library was compiled with (gwo_isa bit 0: the reference's AVX-512 kernels,
+        # RUNQ_ATT512; bit 1: hardware fused multiply-add)
+        self.isa = ("avx512 attention kernels (RUNQ_ATT512)" if isa & 1 else "portable C kernels") + (", fma" if isa & 2 else "")
+        self.library = os.path.relpath(path, os.path.dirname(HERE))
 
     # ---- helpers
     @staticmethod
@@ -273,8 +297,9 @@ _cache = {}
 
 
 def load(which="port"):
-    """which: 'port' (the restatement; built on demand), 'ref' (the reference's code; None when absent),
-    'ref-generic' (its portable build; None when absent)."""
+    """which: 'port' (the restatement; built on demand), 'ref' (the reference's code, the widest build the host can run;
+    None when absent), 'ref-v4' (its AVX-512 baseline build) and 'ref-generic' (its portable build): None when absent or
+    not runnable on this host."""
     if which in _cache:
         return _cache[which]
     if which == "port":
@@ -284,9 +309,10 @@ def load(which="port"):
             build_port()
     elif which == "ref":
         path = ref_path()
-    elif which == "ref-generic":
-        path = os.path.join(HERE, "_ref", "libgwref_generic.so")
-        path = path if os.path.exists(path) else None
+    elif which in ("ref-generic", "ref-v4"):
+        path = os.path.join(HERE, "_ref", "libgwref_generic.so" if which == "ref-generic" else "libgwref_v4.so")
+        need = _V3 if which == "ref-generic" else _V4
+        path = path if os.path.exists(path) and need <= _host_flags() else None
     else:
         raise ValueError(which)
     _cache[which] = Oracle(path) if path else None

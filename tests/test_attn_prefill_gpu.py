@@ -7,7 +7,7 @@ Q and the softmax weights are rounded to f16 for the tensor cores, so the compar
 import numpy as np
 import pytest
 
-from tests.helpers import assert_close, errors
+from tests.helpers import assert_close, bit_equal, errors
 
 pytestmark = pytest.mark.gpu
 F16 = 2
@@ -27,7 +27,7 @@ def fill_seq(c, n, n_kv, hd, seed):
 
 @pytest.mark.parametrize("n_heads,n_kv", [(16, 8), (32, 8), (8, 8), (16, 2)])
 def test_chunk_over_prefix_matches_cpu(checker, n_heads, n_kv):
-    """A chunk of rows over a cached prefix, crossing the 1024-position split edge and the tile edges."""
+    """A chunk of rows over a cached prefix, crossing tile and 256-block edges (the 2,048-position split edge is crossed in test_short_rows_and_mixed_segments)."""
     import gwenedeg_b200 as g
     from gwenedeg_b200 import synth
     hd, n = 128, 1300
@@ -79,8 +79,12 @@ def test_config2_shape_one_layer(checker):
     q = synth.normal(13, (512, n_heads, hd))
     c.pass_begin([(s, 3584, 512)])
     got = c.attn_prefill(0, q)
+    exact = c.attn_decode(0, q)  # the split-K kernels on the same rows: the CPU code's bits
     c.pass_end(commit=False)
     rows = [0, 1, 63, 64, 255, 511]  # the CPU checker on a few rows (the full chunk takes it a while)
     want = checker.attention(F16, s.read_kv(0, 0), s.read_kv(0, 1), n_kv, n_heads, hd, q[rows], np.array([3585 + r for r in rows], np.int32))
     assert_close(got[rows], want, "config-2 rows")
+    assert bit_equal(exact[rows], want), "the split-K path is expected to equal the CPU code bit for bit"
+    # every one of the 512 rows x 16 heads against the bit-exact path
+    assert_close(got, exact, "config-2, all rows")
     c.close()

@@ -205,3 +205,49 @@ def test_prep_chunk_out_pipeline_matches_cpu(checker):
         assert rl <= REL_L2 and ma <= MAX_ABS * max(1.0, float(np.abs(fin_cpu).max())), f"rows {lo}..{hi}: max-abs {ma:.3g}, rel-L2 {rl:.3g}"
     assert_close(s.read_state(0)[d.conv_floats:].reshape(-1, 128), st[d.conv_floats:].reshape(-1, 128), "state after the pipeline")
     c.close()
+
+
+def _rows_fast(seed, n, nk, nv, dk, dv):
+    """Post-prep rows with the distributions of synth.deltanet_rows from numpy's generator (the hash-based one takes most
+    of a minute for 8,192 rows of 16 heads; these inputs only have to be the same for the GPU and the CPU)."""
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((n, nk, dk))
+    k = rng.standard_normal((n, nk, dk))
+    q = q / np.sqrt((q * q).sum(-1, keepdims=True) + 1e-6) / np.sqrt(dk)
+    k = k / np.sqrt((k * k).sum(-1, keepdims=True) + 1e-6)
+    v, z = rng.standard_normal((n, nv * dv)), rng.standard_normal((n, nv * dv))
+    eg = np.exp(-np.log1p(np.exp(rng.standard_normal((n, nv)))))
+    beta = 1.0 / (1.0 + np.exp(-rng.standard_normal((n, nv))))
+    return np.concatenate([q.reshape(n, -1), k.reshape(n, -1), v, z, eg, beta], axis=1).astype(np.float32)
+
+
+def test_chunked_form_at_hybrid_stack_size(checker):
+    """The chunked form at the size of the Qwen3.5-style configuration: one sequence of 8,192 tokens (128 chunks) in
+    prompt passes of 512 rows, 16 key heads and 16 value heads of 128 x 128, against the token recurrence of the CPU code
+    (dn_rec_run, reference src/forward.c:2224).  The form rounds its operands and a copy of the state to f16 in every
+    chunk: outputs of every pass and the state after the last one have to stay inside the bar after 128 chunks."""
+    import gwenedeg_b200 as g
+    from oracle import gwo
+    nk = nv = 16
+    dk = dv = 128
+    tokens, chunk = 8192, 512
+    checker.threads(0)
+    c = g.Context(0, n_lin=1, dn_nk=nk, dn_nv=nv, dn_dk=dk, dn_dv=dv, max_rows=chunk)
+    d = gwo.DeltaNet(checker, nk, nv, dk, dv)
+    rows = _rows_fast(5, tokens, nk, nv, dk, dv)
+    s = c.new_seq(tokens, 2)
+    st = d.new_state()
+    worst = (0.0, 0.0)
+    for pos in range(0, tokens, chunk):
+        c.pass_begin([(s, pos, chunk)])
+        got = c.dn_chunk(0, rows[pos:pos + chunk])
+        c.pass_end()
+        want = d.rec(st, rows[pos:pos + chunk], pos == 0)
+        assert_close(got, want, f"rows {pos}..{pos + chunk - 1}")
+        ma, rl = errors(got, want)
+        worst = (max(worst[0], ma), max(worst[1], rl))
+    gs, ws = s.read_state(0)[d.conv_floats:].reshape(-1, 128), st[d.conv_floats:].reshape(-1, 128)
+    assert_close(gs, ws, "state after 8,192 tokens")
+    print("chunked DeltaNet, 8192 tokens x 16 heads: outputs max-abs %.3g rel-L2 %.3g (worst pass); state max-abs %.3g rel-L2 %.3g"
+          % (worst + errors(gs, ws)))
+    c.close()

@@ -20,7 +20,7 @@ def digest(a):
 
 def checkers():
     out = [("port", gwo.load("port"))]
-    for w in ("ref", "ref-generic"):
+    for w in ("ref", "ref-v4", "ref-generic"):
         o = gwo.load(w)
         if o is not None:
             out.append((w, o))

@@ -11,7 +11,7 @@ def beq(a, b):
     return np.array_equal(np.ascontiguousarray(a, np.float32).view(np.uint32), np.ascontiguousarray(b, np.float32).view(np.uint32))
 
 
-@pytest.mark.parametrize("which", ["ref", "ref-generic"])
+@pytest.mark.parametrize("which", ["ref", "ref-v4", "ref-generic"])
 @pytest.mark.parametrize("kvt,hd,n_kv,n_heads,gated", [(gwo.F16, 128, 2, 4, False), (gwo.Q8, 128, 2, 8, False), (gwo.Q4, 128, 1, 2, True),
                                                         (gwo.Q4K4, 64, 2, 2, False), (gwo.F32, 64, 1, 2, False), (gwo.F16, 256, 1, 4, True),
                                                         (gwo.Q8, 256, 1, 2, False)])
@@ -50,7 +50,7 @@ def test_attention_and_codec_pinned(which, kvt, hd, n_kv, n_heads, gated):
     assert beq(ref.o_unrot(kvt, q[0, 0, :hd], hd), port.o_unrot(kvt, q[0, 0, :hd], hd))
 
 
-@pytest.mark.parametrize("which", ["ref", "ref-generic"])
+@pytest.mark.parametrize("which", ["ref", "ref-v4", "ref-generic"])
 def test_deltanet_pinned(which):
     ref, port = gwo.load(which), gwo.load("port")
     if ref is None:

@@ -35,7 +35,12 @@ def test_noalloc_entry_matches_regular_entry():
             q = synth.normal(900 + call, (len(ctxs), n_heads, hd))
             c.h2d(q_dev, q)
             c.check(L.rq_cuda_attn_decode_dev(c.h, 0, C.c_void_p(q_dev), C.c_void_p(out_a)))
+            free_before = c.mem_info()[0]
             c.check(L.rq_cuda_attn_decode_noalloc(c.h, 0, C.c_void_p(q_dev), C.c_void_p(out_b)))
+            if call == 1:
+                # the second call (kernels and the array's address are in place after the first) takes no device memory
+                c.sync()
+                assert c.mem_info()[0] == free_before
             a, b = np.empty((len(ctxs), n_heads, hd), np.float32), np.empty((len(ctxs), n_heads, hd), np.float32)
             c.d2h(a, out_a)
             c.d2h(b, out_b)
