@@ -630,17 +630,18 @@ __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const Pass
     }
 }
 
-// The same merge for rows with few partials each (the tensor-core prefill path: head_dim 128, 16-bit cache, one
-// partial per split of PF_SPLIT = 2,048 positions): one warp per (row, query head), lane L holds dims 4L .. 4L + 3, so a launch is a
-// few hundred CTAs instead of one per output row.  Arithmetic as attn_combine_kernel: M = max of the m_b,
-// c_b = exp_att(m_b - M), L and out as fma chains in partial order, out * (1 / L), gate.
+// The same merge for rows with few partials each (the tensor-core prefill path: head_dim 128 or 256, 16-bit cache, one
+// partial per split of PF_SPLIT = 2,048 positions): one warp per (row, query head), lane L holds dims 4L .. 4L + 3 of every
+// 128-dim part of the row, so a launch is a few hundred CTAs instead of one per output row.  Arithmetic as
+// attn_combine_kernel: M = max of the m_b, c_b = exp_att(m_b - M), L and out as fma chains in partial order, out * (1 / L), gate.
 constexpr int COMBINE_ROWS_WARPS = 8;
 template <int HD>
 __global__ void __launch_bounds__(32 * COMBINE_ROWS_WARPS) attn_combine_rows_kernel(const PassRow *__restrict__ rows, int nrows, int n_heads,
                                                                                  const float *__restrict__ part, const float *__restrict__ q,
                                                                                  int qh, int gated, float *__restrict__ out, int split_len,
                                                                                  int fixed_stride, const int *err_src, int *err_dst) {
-    static_assert(HD == 128, "a lane holds 4 of the row's 128 dims");
+    static_assert(HD % 128 == 0, "a lane holds 4 dims of every 128 of the row");
+    constexpr int NP = HD / 128;
     const int wi = blockIdx.x * COMBINE_ROWS_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     pdl_wait();
     pdl_launch_dependents();
@@ -650,32 +651,45 @@ __global__ void __launch_bounds__(32 * COMBINE_ROWS_WARPS) attn_combine_rows_ker
     const int nb = (rows[r].np + split_len - 1) / split_len;
     const size_t pst = RQ_PSTRIDE(HD), bstride = (size_t)n_heads * pst;
     const float *p0 = part + ((size_t)r * fixed_stride * n_heads + h) * pst;
-    float4 res;
+    float4 res[NP];
     if (nb == 1) {
         const float inv = 1.0f / p0[HD + 1];
-        const float4 o = *reinterpret_cast<const float4 *>(p0 + 4 * lane);
-        res = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+#pragma unroll
+        for (int c = 0; c < NP; c++) {
+            const float4 o = *reinterpret_cast<const float4 *>(p0 + 128 * c + 4 * lane);
+            res[c] = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+        }
     } else {
         float M = -INFINITY;
         for (int b = 0; b < nb; b++) M = fmaxf(M, p0[b * bstride + HD]);
         float L = 0.0f;
-        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float4 acc[NP];
+#pragma unroll
+        for (int c = 0; c < NP; c++) acc[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 4
         for (int b = 0; b < nb; b++) {
             const float *pb = p0 + b * bstride;
-            const float4 o = *reinterpret_cast<const float4 *>(pb + 4 * lane);
             const float cb = exp_att(pb[HD] - M);
             L = fmaf(cb, pb[HD + 1], L);
-            acc.x = fmaf(cb, o.x, acc.x), acc.y = fmaf(cb, o.y, acc.y), acc.z = fmaf(cb, o.z, acc.z), acc.w = fmaf(cb, o.w, acc.w);
+#pragma unroll
+            for (int c = 0; c < NP; c++) {
+                const float4 o = *reinterpret_cast<const float4 *>(pb + 128 * c + 4 * lane);
+                acc[c].x = fmaf(cb, o.x, acc[c].x), acc[c].y = fmaf(cb, o.y, acc[c].y), acc[c].z = fmaf(cb, o.z, acc[c].z), acc[c].w = fmaf(cb, o.w, acc[c].w);
+            }
         }
         const float inv = 1.0f / L;
-        res = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+#pragma unroll
+        for (int c = 0; c < NP; c++) res[c] = make_float4(acc[c].x * inv, acc[c].y * inv, acc[c].z * inv, acc[c].w * inv);
     }
-    if (gated) {
-        const float4 gq = *reinterpret_cast<const float4 *>(q + ((size_t)r * n_heads + h) * qh + HD + 4 * lane);
-        res.x = res.x * sigmoid_att(gq.x), res.y = res.y * sigmoid_att(gq.y), res.z = res.z * sigmoid_att(gq.z), res.w = res.w * sigmoid_att(gq.w);
+#pragma unroll
+    for (int c = 0; c < NP; c++) {
+        if (gated) {
+            const float4 gq = *reinterpret_cast<const float4 *>(q + ((size_t)r * n_heads + h) * qh + HD + 128 * c + 4 * lane);
+            res[c].x = res[c].x * sigmoid_att(gq.x), res[c].y = res[c].y * sigmoid_att(gq.y), res[c].z = res[c].z * sigmoid_att(gq.z),
+            res[c].w = res[c].w * sigmoid_att(gq.w);
+        }
+        *reinterpret_cast<float4 *>(out + ((size_t)r * n_heads + h) * HD + 128 * c + 4 * lane) = res[c];
     }
-    *reinterpret_cast<float4 *>(out + ((size_t)r * n_heads + h) * HD + 4 * lane) = res;
 }
 
 }  // namespace rq

@@ -15,7 +15,7 @@
 
 #include "../../include/rq_cuda.h"
 #include "attn_decode.cuh"
-#include "attn_prefill.cuh"
+#include "attn_prefill256.cuh"
 #include "deltanet.cuh"
 #include "deltanet_chunk.cuh"
 #include "kv_store.cuh"
@@ -128,22 +128,24 @@ static TmEncodeFn tm_encode() {
 }
 
 static bool seq_make_maps(RqCuda *c, RqCudaSeq *s) {
-    // K: rows of 16 positions x one dim (32 bytes), 32-byte swizzle, box 16 x 256 (two tiles);
-    // V: rows of one position x 128 dims (256 bytes), 128-byte swizzle, box 64 x 128
+    // K: rows of 16 positions x one dim (32 bytes), 32-byte swizzle, box 16 x 256 (two tiles of head_dim 128) or 16 x 128 (the
+    // 128-dim half of one tile of head_dim 256);
+    // V: rows of one position x head_dim dims (256 or 512 bytes), 128-byte swizzle, box 64 x 128
     s->has_tm = false;
-    if (s->kvt != KV_F16 || c->m.head_dim != 128 || c->m.n_attn < 1) return true;
+    const int hd = c->m.head_dim;
+    if (s->kvt != KV_F16 || (hd != 128 && hd != 256) || c->m.n_attn < 1) return true;
     TmEncodeFn enc = tm_encode();
     if (!enc) return false;
     cuuint32_t es[2] = {1, 1};
     {
         cuuint64_t dims[2] = {16, (cuuint64_t)(s->lk * c->m.n_attn / 32)}, strides[1] = {32};
-        cuuint32_t box[2] = {16, 256};
+        cuuint32_t box[2] = {16, hd == 128 ? 256u : 128u};
         if (enc(&s->tm_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, s->k, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return false;
     }
     {
-        cuuint64_t dims[2] = {128, (cuuint64_t)(s->lv * c->m.n_attn / 256)}, strides[1] = {256};
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)(s->lv * c->m.n_attn / (2 * hd))}, strides[1] = {(cuuint64_t)(2 * hd)};
         cuuint32_t box[2] = {64, 128};
         if (enc(&s->tm_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, s->v, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -843,7 +845,7 @@ static int prefill_tables(RqCuda *c) {
     // tensor-core prefill kernel; pf_ready 1: made, -1: the pass does not qualify (cache type, head_dim)
     if (c->pf_ready) return RQ_CUDA_OK;
     c->pf_ready = -1;
-    if (c->m.head_dim != 128 || c->pass_kvt != KV_F16) return RQ_CUDA_OK;
+    if ((c->m.head_dim != 128 && c->m.head_dim != 256) || c->pass_kvt != KV_F16) return RQ_CUDA_OK;
     for (auto &g : c->segs)
         if (!g.seq->has_tm) return RQ_CUDA_OK;
     const int rpt = 128 / c->G, nseg = (int)c->segs.size();
@@ -871,7 +873,7 @@ static int prefill_tables(RqCuda *c) {
 }
 
 static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
-    // tensor-core tiles where the pass qualifies (f16 cache, head_dim 128); other shapes take the split-K kernels,
+    // tensor-core tiles where the pass qualifies (f16 cache, head_dim 128 or 256); other shapes take the split-K kernels,
     // which compute the same attention on the CUDA cores
     int rc0 = prefill_tables(c);
     if (rc0) return rc0;
@@ -901,14 +903,19 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     a.err = c->d_err;
     const bool prof = c->prof_on && (size_t)(2 * c->prof_n + 2) <= c->prof_ev.size();
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n], c->stream);
-    cudaError_t e = launch_attn_prefill(a, c->stream);
+    cudaError_t e = hd == 128 ? launch_attn_prefill(a, c->stream) : launch_attn_prefill_hd256(a, c->stream);
     if (e != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "prefill attention launch: %s", cudaGetErrorString(e));
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n++ + 1], c->stream);
     c->launches++;
-    // (this path is head_dim 128 over a 16-bit cache: a warp per output row merges its few partials)
+    // (a warp per output row merges its few partials, and applies the output gate)
     const int nout = c->nrows * c->n_heads;
-    CU(c, launch_pdl(attn_combine_rows_kernel<128>, dim3((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), dim3(32 * COMBINE_ROWS_WARPS), 0, c->stream,
-                     c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh, c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd));
+    const dim3 cgrid((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), cblock(32 * COMBINE_ROWS_WARPS);
+    if (hd == 128)
+        CU(c, launch_pdl(attn_combine_rows_kernel<128>, cgrid, cblock, 0, c->stream, c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh,
+                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd));
+    else
+        CU(c, launch_pdl(attn_combine_rows_kernel<256>, cgrid, cblock, 0, c->stream, c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh,
+                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd));
     c->launches++;
     return RQ_CUDA_OK;
 }

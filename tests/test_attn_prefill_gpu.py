@@ -25,6 +25,62 @@ def fill_seq(c, n, n_kv, hd, seed):
     return s
 
 
+@pytest.mark.parametrize("n_heads,n_kv,gated", [(16, 4, True), (4, 2, False), (8, 1, True), (3, 3, False)])
+def test_head_dim_256_chunks_match_cpu(checker, n_heads, n_kv, gated):
+    """The head_dim 256 tensor-core kernel (K / V staged in 128-dim halves, one O accumulator): a chunk from position 0, a
+    chunk over a prefix that crosses the 2,048-position split edge, and a decode row of another sequence in one pass;
+    with and without the sigmoid output gate, 1, 2, 4 and 8 query heads per KV head."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    hd = 256
+    c = g.Context(0, n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, gated=gated)
+    a = fill_seq(c, 150, n_kv, hd, 21)
+    b = fill_seq(c, 2300, n_kv, hd, 23)
+    d = fill_seq(c, 700, n_kv, hd, 25)
+    segs = [(a, 0, 150), (b, 1990, 210), (d, 699, 1)]
+    qh = hd * (2 if gated else 1)
+    q = synth.normal(19, (361, n_heads, qh))
+    c.pass_begin(segs)
+    got = c.attn_prefill(0, q)
+    exact = c.attn_decode(0, q)  # the split-K kernels on the same rows: the CPU code's bits
+    c.pass_end(commit=False)
+    assert_close(got, exact, "head_dim 256 against the split-K path")
+    r = 0
+    for s, pos0, n in segs:
+        pick = sorted(set(i for i in (0, 1, n // 2, n - 1) if i < n))
+        want = checker.attention(F16, s.read_kv(0, 0), s.read_kv(0, 1), n_kv, n_heads, hd, q[r:r + n][pick],
+                                 np.array([pos0 + 1 + i for i in pick], np.int32), gated=gated)
+        assert_close(got[r:r + n][pick], want, f"segment at {pos0}")
+        assert bit_equal(exact[r:r + n][pick], want)
+        r += n
+    print("hd256 prefill errors", errors(got, exact))
+    c.close()
+
+
+def test_hybrid_stack_gated_attention_chunk(checker):
+    """The Qwen3.5-style gated attention layer at its benchmark shape: 16 query / 4 KV heads x 256, 512 new rows over a
+    7,680-position f16 prefix (four splits of 2,048 keys), sigmoid output gate; every row against the bit-exact split-K path,
+    a few against the CPU code."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    n_heads, n_kv, hd = 16, 4, 256
+    c = g.Context(0, n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, gated=True)
+    s = c.new_seq(8192, F16)
+    s.fill_synthetic(8192, 31)
+    q = synth.normal(33, (512, n_heads, 2 * hd))
+    c.pass_begin([(s, 7680, 512)])
+    got = c.attn_prefill(0, q)
+    exact = c.attn_decode(0, q)
+    c.pass_end(commit=False)
+    assert_close(got, exact, "gated head_dim 256, all rows")
+    rows = [0, 31, 32, 255, 511]
+    want = checker.attention(F16, s.read_kv(0, 0), s.read_kv(0, 1), n_kv, n_heads, hd, q[rows], np.array([7681 + r for r in rows], np.int32), gated=True)
+    assert_close(got[rows], want, "gated head_dim 256 rows against the CPU code")
+    assert bit_equal(exact[rows], want)
+    print("hybrid-stack gated attention errors", errors(got, exact))
+    c.close()
+
+
 @pytest.mark.parametrize("n_heads,n_kv", [(16, 8), (32, 8), (8, 8), (16, 2)])
 def test_chunk_over_prefix_matches_cpu(checker, n_heads, n_kv):
     """A chunk of rows over a cached prefix, crossing tile and 256-block edges (the 2,048-position split edge is crossed in test_short_rows_and_mixed_segments)."""
