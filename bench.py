@@ -210,6 +210,61 @@ def prefill_leg(device, steps, layers=None, warm=3):
                          "peak_source": how, "kernel": "attn_prefill_kernel", "flops_per_launch": flops_layer, "launches_timed": kern_n}}
 
 
+GA_LAYERS, GA_HEADS, GA_KV, GA_HD, GA_SEQ, GA_TOKENS, GA_CHUNK = 6, 16, 4, 256, 4, 8192, 512
+
+
+def prefill_hd256_leg(device, steps, small=False):
+    """The gated attention layers of the Qwen3.5-style hybrid stack as a prompt pass: 6 layers x (16 query / 4 KV heads,
+    head_dim 256, sigmoid output gate), 4 sequences x 8,192 tokens in chunks of 512 rows per sequence over the f16 cache
+    (the K / V rows of a chunk are in the cache when its attention runs).  TFLOP/s with 4 x head_dim flops per causal
+    (query, key) pair per query head; `roofline` times the tensor-core kernel alone with events around its launches."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    layers, tokens = (2, 2048) if small else (GA_LAYERS, GA_TOKENS)
+    c = g.Context(device, n_attn=layers, n_heads=GA_HEADS, n_kv_heads=GA_KV, head_dim=GA_HD, gated=True, max_rows=GA_SEQ * GA_CHUNK)
+    seqs = []
+    for i in range(GA_SEQ):
+        s = c.new_seq(tokens, g.KV_F16)
+        s.fill_synthetic(tokens, 900 + i)
+        seqs.append(s)
+    q = synth.normal(15, (GA_SEQ * GA_CHUNK, GA_HEADS, 2 * GA_HD))
+    q_dev, out_dev = c.to_device(q), c.malloc(q.nbytes // 2)
+    c.reserve(GA_SEQ * GA_CHUNK, GA_SEQ * GA_CHUNK * tokens, tokens)
+
+    def prompt():
+        for p0 in range(0, tokens, GA_CHUNK):
+            c.pass_begin([(s, p0, GA_CHUNK) for s in seqs])
+            for l in range(layers):
+                c.attn_prefill_dev(l, q_dev, out_dev)
+            c.pass_end(commit=False)
+
+    prompt()
+    c.sync()
+    c.timer_start()
+    for _ in range(steps):
+        prompt()
+    ms = c.timer_stop()
+    c.profile_begin(steps * layers * (tokens // GA_CHUNK))
+    for _ in range(steps):
+        prompt()
+    c.sync()
+    kern_ms, kern_n = c.profile_end()
+    c.close()
+    pairs = tokens * (tokens + 1) // 2
+    flops_prompt = 4.0 * GA_HD * GA_HEADS * GA_SEQ * pairs * layers
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, how = float(json.load(f)["bf16_tflops"]), "measured (burst)"
+    except Exception:
+        peak, how = 1590.0, "fallback"
+    tf_all = flops_prompt * steps / (ms * 1e-3) / 1e12
+    tf_kern = flops_prompt * steps / (kern_ms * 1e-3) / 1e12
+    return {"workload": "qwen3.5-gated-attention-prefill-4x8192-chunks-of-512", "layers": layers, "tokens": tokens, "tflops": tf_all,
+            "ms_per_prompt_all_layers": ms / steps, "tokens_per_s": GA_SEQ * tokens * steps / (ms * 1e-3),
+            "roofline": {"bound": "tensor", "achieved": tf_kern, "peak": peak, "unit": "TFLOP/s", "frac": tf_kern / peak, "traffic": None,
+                         "peak_source": how, "kernel": "attn_prefill_hd256_kernel", "flops_per_prompt": flops_prompt, "launches_timed": kern_n}}
+
+
 Q8_SEQ, Q8_CTX = 32, 40960
 # bytes of K + V per position per layer: 8-bit half = int8 levels + a bf16 scale per 32 dims, 4-bit half = nibbles + the same
 # scales; q8 = both halves 8-bit (2,176 B), q4 = K 8-bit, V 4-bit (1,664 B), q4k4 = both 4-bit (1,152 B)
@@ -515,12 +570,16 @@ def run_ours(args, rank, local_rank, world):
     achieved = reduce_sum(achieved) / world  # mean over ranks of the per-GPU figure
 
     c.close()
-    prefill = deltanet = None
+    prefill = prefill_hd256 = deltanet = None
     if world == 1 and not args.small:  # the other workloads ride on the one-GPU line only (each has its own --workload for N > 1)
         try:
             prefill = prefill_leg(local_rank, max(2, min(args.steps, 5)))
         except Exception as e:
             prefill = {"error": repr(e)}
+        try:
+            prefill_hd256 = prefill_hd256_leg(local_rank, 2)
+        except Exception as e:
+            prefill_hd256 = {"error": repr(e)}
         try:
             d = deltanet_leg(local_rank, 1)
             deltanet = {k: d[k] for k in ("metric", "value", "unit", "ms_per_step", "config", "form", "tflops", "roofline", "exact_recurrence")}
@@ -551,6 +610,7 @@ def run_ours(args, rank, local_rank, world):
                          "algorithmic_bytes_per_launch_rank0": bytes_per_launch, "launches_timed": part_n},
             "cpu_baseline": cpu,
             "prefill": prefill,
+            "prefill_hd256": prefill_hd256,
             "deltanet": deltanet,
         }
         print(json.dumps(line), flush=True)
@@ -565,7 +625,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode-q8", "decode-q4", "decode-q4k4", "deltanet"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill-hd256", "decode-q8", "decode-q4", "decode-q4k4", "deltanet"],
                     help="decode: the headline batched-decode benchmark (default); prefill: only the chunked-prefill leg "
                          "(512 rows over a 3584-position prefix), printed as its own line")
     ap.add_argument("--shard-of", type=int, default=1,
@@ -592,6 +652,14 @@ def main():
         line = deltanet_leg(local_rank, args.steps, small=args.small, rank=rank, world=world)
         if rank == 0:
             print(json.dumps(line), flush=True)
+        return
+    if args.workload == "prefill-hd256":
+        if rank == 0:
+            r = prefill_hd256_leg(local_rank, args.steps, small=args.small)
+            print(json.dumps({"metric": "Qwen3.5 gated attn (head_dim 256): prefill TFLOP/s (4 x 8192 in chunks of 512)", "value": r["tflops"],
+                              "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": 1, "higher_is_better": True, "dtype": "f16",
+                              "data": "synthetic", "config": {"workload": r["workload"], "layers": r["layers"], "tokens": r["tokens"]},
+                              "ms_per_step": r["ms_per_prompt_all_layers"], "tokens_per_s": r["tokens_per_s"], "roofline": r["roofline"]}), flush=True)
         return
     if args.workload == "prefill":
         if rank == 0:

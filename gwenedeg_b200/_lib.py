@@ -39,6 +39,7 @@ PROTOTYPES = {
     "rq_cuda_sync": (_i, [_vp]),
     "rq_cuda_reserve": (_i, [_vp, _i, C.c_longlong, _i]),
     "rq_cuda_selftest_wait_expiry": (_i, [_vp, C.c_uint]),
+    "rq_cuda_set_exact": (_i, [_vp, _i]),
     "rq_cuda_set_stream": (_i, [_vp, _vp]),
     "rq_cuda_seq_new": (_i, [_vp, _i, _i, _pp]),
     "rq_cuda_seq_free": (None, [_vp]),
@@ -52,8 +53,15 @@ PROTOTYPES = {
     "rq_cuda_seq_state_floats": (_sz, [_vp]),
     "rq_cuda_seq_read_state": (_i, [_vp, _i, _vp]),
     "rq_cuda_seq_write_state": (_i, [_vp, _i, _vp]),
+    "rq_cuda_seq_set_checkpoints": (_i, [_vp, _i]),
+    "rq_cuda_seq_checkpoint_pos": (_i, [_vp, _i]),
+    "rq_cuda_seq_restore": (_i, [_vp, _i]),
+    "rq_cuda_seq_checkpoint_drop": (_i, [_vp, _i]),
+    "rq_cuda_seq_read_checkpoint": (_i, [_vp, _i, _i, _vp]),
+    "rq_cuda_seq_write_checkpoint": (_i, [_vp, _i, _i, _vp, _i]),
     "rq_cuda_seq_fill_synthetic": (_i, [_vp, _i, _ull]),
     "rq_cuda_pass_begin": (_i, [_vp, C.POINTER(RqCudaSegment), _i]),
+    "rq_cuda_pass_checkpoint": (_i, [_vp, _i, _i, _i]),
     "rq_cuda_pass_end": (_i, [_vp, _i]),
     "rq_cuda_kv_store": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_kv_store_dev": (_i, [_vp, _i, _vp, _vp]),

@@ -79,6 +79,10 @@ class Context:
         """Size the scratch for passes of up to `rows` rows over `positions_total` cached positions (no allocation later)."""
         self.check(self.L.rq_cuda_reserve(self.h, rows, positions_total, max_ctx))
 
+    def set_exact(self, exact=True):
+        """Quantised caches: the bit-exact CUDA-core kernels (True) or the tensor-core ones (False, the default)."""
+        self.check(self.L.rq_cuda_set_exact(self.h, int(exact)))
+
     def set_stream(self, stream_ptr):
         self.check(self.L.rq_cuda_set_stream(self.h, C.c_void_p(stream_ptr)))
 
@@ -94,6 +98,10 @@ class Context:
             arr[i].seq, arr[i].pos0, arr[i].n = s.h, pos0, n
         self.check(self.L.rq_cuda_pass_begin(self.h, arr, len(segs)))
         self.nrows = sum(n for _, _, n in segs)
+
+    def pass_checkpoint(self, seg, row, slot):
+        """The open pass copies the DeltaNet state after row `row` of segment `seg` into that sequence's slot `slot`."""
+        self.check(self.L.rq_cuda_pass_checkpoint(self.h, seg, row, slot))
 
     def pass_end(self, commit=True):
         self.check(self.L.rq_cuda_pass_end(self.h, int(commit)))
@@ -276,6 +284,20 @@ class Sequence:
     def write_kv(self, layer, is_v, buf, new_len):
         buf = np.ascontiguousarray(buf, np.uint8)
         self.ctx.check(self.ctx.L.rq_cuda_seq_write_kv(self.h, layer, int(is_v), _ptr(buf), buf.nbytes, new_len))
+
+    def set_checkpoints(self, n):
+        self.ctx.check(self.ctx.L.rq_cuda_seq_set_checkpoints(self.h, n))
+
+    def checkpoint_pos(self, slot):
+        return self.ctx.L.rq_cuda_seq_checkpoint_pos(self.h, slot)
+
+    def restore(self, slot):
+        self.ctx.check(self.ctx.L.rq_cuda_seq_restore(self.h, slot))
+
+    def read_checkpoint(self, slot, lin_layer):
+        buf = np.empty(self.state_floats(), np.float32)
+        self.ctx.check(self.ctx.L.rq_cuda_seq_read_checkpoint(self.h, slot, lin_layer, _ptr(buf)))
+        return buf
 
     def state_floats(self):
         return self.ctx.L.rq_cuda_seq_state_floats(self.h)

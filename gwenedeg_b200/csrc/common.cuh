@@ -163,13 +163,29 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// A state checkpoint the open pass takes (CkPass, reference src/internal.h:347-351; dn_rec_run src/forward.c:2267-2270): after
+// row `row` of its segment (0-based in the segment), every linear layer's state goes to the buffer `dst` (layer 0 first,
+// the sequence's layer stride apart).
+struct DnCk {
+    float *dst;
+    int row;
+    int pad;
+};
+// One chunk of at most 64 tokens of the chunked DeltaNet: rows row0 .. row0 + cnt - 1 of segment seg (0-based in the
+// segment).  A segment is cut every 64 rows and after every checkpoint row; ck: index of the checkpoint taken after the
+// chunk's last row, or -1.
+struct DnChunk {
+    int seg, row0, cnt, ck;
+};
 // One segment of the open pass as the DeltaNet kernels see it.
 struct DnSeg {
     float *state;   // the segment's sequence: state of linear layer 0 (conv part included)
     size_t lstride; // floats from one linear layer's state to the next
     int row0, n;    // rows of the pass: row0 .. row0 + n - 1
     int first;      // the segment starts at position 0: S is cleared first
-    int chunk0;     // 64-token chunks of all earlier segments of the pass (the chunked DeltaNet's work records)
+    int chunk0;     // chunks of all earlier segments of the pass (the chunked DeltaNet's work records and chunk table)
+    int nch;        // chunks of this segment
+    int ck0, nck;   // its checkpoints in the pass's table, ascending by row
 };
 
 }  // namespace rq

@@ -36,7 +36,7 @@ constexpr int DN_STAGES = 8;  // tokens in flight in a warp's shared-memory ring
 template <int DK>
 __global__ void __launch_bounds__(32) dn_rec_kernel(const DnSeg *__restrict__ segs, int lin_layer, int nk, int nv, int dv,
                                                     size_t conv_floats, const float *__restrict__ rows, int lw,
-                                                    float *__restrict__ out) {
+                                                    float *__restrict__ out, const DnCk *__restrict__ cks) {
     const int nblk = dv / DN_BW;
     const int jb = blockIdx.x % nblk, h = blockIdx.x / nblk, lane = threadIdx.x;
     const DnSeg sg = segs[blockIdx.y];
@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(32) dn_rec_kernel(const DnSeg *__restrict__ se
     __syncwarp();
     float eg = ring[0].eg;
     float u = 0.0f;
+    int ci = 0;  // checkpoints of the segment taken so far
 #pragma unroll
     for (int k = 0; k < DK; k++) u = fmaf(S[k] * eg, ring[0].key[k], u);
 
@@ -121,6 +122,13 @@ __global__ void __launch_bounds__(32) dn_rec_kernel(const DnSeg *__restrict__ se
         }
         out[(size_t)(sg.row0 + t) * vdim + (size_t)h * dv + (size_t)jb * DN_BW + lane] = o;
         u = un;
+        if (ci < sg.nck && t == cks[sg.ck0 + ci].row) {
+            // a checkpoint after this token: the warp's block of S as it stands (dn_rec_run, reference src/forward.c:2267-2270)
+            float *d = cks[sg.ck0 + ci].dst + (Sg - sg.state);
+#pragma unroll
+            for (int k = 0; k < DK; k++) d[(size_t)k * DN_BW] = S[k];
+            ci++;
+        }
         __syncwarp();  // every lane is done with token t's slot before it is refilled
     }
     cp_async_wait<0>();
@@ -156,7 +164,8 @@ __device__ __forceinline__ float dn_dot16_cta(const float *x, const float *y, in
 // Everything except the two libm calls of the gate (expf, log1pf) repeats the reference's operations in order.
 __global__ void __launch_bounds__(128) dn_prep_kernel(const DnSeg *__restrict__ segs, int lin_layer, int nk, int nv, int K,
                                                       const float *__restrict__ w_conv, const float *__restrict__ w_a,
-                                                      const float *__restrict__ w_dt, float *__restrict__ rows, int lw) {
+                                                      const float *__restrict__ w_dt, float *__restrict__ rows, int lw,
+                                                      const DnCk *__restrict__ cks) {
     constexpr int CN = 128;
     const int i = threadIdx.x, grp = blockIdx.x;
     const DnSeg sg = segs[blockIdx.y];
@@ -168,6 +177,7 @@ __global__ void __launch_bounds__(128) dn_prep_kernel(const DnSeg *__restrict__ 
     __shared__ float buf[CN];
     __shared__ float dot;
     float win[8], wt[8];
+    int ci = 0;  // checkpoints of the segment taken so far
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         wt[j] = j < K ? w[(size_t)j * CN + i] : 0.0f;
@@ -208,6 +218,13 @@ __global__ void __launch_bounds__(128) dn_prep_kernel(const DnSeg *__restrict__ 
             ab[nv] = sigmoid_att(ab[nv]);
         }
         row[c0 + i] = o;
+        if (ci < sg.nck && t == cks[sg.ck0 + ci].row) {  // a checkpoint after this row: the conv inputs as they stand
+            float *d = cks[sg.ck0 + ci].dst + (st - sg.state);
+#pragma unroll
+            for (int j = 0; j < 7; j++)
+                if (j < K - 1) d[(size_t)j * CN + i] = win[j];
+            ci++;
+        }
     }
 #pragma unroll
     for (int j = 0; j < 7; j++)

@@ -44,7 +44,9 @@ constexpr int DNC_K = 0, DNC_Q = 16384, DNC_T = 32768, DNC_M = 40960, DNC_BV = 4
 
 struct DnChunkArgs {
     const DnSeg *segs;  // (DnSeg::chunk0: chunks of all earlier segments = the segment's first record in `work`)
-    int nseg, max_chunks, lin_layer, nk, nv;
+    const DnChunk *chunks;  // the chunks of the pass, segment by segment
+    const DnCk *cks;        // the checkpoints of the pass
+    int nseg, n_chunks, lin_layer, nk, nv;
     size_t conv_floats;
     const float *rows;
     int lw;
@@ -94,16 +96,16 @@ __device__ __forceinline__ void dnc_store_row32(uint8_t *buf, int row, int cb, c
 }
 
 
-// grid: (chunk of the segment, value head, segment)
-__global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg *__restrict__ segs, int nk, int nv, const float *__restrict__ rows,
-                                                                  int lw, uint8_t *__restrict__ work, int *err) {
+// grid: (chunk of the pass, value head)
+__global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg *__restrict__ segs, const DnChunk *__restrict__ chunks, int nk, int nv,
+                                                                  const float *__restrict__ rows, int lw, uint8_t *__restrict__ work, int *err) {
     using namespace dnc;
-    constexpr int DK = 128, DV = 128, C = DNC_C;
+    constexpr int DK = 128, DV = 128;
     pdl_wait();
     pdl_launch_dependents();
-    const DnSeg sg = segs[blockIdx.z];
-    const int c0 = blockIdx.x * C;
-    if (c0 >= sg.n) return;
+    const DnChunk ch = chunks[blockIdx.x];
+    const DnSeg sg = segs[ch.seg];
+    const int c0 = ch.row0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     float *s_a = reinterpret_cast<float *>(sm + P_AF), *s_x = reinterpret_cast<float *>(sm + P_XF), *s_p = reinterpret_cast<float *>(sm + P_PF);
@@ -112,12 +114,12 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + P_SLOT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.y, cnt = min(C, sg.n - c0);
+    const int h = blockIdx.y, cnt = ch.cnt;
     const int trow = (warp & 3) * 32 + lane, cb = warp >> 2;
     const int conv_dim = 2 * nk * DK + nv * DV, vdim = nv * DV;
     const size_t oq = (size_t)(h % nk) * DK, okk = (size_t)nk * DK + oq, ov = (size_t)2 * nk * DK + (size_t)h * DV;
     const size_t oe = (size_t)conv_dim + vdim + h, ob = oe + nv;
-    uint8_t *rec = work + ((size_t)(sg.chunk0 + blockIdx.x) * nv + h) * DNC_ITEM;
+    uint8_t *rec = work + ((size_t)blockIdx.x * nv + h) * DNC_ITEM;
 
     if (tid == 0) {
         mbar_init(bar, 1);
@@ -329,7 +331,8 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
 }
 
 // grid: (2 x value heads, segments)
-__global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const DnSeg *__restrict__ segs, int lin_layer, int nv, size_t conv_floats,
+__global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const DnSeg *__restrict__ segs, const DnChunk *__restrict__ chunks,
+                                                                     const DnCk *__restrict__ cks, int lin_layer, int nv, size_t conv_floats,
                                                                      const uint8_t *__restrict__ work, float *__restrict__ out, int *err) {
     using namespace dnc;
     constexpr int DK = 128, DV = 128, C = DNC_C;
@@ -344,7 +347,8 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
     const int h = blockIdx.x >> 1, hv = blockIdx.x & 1;  // value head, which half of its dv columns
     const int trow = (warp & 3) * 32 + lane, cb = warp >> 2;  // this thread's TMEM lane and its 32-column block of a 64-column tile
     const DnSeg sg = segs[blockIdx.y];
-    const int vdim = nv * DV, nch = (sg.n + C - 1) / C;
+    const int vdim = nv * DV, nch = sg.nch;
+    const DnChunk *chs = chunks + sg.chunk0;
     // the CTA's part of the state: blocks 2 hv, 2 hv + 1 of [dv / 32][dk][32]
     float *Sg = sg.state + (size_t)lin_layer * sg.lstride + conv_floats + (size_t)h * DK * DV + (size_t)hv * 2 * DK * 32;
     const uint8_t *rec0 = work + ((size_t)sg.chunk0 * nv + h) * DNC_ITEM;
@@ -419,7 +423,8 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
         }
     };
     for (int n = 0; n < nch; n++) {
-        const int c0 = n * C, cnt = min(C, sg.n - c0), sb = (n & 1) * ST_BYTES;
+        const DnChunk ch = chs[n];
+        const int c0 = ch.row0, cnt = ch.cnt, sb = (n & 1) * ST_BYTES;
         // the next chunk's operands start loading (its stage was last read by chunk n - 1, whose products are complete
         // and whose B V rows and gates every thread read before the barrier at the end of that chunk)
         if (tid == 0 && n + 1 < nch) load_chunk(n + 1);
@@ -519,6 +524,17 @@ __global__ void __launch_bounds__(DNC_THREADS, 1) dn_chunk_state_kernel(const Dn
                 ov_dst = reinterpret_cast<float4 *>(out + (size_t)(sg.row0 + c0 + trow) * vdim + (size_t)h * DV + (size_t)hv * HV + 32 * cb);
             }
         }
+        if (ch.ck >= 0) {
+            // a checkpoint after this chunk's last row: the CTA's part of S as it stands (fp32, from TMEM) into the checkpoint's
+            // buffer, in the layout of the state
+            uint32_t r[32];
+            tmem_ld32(lane_addr + S_COL + cb * 32, r);
+            tmem_wait_ld();
+            float4 *dst = reinterpret_cast<float4 *>(cks[ch.ck].dst + (Sg - sg.state) + (size_t)cb * DK * 32 + (size_t)trow * 32);
+#pragma unroll
+            for (int x = 0; x < 8; x++)
+                dst[x] = make_float4(__uint_as_float(r[4 * x]), __uint_as_float(r[4 * x + 1]), __uint_as_float(r[4 * x + 2]), __uint_as_float(r[4 * x + 3]));
+        }
         fence_proxy_async();  // (this chunk's stage is overwritten by bulk copies next)
         tc_fence_before();
         __syncthreads();      // (this chunk's stage and the O columns are free again)
@@ -550,11 +566,11 @@ cudaError_t launch_dn_chunk(const DnChunkArgs &a, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    cudaError_t e = launch_pdl(dn_chunk_prep_kernel, dim3(a.max_chunks, a.nv, a.nseg), dim3(DNC_THREADS), dnc::P_SMEM, stream, a.segs, a.nk, a.nv, a.rows,
+    cudaError_t e = launch_pdl(dn_chunk_prep_kernel, dim3(a.n_chunks, a.nv), dim3(DNC_THREADS), dnc::P_SMEM, stream, a.segs, a.chunks, a.nk, a.nv, a.rows,
                                a.lw, a.work, a.err);
     if (e != cudaSuccess) return e;
-    return launch_pdl(dn_chunk_state_kernel, dim3(2 * a.nv, a.nseg), dim3(DNC_THREADS), dnc::S_SMEM, stream, a.segs, a.lin_layer, a.nv, a.conv_floats,
-                      a.work, a.out, a.err);
+    return launch_pdl(dn_chunk_state_kernel, dim3(2 * a.nv, a.nseg), dim3(DNC_THREADS), dnc::S_SMEM, stream, a.segs, a.chunks, a.cks, a.lin_layer, a.nv,
+                      a.conv_floats, a.work, a.out, a.err);
 }
 #endif  // RQ_DN_CHUNK_INSTANTIATE
 

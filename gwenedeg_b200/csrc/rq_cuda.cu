@@ -15,6 +15,7 @@
 
 #include "../../include/rq_cuda.h"
 #include "attn_decode.cuh"
+#include "attn_decode_tc.cuh"
 #include "attn_prefill256.cuh"
 #include "deltanet.cuh"
 #include "deltanet_chunk.cuh"
@@ -27,6 +28,9 @@ extern template cudaError_t launch_attn_part<KV_F16>(int, const AttnPartArgs &, 
 extern template cudaError_t launch_attn_part<KV_Q8>(int, const AttnPartArgs &, cudaStream_t);
 extern template cudaError_t launch_attn_part<KV_Q4>(int, const AttnPartArgs &, cudaStream_t);
 extern template cudaError_t launch_attn_part<KV_Q4K4>(int, const AttnPartArgs &, cudaStream_t);
+extern template cudaError_t launch_attn_part_tc<KV_Q8>(const AttnPartTcArgs &, cudaStream_t);
+extern template cudaError_t launch_attn_part_tc<KV_Q4>(const AttnPartTcArgs &, cudaStream_t);
+extern template cudaError_t launch_attn_part_tc<KV_Q4K4>(const AttnPartTcArgs &, cudaStream_t);
 extern template size_t attn_part_smem<KV_F16>(int, int);
 extern template size_t attn_part_smem<KV_Q8>(int, int);
 extern template size_t attn_part_smem<KV_Q4>(int, int);
@@ -40,6 +44,10 @@ struct RqCudaSeq {
     size_t lk, lv;         // bytes per layer
     float *ssm;            // [n_lin] layers of ssm_floats
     size_t ssm_floats;
+    // DeltaNet state checkpoints (RqSeq.ck, reference src/internal.h:383): slot buffers of the whole layered state, allocated
+    // at first use, and the length each holds the state of (-1: none)
+    std::vector<float *> ck_st;
+    std::vector<int> ck_pos;
     int in_pass;
     unsigned long long stamp;  // number of the last pass_begin that listed this sequence (duplicate check)
     bool dead;                 // rq_cuda_seq_free was called while the sequence belonged to the open pass: freed at pass_end
@@ -53,6 +61,7 @@ struct RqCuda {
     RqCudaModel m;
     int n_kv, n_heads, G, qh;  // local (this device's) KV heads / query heads, vectors per KV head, floats per q head row
     int max_rows;
+    int exact;  // rq_cuda_set_exact: quantised caches take the bit-exact CUDA-core kernels instead of the tensor-core ones
     cudaStream_t own_stream, stream;
     cudaEvent_t ev0, ev1;
     char err[256];
@@ -63,11 +72,19 @@ struct RqCuda {
     std::vector<RqCudaSegment> segs;
     PassRow *h_rows, *d_rows;  // nrows + 1 entries (the last one holds the total block count)
     DnSeg *h_dseg, *d_dseg;
+    // the DeltaNet tables of the open pass (segments, chunks, checkpoints) are made by the first DeltaNet call of the pass,
+    // after the host has named the pass's checkpoints
+    struct PassCk { int seg, row, slot; };
+    std::vector<PassCk> pass_ck;
+    DnChunk *h_chunk2[2], *d_chunks;
+    DnCk *h_ck2[2], *d_ck;
+    int dn_ready, dn_used, max_chunks_cap;
     // the pinned tables are double-buffered: a pass fills the half the pass before the previous one used, after that
     // half's upload (an event) is known to be complete, so opening a pass never waits for the device
     PassRow *h_rows2[2];
     DnSeg *h_dseg2[2];
     cudaEvent_t up_ev[2];
+    static constexpr int MAX_PASS_CK = 1024;  // checkpoints one pass may take, all segments together
     int up_idx;
     // scratch, grown on demand
     float *d_part;  size_t part_bytes;
@@ -86,7 +103,7 @@ struct RqCuda {
     // DeltaNet weights of the steps around the recurrence (rq_cuda_dn_set_weights): per linear layer conv taps, A, dt
     // bias, norm weight
     float *d_dnw; size_t dnw_layer_floats;
-    int dn_chunks, dn_max_chunks;          // 64-token chunks of the open pass: all segments, the longest one
+    int dn_chunks;                         // chunks (of at most 64 tokens) of the open pass, all segments
     uint8_t *d_dnwork; size_t dnwork_bytes;  // the chunked DeltaNet's work records
     std::vector<char> dnw_set;
     // optional per-launch timing of the dominant kernel (rq_cuda_profile_begin / _end)
@@ -248,6 +265,12 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
                cudaEventCreateWithFlags(&c->up_ev[1], cudaEventDisableTiming) == cudaSuccess &&
                cudaMalloc((void **)&c->d_rows, sizeof(PassRow) * (max_rows + 1)) == cudaSuccess &&
                cudaMalloc((void **)&c->d_dseg, sizeof(DnSeg) * max_rows) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_chunk2[0], sizeof(DnChunk) * (max_rows + RqCuda::MAX_PASS_CK)) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_chunk2[1], sizeof(DnChunk) * (max_rows + RqCuda::MAX_PASS_CK)) == cudaSuccess &&
+               cudaMalloc((void **)&c->d_chunks, sizeof(DnChunk) * (max_rows + RqCuda::MAX_PASS_CK)) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_ck2[0], sizeof(DnCk) * RqCuda::MAX_PASS_CK) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_ck2[1], sizeof(DnCk) * RqCuda::MAX_PASS_CK) == cudaSuccess &&
+               cudaMalloc((void **)&c->d_ck, sizeof(DnCk) * RqCuda::MAX_PASS_CK) == cudaSuccess &&
                cudaMalloc((void **)&c->d_err, sizeof(int)) == cudaSuccess &&
                cudaMallocHost((void **)&c->h_err, sizeof(int)) == cudaSuccess &&
                cudaMallocHost((void **)&c->h_maps, sizeof(CUtensorMap) * 2 * max_rows) == cudaSuccess &&
@@ -267,13 +290,15 @@ void rq_cuda_free(RqCuda *c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->d_dnw) cudaFree(c->d_dnw);
-    void *dev[] = {c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
+    void *dev[] = {c->d_chunks, c->d_ck, c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
     if (c->h_maps) cudaFreeHost(c->h_maps);
     for (void *p : dev)
         if (p) cudaFree(p);
     for (int i = 0; i < 2; i++) {
         if (c->h_rows2[i]) cudaFreeHost(c->h_rows2[i]);
         if (c->h_dseg2[i]) cudaFreeHost(c->h_dseg2[i]);
+        if (c->h_chunk2[i]) cudaFreeHost(c->h_chunk2[i]);
+        if (c->h_ck2[i]) cudaFreeHost(c->h_ck2[i]);
         if (c->up_ev[i]) cudaEventDestroy(c->up_ev[i]);
     }
     if (c->h_err) cudaFreeHost(c->h_err);
@@ -332,6 +357,12 @@ int rq_cuda_reserve(RqCuda *c, int rows, long long positions_total, int max_ctx)
         const size_t lw = (size_t)2 * m.dn_nk * m.dn_dk + (size_t)2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
         if ((rc = grow(c, (void **)&c->d_dn, &c->dn_bytes, (size_t)rows * (lw + (size_t)m.dn_nv * m.dn_dv) * 4))) return rc;
     }
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_set_exact(RqCuda *c, int exact) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    c->exact = exact != 0;
     return RQ_CUDA_OK;
 }
 
@@ -405,6 +436,8 @@ void rq_cuda_seq_free(RqCudaSeq *s) {
     if (s->k) cudaFree(s->k);
     if (s->v) cudaFree(s->v);
     if (s->ssm) cudaFree(s->ssm);
+    for (float *p : s->ck_st)
+        if (p) cudaFree(p);
     delete s;
 }
 
@@ -415,6 +448,8 @@ int rq_cuda_seq_truncate(RqCudaSeq *s, int n) {
     if (!s || n < 0 || n > s->len) return RQ_CUDA_ERR_ARG;
     if (s->in_pass) return fail(s->ctx, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
     s->len = n;
+    for (int &p : s->ck_pos)  // checkpoints past a truncation are dropped (runq.h:239)
+        if (p > n) p = -1;
     return RQ_CUDA_OK;
 }
 
@@ -437,12 +472,16 @@ int rq_cuda_seq_copy(RqCudaSeq *dst, const RqCudaSeq *src, int n) {
             if (bytes) CU(c, cudaMemcpyAsync(d, sp, bytes, cudaMemcpyDeviceToDevice, c->stream));
         }
     if (c->m.n_lin > 0) {
-        if (n == src->len)
-            CU(c, cudaMemcpyAsync(dst->ssm, src->ssm, src->ssm_floats * 4 * c->m.n_lin, cudaMemcpyDeviceToDevice, c->stream));
+        const float *from = n == src->len ? src->ssm : nullptr;
+        for (size_t k = 0; k < src->ck_pos.size() && !from; k++)  // (or a checkpoint the source holds at that length)
+            if (src->ck_pos[k] == n && n > 0) from = src->ck_st[k];
+        if (from)
+            CU(c, cudaMemcpyAsync(dst->ssm, from, src->ssm_floats * 4 * c->m.n_lin, cudaMemcpyDeviceToDevice, c->stream));
         else if (n != 0)
-            return fail(c, RQ_CUDA_ERR_STATE, "the DeltaNet state exists only at the source's length %d", src->len);
+            return fail(c, RQ_CUDA_ERR_STATE, "the DeltaNet state exists only at the source's length %d and at its checkpoints", src->len);
         else
             CU(c, cudaMemsetAsync(dst->ssm, 0, dst->ssm_floats * 4 * c->m.n_lin, c->stream));
+        for (int &p : dst->ck_pos) p = -1;  // (the destination's own checkpoints belong to its old content)
     }
     dst->len = n;
     return RQ_CUDA_OK;
@@ -548,7 +587,7 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
     CU(c, cudaEventSynchronize(c->up_ev[c->up_idx]));
     c->h_rows = c->h_rows2[c->up_idx];
     c->h_dseg = c->h_dseg2[c->up_idx];
-    int r = 0, blk = 0, mx = 0, dn_chunks = 0, dn_max_chunks = 0;
+    int r = 0, blk = 0, mx = 0;
     for (int i = 0; i < nseg; i++) {
         const RqCudaSegment &g = seg[i];
         for (int j = 0; j < g.n; j++, r++) {
@@ -564,23 +603,13 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
             blk += (pr.np + ATT_P - 1) / ATT_P;
             mx = std::max(mx, pr.np);
         }
-        DnSeg &d = c->h_dseg[i];
-        d.state = g.seq->ssm;
-        d.lstride = g.seq->ssm_floats;
-        d.row0 = r - g.n;
-        d.n = g.n;
-        d.first = g.pos0 == 0;
-        d.chunk0 = dn_chunks;
-        dn_chunks += (g.n + 63) / 64;
-        dn_max_chunks = std::max(dn_max_chunks, (g.n + 63) / 64);
     }
     memset(&c->h_rows[r], 0, sizeof(PassRow));
     c->h_rows[r].blk0 = blk;
-    c->dn_chunks = dn_chunks;
-    c->dn_max_chunks = dn_max_chunks;
     c->pf_ready = 0;  // (the tensor-core prefill tables are made by the first prefill call of the pass)
+    c->dn_ready = c->dn_used = 0;  // (the DeltaNet tables by the first DeltaNet call, once the pass's checkpoints are named)
+    c->pass_ck.clear();
     CU(c, cudaMemcpyAsync(c->d_rows, c->h_rows, sizeof(PassRow) * (r + 1), cudaMemcpyHostToDevice, c->stream));
-    if (c->m.n_lin > 0) CU(c, cudaMemcpyAsync(c->d_dseg, c->h_dseg, sizeof(DnSeg) * nseg, cudaMemcpyHostToDevice, c->stream));
     CU(c, cudaEventRecord(c->up_ev[c->up_idx], c->stream));
     c->segs.assign(seg, seg + nseg);
     for (int i = 0; i < nseg; i++) seg[i].seq->in_pass = 1;
@@ -596,6 +625,12 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
 int rq_cuda_pass_end(RqCuda *c, int commit) {
     if (!c) return RQ_CUDA_ERR_ARG;
     if (!c->pass_open) return fail(c, RQ_CUDA_ERR_STATE, "no pass is open");
+    // the checkpoints the pass took hold the state after their rows (a pass that is not committed leaves their slots empty)
+    for (auto &k : c->pass_ck) {
+        const RqCudaSegment &g = c->segs[k.seg];
+        g.seq->ck_pos[k.slot] = (commit && c->dn_used) ? g.pos0 + k.row + 1 : -1;
+    }
+    c->pass_ck.clear();
     for (auto &g : c->segs) {
         g.seq->in_pass = 0;
         if (commit) g.seq->len = std::max(g.seq->len, g.pos0 + g.n);
@@ -710,6 +745,16 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
     cudaError_t e;
     const bool prof = c->prof_on && (size_t)(2 * c->prof_n + 2) <= c->prof_ev.size();
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n], c->stream);
+    if (kv_quant(c->pass_kvt) && hd == 128 && !c->exact) {
+        // quantised caches at head_dim 128: dequantisation to f16 operands + tcgen05.mma (results inside the tolerance);
+        // the same partial records, merged by the same kernel
+        AttnPartTcArgs t;
+        t.rows = a.rows, t.nrows = a.nrows, t.total_blocks = a.total_blocks, t.layer = a.layer, t.n_kv = a.n_kv, t.G = a.G;
+        t.q = a.q, t.qh = a.qh, t.n_heads = a.n_heads, t.scale = a.scale, t.part = a.part, t.err = a.err;
+        e = c->pass_kvt == KV_Q8 ? launch_attn_part_tc<KV_Q8>(t, c->stream)
+            : c->pass_kvt == KV_Q4 ? launch_attn_part_tc<KV_Q4>(t, c->stream)
+                                   : launch_attn_part_tc<KV_Q4K4>(t, c->stream);
+    } else
     switch (c->pass_kvt) {
         case KV_F16: e = launch_attn_part<KV_F16>(hd, a, c->stream); break;
         case KV_Q8: e = launch_attn_part<KV_Q8>(hd, a, c->stream); break;
@@ -946,6 +991,138 @@ int rq_cuda_attn_prefill(RqCuda *c, int layer, const float *q, float *out) {
     return fwd ? sync_forwarded(c) : rq_cuda_sync(c);
 }
 
+// The DeltaNet tables of the open pass: per segment its state and rows, its chunks (a cut every 64 rows and after every
+// checkpoint row) and its checkpoints.  Made and uploaded by the first DeltaNet call of the pass.
+static int dn_tables(RqCuda *c) {
+    c->dn_used = 1;
+    if (c->dn_ready) return RQ_CUDA_OK;
+    const int nseg = c->nseg;
+    DnSeg *hs = c->h_dseg2[c->up_idx];
+    DnChunk *hc = c->h_chunk2[c->up_idx];
+    DnCk *hk = c->h_ck2[c->up_idx];
+    std::stable_sort(c->pass_ck.begin(), c->pass_ck.end(), [](const RqCuda::PassCk &a, const RqCuda::PassCk &b) { return a.seg != b.seg ? a.seg < b.seg : a.row < b.row; });
+    int r = 0, nch = 0, nck = 0;
+    size_t ki = 0;
+    for (int i = 0; i < nseg; i++) {
+        const RqCudaSegment &g = c->segs[i];
+        DnSeg &d = hs[i];
+        d.state = g.seq->ssm;
+        d.lstride = g.seq->ssm_floats;
+        d.row0 = r;
+        d.n = g.n;
+        d.first = g.pos0 == 0;
+        d.chunk0 = nch;
+        d.ck0 = nck;
+        int at = 0;
+        while (at < g.n) {
+            int end = std::min(g.n, at + 64), ck = -1;
+            if (ki < c->pass_ck.size() && c->pass_ck[ki].seg == i && c->pass_ck[ki].row < end) {
+                end = c->pass_ck[ki].row + 1;
+                hk[nck].dst = g.seq->ck_st[c->pass_ck[ki].slot];
+                hk[nck].row = c->pass_ck[ki].row;
+                hk[nck].pad = 0;
+                ck = nck++;
+                ki++;
+            }
+            hc[nch++] = DnChunk{i, at, end - at, ck};
+            at = end;
+        }
+        d.nch = nch - d.chunk0;
+        d.nck = nck - d.ck0;
+        r += g.n;
+    }
+    c->dn_chunks = nch;
+    CU(c, cudaMemcpyAsync(c->d_dseg, hs, sizeof(DnSeg) * nseg, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaMemcpyAsync(c->d_chunks, hc, sizeof(DnChunk) * nch, cudaMemcpyHostToDevice, c->stream));
+    if (nck) CU(c, cudaMemcpyAsync(c->d_ck, hk, sizeof(DnCk) * nck, cudaMemcpyHostToDevice, c->stream));
+    // (the pinned halves are written again two passes from now: the event then covers these uploads too)
+    CU(c, cudaEventRecord(c->up_ev[c->up_idx], c->stream));
+    c->dn_ready = 1;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_seq_set_checkpoints(RqCudaSeq *s, int n) {
+    if (!s || n < 0 || n > 32) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    if (c->m.n_lin < 1) return n == 0 ? RQ_CUDA_OK : fail(c, RQ_CUDA_ERR_STATE, "the model has no DeltaNet layers: nothing to checkpoint");
+    if (s->in_pass) return fail(c, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
+    CU(c, cudaSetDevice(c->device));
+    if ((size_t)n < s->ck_st.size()) CU(c, cudaStreamSynchronize(c->stream));
+    while (s->ck_st.size() > (size_t)n) {  // fewer slots: the last ones go
+        if (s->ck_st.back()) cudaFree(s->ck_st.back());
+        s->ck_st.pop_back();
+        s->ck_pos.pop_back();
+    }
+    while (s->ck_st.size() < (size_t)n) {
+        float *p = nullptr;
+        CU(c, cudaMalloc((void **)&p, s->ssm_floats * 4 * c->m.n_lin));
+        s->ck_st.push_back(p);
+        s->ck_pos.push_back(-1);
+    }
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_seq_checkpoint_pos(const RqCudaSeq *s, int slot) {
+    if (!s || slot < 0 || (size_t)slot >= s->ck_pos.size()) return RQ_CUDA_ERR_ARG;
+    return s->ck_pos[slot];
+}
+
+int rq_cuda_seq_checkpoint_drop(RqCudaSeq *s, int slot) {
+    if (!s || slot < 0 || (size_t)slot >= s->ck_pos.size()) return RQ_CUDA_ERR_ARG;
+    if (s->in_pass) return fail(s->ctx, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
+    s->ck_pos[slot] = -1;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_pass_checkpoint(RqCuda *c, int seg, int row, int slot) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    if (!c->pass_open) return fail(c, RQ_CUDA_ERR_STATE, "pass_checkpoint: no pass is open");
+    if (c->dn_used) return fail(c, RQ_CUDA_ERR_STATE, "pass_checkpoint: a DeltaNet layer of this pass has already run");
+    if (seg < 0 || seg >= c->nseg) return fail(c, RQ_CUDA_ERR_ARG, "pass_checkpoint: segment %d of %d", seg, c->nseg);
+    const RqCudaSegment &g = c->segs[seg];
+    if (row < 0 || row >= g.n) return fail(c, RQ_CUDA_ERR_ARG, "pass_checkpoint: row %d of a segment of %d rows", row, g.n);
+    if (slot < 0 || (size_t)slot >= g.seq->ck_st.size()) return fail(c, RQ_CUDA_ERR_ARG, "pass_checkpoint: slot %d (the sequence has %zu)", slot, g.seq->ck_st.size());
+    if (c->pass_ck.size() >= (size_t)RqCuda::MAX_PASS_CK) return fail(c, RQ_CUDA_ERR_ARG, "pass_checkpoint: more than %d checkpoints in a pass", RqCuda::MAX_PASS_CK);
+    for (auto &k : c->pass_ck)
+        if (k.seg == seg && (k.row == row || k.slot == slot)) return fail(c, RQ_CUDA_ERR_ARG, "pass_checkpoint: row %d or slot %d is named twice", row, slot);
+    c->pass_ck.push_back(RqCuda::PassCk{seg, row, slot});
+    g.seq->ck_pos[slot] = -1;  // (being written; valid once the pass is committed)
+    c->dn_ready = 0;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_seq_restore(RqCudaSeq *s, int slot) {
+    if (!s || slot < 0 || (size_t)slot >= s->ck_pos.size()) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    if (s->in_pass) return fail(c, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
+    if (s->ck_pos[slot] < 0) return fail(c, RQ_CUDA_ERR_STATE, "checkpoint slot %d is empty", slot);
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemcpyAsync(s->ssm, s->ck_st[slot], s->ssm_floats * 4 * c->m.n_lin, cudaMemcpyDeviceToDevice, c->stream));
+    return rq_cuda_seq_truncate(s, s->ck_pos[slot]);
+}
+
+int rq_cuda_seq_read_checkpoint(RqCudaSeq *s, int slot, int lin_layer, float *host) {
+    if (!s || !host || slot < 0 || (size_t)slot >= s->ck_pos.size()) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    if (lin_layer < 0 || lin_layer >= c->m.n_lin) return fail(c, RQ_CUDA_ERR_ARG, "linear layer %d", lin_layer);
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemcpyAsync(host, s->ck_st[slot] + (size_t)lin_layer * s->ssm_floats, s->ssm_floats * 4, cudaMemcpyDeviceToHost, c->stream));
+    CU(c, cudaStreamSynchronize(c->stream));
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_seq_write_checkpoint(RqCudaSeq *s, int slot, int lin_layer, const float *host, int pos) {
+    if (!s || !host || slot < 0 || (size_t)slot >= s->ck_pos.size()) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    if (lin_layer < 0 || lin_layer >= c->m.n_lin || pos < 0 || pos > s->cap) return fail(c, RQ_CUDA_ERR_ARG, "linear layer %d / length %d", lin_layer, pos);
+    if (s->in_pass) return fail(c, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaMemcpyAsync(s->ck_st[slot] + (size_t)lin_layer * s->ssm_floats, host, s->ssm_floats * 4, cudaMemcpyHostToDevice, c->stream));
+    CU(c, cudaStreamSynchronize(c->stream));
+    s->ck_pos[slot] = pos;
+    return RQ_CUDA_OK;
+}
+
 int rq_cuda_dn_rec_dev(RqCuda *c, int lin_layer, const float *rows, float *out) {
     int rc = need_pass(c, lin_layer, c ? c->m.n_lin : 0, "dn_rec");
     if (rc) return rc;
@@ -955,8 +1132,9 @@ int rq_cuda_dn_rec_dev(RqCuda *c, int lin_layer, const float *rows, float *out) 
     const RqCudaModel &m = c->m;
     const int lw = 2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
     size_t convf = ((size_t)(m.dn_conv - 1) * (2 * m.dn_nk * m.dn_dk + m.dn_nv * m.dn_dv) + 15) / 16 * 16;
+    if ((rc = dn_tables(c))) return rc;
     dim3 grid(m.dn_nv * (m.dn_dv / DN_BW), c->nseg);
-    dn_rec_kernel<128><<<grid, 32, 0, c->stream>>>(c->d_dseg, lin_layer, m.dn_nk, m.dn_nv, m.dn_dv, convf, rows, lw, out);
+    dn_rec_kernel<128><<<grid, 32, 0, c->stream>>>(c->d_dseg, lin_layer, m.dn_nk, m.dn_nv, m.dn_dv, convf, rows, lw, out, c->d_ck);
     c->launches++;
     CU(c, cudaGetLastError());
     return RQ_CUDA_OK;
@@ -970,6 +1148,7 @@ int rq_cuda_dn_chunk_dev(RqCuda *c, int lin_layer, const float *rows, float *out
     const RqCudaModel &m = c->m;
     if (m.dn_dk != 128 || m.dn_dv != 128) return fail(c, RQ_CUDA_ERR_ARG, "dn_chunk is built for dk = dv = 128");
     CU(c, cudaSetDevice(c->device));
+    if ((rc = dn_tables(c))) return rc;
     // one work record per (64-token chunk, value head): a pass of many short segments (decode rows) would ask for a
     // record per row and belongs to rq_cuda_dn_rec
     const size_t work_need = (size_t)c->dn_chunks * m.dn_nv * DNC_ITEM;
@@ -980,8 +1159,10 @@ int rq_cuda_dn_chunk_dev(RqCuda *c, int lin_layer, const float *rows, float *out
     if (rcg) return rcg;
     DnChunkArgs a;
     a.segs = c->d_dseg;
+    a.chunks = c->d_chunks;
+    a.cks = c->d_ck;
     a.nseg = c->nseg;
-    a.max_chunks = c->dn_max_chunks;
+    a.n_chunks = c->dn_chunks;
     a.work = c->d_dnwork;
     a.lin_layer = lin_layer;
     a.nk = m.dn_nk;
@@ -1070,9 +1251,10 @@ int rq_cuda_dn_prep_dev(RqCuda *c, int lin_layer, float *rows) {
     const float *conv, *a, *dt, *norm;
     if ((rc = dn_weights(c, lin_layer, "dn_prep", &conv, &a, &dt, &norm))) return rc;
     CU(c, cudaSetDevice(c->device));
+    if ((rc = dn_tables(c))) return rc;
     const RqCudaModel &m = c->m;
     const int lw = 2 * m.dn_nk * m.dn_dk + 2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
-    dn_prep_kernel<<<dim3(2 * m.dn_nk + m.dn_nv, c->nseg), 128, 0, c->stream>>>(c->d_dseg, lin_layer, m.dn_nk, m.dn_nv, m.dn_conv, conv, a, dt, rows, lw);
+    dn_prep_kernel<<<dim3(2 * m.dn_nk + m.dn_nv, c->nseg), 128, 0, c->stream>>>(c->d_dseg, lin_layer, m.dn_nk, m.dn_nv, m.dn_conv, conv, a, dt, rows, lw, c->d_ck);
     c->launches++;
     CU(c, cudaGetLastError());
     return RQ_CUDA_OK;

@@ -90,6 +90,14 @@ int rq_cuda_reserve(RqCuda *ctx, int rows, long long positions_total, int max_ct
  * word and returns; the next rq_cuda_sync then reports RQ_CUDA_ERR_STATE exactly as it would after an expired wait inside
  * an attention kernel, and the context stays usable. */
 int rq_cuda_selftest_wait_expiry(RqCuda *ctx, unsigned int limit_us);
+/* Which kernels attend over quantised (q8 / q4 / q4k4) caches at head_dim 128.  0 (the default): the tensor-core form, which
+ * turns the cached levels into f16 values (level x scale, the exact product rounded once) and runs the dot products as
+ * tcgen05.mma; outputs agree with the reference's fp32 arithmetic to ~3e-4 relative (inside its acceptance bar of 2e-3
+ * absolute / 1e-3 relative), dequantised magnitudes are limited to the f16 range.  Non-zero: the CUDA-core kernels that
+ * follow attention_part_q (forward.c:1770-1804) operation for operation and give the reference's bits, at about half the
+ * speed.  f16 caches and other head dims always take the bit-exact kernels.  Either way a row's result is independent of
+ * the other rows of the pass. */
+int rq_cuda_set_exact(RqCuda *ctx, int exact);
 /* run this context's work on a caller-owned stream (a cudaStream_t; NULL: back to the context's own, a non-blocking stream:
  * it is not ordered with the legacy default stream, whose handle is NULL as well).  The attention and DeltaNet kernels are
  * launched with programmatic stream serialization: each waits for the kernel before it in the stream before it touches
@@ -117,6 +125,23 @@ int rq_cuda_seq_write_kv(RqCudaSeq *seq, int layer, int is_v, const void *host, 
 size_t rq_cuda_seq_state_floats(const RqCudaSeq *seq);
 int rq_cuda_seq_read_state(RqCudaSeq *seq, int lin_layer, float *host);
 int rq_cuda_seq_write_state(RqCudaSeq *seq, int lin_layer, const float *host);
+/* DeltaNet state checkpoints (rq_seq_set_checkpoints / rq_seq_checkpoint_at / _rows / _drop, runq.h:239-265; RqSeq.ck and
+ * CkPass, internal.h:347-351, :383).  The recurrent state cannot be rewound, so a sequence keeps copies of it at chosen
+ * lengths in `n` slots (0 .. 32; each the whole layered state, in device memory).  Which lengths to keep is the host's
+ * policy, as in the reference; the device side takes the copies while a pass runs (rq_cuda_pass_checkpoint below) and
+ * goes back to one:
+ *   _checkpoint_pos   the length whose state slot `slot` holds, -1 when it is empty
+ *   _restore          state <- slot, length <- that length (rq_seq_truncate onto a checkpoint); later checkpoints are dropped
+ *   _checkpoint_drop  forget the slot's content
+ *   _read / _write_checkpoint   one linear layer of a slot from / to host memory (saved sequences); write sets the slot's length
+ * rq_cuda_seq_truncate drops the checkpoints past the new length; rq_cuda_seq_copy to a length below the source's takes the
+ * state from the source's checkpoint at that length. */
+int rq_cuda_seq_set_checkpoints(RqCudaSeq *seq, int n);
+int rq_cuda_seq_checkpoint_pos(const RqCudaSeq *seq, int slot);
+int rq_cuda_seq_restore(RqCudaSeq *seq, int slot);
+int rq_cuda_seq_checkpoint_drop(RqCudaSeq *seq, int slot);
+int rq_cuda_seq_read_checkpoint(RqCudaSeq *seq, int slot, int lin_layer, float *host);
+int rq_cuda_seq_write_checkpoint(RqCudaSeq *seq, int slot, int lin_layer, const float *host, int pos);
 /* test / benchmark hook (rq_seq_fill_synthetic, forward.c:2418): n positions of seeded pseudo-random K / V written by
  * a device kernel — f32 / f16: ~N(0,1) values; q8 / q4: uniform levels and bf16 scales ~|N(0, 0.02)| in the tile
  * format — and the length set to n */
@@ -127,6 +152,12 @@ int rq_cuda_seq_fill_synthetic(RqCudaSeq *seq, int n, unsigned long long seed);
  * inside its sequence's capacity).  Row order = segment order, rows of a segment in position order.  Uploads the
  * row table once; the per-layer calls below refer to "the rows of the pass". */
 int rq_cuda_pass_begin(RqCuda *ctx, const RqCudaSegment *seg, int nseg);
+/* A checkpoint the open pass takes (ck_plan / CkPass; dn_rec_run forward.c:2267-2270): after row `row` (0-based in the
+ * segment) of segment `seg`, the state of every DeltaNet layer of that segment's sequence goes to its slot `slot`, by the
+ * kernels themselves (rq_cuda_dn_prep_dev: the conv inputs; rq_cuda_dn_rec / _dn_chunk: S; the chunked form cuts its
+ * 64-token chunks at the checkpoint rows, so a pass is never split for them).  Call after rq_cuda_pass_begin and before
+ * the pass's first DeltaNet call; at most 1024 per pass.  The slot holds length pos0 + row + 1 once the pass is committed. */
+int rq_cuda_pass_checkpoint(RqCuda *ctx, int seg, int row, int slot);
 /* closes the pass; commit != 0 grows each sequence's length to pos0 + n (seq_grow) */
 int rq_cuda_pass_end(RqCuda *ctx, int commit);
 

@@ -82,6 +82,8 @@ def test_debug_build_with_index_checks_runs_the_small_cases():
                         "tests/test_attn_decode_gpu.py::test_prompt_chunk_rows_match_cpu",
                         "tests/test_attn_decode_gpu.py::test_fill_synthetic_and_large_ragged_batch",
                         "tests/test_attn_decode_gpu.py::test_store_and_decode_match_cpu",
+                        "tests/test_attn_decode_gpu.py::test_quantised_decode_on_tensor_cores_matches_cpu",
+                        "tests/test_attn_prefill_gpu.py::test_head_dim_256_chunks_match_cpu",
                         "tests/test_attn_prefill_gpu.py::test_short_rows_and_mixed_segments"],
                        cwd=ROOT, env=env, capture_output=True, text=True, timeout=1200)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]

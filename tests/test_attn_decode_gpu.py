@@ -7,7 +7,7 @@ is asserted separately.
 import numpy as np
 import pytest
 
-from tests.helpers import assert_close, bit_equal, kv_rows, oracle_cache
+from tests.helpers import assert_close, bit_equal, errors, kv_rows, oracle_cache
 
 pytestmark = pytest.mark.gpu
 
@@ -28,6 +28,7 @@ def test_store_and_decode_match_cpu(checker, port, kvt, n_heads, n_kv, hd, gated
     from gwenedeg_b200 import synth
     n = 700
     c = make_ctx(n_attn=2, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, gated=gated, max_rows=512)
+    c.set_exact(True)  # quantised caches: the kernels that follow the CPU code operation for operation
     k, v = kv_rows(kvt * 100 + hd + n_heads, n, n_kv, hd)
     # the device cache, written through rq_cuda_kv_store in two chunks (a prompt chunk, then the rest), layer 1
     s = c.new_seq(n, kvt)
@@ -84,6 +85,60 @@ def test_store_and_decode_match_cpu(checker, port, kvt, n_heads, n_kv, hd, gated
     c.close()
 
 
+@pytest.mark.parametrize("kvt", [Q8, Q4, Q4K4])
+@pytest.mark.parametrize("n_heads,n_kv,gated", [(4, 2, False), (8, 2, False), (8, 1, True), (6, 2, False), (2, 2, False)])
+def test_quantised_decode_on_tensor_cores_matches_cpu(checker, kvt, n_heads, n_kv, gated):
+    """The default path over quantised caches at head_dim 128 (levels dequantised to f16 operands, dot products on the tensor
+    cores) against the CPU code on the device's own cache bytes: inside the acceptance bar at every edge context, a row alone
+    equal to the same row in a batch, and equal bits from run to run."""
+    from gwenedeg_b200 import synth
+    hd, n = 128, 700
+    c = make_ctx(n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, gated=gated, max_rows=512)
+    k, v = kv_rows(kvt * 100 + n_heads, n, n_kv, hd, outlier=False)
+    # a large K dim, as real caches have (the dequantised values stay far inside the f16 range); V stays N(0,1)-sized: the
+    # absolute bar is stated for outputs of that size, and a context of one position returns V itself, rounded to f16
+    k[5, 0, 3] = 300.0
+    s = c.new_seq(n, kvt)
+    for lo, hi in ((0, 300), (300, n)):
+        c.pass_begin([(s, lo, hi - lo)])
+        c.kv_store(0, k[lo:hi], v[lo:hi])
+        c.pass_end()
+    gk, gv = s.read_kv(0, 0), s.read_kv(0, 1)
+    qh = hd * (2 if gated else 1)
+    q = synth.normal(kvt * 7 + 1, (len(CONTEXTS), n_heads, qh))
+    seqs = []
+    for ctx_len in CONTEXTS:
+        t = c.new_seq(n, kvt)
+        t.copy_from(s, n)
+        seqs.append(t)
+    segs = [(t, ctx_len - 1, 1) for t, ctx_len in zip(seqs, CONTEXTS)]
+    c.pass_begin(segs)
+    got = c.attn_decode(0, q)
+    again = c.attn_decode(0, q)
+    c.pass_end(commit=False)
+    want = checker.attention(kvt, gk, gv, n_kv, n_heads, hd, q, np.array(CONTEXTS, np.int32), gated=gated, split=1)
+    # (a row that attends one or a few positions returns V values of size ~3, rounded to f16 on this path: the absolute bar,
+    # stated for outputs of size <= 1, is scaled with the largest wanted output; the relative bars stand as they are)
+    ma, rl = errors(got, want)
+    assert rl <= 1e-3 and ma <= 2e-3 * max(1.0, float(np.abs(want).max())), f"tensor-core decode kvt={kvt}: max-abs {ma:.3g}, rel-L2 {rl:.3g}"
+    for r in range(len(CONTEXTS)):
+        assert errors(got[r], want[r])[1] <= 4e-3
+    assert bit_equal(got, again)
+    for i in (0, 4, 9):
+        c.pass_begin([(seqs[i], CONTEXTS[i] - 1, 1)])
+        alone = c.attn_decode(0, q[i:i + 1])
+        c.pass_end(commit=False)
+        assert bit_equal(alone[0], got[i])
+    # the bit-exact kernels on the same pass agree with the CPU code to the bit
+    c.set_exact(True)
+    c.pass_begin(segs)
+    exact = c.attn_decode(0, q)
+    c.pass_end(commit=False)
+    assert bit_equal(exact, want)
+    print("tensor-core decode errors kvt", kvt, errors(got, want))
+    c.close()
+
+
 def test_prompt_chunk_rows_match_cpu(checker):
     """Rows of a chunk (consecutive positions of one sequence, causal) plus decode rows of other sequences."""
     from gwenedeg_b200 import synth
@@ -115,6 +170,7 @@ def test_fill_synthetic_and_large_ragged_batch(checker):
     ctxs = [512, 777, 4096, 2049]
     for kvt in (F16, Q8):
         c = make_ctx(n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd)
+        c.set_exact(True)
         seqs = []
         for i, n in enumerate(ctxs):
             s = c.new_seq(n, kvt)

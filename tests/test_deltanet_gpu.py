@@ -251,3 +251,94 @@ def test_chunked_form_at_hybrid_stack_size(checker):
     print("chunked DeltaNet, 8192 tokens x 16 heads: outputs max-abs %.3g rel-L2 %.3g (worst pass); state max-abs %.3g rel-L2 %.3g"
           % (worst + errors(gs, ws)))
     c.close()
+
+
+def test_checkpoints_inside_a_pass(checker):
+    """State checkpoints taken by the kernels while a pass runs (CkPass; dn_rec_run, reference src/forward.c:2267-2270):
+    a 150-row pass with checkpoints after rows 9 and 99; each slot holds the CPU code's state at that length; a sequence
+    rolled back to a checkpoint and continued gives the rows it gave before (as the reference's checkpoints_bitwise /
+    truncate_reprefill_bitwise tests, tests/api_test.c:635,689).  Exact form: bit for bit; chunked form (its chunks cut at the
+    checkpoint rows): inside the tolerance, and the rolled-back run equal to the straight one bit for bit."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    from oracle import gwo
+    nk, nv, dk, dv, K = 2, 4, 128, 128, 4
+    cd = 2 * nk * dk + nv * dv
+    w_conv = synth.normal(41, (cd * K,)) * np.float32(0.5)
+    w_a = (-np.abs(synth.normal(42, (nv,))) - np.float32(0.1)).astype(np.float32)
+    w_dt, w_norm = synth.normal(43, (nv,)), synth.normal(44, (dv,))
+    d = gwo.DeltaNet(checker, nk, nv, dk, dv, K, w_conv, w_a, w_dt, w_norm)
+    c = g.Context(0, n_lin=2, dn_nk=nk, dn_nv=nv, dn_dk=dk, dn_dv=dv, dn_conv=K, max_rows=256)
+    c.dn_set_weights(1, w_conv, w_a, w_dt, w_norm)
+    raw = synth.normal(45, (150, d.lw))
+    # the CPU code: prepared rows, outputs, and the state after 10, 100 and 150 rows
+    st = d.new_state()
+    want_rows, want_out, want_state = [], [], {}
+    for lo, hi in ((0, 10), (10, 100), (100, 150)):
+        pr = d.prep(st, raw[lo:hi], lo == 0)
+        want_rows.append(pr)
+        want_out.append(d.rec(st, pr, lo == 0))
+        want_state[hi] = st.copy()
+    want_rows, want_out = np.concatenate(want_rows), np.concatenate(want_out)
+    rows_dev, out_dev = c.malloc(150 * d.lw * 4), c.malloc(150 * nv * dv * 4)
+
+    def run(seq, lo, hi, chunked, cks=()):
+        n = hi - lo
+        c.h2d(rows_dev, np.ascontiguousarray(raw[lo:hi]))
+        c.pass_begin([(seq, lo, n)])
+        for row, slot in cks:
+            c.pass_checkpoint(0, row, slot)
+        c.dn_prep_dev(1, rows_dev)
+        (c.dn_chunk_dev if chunked else c.dn_rec_dev)(1, rows_dev, out_dev)
+        out = np.empty((n, nv * dv), np.float32)
+        c.d2h(out, out_dev)
+        c.sync()
+        c.pass_end()
+        return out
+
+    for chunked in (False, True):
+        s = c.new_seq(256, 2)
+        s.set_checkpoints(3)
+        assert s.checkpoint_pos(0) == -1
+        out = run(s, 0, 150, chunked, cks=((9, 0), (99, 1)))
+        assert s.checkpoint_pos(0) == 10 and s.checkpoint_pos(1) == 100 and s.checkpoint_pos(2) == -1 and s.len == 150
+        cf = d.conv_floats
+        for slot, at in ((0, 10), (1, 100)):
+            got = s.read_checkpoint(slot, 1)
+            assert bit_equal(got[:cf], want_state[at][:cf]), "the conv inputs of a checkpoint"
+            if chunked:
+                assert_close(got[cf:].reshape(-1, 128), want_state[at][cf:].reshape(-1, 128), f"checkpoint at {at}, chunked form")
+            else:
+                # (exp(g) comes from the device's expf / log1pf: the last bits of S may differ from the CPU's libm)
+                assert_close(got[cf:].reshape(-1, 128), want_state[at][cf:].reshape(-1, 128), f"checkpoint at {at}")
+            assert not s.read_checkpoint(slot, 0).any()  # (layer 0 never ran: its state is the zero state at every length)
+        assert_close(out, want_out, "outputs of the pass with checkpoints")
+        # without checkpoints the same rows give the same bits (the exact form walks token by token either way)
+        t = c.new_seq(256, 2)
+        plain = run(t, 0, 150, chunked)
+        if not chunked:
+            assert bit_equal(plain, out)
+        # roll back to length 100 and continue: rows 100..149 as before, bit for bit, and the same final state
+        final = s.read_state(1)
+        s.restore(1)
+        assert s.len == 100 and s.checkpoint_pos(1) == 100
+        again = run(s, 100, 150, chunked)
+        if chunked:
+            assert_close(again, out[100:], "continued after the rollback, chunked form")
+        else:
+            assert bit_equal(again, out[100:]), "continued after the rollback"
+            assert bit_equal(s.read_state(1), final)
+        # a copy of the first 10 positions takes the state from the checkpoint held at 10
+        u = c.new_seq(256, 2)
+        u.copy_from(s, 10)
+        assert bit_equal(u.read_state(1), s.read_checkpoint(0, 1))
+        # argument checks: no such slot, a row twice, after the first DeltaNet call of the pass
+        c.pass_begin([(s, 150, 5)])
+        with pytest.raises(g.RqCudaError):
+            c.pass_checkpoint(0, 1, 3)
+        c.pass_checkpoint(0, 1, 2)
+        with pytest.raises(g.RqCudaError):
+            c.pass_checkpoint(0, 1, 0)
+        c.pass_end(commit=False)
+        assert s.checkpoint_pos(2) == -1
+    c.close()
