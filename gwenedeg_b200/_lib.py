@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # RQ_CUDA_LIB selects another build of the same library (the debug build with index checks: librq_cuda_debug.so)
 LIB_PATH = os.environ.get("RQ_CUDA_LIB") or os.path.join(HERE, "librq_cuda.so")
 
-OK, ERR_ARG, ERR_NOMEM, ERR_CONTEXT, ERR_STATE, ERR_DEVICE = 0, -1, -2, -3, -4, -16
+OK, ERR_ARG, ERR_NOMEM, ERR_CONTEXT, ERR_STATE, ERR_IO, ERR_MISMATCH, ERR_DEVICE = 0, -1, -2, -3, -4, -6, -7, -16
 KV_F32, KV_F16, KV_Q8, KV_Q4, KV_Q4K4 = 0, 2, 3, 8, 9
 KV_NAMES = {"f16": KV_F16, "q8": KV_Q8, "q4": KV_Q4, "q4k4": KV_Q4K4}
 
@@ -39,6 +39,7 @@ PROTOTYPES = {
     "rq_cuda_sync": (_i, [_vp]),
     "rq_cuda_reserve": (_i, [_vp, _i, C.c_longlong, _i]),
     "rq_cuda_selftest_wait_expiry": (_i, [_vp, C.c_uint]),
+    "rq_cuda_set_wo_quant": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_set_exact": (_i, [_vp, _i]),
     "rq_cuda_set_stream": (_i, [_vp, _vp]),
     "rq_cuda_seq_new": (_i, [_vp, _i, _i, _pp]),
@@ -59,6 +60,9 @@ PROTOTYPES = {
     "rq_cuda_seq_checkpoint_drop": (_i, [_vp, _i]),
     "rq_cuda_seq_read_checkpoint": (_i, [_vp, _i, _i, _vp]),
     "rq_cuda_seq_write_checkpoint": (_i, [_vp, _i, _i, _vp, _i]),
+    "rq_cuda_seq_save_bytes": (C.c_longlong, [_vp]),
+    "rq_cuda_seq_save": (_i, [_vp, C.c_char_p, _vp, _ull, _ull]),
+    "rq_cuda_seq_load": (_i, [_vp, C.c_char_p, _ull, _i, _vp, C.POINTER(_ull)]),
     "rq_cuda_seq_fill_synthetic": (_i, [_vp, _i, _ull]),
     "rq_cuda_pass_begin": (_i, [_vp, C.POINTER(RqCudaSegment), _i]),
     "rq_cuda_pass_checkpoint": (_i, [_vp, _i, _i, _i]),

@@ -79,6 +79,10 @@ class Context:
         """Size the scratch for passes of up to `rows` rows over `positions_total` cached positions (no allocation later)."""
         self.check(self.L.rq_cuda_reserve(self.h, rows, positions_total, max_ctx))
 
+    def set_wo_quant(self, gs, xq_dev, xs_dev):
+        """Attention calls also write int8 levels + scales of their output rows (None, None: off)."""
+        self.check(self.L.rq_cuda_set_wo_quant(self.h, gs, _ptr(xq_dev), _ptr(xs_dev)))
+
     def set_exact(self, exact=True):
         """Quantised caches: the bit-exact CUDA-core kernels (True) or the tensor-core ones (False, the default)."""
         self.check(self.L.rq_cuda_set_exact(self.h, int(exact)))
@@ -284,6 +288,19 @@ class Sequence:
     def write_kv(self, layer, is_v, buf, new_len):
         buf = np.ascontiguousarray(buf, np.uint8)
         self.ctx.check(self.ctx.L.rq_cuda_seq_write_kv(self.h, layer, int(is_v), _ptr(buf), buf.nbytes, new_len))
+
+    def save(self, path, tokens, model_fp=0, rng=0):
+        """Write the sequence in the reference's saved-sequence format (tokens: its len token ids)."""
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        assert tokens.size >= self.len
+        self.ctx.check(self.ctx.L.rq_cuda_seq_save(self.h, str(path).encode(), _ptr(tokens), model_fp, rng))
+
+    def load(self, path, n, model_fp=0):
+        """Load the first n positions of a saved sequence; returns (tokens kept, rng)."""
+        tokens = np.zeros(max(n, 1), np.int32)
+        rng = C.c_ulonglong()
+        self.ctx.check(self.ctx.L.rq_cuda_seq_load(self.h, str(path).encode(), model_fp, n, _ptr(tokens), C.byref(rng)))
+        return tokens[:self.len], rng.value
 
     def set_checkpoints(self, n):
         self.ctx.check(self.ctx.L.rq_cuda_seq_set_checkpoints(self.h, n))

@@ -536,6 +536,22 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_part_kernel(const PassRow *_
 // :2291).  One CTA of HD threads per (row, query head).
 // split_len / fixed_stride: the partials of a row are one per `split_len` positions, the first one at record index
 // row.blk0 (fixed_stride 0: the decode kernel's 256-position blocks) or r * fixed_stride (the prefill kernel's splits).
+// The activation quantiser the reference runs on the attention's outputs right before the `wo` matmul (quantize,
+// reference src/forward.c:803; call site :2716-2719), operation for operation: per group of gs values scale = wmax * (1 / 127),
+// inv = 127 / wmax, level = (int) trunc(x inv + copysign(0.49999997, x inv)); an all-zero group gives zero levels.
+__device__ __forceinline__ int8_t wo_quant_level(float x, float wmax) {
+    if (!(wmax > 0.0f)) return 0;
+    const float v = x * (127.0f / wmax);
+    return (int8_t)__float2int_rz(v + copysignf(0.49999997f, v));
+}
+// where the merge kernels leave the quantised copy of their output rows: levels [rows][n_heads * head_dim] and one scale per
+// gs values (gs: 32, 64, 128 or 256, dividing head_dim); xq null: none
+struct WoQuant {
+    int8_t *xq;
+    float *xs;
+    int gs;
+};
+
 constexpr int COMBINE_NG = 4;  // thread groups of the merge kernel: each fetches a quarter of the partials
 
 // One CTA of COMBINE_NG x HD threads per (row, query head).  The partial results are fetched into shared memory by all
@@ -545,7 +561,7 @@ template <int HD, bool QUANT>
 __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const PassRow *__restrict__ rows, int n_heads,
                                                                       const float *__restrict__ part, const float *__restrict__ q, int qh,
                                                                       int gated, float *__restrict__ out, int split_len, int fixed_stride,
-                                                                      const int *err_src, int *err_dst) {
+                                                                      const int *err_src, int *err_dst, WoQuant wq) {
     constexpr int CH = 8192 / HD;  // partials per chunk: 32 KB of shared memory
     const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, i = tid % HD, grp = tid / HD;
     pdl_wait();
@@ -628,6 +644,22 @@ __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const Pass
         if (gated) res = res * sigmoid_att(q[((size_t)r * n_heads + h) * qh + HD + i]);
         out[((size_t)r * n_heads + h) * HD + i] = res;
     }
+    if (wq.xq) {  // (uniform over the CTA) the quantised copy for the `wo` matmul
+        __shared__ float wmaxs[HD / 32];
+        float a = grp == 0 ? fabsf(res) : 0.0f;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        if (grp == 0 && (tid & 31) == 0) wmaxs[tid >> 5] = a;
+        __syncthreads();
+        if (grp == 0) {
+            const int nw = wq.gs >> 5, w0 = (i / wq.gs) * nw;
+            float wmax = wmaxs[w0];
+            for (int x2 = 1; x2 < nw; x2++) wmax = fmaxf(wmax, wmaxs[w0 + x2]);
+            const size_t at = ((size_t)r * n_heads + h) * HD + i;
+            if (i % wq.gs == 0) wq.xs[at / wq.gs] = wmax * (1.0f / 127.0f);
+            wq.xq[at] = wo_quant_level(res, wmax);
+        }
+    }
 }
 
 // The same merge for rows with few partials each (the tensor-core prefill path: head_dim 128 or 256, 16-bit cache, one
@@ -639,7 +671,7 @@ template <int HD>
 __global__ void __launch_bounds__(32 * COMBINE_ROWS_WARPS) attn_combine_rows_kernel(const PassRow *__restrict__ rows, int nrows, int n_heads,
                                                                                  const float *__restrict__ part, const float *__restrict__ q,
                                                                                  int qh, int gated, float *__restrict__ out, int split_len,
-                                                                                 int fixed_stride, const int *err_src, int *err_dst) {
+                                                                                 int fixed_stride, const int *err_src, int *err_dst, WoQuant wq) {
     static_assert(HD % 128 == 0, "a lane holds 4 dims of every 128 of the row");
     constexpr int NP = HD / 128;
     const int wi = blockIdx.x * COMBINE_ROWS_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -689,6 +721,27 @@ __global__ void __launch_bounds__(32 * COMBINE_ROWS_WARPS) attn_combine_rows_ker
             res[c].w = res[c].w * sigmoid_att(gq.w);
         }
         *reinterpret_cast<float4 *>(out + ((size_t)r * n_heads + h) * HD + 128 * c + 4 * lane) = res[c];
+    }
+    if (wq.xq) {  // the quantised copy for the `wo` matmul: a group of gs dims is gs / 4 adjacent lanes of one 128-dim part
+        float wm[NP];
+#pragma unroll
+        for (int c = 0; c < NP; c++) {
+            float a = fmaxf(fmaxf(fabsf(res[c].x), fabsf(res[c].y)), fmaxf(fabsf(res[c].z), fabsf(res[c].w)));
+            const int span = (wq.gs < 128 ? wq.gs : 128) >> 2;
+            for (int o = 1; o < span; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+            wm[c] = a;
+        }
+        if (wq.gs > 128)  // (head_dim 256 with one group per head)
+#pragma unroll
+            for (int c = 1; c < NP; c++) wm[0] = wm[c] = fmaxf(wm[0], wm[c]);
+#pragma unroll
+        for (int c = 0; c < NP; c++) {
+            const size_t at = ((size_t)r * n_heads + h) * HD + 128 * c + 4 * lane;
+            if ((128 * c + 4 * lane) % wq.gs == 0) wq.xs[at / wq.gs] = wm[c] * (1.0f / 127.0f);
+            char4 lv;
+            lv.x = wo_quant_level(res[c].x, wm[c]), lv.y = wo_quant_level(res[c].y, wm[c]), lv.z = wo_quant_level(res[c].z, wm[c]), lv.w = wo_quant_level(res[c].w, wm[c]);
+            *reinterpret_cast<char4 *>(wq.xq + at) = lv;
+        }
     }
 }
 

@@ -2,15 +2,19 @@
 // pass, and the launches of the kernels in this directory.  No PyTorch, no CPU fallback: every compute entry point
 // needs a CUDA device and fails with RQ_CUDA_ERR_DEVICE otherwise.
 #include <cuda_runtime.h>
+#include <fcntl.h>
 #include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/stat.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <atomic>
 #include <new>
+#include <string>
 #include <vector>
 
 #include "../../include/rq_cuda.h"
@@ -61,6 +65,7 @@ struct RqCuda {
     RqCudaModel m;
     int n_kv, n_heads, G, qh;  // local (this device's) KV heads / query heads, vectors per KV head, floats per q head row
     int max_rows;
+    WoQuant wo_quant;  // rq_cuda_set_wo_quant: the merge kernels also leave int8 levels + scales of their output rows
     int exact;  // rq_cuda_set_exact: quantised caches take the bit-exact CUDA-core kernels instead of the tensor-core ones
     cudaStream_t own_stream, stream;
     cudaEvent_t ev0, ev1;
@@ -88,6 +93,8 @@ struct RqCuda {
     int up_idx;
     // scratch, grown on demand
     float *d_part;  size_t part_bytes;
+    uint8_t *d_tcq; size_t tcq_bytes;    // tensor-core decode over quantised caches: the prepared query tiles ...
+    int *d_blk2row; size_t blk2row_bytes;  // ... and the block -> row table of the pass
     float *d_q;     size_t q_bytes;     // staging of host q rows
     float *d_out;   size_t out_bytes;   // staging of outputs
     float *d_k, *d_v; size_t k_bytes, v_bytes;  // staging of host K / V rows
@@ -254,6 +261,7 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
     c->n_heads = c->n_kv * c->G;
     c->qh = (m.gated ? 2 : 1) * m.head_dim;
     c->max_rows = max_rows;
+    c->exact = 1;
     c->err[0] = 0;
     bool okk = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) == cudaSuccess &&
                cudaEventCreate(&c->ev0) == cudaSuccess && cudaEventCreate(&c->ev1) == cudaSuccess &&
@@ -290,7 +298,7 @@ void rq_cuda_free(RqCuda *c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->d_dnw) cudaFree(c->d_dnw);
-    void *dev[] = {c->d_chunks, c->d_ck, c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
+    void *dev[] = {c->d_tcq, c->d_blk2row, c->d_chunks, c->d_ck, c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
     if (c->h_maps) cudaFreeHost(c->h_maps);
     for (void *p : dev)
         if (p) cudaFree(p);
@@ -357,6 +365,19 @@ int rq_cuda_reserve(RqCuda *c, int rows, long long positions_total, int max_ctx)
         const size_t lw = (size_t)2 * m.dn_nk * m.dn_dk + (size_t)2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
         if ((rc = grow(c, (void **)&c->d_dn, &c->dn_bytes, (size_t)rows * (lw + (size_t)m.dn_nv * m.dn_dv) * 4))) return rc;
     }
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_set_wo_quant(RqCuda *c, int gs, signed char *xq_dev, float *xs_dev) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    if (!xq_dev && !xs_dev) {
+        c->wo_quant = WoQuant{nullptr, nullptr, 0};
+        return RQ_CUDA_OK;
+    }
+    if (!xq_dev || !xs_dev || c->m.n_attn < 1 || (gs != 32 && gs != 64 && gs != 128 && gs != 256) || c->m.head_dim % gs)
+        return fail(c, RQ_CUDA_ERR_ARG, "set_wo_quant: groups of %d values (head_dim %d)", gs, c->m.head_dim);
+    if (((uintptr_t)xq_dev & 3) || ((uintptr_t)xs_dev & 3)) return fail(c, RQ_CUDA_ERR_ARG, "set_wo_quant: pointers must be 4-byte aligned");
+    c->wo_quant = WoQuant{(int8_t *)xq_dev, xs_dev, gs};
     return RQ_CUDA_OK;
 }
 
@@ -716,7 +737,7 @@ int rq_cuda_qk_norm_rope_store_dev(RqCuda *c, int layer, float *q, const float *
     return RQ_CUDA_OK;
 }
 
-static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, float *part);
+static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, float *part, bool may_allocate);
 static int launch_combine(RqCuda *c, const float *q, float *out, const float *part, int split_len, int fixed_stride);
 
 static int launch_decode(RqCuda *c, int layer, const float *q, float *out) {
@@ -724,10 +745,10 @@ static int launch_decode(RqCuda *c, int layer, const float *q, float *out) {
     size_t need = (size_t)c->total_blocks * c->n_heads * RQ_PSTRIDE(hd) * 4;
     int rc = grow(c, (void **)&c->d_part, &c->part_bytes, need);
     if (rc) return rc;
-    return launch_decode_with(c, layer, q, out, c->d_part);
+    return launch_decode_with(c, layer, q, out, c->d_part, true);
 }
 
-static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, float *part) {
+static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, float *part, bool may_allocate) {
     const int hd = c->m.head_dim;
     AttnPartArgs a;
     a.rows = c->d_rows;
@@ -745,10 +766,14 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
     cudaError_t e;
     const bool prof = c->prof_on && (size_t)(2 * c->prof_n + 2) <= c->prof_ev.size();
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n], c->stream);
-    if (kv_quant(c->pass_kvt) && hd == 128 && !c->exact) {
-        // quantised caches at head_dim 128: dequantisation to f16 operands + tcgen05.mma (results inside the tolerance);
-        // the same partial records, merged by the same kernel
+    if (kv_quant(c->pass_kvt) && hd == 128 && !c->exact && may_allocate) {
+        // quantised caches at head_dim 128: levels as f16 operands + tcgen05.mma (results inside the tolerance); the same
+        // partial records, merged by the same kernel
+        int rcg;
+        if ((rcg = grow(c, (void **)&c->d_tcq, &c->tcq_bytes, (size_t)c->nrows * c->n_kv * TCD_QT_BYTES))) return rcg;
+        if ((rcg = grow(c, (void **)&c->d_blk2row, &c->blk2row_bytes, (size_t)c->total_blocks * sizeof(int)))) return rcg;
         AttnPartTcArgs t;
+        t.qt = c->d_tcq, t.blk2row = c->d_blk2row;
         t.rows = a.rows, t.nrows = a.nrows, t.total_blocks = a.total_blocks, t.layer = a.layer, t.n_kv = a.n_kv, t.G = a.G;
         t.q = a.q, t.qh = a.qh, t.n_heads = a.n_heads, t.scale = a.scale, t.part = a.part, t.err = a.err;
         e = c->pass_kvt == KV_Q8 ? launch_attn_part_tc<KV_Q8>(t, c->stream)
@@ -774,8 +799,8 @@ static int launch_combine(RqCuda *c, const float *q, float *out, const float *pa
     const bool quant = kv_quant(c->pass_kvt);
     cudaError_t ce = cudaSuccess;
 #define COMBINE(HD_)                                                                                                          \
-    if (quant) ce = launch_pdl(attn_combine_kernel<HD_, true>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd); \
-    else ce = launch_pdl(attn_combine_kernel<HD_, false>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd);
+    if (quant) ce = launch_pdl(attn_combine_kernel<HD_, true>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd, c->wo_quant); \
+    else ce = launch_pdl(attn_combine_kernel<HD_, false>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd, c->wo_quant);
     switch (hd) {
         case 64: COMBINE(64) break;
         case 128: COMBINE(128) break;
@@ -882,7 +907,7 @@ int rq_cuda_attn_decode_noalloc(RqCuda *c, int layer, const float *q, float *out
         g_noalloc_ptr[c->device].store(part, std::memory_order_release);
     }
     // nothing in the array has to start at zero: every record the merge reads was written by this call's first kernel
-    return launch_decode_with(c, layer, q, out, part);
+    return launch_decode_with(c, layer, q, out, part, false);  // (never the kernels that need growable scratch)
 }
 
 static int prefill_tables(RqCuda *c) {
@@ -957,10 +982,10 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     const dim3 cgrid((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), cblock(32 * COMBINE_ROWS_WARPS);
     if (hd == 128)
         CU(c, launch_pdl(attn_combine_rows_kernel<128>, cgrid, cblock, 0, c->stream, c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh,
-                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd));
+                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd, c->wo_quant));
     else
         CU(c, launch_pdl(attn_combine_rows_kernel<256>, cgrid, cblock, 0, c->stream, c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh,
-                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd));
+                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd, c->wo_quant));
     c->launches++;
     return RQ_CUDA_OK;
 }
@@ -1273,6 +1298,238 @@ int rq_cuda_dn_out_dev(RqCuda *c, int lin_layer, const float *rows, float *out) 
     dn_out_kernel<<<dim3(c->nrows, m.dn_nv), 128, 0, c->stream>>>(m.dn_nk, m.dn_nv, norm, rows, lw, out);
     c->launches++;
     CU(c, cudaGetLastError());
+    return RQ_CUDA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------- saved sequences
+// The reference's sequence file (src/seqfile.c): every section at a multiple of 4096 bytes — the header (SeqFileHdr,
+// seqfile.c:32-41), the tokens, per attention layer its first nblk K blocks then V blocks of 256 positions as they lie in
+// the cache, then (Qwen3.5) the recurrent state and the checkpoints held, ascending by length.  A file written here is
+// read by the reference's rq_seq_load and the other way round: the caches have the same bytes on both sides.
+namespace {
+constexpr uint64_t SF_ALIGN = 4096;
+const char sf_magic[8] = {'R', 'Q', 'S', 'E', 'Q', '\r', '\n', 0x1a};
+struct SeqFileHdr {  // version 1's layout, 264 bytes
+    char magic[8];
+    uint32_t version, endian;
+    uint64_t model_fp;
+    int32_t n_attn, kv_dim, n_kv_heads, head_dim, att_p, att_t, att, kv_esz, n_lin, len, nblk, nck;
+    int32_t ck[32];
+    uint64_t ssm_bytes, ssm_stride, blk_bytes;
+    uint64_t off_kv, off_ssm, file_bytes, rng;
+    uint64_t hash;
+};
+static_assert(sizeof(SeqFileHdr) == 264, "the reference's header layout");
+uint64_t sf_round(uint64_t n) { return (n + SF_ALIGN - 1) / SF_ALIGN * SF_ALIGN; }
+uint64_t fnv1a64(uint64_t h, const void *p, size_t n) {
+    const unsigned char *b = (const unsigned char *)p;
+    for (size_t i = 0; i < n; i++) h = (h ^ b[i]) * 1099511628211ull;
+    return h;
+}
+uint64_t sf_hash(const SeqFileHdr &h, const int *tokens) {
+    SeqFileHdr c = h;
+    c.hash = 0;
+    return fnv1a64(fnv1a64(1469598103934665603ull, &c, sizeof(c)), tokens, (size_t)h.len * sizeof(int));
+}
+// the derived fields of a header whose shape fields (and len, nck, ck) are set
+void sf_layout(SeqFileHdr &h) {
+    const uint64_t bk = (uint64_t)ATT_PT * h.n_kv_heads * kv_tile_bytes(h.att, h.head_dim, 0);
+    const uint64_t bv = (uint64_t)ATT_PT * h.n_kv_heads * kv_tile_bytes(h.att, h.head_dim, 1);
+    h.kv_esz = (int32_t)(kv_tile_bytes(h.att, h.head_dim, 1) / (ATT_T * h.head_dim));
+    h.nblk = (h.len + ATT_P - 1) / ATT_P;
+    h.ssm_stride = sf_round(h.ssm_bytes);
+    h.blk_bytes = bk;
+    h.off_kv = SF_ALIGN + sf_round((uint64_t)h.len * sizeof(int));
+    h.off_ssm = h.off_kv + (uint64_t)h.n_attn * h.nblk * (bk + bv);
+    h.file_bytes = h.off_ssm + (h.n_lin > 0 ? (uint64_t)(1 + h.nck) * h.ssm_stride : 0);
+}
+bool sf_io(int fd, bool wr, void *buf, size_t n, uint64_t off) {
+    char *p = (char *)buf;
+    while (n) {
+        ssize_t r = wr ? pwrite(fd, p, n, (off_t)off) : pread(fd, p, n, (off_t)off);
+        if (r <= 0) return false;
+        p += r, off += (uint64_t)r, n -= (size_t)r;
+    }
+    return true;
+}
+void sf_header_of(const RqCudaSeq *s, uint64_t model_fp, uint64_t rng, SeqFileHdr &h, int *slots) {
+    const RqCuda *c = s->ctx;
+    memset(&h, 0, sizeof(h));
+    memcpy(h.magic, sf_magic, 8);
+    h.version = 1;
+    h.endian = 0x01020304;
+    h.model_fp = model_fp;
+    h.n_attn = c->m.n_attn;
+    h.kv_dim = c->m.n_kv_heads * c->m.head_dim;
+    h.n_kv_heads = c->m.n_kv_heads;
+    h.head_dim = c->m.head_dim;
+    h.att_p = ATT_P;
+    h.att_t = ATT_T;
+    h.att = s->kvt;
+    h.n_lin = c->m.n_lin;
+    h.len = s->len;
+    // the checkpoints held, ascending by length
+    std::vector<std::pair<int, int>> ck;
+    for (size_t k = 0; k < s->ck_pos.size(); k++)
+        if (s->ck_pos[k] >= 0 && s->ck_pos[k] <= s->len) ck.push_back({s->ck_pos[k], (int)k});
+    std::sort(ck.begin(), ck.end());
+    h.nck = (int32_t)ck.size();
+    for (size_t i = 0; i < ck.size(); i++) h.ck[i] = ck[i].first, slots[i] = ck[i].second;
+    h.ssm_bytes = (uint64_t)c->m.n_lin * s->ssm_floats * 4;
+    h.rng = rng;
+    sf_layout(h);
+}
+}  // namespace
+
+long long rq_cuda_seq_save_bytes(const RqCudaSeq *s) {
+    if (!s || s->len < 1) return 0;
+    SeqFileHdr h;
+    int slots[32];
+    sf_header_of(s, 0, 0, h, slots);
+    return (long long)h.file_bytes;
+}
+
+int rq_cuda_seq_save(RqCudaSeq *s, const char *path, const int *tokens, unsigned long long model_fp, unsigned long long rng) {
+    if (!s || !path || !tokens) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    if (s->len < 1) return fail(c, RQ_CUDA_ERR_ARG, "seq_save: an empty sequence");
+    if (s->in_pass) return fail(c, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
+    if (c->m.n_attn > 0 && c->n_kv != c->m.n_kv_heads) return fail(c, RQ_CUDA_ERR_STATE, "seq_save: this context holds a group of the KV heads only");
+    CU(c, cudaSetDevice(c->device));
+    SeqFileHdr h;
+    int slots[32];
+    sf_header_of(s, model_fp, rng, h, slots);
+    h.hash = sf_hash(h, tokens);
+    const std::string tmp = std::string(path) + ".tmp";
+    int fd = open(tmp.c_str(), O_WRONLY | O_CREAT | O_TRUNC | O_CLOEXEC, 0644);
+    if (fd < 0) return fail(c, RQ_CUDA_ERR_IO, "seq_save: cannot create %s", tmp.c_str());
+    bool good = ftruncate(fd, (off_t)h.file_bytes) == 0;
+    std::vector<char> head(h.off_kv, 0);
+    memcpy(head.data(), &h, sizeof(h));
+    memcpy(head.data() + SF_ALIGN, tokens, (size_t)h.len * sizeof(int));
+    good = good && sf_io(fd, true, head.data(), head.size(), 0);
+    // the first nblk blocks of every layer's K, then V (a layer's blocks are contiguous from its start)
+    const uint64_t bk = h.blk_bytes, bv = (uint64_t)ATT_PT * h.n_kv_heads * kv_tile_bytes(h.att, h.head_dim, 1);
+    std::vector<char> buf((size_t)h.nblk * std::max(bk, bv));
+    cudaError_t ce = cudaSuccess;
+    for (int l = 0; l < h.n_attn && good && ce == cudaSuccess; l++)
+        for (int kv = 0; kv < 2 && good && ce == cudaSuccess; kv++) {
+            const size_t n = (size_t)h.nblk * (kv ? bv : bk);
+            ce = cudaMemcpyAsync(buf.data(), (kv ? s->v : s->k) + (size_t)l * (kv ? s->lv : s->lk), n, cudaMemcpyDeviceToHost, c->stream);
+            if (ce == cudaSuccess) ce = cudaStreamSynchronize(c->stream);
+            good = sf_io(fd, true, buf.data(), n, h.off_kv + (uint64_t)h.nblk * ((uint64_t)l * (bk + bv) + (kv ? bk : 0)));
+        }
+    if (h.n_lin > 0 && good && ce == cudaSuccess) {
+        std::vector<char> st(h.ssm_stride, 0);
+        for (int i = 0; i <= h.nck && good && ce == cudaSuccess; i++) {
+            const float *src = i == 0 ? s->ssm : s->ck_st[slots[i - 1]];
+            ce = cudaMemcpyAsync(st.data(), src, h.ssm_bytes, cudaMemcpyDeviceToHost, c->stream);
+            if (ce == cudaSuccess) ce = cudaStreamSynchronize(c->stream);
+            good = sf_io(fd, true, st.data(), st.size(), h.off_ssm + (uint64_t)i * h.ssm_stride);
+        }
+    }
+    good = good && fdatasync(fd) == 0;
+    good = (close(fd) == 0) && good;
+    if (ce != cudaSuccess || !good || rename(tmp.c_str(), path) != 0) {
+        unlink(tmp.c_str());
+        return ce != cudaSuccess ? fail(c, RQ_CUDA_ERR_DEVICE, "seq_save: %s", cudaGetErrorString(ce)) : fail(c, RQ_CUDA_ERR_IO, "seq_save: writing %s failed", path);
+    }
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_seq_load(RqCudaSeq *s, const char *path, unsigned long long model_fp, int n, int *tokens, unsigned long long *rng) {
+    if (!s || !path) return RQ_CUDA_ERR_ARG;
+    RqCuda *c = s->ctx;
+    if (n < 0 || n > s->cap) return fail(c, RQ_CUDA_ERR_ARG, "seq_load: %d positions (capacity %d)", n, s->cap);
+    if (s->in_pass) return fail(c, RQ_CUDA_ERR_STATE, "the sequence is part of the open pass");
+    if (c->m.n_attn > 0 && c->n_kv != c->m.n_kv_heads) return fail(c, RQ_CUDA_ERR_STATE, "seq_load: this context holds a group of the KV heads only");
+    CU(c, cudaSetDevice(c->device));
+    int fd = open(path, O_RDONLY | O_CLOEXEC);
+    if (fd < 0) return fail(c, RQ_CUDA_ERR_IO, "seq_load: cannot open %s", path);
+    struct stat stt;
+    SeqFileHdr h, w;
+    std::vector<char> page(SF_ALIGN);
+    int rc = RQ_CUDA_OK;
+    std::vector<char> head;
+    if (fstat(fd, &stt) || (uint64_t)stt.st_size < SF_ALIGN || !sf_io(fd, false, page.data(), SF_ALIGN, 0)) rc = RQ_CUDA_ERR_IO;
+    if (rc == RQ_CUDA_OK) {
+        // the header against this context's shape, the sequence's cache type, and itself (sf_check, seqfile.c:183-217)
+        memcpy(&h, page.data(), sizeof(h));
+        w = h;
+        if (memcmp(h.magic, sf_magic, 8) || h.version != 1 || h.endian != 0x01020304 || h.model_fp != model_fp || h.n_attn != c->m.n_attn ||
+            h.kv_dim != c->m.n_kv_heads * c->m.head_dim || h.n_kv_heads != c->m.n_kv_heads || h.head_dim != c->m.head_dim || h.att_p != ATT_P ||
+            h.att_t != ATT_T || h.att != s->kvt || h.n_lin != c->m.n_lin || h.len < 1 || h.nck < 0 || h.nck > 32 || (h.n_lin == 0 && h.nck) ||
+            h.ssm_bytes != (uint64_t)c->m.n_lin * s->ssm_floats * 4)
+            rc = RQ_CUDA_ERR_MISMATCH;
+        for (int i = 0; rc == RQ_CUDA_OK && i < h.nck; i++)
+            if (h.ck[i] < 0 || h.ck[i] > h.len || (i && h.ck[i] <= h.ck[i - 1])) rc = RQ_CUDA_ERR_MISMATCH;
+        if (rc == RQ_CUDA_OK) {
+            sf_layout(w);
+            if (w.kv_esz != h.kv_esz || w.nblk != h.nblk || w.ssm_stride != h.ssm_stride || w.blk_bytes != h.blk_bytes || w.off_kv != h.off_kv ||
+                w.off_ssm != h.off_ssm || w.file_bytes != h.file_bytes || (uint64_t)stt.st_size != h.file_bytes)
+                rc = RQ_CUDA_ERR_MISMATCH;
+        }
+    }
+    if (rc == RQ_CUDA_OK) {
+        head.resize(h.off_kv);
+        if (!sf_io(fd, false, head.data(), head.size(), 0)) rc = RQ_CUDA_ERR_IO;
+        else if (sf_hash(h, (const int *)(head.data() + SF_ALIGN)) != h.hash) rc = RQ_CUDA_ERR_MISMATCH;
+    }
+    if (rc == RQ_CUDA_OK && n > h.len) rc = RQ_CUDA_ERR_ARG;
+    if (rc != RQ_CUDA_OK) {
+        close(fd);
+        return fail(c, rc, "seq_load: %s %s", path, rc == RQ_CUDA_ERR_IO ? "could not be read" : rc == RQ_CUDA_ERR_ARG ? "holds fewer positions" : "is not a saved sequence of this model shape and cache type");
+    }
+    // the length kept (rq_seq_file_keep, seqfile.c:409): n itself without DeltaNet layers, else the saved length or the longest
+    // checkpoint at or below n
+    int L = n;
+    if (h.n_lin > 0 && n != h.len) {
+        L = 0;
+        for (int i = 0; i < h.nck; i++)
+            if (h.ck[i] <= n) L = h.ck[i];
+    }
+    const uint64_t bk = h.blk_bytes, bv = (uint64_t)ATT_PT * h.n_kv_heads * kv_tile_bytes(h.att, h.head_dim, 1);
+    const int nblk = (L + ATT_P - 1) / ATT_P;
+    std::vector<char> buf((size_t)std::max(nblk, 1) * std::max(bk, bv));
+    bool good = true;
+    cudaError_t ce = cudaSuccess;
+    for (int l = 0; l < h.n_attn && good && ce == cudaSuccess && L > 0; l++)
+        for (int kv = 0; kv < 2 && good && ce == cudaSuccess; kv++) {
+            const size_t nb = (size_t)nblk * (kv ? bv : bk);
+            good = sf_io(fd, false, buf.data(), nb, h.off_kv + (uint64_t)h.nblk * ((uint64_t)l * (bk + bv) + (kv ? bk : 0)));
+            if (good) ce = cudaMemcpyAsync((kv ? s->v : s->k) + (size_t)l * (kv ? s->lv : s->lk), buf.data(), nb, cudaMemcpyHostToDevice, c->stream);
+            if (ce == cudaSuccess) ce = cudaStreamSynchronize(c->stream);
+        }
+    for (int &p : s->ck_pos) p = -1;
+    if (h.n_lin > 0 && L > 0 && good && ce == cudaSuccess) {
+        // the state at L: the saved one, or the checkpoint there; the saved checkpoints at or below L into the slots (the
+        // highest ones if the sequence has fewer slots)
+        int top = 0;
+        while (top < h.nck && h.ck[top] <= L) top++;
+        std::vector<char> st(h.ssm_stride);
+        auto fetch = [&](uint64_t off, float *dst) {
+            good = good && sf_io(fd, false, st.data(), st.size(), off);
+            if (good && ce == cudaSuccess) ce = cudaMemcpyAsync(dst, st.data(), h.ssm_bytes, cudaMemcpyHostToDevice, c->stream);
+            if (ce == cudaSuccess) ce = cudaStreamSynchronize(c->stream);
+        };
+        fetch(h.off_ssm + (L == h.len ? 0 : (uint64_t)top * h.ssm_stride), s->ssm);
+        const int nslot = (int)s->ck_st.size();
+        for (int i = std::max(0, top - nslot), k = 0; i < top && good && ce == cudaSuccess; i++, k++) {
+            fetch(h.off_ssm + (uint64_t)(1 + i) * h.ssm_stride, s->ck_st[k]);
+            s->ck_pos[k] = h.ck[i];
+        }
+    } else if (h.n_lin > 0 && L == 0) {
+        ce = cudaMemsetAsync(s->ssm, 0, s->ssm_floats * 4 * c->m.n_lin, c->stream);
+    }
+    close(fd);
+    if (!good || ce != cudaSuccess) {
+        s->len = 0;  // (RQ_ERR_IO: the destination is then empty, runq.h:313)
+        for (int &p : s->ck_pos) p = -1;
+        return ce != cudaSuccess ? fail(c, RQ_CUDA_ERR_DEVICE, "seq_load: %s", cudaGetErrorString(ce)) : fail(c, RQ_CUDA_ERR_IO, "seq_load: reading %s failed", path);
+    }
+    if (tokens) memcpy(tokens, head.data() + SF_ALIGN, (size_t)L * sizeof(int));
+    if (rng) *rng = h.rng;
+    s->len = L;
     return RQ_CUDA_OK;
 }
 

@@ -31,6 +31,8 @@ enum {
     RQ_CUDA_ERR_NOMEM = -2,   /* host or device allocation failed */
     RQ_CUDA_ERR_CONTEXT = -3, /* positions do not fit in the sequence's capacity */
     RQ_CUDA_ERR_STATE = -4,   /* not possible on this object / in this state (e.g. no pass open, device wait expired) */
+    RQ_CUDA_ERR_IO = -6,      /* a saved sequence could not be written or read */
+    RQ_CUDA_ERR_MISMATCH = -7, /* not a saved sequence of this model shape and KV type (another file, model, layout; corrupt) */
     RQ_CUDA_ERR_DEVICE = -16  /* no usable CUDA device, or a CUDA call failed (text in rq_cuda_error) */
 };
 
@@ -90,13 +92,20 @@ int rq_cuda_reserve(RqCuda *ctx, int rows, long long positions_total, int max_ct
  * word and returns; the next rq_cuda_sync then reports RQ_CUDA_ERR_STATE exactly as it would after an expired wait inside
  * an attention kernel, and the context stays usable. */
 int rq_cuda_selftest_wait_expiry(RqCuda *ctx, unsigned int limit_us);
-/* Which kernels attend over quantised (q8 / q4 / q4k4) caches at head_dim 128.  0 (the default): the tensor-core form, which
- * turns the cached levels into f16 values (level x scale, the exact product rounded once) and runs the dot products as
- * tcgen05.mma; outputs agree with the reference's fp32 arithmetic to ~3e-4 relative (inside its acceptance bar of 2e-3
- * absolute / 1e-3 relative), dequantised magnitudes are limited to the f16 range.  Non-zero: the CUDA-core kernels that
- * follow attention_part_q (forward.c:1770-1804) operation for operation and give the reference's bits, at about half the
- * speed.  f16 caches and other head dims always take the bit-exact kernels.  Either way a row's result is independent of
- * the other rows of the pass. */
+/* The quantised copy of the attention's outputs that the reference makes right before the `wo` matmul (quantize,
+ * forward.c:803, at :2716-2719 / :3616), fused into the merge kernels: with xq_dev / xs_dev set, every attention call of the
+ * context (decode and prefill) also writes int8 levels xq [rows][heads_local * head_dim] and one fp32 scale per `gs`
+ * values xs [rows][heads_local * head_dim / gs] (gs = the model's activation group size GS: 32, 64, 128 or 256, dividing
+ * head_dim), the reference's operations in its order (scale = max|x| (1 / 127), level = trunc(x (127 / max|x|) + copysign(
+ * 0.49999997, .))): the bits quantize() gives on the same fp32 rows.  Both NULL: off.  Device pointers the host owns, sized
+ * for the largest pass. */
+int rq_cuda_set_wo_quant(RqCuda *ctx, int gs, signed char *xq_dev, float *xs_dev);
+/* Which kernels attend over quantised (q8 / q4 / q4k4) caches at head_dim 128.  Non-zero (the default): the CUDA-core kernels
+ * that follow attention_part_q (forward.c:1770-1804) operation for operation and give the reference's bits.  0: the
+ * tensor-core form, which turns the cached levels into f16 operands and runs the dot products as tcgen05.mma; outputs agree
+ * with the reference's fp32 arithmetic to ~3e-4 relative (inside its acceptance bar of 2e-3 absolute / 1e-3 relative),
+ * dequantised magnitudes are limited to the f16 range.  f16 caches and other head dims always take the bit-exact kernels.
+ * Either way a row's result is independent of the other rows of the pass. */
 int rq_cuda_set_exact(RqCuda *ctx, int exact);
 /* run this context's work on a caller-owned stream (a cudaStream_t; NULL: back to the context's own, a non-blocking stream:
  * it is not ordered with the legacy default stream, whose handle is NULL as well).  The attention and DeltaNet kernels are
@@ -142,6 +151,19 @@ int rq_cuda_seq_restore(RqCudaSeq *seq, int slot);
 int rq_cuda_seq_checkpoint_drop(RqCudaSeq *seq, int slot);
 int rq_cuda_seq_read_checkpoint(RqCudaSeq *seq, int slot, int lin_layer, float *host);
 int rq_cuda_seq_write_checkpoint(RqCudaSeq *seq, int slot, int lin_layer, const float *host, int pos);
+/* Saved sequences in the reference's file format (rq_seq_save / rq_seq_load / rq_seq_save_bytes, runq.h:283-314; header and
+ * section layout seqfile.c:10-41): the header page, the tokens, per attention layer the first ceil(len / 256) K blocks then V
+ * blocks exactly as cached, then the DeltaNet state and the checkpoints held, ascending.  Files written here load into the
+ * reference's host sequences and files it wrote load here.  tokens: the host's token ids of positions 0 .. len - 1 (the
+ * host owns them; they are stored and hashed with the header); model_fp: the model's fingerprint (RqModel.fp), checked on
+ * load; rng: the sequence's sampling state, stored and returned.  rq_cuda_seq_load keeps the first n positions (n <= the
+ * saved length and the capacity; with DeltaNet layers: the saved length, else the longest saved checkpoint at or below n,
+ * rq_seq_file_keep) and tells the kept length through rq_cuda_seq_len; tokens (room for n ints) and rng may be NULL.
+ * RQ_CUDA_ERR_IO / RQ_CUDA_ERR_MISMATCH as the reference (after an I/O error the sequence is empty).  Contexts that hold
+ * only a group of the KV heads cannot save or load (RQ_CUDA_ERR_STATE). */
+long long rq_cuda_seq_save_bytes(const RqCudaSeq *seq);
+int rq_cuda_seq_save(RqCudaSeq *seq, const char *path, const int *tokens, unsigned long long model_fp, unsigned long long rng);
+int rq_cuda_seq_load(RqCudaSeq *seq, const char *path, unsigned long long model_fp, int n, int *tokens, unsigned long long *rng);
 /* test / benchmark hook (rq_seq_fill_synthetic, forward.c:2418): n positions of seeded pseudo-random K / V written by
  * a device kernel — f32 / f16: ~N(0,1) values; q8 / q4: uniform levels and bf16 scales ~|N(0, 0.02)| in the tile
  * format — and the length set to n */

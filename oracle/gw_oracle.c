@@ -571,3 +571,28 @@ GWO_API double gwo_bench_dn(void *p, int nseq, float *const *state, const float 
     if (best) *best = bst;
     return total;
 }
+
+/* ------------------------------------------------------------------------------------------ activation quantiser */
+/* The quantiser the reference runs on the attention's output rows before the `wo` matmul (quantize, reference
+ * src/forward.c:803-836): per group of gs values scale = wmax * (1 / 127) with wmax the largest magnitude, inv = 127 / wmax,
+ * level = (int) trunc(x inv + copysign(0.49999997, x inv)); an all-zero group gives zero levels. */
+GWO_API void gwo_quantize(const float *x, int n, int gs, int8_t *q, float *s) {
+    for (int g = 0; g < n / gs; g++) {
+        const float *xg = x + (size_t)g * gs;
+        float wmax = 0.0f;
+        for (int i = 0; i < gs; i++) {
+            float v = fabsf(xg[i]);
+            if (v > wmax) wmax = v;
+        }
+        s[g] = wmax * (1.0f / 127.0f);
+        if (!(wmax > 0.0f)) {
+            memset(q + (size_t)g * gs, 0, (size_t)gs);
+            continue;
+        }
+        float inv = 127.0f / wmax;
+        for (int i = 0; i < gs; i++) {
+            float v = xg[i] * inv;
+            q[(size_t)g * gs + i] = (int8_t)(int32_t)(v + copysignf(0.49999997f, v));
+        }
+    }
+}

@@ -115,6 +115,8 @@ class Oracle:
         L.gwo_dn_out.restype = None
         L.gwo_bench_dn.argtypes = [_vp, _i, _vp, _vp, _sz, _vp, _sz, _i, _i, _vp]
         L.gwo_bench_dn.restype = _d
+        L.gwo_quantize.argtypes = [_vp, _i, _i, _vp, _vp]
+        L.gwo_quantize.restype = None
         self.kind = "ref" if L.gwo_kind() == 1 else "port"
         isa = L.gwo_isa()
         # which attention kernels the library was compiled with (gwo_isa bit 0: the reference's AVX-512 kernels,
@@ -159,6 +161,14 @@ class Oracle:
         y = np.empty_like(x)
         self.L.gwo_sigmoid(self._p(x), self._p(y), x.size)
         return y
+
+    def quantize(self, x, gs):
+        """The activation quantiser in front of the `wo` matmul: x [..., n] -> (int8 levels, fp32 scales per gs values)."""
+        x = np.ascontiguousarray(x, np.float32)
+        q = np.empty(x.shape, np.int8)
+        s = np.empty(x.size // gs, np.float32)
+        self.L.gwo_quantize(self._p(x), x.size, gs, self._p(q), self._p(s))
+        return q, s
 
     def qk_norm_rope(self, rows, norm_w, hd, positions, theta=1e6, rd=None, gated=False):
         """rows [n][heads][hd (or 2 hd when gated)] -> normed + rotated copy (the gate half untouched)."""
@@ -291,6 +301,72 @@ class DeltaNet:
         o = np.array(o, np.float32, order="C")
         self.o.L.gwo_dn_out(self.h, Oracle._p(rows), rows.shape[1], Oracle._p(o), o.shape[1], rows.shape[0])
         return o
+
+
+class RefSeq:
+    """A host sequence of the reference (rq_seq_new) for the saved-sequence tests: the reference's own rq_seq_save /
+    rq_seq_load behind it.  Only on the reference builds (the restatement has no file code)."""
+
+    def __init__(self, orc, kvt, n_attn, n_kv, hd, cap, fp=0, n_lin=0, nk=0, nv=0, dk=128, dv=128, conv=4):
+        L = self.L = orc.L
+        if not hasattr(L, "gwo_seq_new"):
+            raise RuntimeError("this checker has no sequence-file code")
+        L.gwo_seq_new.restype = _vp
+        L.gwo_seq_new.argtypes = [_i, _i, _i, _i, _i, C.c_ulonglong, _i, _i, _i, _i, _i, _i]
+        L.gwo_seq_free.argtypes = [_vp]
+        L.gwo_seq_cache_bytes.restype = _sz
+        L.gwo_seq_cache_bytes.argtypes = [_vp, _i]
+        L.gwo_seq_state_floats.restype = _sz
+        L.gwo_seq_state_floats.argtypes = [_vp]
+        L.gwo_seq_set.argtypes = [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp]
+        L.gwo_seq_get.argtypes = [_vp, _vp, _vp, _vp, _vp, C.POINTER(_i), _vp]
+        L.gwo_seq_rng.restype = C.c_ulonglong
+        L.gwo_seq_rng.argtypes = [_vp, _i, C.c_ulonglong]
+        L.gwo_seq_save.argtypes = [_vp, C.c_char_p]
+        L.gwo_seq_load.argtypes = [_vp, C.c_char_p, _i]
+        L.gwo_seq_save_bytes.restype = C.c_longlong
+        L.gwo_seq_save_bytes.argtypes = [_vp]
+        self.h = L.gwo_seq_new(kvt, n_attn, n_kv, hd, cap, fp, n_lin, nk, nv, dk, dv, conv)
+        if not self.h:
+            raise RuntimeError("rq_seq_new refused the shape")
+        self.cap = cap
+        self.kbytes, self.vbytes = L.gwo_seq_cache_bytes(self.h, 0), L.gwo_seq_cache_bytes(self.h, 1)
+        self.state_floats = L.gwo_seq_state_floats(self.h)
+
+    def __del__(self):
+        try:
+            self.L.gwo_seq_free(self.h)
+        except Exception:
+            pass
+
+    def set(self, tokens, k, v, ssm=None, ck_pos=-1, ck=None, rng=0):
+        """tokens [len]; k, v: all layers' cache bytes; ssm: the layered state; (ck_pos, ck): a checkpoint in slot 0."""
+        tokens = np.ascontiguousarray(tokens, np.int32)
+        k, v = np.ascontiguousarray(k, np.uint8), np.ascontiguousarray(v, np.uint8)
+        assert k.size == self.kbytes and v.size == self.vbytes
+        ssm = None if ssm is None else np.ascontiguousarray(ssm, np.float32)
+        ck = None if ck is None else np.ascontiguousarray(ck, np.float32)
+        rc = self.L.gwo_seq_set(self.h, tokens.size, Oracle._p(tokens), Oracle._p(k), Oracle._p(v), Oracle._p(ssm), ck_pos, Oracle._p(ck))
+        assert rc == 0
+        self.L.gwo_seq_rng(self.h, 1, rng)
+
+    def get(self):
+        """-> (tokens, k bytes, v bytes, state, checkpoint length or -1, checkpoint state, rng)"""
+        tokens = np.zeros(self.cap, np.int32)
+        k, v = np.zeros(self.kbytes, np.uint8), np.zeros(self.vbytes, np.uint8)
+        ssm, ck = np.zeros(max(self.state_floats, 1), np.float32), np.zeros(max(self.state_floats, 1), np.float32)
+        pos = _i(-1)
+        n = self.L.gwo_seq_get(self.h, Oracle._p(tokens), Oracle._p(k), Oracle._p(v), Oracle._p(ssm), C.byref(pos), Oracle._p(ck))
+        return tokens[:n], k, v, ssm[:self.state_floats], pos.value, ck[:self.state_floats], self.L.gwo_seq_rng(self.h, 0, 0)
+
+    def save(self, path):
+        return self.L.gwo_seq_save(self.h, str(path).encode())
+
+    def load(self, path, n):
+        return self.L.gwo_seq_load(self.h, str(path).encode(), n)
+
+    def save_bytes(self):
+        return self.L.gwo_seq_save_bytes(self.h)
 
 
 _cache = {}

@@ -484,3 +484,98 @@ GWO_API double gwo_bench_dn(void *p, int nseq, float *const *state, const float 
     if (best) *best = bst;
     return total;
 }
+
+/* ------------------------------------------------------------------------------------------ saved sequences */
+/* A host sequence of the reference (rq_seq_new, forward.c:148) over a model that holds only the shapes its sequence files
+ * depend on, so that the reference's own rq_seq_save / rq_seq_load (seqfile.c) can write and read files next to this
+ * repository's writer and reader. */
+typedef struct {
+    RqModel m;
+    RqSeq *s;
+} SfSeq;
+
+GWO_API void *gwo_seq_new(int kvt, int n_attn, int n_kv, int hd, int cap, unsigned long long fp, int n_lin, int nk, int nv, int dk,
+                          int dv, int conv) {
+    SfSeq *q = calloc(1, sizeof(SfSeq));
+    int err = 0;
+    q->m.config.n_kv_heads = n_kv;
+    q->m.config.head_dim = hd;
+    q->m.config.seq_len = cap;
+    q->m.ctx_max = cap;
+    q->m.n_attn = n_attn;
+    q->m.kv_dim = n_kv * hd;
+    q->m.fp = fp;
+    q->m.has_weights = 1;
+    if (n_lin > 0) {
+        Hybrid *hy = &q->m.hy;
+        hy->on = 1; hy->interval = 4; hy->conv = conv; hy->dk = dk; hy->nk = nk; hy->dv = dv; hy->nv = nv;
+        hy->conv_dim = 2 * nk * dk + nv * dv;
+        hy->vdim = nv * dv;
+        hy->n_lin = n_lin;
+        q->m.ssm_layer = ssm_conv_floats(hy) + (size_t)nv * dk * dv;
+    }
+    gwo_threads_init(0);
+    q->s = rq_seq_new(&q->m, cap, kvt, &err);
+    if (!q->s) {
+        free(q);
+        return NULL;
+    }
+    return q;
+}
+GWO_API void gwo_seq_free(void *p) {
+    if (p) rq_seq_free(((SfSeq *)p)->s);
+    free(p);
+}
+/* bytes of all layers of the K (kv 0) / V (kv 1) cache, and floats of the layered DeltaNet state */
+GWO_API size_t gwo_seq_cache_bytes(void *p, int kv) { RqSeq *s = ((SfSeq *)p)->s; return seq_kvb(s, s->kv_size, kv); }
+GWO_API size_t gwo_seq_state_floats(void *p) { return ((SfSeq *)p)->s->ssm_bytes / sizeof(float); }
+/* the sequence's content from the caller's buffers (whole caches, len tokens, the layered state; ck_pos >= 0: a checkpoint
+ * at that length with the given state in slot 0) */
+GWO_API int gwo_seq_set(void *p, int len, const int *tokens, const void *k, const void *v, const float *ssm, int ck_pos, const float *ck) {
+    RqSeq *s = ((SfSeq *)p)->s;
+    if (len < 0 || len > s->cap) return -1;
+    memcpy(s->key_cache, k, seq_kvb(s, s->kv_size, 0));
+    memcpy(s->value_cache, v, seq_kvb(s, s->kv_size, 1));
+    memcpy(s->tokens, tokens, (size_t)len * sizeof(int));
+    if (s->ssm_bytes && ssm) memcpy(s->ssm, ssm, s->ssm_bytes);
+    if (s->ssm_bytes && ck_pos >= 0) {
+        if (!s->ck[0].st && !(s->ck[0].st = alloc_big(s->ssm_bytes))) return -2;
+        memcpy(s->ck[0].st, ck, s->ssm_bytes);
+        s->ck[0].pos = ck_pos;
+        s->ck[0].rows = s->ck[0].wr = 0;
+    }
+    seq_grow(s, len);
+    return 0;
+}
+/* the other way round: returns the length; ck_pos: the length of the checkpoint in slot 0 or -1 */
+GWO_API int gwo_seq_get(void *p, int *tokens, void *k, void *v, float *ssm, int *ck_pos, float *ck) {
+    RqSeq *s = ((SfSeq *)p)->s;
+    memcpy(k, s->key_cache, seq_kvb(s, s->kv_size, 0));
+    memcpy(v, s->value_cache, seq_kvb(s, s->kv_size, 1));
+    memcpy(tokens, s->tokens, (size_t)s->len * sizeof(int));
+    if (s->ssm_bytes && ssm) memcpy(ssm, s->ssm, s->ssm_bytes);
+    if (ck_pos) {
+        *ck_pos = s->ssm_bytes ? s->ck[0].pos : -1;
+        if (*ck_pos >= 0 && ck) memcpy(ck, s->ck[0].st, s->ssm_bytes);
+    }
+    return s->len;
+}
+GWO_API unsigned long long gwo_seq_rng(void *p, int set, unsigned long long v) {
+    RqSeq *s = ((SfSeq *)p)->s;
+    if (set) s->rng = v;
+    return s->rng;
+}
+GWO_API int gwo_seq_save(void *p, const char *path) { return rq_seq_save(((SfSeq *)p)->s, path); }
+GWO_API int gwo_seq_load(void *p, const char *path, int n) { return rq_seq_load(((SfSeq *)p)->s, path, n); }
+GWO_API long long gwo_seq_save_bytes(void *p) { return rq_seq_save_bytes(((SfSeq *)p)->s); }
+
+/* the activation quantiser (quantize, forward.c:803) on n values in groups of gs */
+GWO_API void gwo_quantize(const float *x, int n, int gs, int8_t *q, float *s) {
+    QuantizedTensor t = { 0 };
+    int keep = GS;
+    t.q = q;
+    t.s = s;
+    GS = gs;
+    quantize(&t, (float *)x, n);
+    GS = keep;
+}

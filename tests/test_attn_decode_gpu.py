@@ -88,12 +88,13 @@ def test_store_and_decode_match_cpu(checker, port, kvt, n_heads, n_kv, hd, gated
 @pytest.mark.parametrize("kvt", [Q8, Q4, Q4K4])
 @pytest.mark.parametrize("n_heads,n_kv,gated", [(4, 2, False), (8, 2, False), (8, 1, True), (6, 2, False), (2, 2, False)])
 def test_quantised_decode_on_tensor_cores_matches_cpu(checker, kvt, n_heads, n_kv, gated):
-    """The default path over quantised caches at head_dim 128 (levels dequantised to f16 operands, dot products on the tensor
+    """The tensor-core path over quantised caches at head_dim 128 (levels dequantised to f16 operands, dot products on the tensor
     cores) against the CPU code on the device's own cache bytes: inside the acceptance bar at every edge context, a row alone
     equal to the same row in a batch, and equal bits from run to run."""
     from gwenedeg_b200 import synth
     hd, n = 128, 700
     c = make_ctx(n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, gated=gated, max_rows=512)
+    c.set_exact(False)
     k, v = kv_rows(kvt * 100 + n_heads, n, n_kv, hd, outlier=False)
     # a large K dim, as real caches have (the dequantised values stay far inside the f16 range); V stays N(0,1)-sized: the
     # absolute bar is stated for outputs of that size, and a context of one position returns V itself, rounded to f16
@@ -277,4 +278,33 @@ def test_page_locked_result_buffer_is_written_in_place(kvt):
         c.pass_end(commit=False)
         assert bit_equal(plain, pinned[:rows]), name
         assert np.all(pinned[rows] == 7.0), name
+    c.close()
+
+
+@pytest.mark.parametrize("kvt,hd,gs", [(F16, 128, 32), (Q8, 128, 64), (F16, 256, 256), (F16, 64, 32), (F16, 128, 128)])
+def test_quantised_copy_of_the_outputs_for_the_wo_matmul(checker, kvt, hd, gs):
+    """rq_cuda_set_wo_quant: the merge kernels (decode and prefill) leave int8 levels and scales of their output rows, the
+    bits the reference's quantize() gives on the same fp32 rows (forward.c:803; its call right after the attention,
+    :2716-2719)."""
+    from gwenedeg_b200 import synth
+    n_heads, n_kv = 8, 2
+    gated = hd == 256
+    c = make_ctx(n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, gated=gated, max_rows=512)
+    s = c.new_seq(2600, kvt)
+    s.fill_synthetic(2600, 17)
+    rows = 70
+    xq_dev, xs_dev = c.malloc(rows * n_heads * hd), c.malloc(rows * n_heads * hd // gs * 4)
+    c.set_wo_quant(gs, xq_dev, xs_dev)
+    q = synth.normal(3, (rows, n_heads, hd * (2 if gated else 1)))
+    for fn in (c.attn_decode, c.attn_prefill):
+        c.pass_begin([(s, 2300, rows)])
+        out = fn(0, q)
+        xq, xs = np.empty((rows, n_heads * hd), np.int8), np.empty((rows, n_heads * hd // gs), np.float32)
+        c.d2h(xq, xq_dev)
+        c.d2h(xs, xs_dev)
+        c.sync()
+        c.pass_end(commit=False)
+        wq, ws = checker.quantize(out.reshape(rows, -1), gs)
+        assert np.array_equal(xq, wq) and bit_equal(xs.reshape(-1), ws), fn.__name__
+    c.set_wo_quant(0, None, None)
     c.close()

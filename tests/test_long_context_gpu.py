@@ -24,7 +24,7 @@ def test_long_context_rows_equal_cpu(checker, kvt, ctxs):
     from gwenedeg_b200 import synth
     n_heads, n_kv, hd = 32, 8, 128
     c = g.Context(0, n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, max_rows=8)
-    c.set_exact(True)  # (quantised caches: the kernels that give the CPU code's bits; the default ones are checked below)
+    c.set_exact(True)  # (quantised caches: the kernels that give the CPU code's bits; the tensor-core ones are checked below)
     seqs = []
     for i, n in enumerate(ctxs):
         s = c.new_seq(n, kvt)
@@ -45,7 +45,7 @@ def test_long_context_rows_equal_cpu(checker, kvt, ctxs):
         c.pass_end(commit=False)
         assert bit_equal(alone, got[i:i + 1])
     if kvt != F16:
-        # the default path over quantised caches (tensor cores): the same rows inside the acceptance bar
+        # the tensor-core path over quantised caches: the same rows inside the acceptance bar
         c.set_exact(False)
         c.pass_begin([(s, n - 1, 1) for s, n in zip(seqs, ctxs)])
         fast = c.attn_decode(0, q)

@@ -72,3 +72,18 @@ def test_deltanet_pinned(which):
         res.append((p1, r1, f1, p2, r2, st.copy()))
     for a, b in zip(*res):
         assert beq(a, b)
+
+
+@pytest.mark.parametrize("which", ["ref", "ref-v4", "ref-generic"])
+def test_activation_quantiser_pinned(which):
+    ref, port = gwo.load(which), gwo.load("port")
+    if ref is None:
+        pytest.skip("oracle/_ref not built")
+    x = synth.normal(77, (64, 512)) * np.float32(0.03)
+    x[3, :64] = 0.0          # an all-zero group
+    x[5, 7] = 1e-30          # a tiny maximum
+    x[9, 100] = 5.0e4
+    for gs in (32, 64, 128, 256):
+        q1, s1 = port.quantize(x, gs)
+        q2, s2 = ref.quantize(x, gs)
+        assert np.array_equal(q1, q2) and beq(s1, s2), gs
