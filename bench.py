@@ -272,31 +272,42 @@ _H8, _H4 = N_KV * (HD + HD // 32 * 2), N_KV * (HD // 2 + HD // 32 * 2)
 Q_BYTES_PER_POS = {"q8": 2 * _H8, "q4": _H8 + _H4, "q4k4": 2 * _H4}
 
 
-def q8_leg(args, rank, local_rank, world, kv="q8"):
-    """Qwen3-8B-shaped quantised-KV decode: 32 sequences at context 40,960, K and V as int8 (q8), 4-bit V (q4) or 4-bit K and V (q4k4) levels in
-    blocks of 32 dims with bf16 scales (the reference's tile format), dequantisation fused into the kernel.  With N > 1 every rank holds a group
-    of KV heads of every sequence and the outputs are all-gathered (NCCL)."""
+def q8_leg(args, rank, local_rank, world, kv="q8", dist=None, steps=None, warmup=None):
+    """Qwen3-8B-shaped quantised-KV decode: 32 sequences at context 40,960, K and V as int8 (q8), 4-bit V (q4) or 4-bit K and V
+    (q4k4) levels in blocks of 32 dims with bf16 scales (the reference's tile format).  q8 runs on the integer tensor cores (the
+    cached levels are the MMA operands; --exact: the bit-exact CUDA-core kernels), the 4-bit types on the CUDA-core kernels.  With
+    N > 1 every rank holds a group of KV heads of every sequence and the outputs are all-gathered (NCCL): returned beside the
+    rows/s are the share of the step spent outside the attention kernels (gather + slicing copies) and whether a small pass
+    gathered over the ranks equals the same pass on one GPU bit for bit.  Returns the JSON object of the leg (rank 0; else None)."""
+    import hashlib
     import gwenedeg_b200 as g
     from gwenedeg_b200 import synth
     from gwenedeg_b200.sharded import HeadShardedContext
     import torch
-    dist = None
-    if world > 1:
+    steps = args.steps if steps is None else steps
+    warmup = args.warmup if warmup is None else warmup
+    own_group = False
+    if world > 1 and dist is None:
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        own_group = True
     layers = 2 if args.small else N_LAYERS
     nseq = 4 if args.small else Q8_SEQ
+    kvt = {"q8": g.KV_Q8, "q4": g.KV_Q4, "q4k4": g.KV_Q4K4}[kv]
     sh = HeadShardedContext(local_rank, rank, world, n_attn=layers, n_heads=N_HEADS, n_kv_heads=N_KV, head_dim=HD, max_rows=nseq)
     c = sh.ctx
+    c.set_exact(bool(args.exact))
     seqs = []
     for i in range(nseq):
-        s = c.new_seq(Q8_CTX, {"q8": g.KV_Q8, "q4": g.KV_Q4, "q4k4": g.KV_Q4K4}[kv])
+        s = c.new_seq(Q8_CTX, kvt)
         s.fill_synthetic(Q8_CTX, 500 + i)
         seqs.append(s)
     c.sync()
     q = torch.from_numpy(synth.normal(11, (layers, nseq, N_HEADS, HD))).cuda()
     segs = [(s, Q8_CTX - 1, 1) for s in seqs]
+    ql = [sh.local_q(q[l]) for l in range(layers)]
+    out_l = torch.empty((nseq, sh.heads_local, HD), dtype=torch.float32, device="cuda")
 
     def step():
         c.pass_begin(segs)
@@ -304,42 +315,97 @@ def q8_leg(args, rank, local_rank, world, kv="q8"):
         c.pass_end(commit=False)
         return outs
 
-    for _ in range(args.warmup):
+    def step_local():  # the attention kernels alone: no gather, no slicing copies
+        c.pass_begin(segs)
+        with torch.cuda.stream(sh.stream):
+            for l in range(layers):
+                c.attn_decode_dev(l, ql[l].data_ptr(), out_l.data_ptr())
+        c.pass_end(commit=False)
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(sh.stream):
+            e0.record()
+        for _ in range(n):
+            fn()
+        with torch.cuda.stream(sh.stream):
+            e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(warmup):
         step()
-    torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()  # (on the caller's stream, which every attn_decode call orders itself with)
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    c.profile_begin(args.steps * layers)  # the kernel time of the roofline: a second pass with events around each launch
-    for _ in range(args.steps):
-        step()
+    ms = timed(step, steps)
+    ms_local = timed(step_local, steps) if world > 1 else ms
+    c.profile_begin(steps * layers)  # the kernel time of the roofline: a second pass with events around each launch
+    for _ in range(steps):
+        step_local()
     torch.cuda.synchronize()
     kern_ms, kern_n = c.profile_end()
-    if dist is not None:
-        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    sh.close()
+
+    # a small pass whose gathered rows must be the one-GPU rows: 2 sequences, one layer, rows written through kv_store
+    digest_equal = None
+    if world > 1:
+        n = 1500
+        k, v = synth.normal(1, (n, N_KV, HD)), synth.normal(2, (n, N_KV, HD))
+        qv = synth.normal(3, (2, N_HEADS, HD))
+        sv = HeadShardedContext(local_rank, rank, world, n_attn=1, n_heads=N_HEADS, n_kv_heads=N_KV, head_dim=HD)
+        sv.ctx.set_exact(bool(args.exact))
+
+        def fill(ctx, kk, vv):
+            a = ctx.new_seq(n, kvt)
+            for lo in range(0, n, 512):
+                hi = min(n, lo + 512)
+                ctx.pass_begin([(a, lo, hi - lo)])
+                ctx.kv_store(0, np.ascontiguousarray(kk[lo:hi]), np.ascontiguousarray(vv[lo:hi]))
+                ctx.pass_end()
+            b = ctx.new_seq(n, kvt)
+            b.copy_from(a, n)
+            return a, b
+
+        a, b = fill(sv.ctx, sv.local_kv(k), sv.local_kv(v))
+        sv.ctx.pass_begin([(a, n - 1, 1), (b, 700, 1)])
+        got = sv.attn_decode(0, torch.from_numpy(qv).cuda())
+        torch.cuda.synchronize()
+        sv.ctx.pass_end(commit=False)
+        sv.close()
+        if rank == 0:
+            full = g.Context(local_rank, n_attn=1, n_heads=N_HEADS, n_kv_heads=N_KV, head_dim=HD)
+            full.set_exact(bool(args.exact))
+            a, b = fill(full, k, v)
+            full.pass_begin([(a, n - 1, 1), (b, 700, 1)])
+            want = full.attn_decode(0, qv)
+            full.pass_end(commit=False)
+            full.close()
+            digest_equal = hashlib.sha256(got.cpu().numpy().tobytes()).hexdigest() == hashlib.sha256(want.tobytes()).hexdigest()
+        dist.barrier()
+    if own_group:
+        dist.destroy_process_group()
+    if rank != 0:
+        return None
     peak, how = peaks()
     bytes_launch = nseq * Q8_CTX * Q_BYTES_PER_POS[kv] / world
     achieved = bytes_launch / (kern_ms / max(kern_n, 1) * 1e-3) / 1e9
-    if rank == 0:
-        print(json.dumps({"metric": f"Qwen3-8B attn: {kv} KV decode rows/s (B=32, ctx 40960)", "value": nseq * args.steps / (ms * 1e-3),
-                          "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-                          "higher_is_better": True, "scaling": "strong", "dtype": "f32", "data": "synthetic",
-                          "config": {"workload": f"qwen3-8b-decode-{kv}-b32-ctx40960", "layers": layers, "sequences": nseq,
-                                     "parallelism": f"kv-head-sharded x{world} + all-gather"},
-                          "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                                       "traffic": None, "peak_source": how, "kernel": f"attn_part_kernel<{kv},128,4>",
-                                       "algorithmic_bytes_per_launch_rank0": bytes_launch, "launches_timed": kern_n}}), flush=True)
-    sh.close()
-    if dist is not None:
-        dist.destroy_process_group()
+    tc = kv == "q8" and not args.exact
+    return {"metric": f"Qwen3-8B attn: {kv} KV decode rows/s (B=32, ctx 40960)", "value": nseq * steps / (ms * 1e-3),
+            "unit": "rows/s", "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
+            "higher_is_better": True, "scaling": "strong", "dtype": "int8 x int8 -> int32, scales in f32" if tc else "f32", "data": "synthetic",
+            "config": {"workload": f"qwen3-8b-decode-{kv}-b32-ctx40960", "layers": layers, "sequences": nseq},
+            "run": {"parallelism": f"kv-head-sharded x{world} + all-gather", "kernels": "int8 tensor cores" if tc else "bit-exact CUDA cores"},
+            "outside_attention_kernels_share": max(0.0, 1.0 - ms_local / ms) if world > 1 else 0.0,
+            "digest_equal_1gpu": digest_equal,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": how, "kernel": "attn_part_tc_kernel<4>" if tc else f"attn_part_kernel<{kv},128,4>",
+                         "algorithmic_bytes_per_launch_rank0": bytes_launch, "launches_timed": kern_n}}
 
 
 DN_LAYERS, DN_SEQ, DN_TOKENS, DN_HEADS, DN_DK = 18, 4, 8192, 16, 128
@@ -430,7 +496,7 @@ def run_reference(args, rank, world):
     ctx_all = contexts()
     reps = max(1, args.steps)
     t0 = time.time()
-    info = cpu_leg(ctx_all, reps, sample_every=8)
+    info = cpu_leg(ctx_all, reps, sample_every=2)
     line = {"metric": METRIC, "value": info["value"], "unit": "rows/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 * N_SEQ / info["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "impl": "reference",
@@ -570,7 +636,18 @@ def run_ours(args, rank, local_rank, world):
     achieved = reduce_sum(achieved) / world  # mean over ranks of the per-GPU figure
 
     c.close()
-    prefill = prefill_hd256 = deltanet = None
+    prefill = prefill_hd256 = deltanet = decode_q8 = decode_q8_sharded = None
+    if not args.small:
+        # the quantised-cache configuration (32 sequences at context 40,960, q8): on one GPU the whole batch; on N GPUs split by
+        # KV-head group over the same process group, outputs all-gathered
+        try:
+            obj = q8_leg(args, rank, local_rank, world, kv="q8", dist=dist, steps=max(2, min(args.steps, 5)), warmup=3)
+            if world == 1:
+                decode_q8 = obj
+            else:
+                decode_q8_sharded = obj
+        except Exception as e:
+            decode_q8 = {"error": repr(e)}
     if world == 1 and not args.small:  # the other workloads ride on the one-GPU line only (each has its own --workload for N > 1)
         try:
             prefill = prefill_leg(local_rank, max(2, min(args.steps, 5)))
@@ -589,7 +666,7 @@ def run_ours(args, rank, local_rank, world):
         cpu = None
         if world == 1 and not args.no_cpu:
             try:
-                cpu = cpu_leg(ctx_all, reps=3, sample_every=8)
+                cpu = cpu_leg(ctx_all, reps=50, sample_every=2)
             except Exception as e:  # the baseline is reported, never required
                 cpu = {"value": None, "unit": "rows/s", "cores": 0, "kind": "unavailable", "sample": repr(e)}
         value = (len(mine) if args.shard_of > 1 else N_SEQ) * args.steps / (ms_max * 1e-3)
@@ -609,6 +686,8 @@ def run_ours(args, rank, local_rank, world):
                          "traffic": bytes_per_launch * TRAFFIC_RATIO, "traffic_source": "ncu dram read + write of the small case of the same kernel, scaled by positions", "peak_source": how, "kernel": "attn_part_kernel<f16,128,4>",
                          "algorithmic_bytes_per_launch_rank0": bytes_per_launch, "launches_timed": part_n},
             "cpu_baseline": cpu,
+            "decode_q8": decode_q8,
+            "decode_q8_head_sharded": decode_q8_sharded,
             "prefill": prefill,
             "prefill_hd256": prefill_hd256,
             "deltanet": deltanet,
@@ -625,6 +704,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--exact", action="store_true", help="quantised-cache workloads: the bit-exact CUDA-core kernels instead of the "
+                    "int8 tensor-core ones")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill-hd256", "decode-q8", "decode-q4", "decode-q4k4", "deltanet"],
                     help="decode: the headline batched-decode benchmark (default); prefill: only the chunked-prefill leg "
                          "(512 rows over a 3584-position prefix), printed as its own line")
@@ -646,7 +727,9 @@ def main():
         run_reference(args, rank, world)
         return
     if args.workload in ("decode-q8", "decode-q4", "decode-q4k4"):
-        q8_leg(args, rank, local_rank, world, kv=args.workload[7:])
+        line = q8_leg(args, rank, local_rank, world, kv=args.workload[7:])
+        if rank == 0:
+            print(json.dumps(line), flush=True)
         return
     if args.workload == "deltanet":
         line = deltanet_leg(local_rank, args.steps, small=args.small, rank=rank, world=world)

@@ -99,7 +99,9 @@ __device__ __forceinline__ bool mbar_wait_bounded_ns(uint64_t *bar, uint32_t par
     unsigned long long t0 = 0;
     for (int it = 0; it < (1 << 26); it++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63) == 63) {
+        // (the clock and the status word are looked at every 1024 polls only: the status word is a global-memory load of several
+        // hundred cycles, which a thread that is about to be released should not be sitting in)
+        if ((it & 1023) == 1023) {
             unsigned long long now;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
             if (t0 == 0) t0 = now;

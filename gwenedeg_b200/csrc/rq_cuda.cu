@@ -32,9 +32,6 @@ extern template cudaError_t launch_attn_part<KV_F16>(int, const AttnPartArgs &, 
 extern template cudaError_t launch_attn_part<KV_Q8>(int, const AttnPartArgs &, cudaStream_t);
 extern template cudaError_t launch_attn_part<KV_Q4>(int, const AttnPartArgs &, cudaStream_t);
 extern template cudaError_t launch_attn_part<KV_Q4K4>(int, const AttnPartArgs &, cudaStream_t);
-extern template cudaError_t launch_attn_part_tc<KV_Q8>(const AttnPartTcArgs &, cudaStream_t);
-extern template cudaError_t launch_attn_part_tc<KV_Q4>(const AttnPartTcArgs &, cudaStream_t);
-extern template cudaError_t launch_attn_part_tc<KV_Q4K4>(const AttnPartTcArgs &, cudaStream_t);
 extern template size_t attn_part_smem<KV_F16>(int, int);
 extern template size_t attn_part_smem<KV_Q8>(int, int);
 extern template size_t attn_part_smem<KV_Q4>(int, int);
@@ -55,9 +52,10 @@ struct RqCudaSeq {
     int in_pass;
     unsigned long long stamp;  // number of the last pass_begin that listed this sequence (duplicate check)
     bool dead;                 // rq_cuda_seq_free was called while the sequence belonged to the open pass: freed at pass_end
-    // 2-D views of the K and V caches for the tensor-core prefill kernel (f16, head_dim 128)
-    CUtensorMap tm_k, tm_v;
-    bool has_tm;
+    // 2-D views of the K and V caches for the tensor-core prefill kernels (f16, head_dim 128 / 256); q8 at head_dim 128: tm_v is
+    // the 3-D view of the V levels for the tensor-core decode kernel (has_tm_q8)
+    CUtensorMap tm_k, tm_v, tm_ks, tm_vs;  // (tm_ks, tm_vs: the scales behind each tile's levels, q8 only)
+    bool has_tm, has_tm_q8;
 };
 
 struct RqCuda {
@@ -104,9 +102,11 @@ struct RqCuda {
     int *err_fwd = nullptr;  // set around a launch whose merge kernel should store the status word to h_err itself
     // tensor-core prefill: the segments' tensor maps and the work list of the open pass
     CUtensorMap *h_maps, *d_maps;  // [max_rows][2]
+    CUtensorMap *h_maps8, *d_maps8;  // [max_rows][4]: the q8 views of the tensor-core decode kernel
     PfWork *d_work; size_t work_bytes;
     std::vector<PfWork> h_work;
     int pf_ready, pf_max_splits;
+    int tc_ready;  // the open pass's tensor maps for the tensor-core decode kernel are on the device (1), or it does not qualify (-1)
     // DeltaNet weights of the steps around the recurrence (rq_cuda_dn_set_weights): per linear layer conv taps, A, dt
     // bias, norm weight
     float *d_dnw; size_t dnw_layer_floats;
@@ -155,8 +155,29 @@ static bool seq_make_maps(RqCuda *c, RqCudaSeq *s) {
     // K: rows of 16 positions x one dim (32 bytes), 32-byte swizzle, box 16 x 256 (two tiles of head_dim 128) or 16 x 128 (the
     // 128-dim half of one tile of head_dim 256);
     // V: rows of one position x head_dim dims (256 or 512 bytes), 128-byte swizzle, box 64 x 128
-    s->has_tm = false;
+    s->has_tm = s->has_tm_q8 = false;
     const int hd = c->m.head_dim;
+    if (s->kvt == KV_Q8 && hd == 128 && c->m.n_attn >= 1) {
+        // The V levels of a q8 cache as the tensor-core decode kernel wants them in shared memory: half a block of one head (8 tiles)
+        // as 128 rows (positions) of 128 bytes with the 128-byte swizzle, an MN-major MMA operand: {128 dims, 16 positions, tiles}
+        // with strides {128, tile bytes}, box 128 x 16 x 8.
+        TmEncodeFn enc8 = tm_encode();
+        if (!enc8) return false;
+        const cuuint64_t tb = kv_tile_bytes(KV_Q8, 128, 0), tiles = (cuuint64_t)(s->lk * c->m.n_attn / tb);
+        cuuint32_t es3[3] = {1, 1, 1};
+        const auto u8 = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+        const auto il = CU_TENSOR_MAP_INTERLEAVE_NONE;
+        const auto l2 = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+        const auto oob = CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE;
+        {
+            cuuint64_t dims[3] = {128, 16, tiles}, strides[2] = {128, tb};
+            cuuint32_t box[3] = {128, 16, 8};
+            if (enc8(&s->tm_v, u8, 3, s->v, dims, strides, box, es3, il, CU_TENSOR_MAP_SWIZZLE_128B, l2, oob) != CUDA_SUCCESS) return false;
+        }
+        s->tm_k = s->tm_ks = s->tm_vs = s->tm_v;  // (only the V view is used: the K tiles and the scales go by plain bulk copies)
+        s->has_tm_q8 = true;
+        return true;
+    }
     if (s->kvt != KV_F16 || (hd != 128 && hd != 256) || c->m.n_attn < 1) return true;
     TmEncodeFn enc = tm_encode();
     if (!enc) return false;
@@ -261,7 +282,7 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
     c->n_heads = c->n_kv * c->G;
     c->qh = (m.gated ? 2 : 1) * m.head_dim;
     c->max_rows = max_rows;
-    c->exact = 1;
+    c->exact = 0;
     c->err[0] = 0;
     bool okk = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) == cudaSuccess &&
                cudaEventCreate(&c->ev0) == cudaSuccess && cudaEventCreate(&c->ev1) == cudaSuccess &&
@@ -283,6 +304,8 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
                cudaMallocHost((void **)&c->h_err, sizeof(int)) == cudaSuccess &&
                cudaMallocHost((void **)&c->h_maps, sizeof(CUtensorMap) * 2 * max_rows) == cudaSuccess &&
                cudaMalloc((void **)&c->d_maps, sizeof(CUtensorMap) * 2 * max_rows) == cudaSuccess &&
+               cudaMallocHost((void **)&c->h_maps8, sizeof(CUtensorMap) * 4 * max_rows) == cudaSuccess &&
+               cudaMalloc((void **)&c->d_maps8, sizeof(CUtensorMap) * 4 * max_rows) == cudaSuccess &&
                cudaMemset(c->d_err, 0, sizeof(int)) == cudaSuccess;
     c->stream = c->own_stream;
     if (!okk) {
@@ -298,7 +321,8 @@ void rq_cuda_free(RqCuda *c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->d_dnw) cudaFree(c->d_dnw);
-    void *dev[] = {c->d_tcq, c->d_blk2row, c->d_chunks, c->d_ck, c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
+    if (c->h_maps8) cudaFreeHost(c->h_maps8);
+    void *dev[] = {c->d_maps8, c->d_tcq, c->d_blk2row, c->d_chunks, c->d_ck, c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
     if (c->h_maps) cudaFreeHost(c->h_maps);
     for (void *p : dev)
         if (p) cudaFree(p);
@@ -627,7 +651,7 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
     }
     memset(&c->h_rows[r], 0, sizeof(PassRow));
     c->h_rows[r].blk0 = blk;
-    c->pf_ready = 0;  // (the tensor-core prefill tables are made by the first prefill call of the pass)
+    c->pf_ready = c->tc_ready = 0;  // (the tensor-core tables are made by the first call of the pass that needs them)
     c->dn_ready = c->dn_used = 0;  // (the DeltaNet tables by the first DeltaNet call, once the pass's checkpoints are named)
     c->pass_ck.clear();
     CU(c, cudaMemcpyAsync(c->d_rows, c->h_rows, sizeof(PassRow) * (r + 1), cudaMemcpyHostToDevice, c->stream));
@@ -766,19 +790,31 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
     cudaError_t e;
     const bool prof = c->prof_on && (size_t)(2 * c->prof_n + 2) <= c->prof_ev.size();
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n], c->stream);
-    if (kv_quant(c->pass_kvt) && hd == 128 && !c->exact && may_allocate) {
-        // quantised caches at head_dim 128: levels as f16 operands + tcgen05.mma (results inside the tolerance); the same
-        // partial records, merged by the same kernel
+    if (c->pass_kvt == KV_Q8 && hd == 128 && !c->exact && may_allocate && c->tc_ready == 0) {
+        // once per pass: the tensor maps of the segments' sequences
+        c->tc_ready = 1;
+        for (auto &g : c->segs)
+            if (!g.seq->has_tm_q8) c->tc_ready = -1;
+        if (c->tc_ready == 1) {
+            for (size_t i = 0; i < c->segs.size(); i++) {
+                const RqCudaSeq *sq = c->segs[i].seq;
+                c->h_maps8[4 * i] = sq->tm_k, c->h_maps8[4 * i + 1] = sq->tm_v, c->h_maps8[4 * i + 2] = sq->tm_ks, c->h_maps8[4 * i + 3] = sq->tm_vs;
+            }
+            CU(c, cudaMemcpyAsync(c->d_maps8, c->h_maps8, sizeof(CUtensorMap) * 4 * c->segs.size(), cudaMemcpyHostToDevice, c->stream));
+            CU(c, cudaStreamSynchronize(c->stream));  // (the pinned table is reused by the next pass)
+        }
+    }
+    if (c->pass_kvt == KV_Q8 && hd == 128 && !c->exact && may_allocate && c->tc_ready == 1) {
+        // 8-bit caches at head_dim 128: the cached levels as int8 MMA operands (results inside the tolerance); the same partial
+        // records, merged by the same kernel
         int rcg;
         if ((rcg = grow(c, (void **)&c->d_tcq, &c->tcq_bytes, (size_t)c->nrows * c->n_kv * TCD_QT_BYTES))) return rcg;
         if ((rcg = grow(c, (void **)&c->d_blk2row, &c->blk2row_bytes, (size_t)c->total_blocks * sizeof(int)))) return rcg;
         AttnPartTcArgs t;
-        t.qt = c->d_tcq, t.blk2row = c->d_blk2row;
+        t.qt = c->d_tcq, t.blk2row = c->d_blk2row, t.maps = c->d_maps8;
         t.rows = a.rows, t.nrows = a.nrows, t.total_blocks = a.total_blocks, t.layer = a.layer, t.n_kv = a.n_kv, t.G = a.G;
         t.q = a.q, t.qh = a.qh, t.n_heads = a.n_heads, t.scale = a.scale, t.part = a.part, t.err = a.err;
-        e = c->pass_kvt == KV_Q8 ? launch_attn_part_tc<KV_Q8>(t, c->stream)
-            : c->pass_kvt == KV_Q4 ? launch_attn_part_tc<KV_Q4>(t, c->stream)
-                                   : launch_attn_part_tc<KV_Q4K4>(t, c->stream);
+        e = launch_attn_part_tc(t, c->stream);
     } else
     switch (c->pass_kvt) {
         case KV_F16: e = launch_attn_part<KV_F16>(hd, a, c->stream); break;
