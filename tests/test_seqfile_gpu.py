@@ -13,13 +13,13 @@ pytestmark = pytest.mark.gpu
 
 def _fill(c, s, n, n_kv, hd, layers, seed):
     from gwenedeg_b200 import synth
-    for l in range(layers):
-        k, v = synth.normal(seed + 2 * l, (n, n_kv, hd)), synth.normal(seed + 2 * l + 1, (n, n_kv, hd))
-        for lo in range(0, n, 512):
-            hi = min(n, lo + 512)
-            c.pass_begin([(s, lo, hi - lo)])
-            c.kv_store(l, k[lo:hi], v[lo:hi])
-            c.pass_end(commit=(l == layers - 1))
+    kv = [(synth.normal(seed + 2 * l, (n, n_kv, hd)), synth.normal(seed + 2 * l + 1, (n, n_kv, hd))) for l in range(layers)]
+    for lo in range(0, n, 512):
+        hi = min(n, lo + 512)
+        c.pass_begin([(s, lo, hi - lo)])
+        for l in range(layers):
+            c.kv_store(l, kv[l][0][lo:hi], kv[l][1][lo:hi])
+        c.pass_end()
 
 
 @pytest.mark.parametrize("kvt", [2, 3, 8], ids=["f16", "q8", "q4"])
