@@ -22,6 +22,10 @@ class RqCudaModel(C.Structure):
         "kv_head0", "kv_heads_local")]
 
 
+class RqCudaPassTime(C.Structure):
+    _fields_ = [("seconds", C.c_double), ("rows", C.c_int), ("pos_first", C.c_double), ("pos_more", C.c_double)]
+
+
 class RqCudaSegment(C.Structure):
     _fields_ = [("seq", C.c_void_p), ("pos0", C.c_int), ("n", C.c_int)]
 
@@ -67,6 +71,9 @@ PROTOTYPES = {
     "rq_cuda_pass_begin": (_i, [_vp, C.POINTER(RqCudaSegment), _i]),
     "rq_cuda_pass_checkpoint": (_i, [_vp, _i, _i, _i]),
     "rq_cuda_pass_end": (_i, [_vp, _i]),
+    "rq_cuda_pass_timing": (_i, [_vp, _i]),
+    "rq_cuda_pass_time": (_i, [_vp, C.POINTER(RqCudaPassTime)]),
+    "rq_cuda_pass_cost_measure": (_i, [_vp, _vp, _i, _i, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "rq_cuda_kv_store": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_kv_store_dev": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_qk_norm_rope_store_dev": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, C.c_float]),

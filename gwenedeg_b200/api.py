@@ -79,6 +79,21 @@ class Context:
         """Size the scratch for passes of up to `rows` rows over `positions_total` cached positions (no allocation later)."""
         self.check(self.L.rq_cuda_reserve(self.h, rows, positions_total, max_ctx))
 
+    def pass_timing(self, on=True):
+        self.check(self.L.rq_cuda_pass_timing(self.h, int(on)))
+
+    def pass_time(self):
+        """(device seconds, rows, S1, S2) of the last closed pass (pass_timing on)."""
+        t = _lib.RqCudaPassTime()
+        self.check(self.L.rq_cuda_pass_time(self.h, C.byref(t)))
+        return t.seconds, t.rows, t.pos_first, t.pos_more
+
+    def pass_cost_measure(self, seq, L, reps=3):
+        """(t_w, att, att_x) of the reference's pass-cost model for the attention path on this device."""
+        tw, att, attx = C.c_double(), C.c_double(), C.c_double()
+        self.check(self.L.rq_cuda_pass_cost_measure(self.h, seq.h, L, reps, C.byref(tw), C.byref(att), C.byref(attx)))
+        return tw.value, att.value, attx.value
+
     def set_wo_quant(self, gs, xq_dev, xs_dev):
         """Attention calls also write int8 levels + scales of their output rows (None, None: off)."""
         self.check(self.L.rq_cuda_set_wo_quant(self.h, gs, _ptr(xq_dev), _ptr(xs_dev)))

@@ -67,6 +67,10 @@ struct RqCuda {
     int exact;  // rq_cuda_set_exact: quantised caches take the bit-exact CUDA-core kernels instead of the tensor-core ones
     cudaStream_t own_stream, stream;
     cudaEvent_t ev0, ev1;
+    // rq_cuda_pass_timing: events around every pass, and what the reference's cost model multiplies (seg_cost, engine.c:2631)
+    cudaEvent_t ev_p0, ev_p1;
+    int pass_timing, pass_timed, pt_rows;
+    double pt_first, pt_more;
     char err[256];
     unsigned long long launches;
     // the open pass
@@ -286,6 +290,7 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
     c->err[0] = 0;
     bool okk = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) == cudaSuccess &&
                cudaEventCreate(&c->ev0) == cudaSuccess && cudaEventCreate(&c->ev1) == cudaSuccess &&
+               cudaEventCreate(&c->ev_p0) == cudaSuccess && cudaEventCreate(&c->ev_p1) == cudaSuccess &&
                cudaMallocHost((void **)&c->h_rows2[0], sizeof(PassRow) * (max_rows + 1)) == cudaSuccess &&
                cudaMallocHost((void **)&c->h_rows2[1], sizeof(PassRow) * (max_rows + 1)) == cudaSuccess &&
                cudaMallocHost((void **)&c->h_dseg2[0], sizeof(DnSeg) * max_rows) == cudaSuccess &&
@@ -335,6 +340,8 @@ void rq_cuda_free(RqCuda *c) {
     }
     if (c->h_err) cudaFreeHost(c->h_err);
     for (cudaEvent_t ev : c->prof_ev) cudaEventDestroy(ev);
+    if (c->ev_p0) cudaEventDestroy(c->ev_p0);
+    if (c->ev_p1) cudaEventDestroy(c->ev_p1);
     if (c->ev0) cudaEventDestroy(c->ev0);
     if (c->ev1) cudaEventDestroy(c->ev1);
     if (c->own_stream) cudaStreamDestroy(c->own_stream);
@@ -402,6 +409,70 @@ int rq_cuda_set_wo_quant(RqCuda *c, int gs, signed char *xq_dev, float *xs_dev) 
         return fail(c, RQ_CUDA_ERR_ARG, "set_wo_quant: groups of %d values (head_dim %d)", gs, c->m.head_dim);
     if (((uintptr_t)xq_dev & 3) || ((uintptr_t)xs_dev & 3)) return fail(c, RQ_CUDA_ERR_ARG, "set_wo_quant: pointers must be 4-byte aligned");
     c->wo_quant = WoQuant{(int8_t *)xq_dev, xs_dev, gs};
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_pass_timing(RqCuda *c, int on) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    if (c->pass_open) return fail(c, RQ_CUDA_ERR_STATE, "pass_timing: a pass is open");
+    c->pass_timing = on != 0;
+    c->pass_timed = 0;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_pass_time(RqCuda *c, RqCudaPassTime *out) {
+    if (!c || !out) return RQ_CUDA_ERR_ARG;
+    if (!c->pass_timing || !c->pass_timed) return fail(c, RQ_CUDA_ERR_STATE, "pass_time: no timed pass has been closed (rq_cuda_pass_timing)");
+    CU(c, cudaSetDevice(c->device));
+    CU(c, cudaEventSynchronize(c->ev_p1));
+    float ms = 0.0f;
+    CU(c, cudaEventElapsedTime(&ms, c->ev_p0, c->ev_p1));
+    out->seconds = ms * 1e-3;
+    out->rows = c->pt_rows;
+    out->pos_first = c->pt_first;
+    out->pos_more = c->pt_more;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_pass_cost_measure(RqCuda *c, RqCudaSeq *s, int L, int reps, double *t_w, double *att, double *att_x) {
+    if (!c || !s || s->ctx != c || !t_w || !att || !att_x) return RQ_CUDA_ERR_ARG;
+    if (c->m.n_attn < 1 || L < 64 || L + 16 > s->cap || reps < 1 || c->max_rows < 16) return fail(c, RQ_CUDA_ERR_ARG, "pass_cost_measure: context %d (capacity %d)", L, s->cap);
+    if (c->pass_open || s->in_pass) return fail(c, RQ_CUDA_ERR_STATE, "pass_cost_measure: a pass is open");
+    int rc;
+    if ((rc = rq_cuda_seq_fill_synthetic(s, L + 16, 12345))) return rc;
+    const size_t qb = (size_t)16 * c->n_heads * c->qh * 4, ob = (size_t)16 * c->n_heads * c->m.head_dim * 4;
+    if ((rc = grow(c, (void **)&c->d_q, &c->q_bytes, qb))) return rc;
+    if ((rc = grow(c, (void **)&c->d_out, &c->out_bytes, ob))) return rc;
+    CU(c, cudaMemsetAsync(c->d_q, 0, qb, c->stream));
+    const int keep = c->pass_timing;
+    c->pass_timing = 1;
+    // the fastest of `reps` passes over all attention layers: one row at L / 2, one row at L, a segment of 16 rows at L
+    auto run = [&](int pos0, int n, double *secs) -> int {
+        double best = 1e30;
+        for (int r = 0; r < reps + 1; r++) {  // (the first one warms the kernels up)
+            RqCudaSegment g = {s, pos0, n};
+            int e = rq_cuda_pass_begin(c, &g, 1);
+            for (int l = 0; l < c->m.n_attn && !e; l++) e = n == 1 ? rq_cuda_attn_decode_dev(c, l, c->d_q, c->d_out) : rq_cuda_attn_prefill_dev(c, l, c->d_q, c->d_out);
+            if (c->pass_open) rq_cuda_pass_end(c, 0);
+            RqCudaPassTime t;
+            if (!e) e = rq_cuda_pass_time(c, &t);
+            if (e) return e;
+            if (r > 0 && t.seconds < best) best = t.seconds;
+        }
+        *secs = best;
+        return RQ_CUDA_OK;
+    };
+    double t_half = 0, t_one = 0, t_16 = 0;
+    rc = run(L / 2, 1, &t_half);
+    if (!rc) rc = run(L, 1, &t_one);
+    if (!rc) rc = run(L, 16, &t_16);
+    c->pass_timing = keep;
+    rq_cuda_seq_truncate(s, 0);
+    if (rc) return rc;
+    // t(1 row at p) = t_w + att p;  t(16 rows at L) = t_w + att L + att_x sum of the 15 further positions
+    *att = std::max(0.0, (t_one - t_half) / (double)(L - L / 2));
+    *t_w = std::max(0.0, t_one - *att * L);
+    *att_x = std::max(0.0, (t_16 - t_one) / (15.0 * L + 15.0 * 16.0 / 2.0));
     return RQ_CUDA_OK;
 }
 
@@ -652,6 +723,16 @@ int rq_cuda_pass_begin(RqCuda *c, const RqCudaSegment *seg, int nseg) {
     memset(&c->h_rows[r], 0, sizeof(PassRow));
     c->h_rows[r].blk0 = blk;
     c->pf_ready = c->tc_ready = 0;  // (the tensor-core tables are made by the first call of the pass that needs them)
+    if (c->pass_timing) {
+        double s1 = 0, s2 = 0;
+        for (int i = 0; i < nseg; i++) {
+            s1 += seg[i].pos0;
+            s2 += (double)(seg[i].n - 1) * seg[i].pos0 + (double)(seg[i].n - 1) * seg[i].n / 2.0;
+        }
+        c->pt_rows = r, c->pt_first = s1, c->pt_more = s2;
+        c->pass_timed = 0;
+        CU(c, cudaEventRecord(c->ev_p0, c->stream));
+    }
     c->dn_ready = c->dn_used = 0;  // (the DeltaNet tables by the first DeltaNet call, once the pass's checkpoints are named)
     c->pass_ck.clear();
     CU(c, cudaMemcpyAsync(c->d_rows, c->h_rows, sizeof(PassRow) * (r + 1), cudaMemcpyHostToDevice, c->stream));
@@ -683,6 +764,10 @@ int rq_cuda_pass_end(RqCuda *c, int commit) {
     }
     c->segs.clear();
     c->pass_open = 0;
+    if (c->pass_timing) {
+        CU(c, cudaEventRecord(c->ev_p1, c->stream));
+        c->pass_timed = 1;
+    }
     return RQ_CUDA_OK;
 }
 

@@ -184,6 +184,27 @@ int rq_cuda_pass_checkpoint(RqCuda *ctx, int seg, int row, int slot);
 /* closes the pass; commit != 0 grows each sequence's length to pos0 + n (seq_grow) */
 int rq_cuda_pass_end(RqCuda *ctx, int commit);
 
+/* What the reference's server feeds its pass-cost model with (RqPassCost, runq.h:660-685: a pass of R rows takes
+ * t_w f(R) + att S1 + att_x S2 seconds; cost_learn engine.c:2641 corrects the calibrated model by the measured time of each
+ * pass; seg_cost :2631 forms S1 and S2).  Host wall time says nothing about work that runs asynchronously on a device, so the
+ * library measures: with rq_cuda_pass_timing on, every pass is bracketed by CUDA events on the context's stream, and
+ * rq_cuda_pass_time returns, for the last closed pass, the device seconds between rq_cuda_pass_begin and rq_cuda_pass_end
+ * (it waits for that pass to finish) with the pass's rows, S1 = the sum of the segments' first positions and S2 = the sum of
+ * the positions of every further row: `took` and the arguments of rq_pass_cost for cost_learn.
+ * rq_cuda_pass_cost_measure is rq_pass_cost_measure (runq.h:678) for the attention path on the device: on a sequence of this
+ * context filled with synthetic values it times (fastest of `reps`) one row at L / 2, one row at L and a segment of 16 rows at
+ * L over all attention layers and solves for t_w (the part of a pass that does not depend on the context: launches), att
+ * (seconds per position of context for a segment's first row) and att_x (for each further row).  The sequence is left empty. */
+typedef struct {
+    double seconds;    /* device time of the pass */
+    int rows;          /* its rows */
+    double pos_first;  /* S1 */
+    double pos_more;   /* S2 */
+} RqCudaPassTime;
+int rq_cuda_pass_timing(RqCuda *ctx, int on);
+int rq_cuda_pass_time(RqCuda *ctx, RqCudaPassTime *out);
+int rq_cuda_pass_cost_measure(RqCuda *ctx, RqCudaSeq *seq, int L, int reps, double *t_w, double *att, double *att_x);
+
 /* K and V rows of the pass into the caches of attention layer `layer`, replacing kv_store (forward.c:1901; call
  * sites :2682/:2686, :3067-3085, :3568-3578).  k, v: host fp32 [rows][kv_heads_local][head_dim], after QK-norm and
  * RoPE; either may be NULL.  f16: round to nearest even, saturating (f32_f16 :1325); q8 / q4: rotate + quantise

@@ -308,3 +308,37 @@ def test_quantised_copy_of_the_outputs_for_the_wo_matmul(checker, kvt, hd, gs):
         assert np.array_equal(xq, wq) and bit_equal(xs.reshape(-1), ws), fn.__name__
     c.set_wo_quant(0, None, None)
     c.close()
+
+
+def test_pass_timing_feeds_the_cost_model():
+    """rq_cuda_pass_timing / _pass_time / _pass_cost_measure: the device time of a pass with the sums S1, S2 that the reference's
+    cost model multiplies (seg_cost, engine.c:2631), and a calibration whose terms are positive and ordered as the model says
+    (further rows of a segment share the first row's read of the cache: att_x <= att)."""
+    c = make_ctx(n_attn=4, n_heads=32, n_kv_heads=8, head_dim=128, max_rows=64)
+    a, b = c.new_seq(20000, F16), c.new_seq(20000, F16)
+    a.fill_synthetic(9000, 1)
+    b.fill_synthetic(500, 2)
+    qd, od = c.malloc(21 * 32 * 128 * 4), c.malloc(21 * 32 * 128 * 4)
+    c.pass_timing(True)
+    c.pass_begin([(a, 9000, 20), (b, 500, 1)])
+    for l in range(4):
+        c.attn_prefill_dev(l, qd, od)
+    c.pass_end(commit=False)
+    secs, rows, s1, s2 = c.pass_time()
+    assert rows == 21 and s1 == 9500 and s2 == 19 * 9000 + 19 * 20 / 2
+    assert 1e-6 < secs < 0.1
+    c.pass_timing(False)
+    tw, att, attx = c.pass_cost_measure(a, 16384, reps=3)
+    assert a.len == 0
+    assert 0 < att < 1e-6 and 0 <= attx <= att and 0 <= tw < 1e-2, (tw, att, attx)
+    # a decode step at 16,384 positions by the model is the time the step takes (4 layers), to a factor of two
+    a.fill_synthetic(16385, 3)
+    c.pass_timing(True)
+    for _ in range(3):
+        c.pass_begin([(a, 16384, 1)])
+        for l in range(4):
+            c.attn_decode_dev(l, qd, od)
+        c.pass_end(commit=False)
+    took = c.pass_time()[0]
+    assert 0.5 < took / (tw + att * 16384) < 2.0, (took, tw, att)
+    c.close()
