@@ -37,16 +37,28 @@ struct TcdCfg {
     static constexpr int KTB = kv_tile_bytes(KV_Q8, HD, 0), VTB = kv_tile_bytes(KV_Q8, HD, 1);  // 2176 each
     static constexpr int NS = NVT <= 4 ? 8 : 16;  // N of a score MMA: rows 2 v + plane
     static constexpr int NO = 8 * NVT;            // N of an output MMA: rows ((c NVT + v) 2 + plane)
-    // shared memory (from a 1024-byte aligned base): K levels of the two halves (2 x 16 KB: 128 rows = dims of 128 keys; later
-    // P^T: 2 x NO rows of 128 bytes) | V levels (2 x 16 KB: 128 rows = positions of 128 dims, swizzled by the TMA) | Q^T planes
-    // and scales (2304 B) | the rest
-    static constexpr int KLEV = 0, VLEV = 32768, QT = 65536;
-    static constexpr int PT = KLEV;
-    static constexpr int MISC = QT + 2304;  // red [3][8 warps][8] floats (768 B) | bars [4] | TMEM slot
-    static constexpr int SMEM = MISC + 768 + 64 + 16 + 1024;
-    static constexpr int TM_COLS = NVT <= 4 ? 128 : 256, S_COL = 0, O_COL = 8 * NS;
-    static_assert(QT % 1024 == 0 && 2 * NO * 128 <= 32768, "operand alignment; P^T fits the K levels");
+    // shared memory (from a 1024-byte aligned base): the next block's 16 K tiles as cached (one bulk copy) | K levels of the two
+    // halves as the operand wants them (2 x 16 KB: 128 rows = dims of 128 keys) | V levels (2 x 16 KB: 128 rows = positions of 128
+    // dims, swizzled by the TMA) | P^T (2 x NO rows of 128 bytes) | Q^T planes, two buffers of 2 KB, and their scales, 2 x 256 B | the rest
+    static constexpr int KRAW = 0, KLEV = 16 * KTB, VLEV = KLEV + 32768, PT = VLEV + 32768, QT = PT + 2 * NO * 128, QS = QT + 4096;
+    static constexpr int MISC = QS + 512;  // red [3][8 warps][8] floats (768 B) | bars [6] (64 B) | TMEM slot (16 B) | items [4] (128 B)
+    static constexpr int SMEM = MISC + 768 + 64 + 16 + 128 + 1024;
+    // TMEM columns: the score products of two blocks (2 x 8 NS) | the output products
+    static constexpr int S_COL = 0, O_COL = 16 * NS, TM_COLS = NVT <= 4 ? 256 : 512;
+    static_assert(KLEV % 1024 == 0 && VLEV % 1024 == 0 && PT % 1024 == 0 && QT % 1024 == 0, "operand alignment");
+    static_assert(O_COL + NO <= TM_COLS, "TMEM columns");
+    static_assert(NVT > 4 || 2 * (SMEM + 1024) <= 228 * 1024, "two CTAs per SM");
 };
+
+// a work item as the describing thread leaves it in shared memory for the others
+struct TcdItem {
+    int n;                  // positions of the block (1 .. 256)
+    int q;                  // query planes: buffer (bit 0), phase parity of its barrier (bit 1)
+    int vt, seg;            // first tile of the block in the 3-D view of its sequence's V cache; the row's segment
+    int gb, g;              // block of the pass, KV head: where the partial records go
+    unsigned long long vs;  // the block's V tiles in global memory (their scales are read from there)
+};
+static_assert(sizeof(TcdItem) == 32, "four items in 128 bytes");
 
 struct AttnPartTcArgs {
     const PassRow *rows;
@@ -58,6 +70,7 @@ struct AttnPartTcArgs {
     uint8_t *qt;              // scratch: nrows x n_kv records of TCD_QT_BYTES
     int *blk2row;             // scratch: total_blocks ints
     const CUtensorMap *maps;  // per segment: [4 seg + 1] = the 3-D view of its sequence's V cache levels
+    int n_sm;                 // SMs of the device: the grid is a fixed number of CTAs per SM
     int *err;
 };
 // launches tcd_q_prep_kernel and attn_part_tc_kernel on `stream`; cudaErrorInvalidValue for an unsupported shape
@@ -150,41 +163,56 @@ __global__ void __launch_bounds__(128) tcd_q_prep_kernel(const PassRow *__restri
     }
 }
 
+// One CTA's teardown wait for a copy that may still be in flight once a wait has expired: polls for at most ~2 ms whatever
+// the status word says, so that the CTA does not leave while a copy still writes its shared memory.
+__device__ __forceinline__ void mbar_drain(uint64_t *bar, uint32_t parity) {
+    unsigned long long t0 = 0;
+    for (int it = 0; it < (1 << 22); it++) {
+        if (mbar_try_wait(bar, parity)) return;
+        if ((it & 255) == 255) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            if (now - t0 > 2000000ull) return;
+        }
+    }
+}
+
+// Persistent form: the grid is two CTAs per SM (one for 5..8 vectors per KV head), each CTA walks a contiguous range of the work
+// items (KV head g, block gb of the pass) in the order j = g total_blocks + gb, so that consecutive items mostly share their row
+// and its query planes.  Everything an item needs from global memory is asked for ahead of its use and by copy engines, not by
+// the threads' own loads: item i + 2's K tiles (one bulk copy of the 16 tiles as cached) while item i is computed, item i's V
+// levels (TMA) as soon as the output products of item i - 1 have released the buffer.  Item i + 1's K chunks are moved to the
+// operand's layout (shared -> shared) and its score MMAs issued while item i goes through its softmax, so a block's scores are
+// complete when its turn comes (two score buffers in TMEM).  Per item two CTA barriers:
+//   S2  block maxima of every warp; next item's K levels in place  -> weights (all), next item's score MMAs (one thread)
+//   S3  P^T planes in place                                        -> output MMAs (the same thread)
+// The single-thread duties are spread over the first lanes of warps 4 .. 7 (warps 0 .. 3 store the partial results): V copies,
+// items + K and Q copies, (m, l), MMAs.
 // maps: per segment [4 seg + 1] the tensor map of its sequence's V cache: {128 bytes of levels, 16 positions, tiles} with
 // strides {128, tile bytes}, box 128 x 16 x 8, 128-byte swizzle.
 template <int NVT>
-__global__ void __launch_bounds__(TCD_THREADS, 3) attn_part_tc_kernel(const PassRow *__restrict__ rows, const int *__restrict__ blk2row,
-                                                                   const uint8_t *__restrict__ qtg, const CUtensorMap *__restrict__ maps, int layer,
-                                                                   int n_kv, int G, int n_heads, float scale, float *__restrict__ part, int *err) {
+__global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
+    attn_part_tc_kernel(const PassRow *__restrict__ rows, const int *__restrict__ blk2row, const uint8_t *__restrict__ qtg,
+                        const CUtensorMap *__restrict__ maps, int layer, int n_kv, int G, int n_heads, float scale, float *__restrict__ part,
+                        int total_blocks, int *err) {
     using C = TcdCfg<NVT>;
     constexpr int HD = C::HD, NS = C::NS, NO = C::NO;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *pt = sm + C::PT;
-    const float *qsc = reinterpret_cast<const float *>(sm + C::QT + 2048);  // [8][4]
-    float *red = reinterpret_cast<float *>(sm + C::MISC);                   // [3][8][8]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + C::MISC + 768);      // V half 0, V half 1, Q^T landed; MMAs complete
+    float *red = reinterpret_cast<float *>(sm + C::MISC);               // [3][8][8]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + C::MISC + 768);  // K tiles, V levels, Q^T buffer 0 / 1, scores, outputs
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + C::MISC + 768 + 64);
-    uint64_t *bar_q = bars + 2, *bar_mma = bars + 3;
+    TcdItem *items = reinterpret_cast<TcdItem *>(sm + C::MISC + 768 + 64 + 16);  // [4]: item i in items[i % 4]
+    uint64_t *bar_k = bars, *bar_v = bars + 1, *bar_q = bars + 2, *bar_s = bars + 4, *bar_o = bars + 5;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    pdl_wait();
-    pdl_launch_dependents();
-
-    const int lo = blk2row[blockIdx.x];
-    const PassRow row = rows[lo];
-    const int b = blockIdx.x - row.blk0, g = blockIdx.y;
-    const int n = min(row.np - b * ATT_P, ATT_P);  // positions of this block
-    const int nh = (n + 127) >> 7;                 // its halves of 128 positions
-    // (whole halves are fetched: a layer is a whole number of 256-position blocks, so the tiles past the block's last
-    // position exist; what they hold is masked below and enters the integer products as finite values times zero weights)
-    const size_t tile0 = ((size_t)b * n_kv + g) * ATT_PT;
-    const uint8_t *kg = row.k + (size_t)layer * row.lk + tile0 * C::KTB;
-    const uint8_t *vg = row.v + (size_t)layer * row.lv + tile0 * C::VTB;
-    RQ_CHECK(lo >= 0 && b >= 0 && n >= 1 && g < n_kv && (tile0 + 16) * C::KTB <= row.lk && (tile0 + 16) * C::VTB <= row.lv, err, 47);
+    const long long n_items = (long long)total_blocks * n_kv;
+    const int j0 = (int)(n_items * blockIdx.x / gridDim.x), cnt = (int)(n_items * (blockIdx.x + 1) / gridDim.x) - j0;
 
     if (tid == 0) {
-        for (int i = 0; i < 4; i++) mbar_init(bars + i, 1);
+        for (int i = 0; i < 6; i++) mbar_init(bars + i, 1);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -197,51 +225,104 @@ __global__ void __launch_bounds__(TCD_THREADS, 3) attn_part_tc_kernel(const Pass
     const uint32_t tbase = *tmem_slot;
     const uint32_t lane_addr = tbase + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t sbase = smem_u32(sm);
+    const int h2 = tid >> 7, t = tid & 127, pos = 128 * h2 + t;  // this thread's key of a block
+    const float c2 = scale * 1.44269504088896341f;
+    constexpr int T_V = 128, T_ITEMS = 160, T_ML = 192, T_MMA = 224;  // the threads with a duty of their own
     bool ok = true;
-    if (tid == 0) {
-        // V and the query planes by TMA, at once
-        mbar_expect_tx(bar_q, TCD_QT_BYTES);
-        bulk_g2s(sm + C::QT, qtg + ((size_t)lo * n_kv + g) * TCD_QT_BYTES, TCD_QT_BYTES, bar_q);
-        const CUtensorMap *mv = maps + 4 * row.seg + 1;
-        const int vt0 = (int)((size_t)layer * (row.lv / C::VTB) + tile0);  // first tile of the block in the 3-D view
-        for (int h = 0; h < nh; h++) {
-            mbar_expect_tx(bars + h, 16384);
-            tma_load_3d(sm + C::VLEV + h * 16384, mv, 0, 0, vt0 + 8 * h, bars + h);
+    pdl_wait();
+
+    // ---- thread T_ITEMS: the row of the item last described (re-read when an item leaves its blocks), the query planes copied so far
+    int r_lo = 0, r_blk0 = 0, r_nb = 0, r_np = 0, r_seg = 0, r_vt0 = 0, r_g = -1, nq = 0;
+    const uint8_t *r_k = nullptr, *r_v = nullptr;
+#ifdef RQ_DEBUG
+    unsigned long long r_lk = 0, r_lv = 0;
+#endif
+    // describes item i of this CTA into items[i % 4] and asks for its K tiles (and its query planes where they are new)
+    auto describe = [&](int i) {
+        const int j = j0 + i, g = j / total_blocks, gb = j - g * total_blocks;
+        bool qnew = g != r_g;
+        if (r_g < 0 || gb < r_blk0 || gb >= r_blk0 + r_nb) {
+            r_lo = __ldg(blk2row + gb);
+            const PassRow row = rows[r_lo];
+            r_blk0 = row.blk0, r_np = row.np, r_nb = (row.np + ATT_P - 1) / ATT_P, r_seg = row.seg;
+            r_k = row.k + (size_t)layer * row.lk, r_v = row.v + (size_t)layer * row.lv;
+            r_vt0 = (int)((size_t)layer * (row.lv / C::VTB));
+#ifdef RQ_DEBUG
+            r_lk = row.lk, r_lv = row.lv;
+#endif
+            qnew = true;
         }
-    }
-    // ---- K: every thread fetches 4 chunks of 16 positions x one dim per half and the scales of its own key, then puts the chunks
-    // where the operand wants them: row = dim, chunk = tile ^ (dim % 8) (the 128-byte swizzle)
-    const int h2 = tid >> 7, t = tid & 127, pos = 128 * h2 + t;
-    const bool valid = pos < n;
-    float dk[4] = {0.0f, 0.0f, 0.0f, 0.0f}, dv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    {
-        uint4 w[8];
+        r_g = g;
+        const int b = gb - r_blk0, n = min(r_np - b * ATT_P, ATT_P), nh = (n + 127) >> 7;
+        // (whole halves are fetched: a layer is a whole number of 256-position blocks, so the tiles past the block's last
+        // position exist; what they hold is masked below and enters the integer products as finite values times zero weights)
+        const size_t tile0 = ((size_t)b * n_kv + g) * ATT_PT;
+        if (qnew) nq++;
+        TcdItem d;
+        d.n = n, d.q = ((nq - 1) & 1) | ((((nq - 1) >> 1) & 1) << 1), d.vt = r_vt0 + (int)tile0, d.seg = r_seg, d.gb = gb, d.g = g;
+        d.vs = (unsigned long long)(uintptr_t)(r_v + tile0 * C::VTB);
+        items[i & 3] = d;
+#ifdef RQ_DEBUG
+        // (debug build: an item that does not fit its row or cache is not fetched: the CTA records it and ends its loop at the next
+        // barrier that votes; the waits for its copies give up at once because the status word is set)
+        if (!(r_lo >= 0 && b >= 0 && n >= 1 && g < n_kv && (tile0 + 16) * C::KTB <= r_lk && (tile0 + 16) * C::VTB <= r_lv)) {
+            atomicExch(err, 47);
+            ok = false;
+            return;
+        }
+#endif
+        fence_proxy_async();  // (the threads' reads of the tiles before, ordered by the CTA barrier, before the copy's writes)
+        mbar_expect_tx(bar_k, 8u * C::KTB * (uint32_t)nh);
+        bulk_g2s(sm + C::KRAW, r_k + tile0 * C::KTB, 8u * C::KTB * (uint32_t)nh, bar_k);
+        if (qnew) {
+            const int qb = (nq - 1) & 1;
+            const uint8_t *src = qtg + ((size_t)r_lo * n_kv + g) * TCD_QT_BYTES;
+            mbar_expect_tx(bar_q + qb, TCD_QT_BYTES);
+            bulk_g2s(sm + C::QT + qb * 2048, src, 2048, bar_q + qb);
+            bulk_g2s(sm + C::QS + qb * 256, src + 2048, 256, bar_q + qb);
+        }
+    };
+    // item i's V levels (thread T_V), once the output products of item i - 1 have released the buffer
+    auto fetch_v = [&](int i) {
+        const TcdItem d = items[i & 3];
+        const int nh = (d.n + 127) >> 7;
+        const CUtensorMap *mv = maps + 4 * d.seg + 1;
+        mbar_expect_tx(bar_v, 16384u * (uint32_t)nh);
+        for (int h = 0; h < nh; h++) tma_load_3d(sm + C::VLEV + h * 16384, mv, 0, 0, d.vt + 8 * h, bar_v);
+    };
+    // item i's K chunks from the tiles as cached to where the operand wants them (row = dim, chunk = tile ^ (dim % 8): the 128-byte
+    // swizzle), and the scales of this thread's key: K [group][16 positions] behind the tile's levels in shared memory, V
+    // [position][group] from global memory
+    uint32_t ks_n[4];
+    uint2 vs_n;
+    auto stage_k = [&](int i) {
+        const TcdItem d = items[i & 3];
+        const int nh = (d.n + 127) >> 7;
+        if (lane == 0) ok = mbar_wait_bounded(bar_k, (uint32_t)i & 1u, err, 72) && ok;
+        __syncwarp();
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-            const int idx = tid + TCD_THREADS * (k & 3), u = (idx >> 7) + 8 * (k >> 2), i = idx & 127;  // tile u of the block, dim i
-            w[k] = (k >> 2) < nh ? __ldg(reinterpret_cast<const uint4 *>(kg + (size_t)u * C::KTB + i * 16)) : make_uint4(0u, 0u, 0u, 0u);
+        for (int k = 0; k < 8; k++) {  // chunk (tile u, dim i): 16 positions of one dim
+            const int idx = tid + TCD_THREADS * (k & 3), u = (idx >> 7) + 8 * (k >> 2), dim = idx & 127;
+            if ((k >> 2) < nh)
+                *reinterpret_cast<uint4 *>(sm + C::KLEV + (k >> 2) * 16384 + dim * 128 + (((u & 7) ^ (dim & 7)) << 4)) =
+                    *reinterpret_cast<const uint4 *>(sm + C::KRAW + u * C::KTB + dim * 16);
         }
-        if (valid) {  // the key's scales: K [group][16 positions], V [position][group], bf16, behind their tile's levels
-            const uint16_t *ks = reinterpret_cast<const uint16_t *>(kg + (size_t)(pos >> 4) * C::KTB + 16 * HD) + (pos & 15);
+        if (pos < d.n) {
+            const uint16_t *ks = reinterpret_cast<const uint16_t *>(sm + C::KRAW + (pos >> 4) * C::KTB + 16 * HD) + (pos & 15);
 #pragma unroll
-            for (int c = 0; c < 4; c++) dk[c] = bf16_bits_to_f32(__ldg(ks + c * 16));
-            const uint2 wv = __ldg(reinterpret_cast<const uint2 *>(vg + (size_t)(pos >> 4) * C::VTB + 16 * HD) + (pos & 15));
-            dv[0] = __uint_as_float(wv.x << 16), dv[1] = __uint_as_float(wv.x & 0xffff0000u);
-            dv[2] = __uint_as_float(wv.y << 16), dv[3] = __uint_as_float(wv.y & 0xffff0000u);
+            for (int c = 0; c < 4; c++) ks_n[c] = ks[c * 16];
+            vs_n = __ldg(reinterpret_cast<const uint2 *>((const uint8_t *)(uintptr_t)d.vs + (size_t)(pos >> 4) * C::VTB + 16 * HD) + (pos & 15));
+        } else {
+            ks_n[0] = ks_n[1] = ks_n[2] = ks_n[3] = 0u;
+            vs_n = make_uint2(0u, 0u);
         }
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            const int idx = tid + TCD_THREADS * (k & 3), u = idx >> 7, i = idx & 127;
-            *reinterpret_cast<uint4 *>(sm + C::KLEV + (k >> 2) * 16384 + i * 128 + ((u ^ (i & 7)) << 4)) = w[k];
-        }
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-        // ---- S_c^T (half h) = K_c (half h) Q_c^T: one MMA per 32-dim group
+    };
+    // item i's score MMAs (thread T_MMA): S_c^T (half h) = K_c (half h) Q_c^T, one MMA per 32-dim group, into score buffer i % 2
+    auto issue_s = [&](int i) {
+        const TcdItem d = items[i & 3];
+        const int nh = (d.n + 127) >> 7, qb = d.q & 1;
         tc_fence_after();
-        ok = mbar_wait_bounded(bar_q, 0, err, 74) && ok;
+        ok = mbar_wait_bounded(bar_q + qb, (uint32_t)(d.q >> 1) & 1u, err, 74) && ok;
         constexpr uint32_t idesc_s = umma_idesc_i8(128, NS, 1, 0, 1, 1);
         for (int h = 0; h < nh; h++) {
 #pragma unroll
@@ -249,143 +330,197 @@ __global__ void __launch_bounds__(TCD_THREADS, 3) attn_part_tc_kernel(const Pass
                 // A: rows of 128 bytes (one dim, the half's 128 keys = one swizzle atom along MN), 8 dims = 1024 bytes (SBO); the group's
                 // 32 dims are 4096 bytes; B: rows of 128 bytes, 128-byte swizzle, the group's 32 dims at 32 c
                 const uint64_t da = umma_desc(sbase + C::KLEV + h * 16384 + c * 4096, 16, 1024, 2);
-                const uint64_t db = umma_desc(sbase + C::QT + c * 32, 16, 1024, 2);
-                umma_i8(tbase + C::S_COL + (4 * h + c) * NS, da, db, idesc_s, 0);
+                const uint64_t db = umma_desc(sbase + C::QT + qb * 2048 + c * 32, 16, 1024, 2);
+                umma_i8(tbase + C::S_COL + (i & 1) * 8 * NS + (4 * h + c) * NS, da, db, idesc_s, 0);
             }
         }
-        umma_commit(bar_mma);
-    }
-
-    // ---- softmax of the block: thread (half h2, key t) holds the scores of its key for the G vectors
-    // the block's largest V scale per group: what the weight planes are scaled by
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        float mx = dv[c];
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) red[128 + warp * 8 + c] = mx;
-    }
-    if (lane == 0) {  // (one poller per warp)
-        ok = mbar_wait_bounded(bar_q, 0, err, 74) && ok;   // (the query scales)
-        ok = mbar_wait_bounded(bar_mma, 0, err, 71) && ok;  // (the score products)
-    }
-    __syncwarp();
-    tc_fence_after();
-    const float c2 = scale * 1.44269504088896341f;
-    float s[NVT], e[NVT];
-#pragma unroll
-    for (int v = 0; v < NVT; v++) s[v] = 0.0f;
-    __syncwarp();
-    if (h2 < nh) {  // (uniform per warp)
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            uint32_t r[NS];
-            tmem_ld8(lane_addr + C::S_COL + (4 * h2 + c) * NS, r);
-            if constexpr (NVT == 8) tmem_ld8(lane_addr + C::S_COL + (4 * h2 + c) * NS + 8, r + 8);
-            tmem_wait_ld();
-#pragma unroll
-            for (int v = 0; v < NVT; v++)
-                s[v] = fmaf(dk[c] * qsc[v * 4 + c], (float)(((int)r[2 * v] << 8) + (int)r[2 * v + 1]), s[v]);
-        }
-    }
-#pragma unroll
-    for (int v = 0; v < NVT; v++) {
-        float mx = valid ? s[v] : -INFINITY;
-        s[v] = mx;
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) red[warp * 8 + v] = mx;
-    }
-    __syncthreads();  // (also: every thread has seen the score products complete: P^T may take the place of the K levels)
-    float m[NVT], l[NVT], ps_inv[4], ps[4];
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        float mx = red[128 + c];
-#pragma unroll
-        for (int wv = 1; wv < 8; wv++) mx = fmaxf(mx, red[128 + wv * 8 + c]);
-        ps[c] = mx;
-        ps_inv[c] = mx > 0.0f ? 65535.0f / mx : 0.0f;
-    }
-#pragma unroll
-    for (int v = 0; v < NVT; v++) {
-        float mx = red[v];
-#pragma unroll
-        for (int wv = 1; wv < 8; wv++) mx = fmaxf(mx, red[wv * 8 + v]);
-        m[v] = mx;
-        e[v] = valid ? ex2((s[v] - mx) * c2) : 0.0f;
-        float sum = e[v];
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        if (lane == 0) red[64 + warp * 8 + v] = sum;
-    }
-    // P^T: the B operand of O^T += V^T P^T, per half [NO rows][128 keys] uint8, K-major with the 128-byte swizzle: rows
-    // ((c NVT + v) 2 + plane) hold the two planes of round(p[.][v] d_V[.][c] 65535 / ps[c]); it takes the place of the K levels
-    if (h2 < nh) {
-        uint8_t *pb = pt + h2 * (NO * 128) + (t & 15);
-        const int ch = t >> 4;
-#pragma unroll
-        for (int c = 0; c < 4; c++)
-#pragma unroll
-            for (int v = 0; v < NVT; v++) {
-                const uint32_t u16 = (uint32_t)__float2int_rn(fminf(e[v] * dv[c] * ps_inv[c], 65535.0f));
-                const int rw = (c * NVT + v) * 2;
-                pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)(u16 >> 8);
-                pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)(u16 & 255u);
-            }
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-#pragma unroll
-    for (int v = 0; v < NVT; v++) {
-        float sum = red[64 + v];
-#pragma unroll
-        for (int wv = 1; wv < 8; wv++) sum += red[64 + wv * 8 + v];
-        l[v] = sum;
-    }
-
-    // ---- O^T += V^T (half h) P^T (half h): 4 k-steps of 32 keys per half
-    if (tid == 0) {
+        umma_commit(bar_s);
+    };
+    // the partial result of item i: o[hd] (unnormalised; m and l are stored by its softmax).  Thread = dim of group c = dim / 32
+    // (uniform over the warp): the columns (c, v, plane) of O.  Warps 0 .. 3.
+    auto store_o = [&](int i, float back, long long pidx) {
+        if (lane == 0) ok = mbar_wait_bounded(bar_o, (uint32_t)i & 1u, err, 75) && ok;
+        ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
-        constexpr uint32_t idesc_o = umma_idesc_i8(128, NO, 1, 0, 1, 0);
-        for (int h = 0; h < nh; h++) {
-            ok = mbar_wait_bounded(bars + h, 0, err, 73) && ok;  // (the half's V levels have landed)
-#pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-                // A: rows of 128 bytes (one position, all 128 dims = one swizzle atom along MN), 8 positions = 1024 bytes (SBO); 32 keys
-                // = 4096 bytes per k-step; B: the half's P^T rows, 32 keys = 32 bytes per k-step
-                const uint64_t da = umma_desc(sbase + C::VLEV + h * 16384 + ks * 4096, 16, 1024, 2);
-                const uint64_t db = umma_desc(sbase + C::PT + h * (NO * 128) + ks * 32, 16, 1024, 2);
-                umma_i8(tbase + C::O_COL, da, db, idesc_o, (h > 0) | (ks > 0));
-            }
-        }
-        umma_commit(bar_mma);
-    }
-    if (lane == 0) ok = mbar_wait_bounded(bar_mma, 1, err, 75) && ok;
-    __syncwarp();
-    tc_fence_after();
-
-    // ---- the partial result of (row, head, block): o[hd] (unnormalised), m (in scaled-score units), l.  Thread = dim i of
-    // group c = i / 32 (uniform over the warp): the columns (c, v, plane) of O
-    ok = __all_sync(0xffffffffu, ok);
-    if (warp < 4) {
         uint32_t r[2 * NVT < 8 ? 8 : 2 * NVT];
         tmem_ld8(lane_addr + C::O_COL + warp * 2 * NVT, r);
         if constexpr (NVT == 8) tmem_ld8(lane_addr + C::O_COL + warp * 2 * NVT + 8, r + 8);
         tmem_wait_ld();
-        const float back = ps[warp] * (1.0f / 65535.0f);
 #pragma unroll
-        for (int v = 0; v < NVT; v++) {
+        for (int v = 0; v < NVT; v++)
             if (v < G) {
-                float *p = part + ((size_t)(row.blk0 + b) * n_heads + (size_t)g * G + v) * RQ_PSTRIDE(HD);
                 const float o = fmaf((float)(int)r[2 * v], 256.0f, (float)(int)r[2 * v + 1]) * back;
-                p[tid] = ok ? o : 0.0f;  // (tid = TMEM lane = dim)
-                if (tid == 0) {
-                    p[HD] = m[v] * scale;
-                    p[HD + 1] = l[v];
-                }
+                part[pidx + (long long)v * RQ_PSTRIDE(HD) + tid] = ok ? o : 0.0f;  // (tid = TMEM lane = dim)
+            }
+    };
+
+    // ---- prologue: items 0 and 1 described and asked for, item 0's K in place and its score MMAs issued
+    if (tid == T_ITEMS) describe(0);
+    __syncthreads();
+    if (tid == T_V) fetch_v(0);
+    stage_k(0);
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == T_MMA) issue_s(0);
+    if (tid == T_ITEMS && cnt > 1) describe(1);
+    __syncthreads();
+
+    float back_prev = 0.0f;   // of the item before: what its output columns are scaled back by (warps 0..3: their group)
+    long long pidx_prev = 0;  // ... and its first partial record
+    int it = 0;
+    bool failed = false;
+    for (; it < cnt; it++) {
+        const TcdItem d = items[it & 3];
+        const int n = d.n, nh = (n + 127) >> 7, qb = d.q & 1;
+        const bool valid = pos < n, more = it + 1 < cnt;
+        const long long pidx = ((long long)d.gb * n_heads + (long long)d.g * G) * RQ_PSTRIDE(HD);
+        const float *qsc = reinterpret_cast<const float *>(sm + C::QS + qb * 256);  // [8][4]
+        if (tid == T_V && it > 0) {
+            ok = mbar_wait_bounded(bar_o, (uint32_t)(it - 1) & 1u, err, 75) && ok;
+            fetch_v(it);
+        }
+        // ---- the scales of this thread's key
+        float dk[4], dv[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) dk[c] = bf16_bits_to_f32(ks_n[c]);
+        dv[0] = __uint_as_float(vs_n.x << 16), dv[1] = __uint_as_float(vs_n.x & 0xffff0000u);
+        dv[2] = __uint_as_float(vs_n.y << 16), dv[3] = __uint_as_float(vs_n.y & 0xffff0000u);
+        // ---- softmax of the block: thread (half h2, key t) holds the scores of its key for the G vectors
+        // the block's largest V scale per group: what the weight planes are scaled by
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            float mx = dv[c];
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            if (lane == 0) red[128 + warp * 8 + c] = mx;
+        }
+        if (lane == 0) {  // (one poller per warp)
+            ok = mbar_wait_bounded(bar_q + qb, (uint32_t)(d.q >> 1) & 1u, err, 74) && ok;  // (the query scales)
+            ok = mbar_wait_bounded(bar_s, (uint32_t)it & 1u, err, 71) && ok;               // (the score products)
+        }
+        __syncwarp();
+        tc_fence_after();
+        float s[NVT], e[NVT];
+#pragma unroll
+        for (int v = 0; v < NVT; v++) s[v] = 0.0f;
+        if (h2 < nh) {  // (uniform per warp)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t r[NS];
+                tmem_ld8(lane_addr + C::S_COL + (it & 1) * 8 * NS + (4 * h2 + c) * NS, r);
+                if constexpr (NVT == 8) tmem_ld8(lane_addr + C::S_COL + (it & 1) * 8 * NS + (4 * h2 + c) * NS + 8, r + 8);
+                tmem_wait_ld();
+#pragma unroll
+                for (int v = 0; v < NVT; v++)
+                    s[v] = fmaf(dk[c] * qsc[v * 4 + c], (float)(((int)r[2 * v] << 8) + (int)r[2 * v + 1]), s[v]);
             }
         }
+#pragma unroll
+        for (int v = 0; v < NVT; v++) {
+            float mx = valid ? s[v] : -INFINITY;
+            s[v] = mx;
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            if (lane == 0) red[warp * 8 + v] = mx;
+        }
+        if (it > 0 && warp < 4) store_o(it - 1, back_prev, pidx_prev);
+        // ---- the next item's K levels and this thread's scales of it (the score products of this item are complete: the K levels
+        // it used may go)
+        if (more) stage_k(it + 1);
+        fence_proxy_async();
+        tc_fence_before();
+        // S2 (also: every thread now knows the output products of the item before complete: P^T may be overwritten); a wait that
+        // ran out anywhere ends the CTA's loop here
+        if (__syncthreads_or(!ok)) {
+            failed = true;
+            break;
+        }
+        if (tid == T_MMA && more) issue_s(it + 1);
+        if (tid == T_ITEMS && it + 2 < cnt) describe(it + 2);
+        float m[NVT], ps_inv[4];
+        float ps_mine = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            float mx = red[128 + c];
+#pragma unroll
+            for (int wv = 1; wv < 8; wv++) mx = fmaxf(mx, red[128 + wv * 8 + c]);
+            if (c == (warp & 3)) ps_mine = mx;
+            ps_inv[c] = mx > 0.0f ? 65535.0f / mx : 0.0f;
+        }
+#pragma unroll
+        for (int v = 0; v < NVT; v++) {
+            float mx = red[v];
+#pragma unroll
+            for (int wv = 1; wv < 8; wv++) mx = fmaxf(mx, red[wv * 8 + v]);
+            m[v] = mx;
+            e[v] = valid ? ex2((s[v] - mx) * c2) : 0.0f;
+            float sum = e[v];
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) red[64 + warp * 8 + v] = sum;
+        }
+        // P^T: the B operand of O^T += V^T P^T, per half [NO rows][128 keys] uint8, K-major with the 128-byte swizzle: rows
+        // ((c NVT + v) 2 + plane) hold the two planes of round(p[.][v] d_V[.][c] 65535 / ps[c])
+        if (h2 < nh) {
+            uint8_t *pb = pt + h2 * (NO * 128) + (t & 15);
+            const int ch = t >> 4;
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+#pragma unroll
+                for (int v = 0; v < NVT; v++) {
+                    const uint32_t u16 = (uint32_t)__float2int_rn(fminf(e[v] * dv[c] * ps_inv[c], 65535.0f));
+                    const int rw = (c * NVT + v) * 2;
+                    pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)(u16 >> 8);
+                    pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)(u16 & 255u);
+                }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();  // S3
+        if (tid == T_MMA) {
+            // ---- O^T += V^T (half h) P^T (half h): 4 k-steps of 32 keys per half
+            tc_fence_after();
+            ok = mbar_wait_bounded(bar_v, (uint32_t)it & 1u, err, 73) && ok;  // (the item's V levels have landed)
+            constexpr uint32_t idesc_o = umma_idesc_i8(128, NO, 1, 0, 1, 0);
+            for (int h = 0; h < nh; h++) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) {
+                    // A: rows of 128 bytes (one position, all 128 dims = one swizzle atom along MN), 8 positions = 1024 bytes (SBO); 32 keys
+                    // = 4096 bytes per k-step; B: the half's P^T rows, 32 keys = 32 bytes per k-step
+                    const uint64_t da = umma_desc(sbase + C::VLEV + h * 16384 + ks * 4096, 16, 1024, 2);
+                    const uint64_t db = umma_desc(sbase + C::PT + h * (NO * 128) + ks * 32, 16, 1024, 2);
+                    umma_i8(tbase + C::O_COL, da, db, idesc_o, (h > 0) | (ks > 0));
+                }
+            }
+            umma_commit(bar_o);
+        }
+        if (tid == T_ML) {  // m (in scaled-score units) and l of the block, for each vector
+#pragma unroll
+            for (int v = 0; v < NVT; v++)
+                if (v < G) {
+                    float sum = red[64 + v];
+#pragma unroll
+                    for (int wv = 1; wv < 8; wv++) sum += red[64 + wv * 8 + v];
+                    float *p = part + pidx + (long long)v * RQ_PSTRIDE(HD);
+                    p[HD] = m[v] * scale;
+                    p[HD + 1] = sum;
+                }
+        }
+        back_prev = ps_mine * (1.0f / 65535.0f);
+        pidx_prev = pidx;
+    }
+    pdl_launch_dependents();
+    if (!failed && warp < 4) store_o(cnt - 1, back_prev, pidx_prev);  // the last item's partial result
+    if (failed && tid == T_MMA) {
+        // a wait ran out: give what may still be in flight (the V levels of this item, the K tiles of the next, query planes,
+        // the MMAs issued last) a bounded time to finish before the CTA's shared memory and TMEM are released
+        mbar_drain(bar_v, (uint32_t)it & 1u);
+        if (it + 1 < cnt) mbar_drain(bar_k, (uint32_t)(it + 1) & 1u);
+        const TcdItem d = items[(it + (it + 1 < cnt ? 1 : 0)) & 3];
+        mbar_drain(bar_q + (d.q & 1), (uint32_t)(d.q >> 1) & 1u);
+        mbar_drain(bar_s, (uint32_t)it & 1u);
+        if (it > 0) mbar_drain(bar_o, (uint32_t)(it - 1) & 1u);
     }
     tc_fence_before();
     __syncthreads();
@@ -407,8 +542,10 @@ static cudaError_t launch_tc_one(const AttnPartTcArgs &a, cudaStream_t stream) {
     }
     cudaError_t e = launch_pdl(tcd_q_prep_kernel, dim3(a.nrows, a.n_kv), dim3(128), 0, stream, a.rows, a.n_kv, a.G, a.q, a.qh, a.n_heads, a.qt, a.blk2row);
     if (e != cudaSuccess) return e;
-    return launch_pdl(kern, dim3(a.total_blocks, a.n_kv), dim3(TCD_THREADS), (size_t)smem, stream, a.rows, (const int *)a.blk2row, (const uint8_t *)a.qt,
-                      a.maps, a.layer, a.n_kv, a.G, a.n_heads, a.scale, a.part, a.err);
+    const long long items = (long long)a.total_blocks * a.n_kv, slots = (long long)a.n_sm * (NVT <= 4 ? 2 : 1);
+    const int grid = (int)(items < slots ? items : slots);
+    return launch_pdl(kern, dim3(grid), dim3(TCD_THREADS), (size_t)smem, stream, a.rows, (const int *)a.blk2row, (const uint8_t *)a.qt, a.maps, a.layer,
+                      a.n_kv, a.G, a.n_heads, a.scale, a.part, a.total_blocks, a.err);
 }
 
 cudaError_t launch_attn_part_tc(const AttnPartTcArgs &a, cudaStream_t stream) {

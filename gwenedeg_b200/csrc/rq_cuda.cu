@@ -60,6 +60,7 @@ struct RqCudaSeq {
 
 struct RqCuda {
     int device;
+    int n_sm = 0;  // SMs of the device
     RqCudaModel m;
     int n_kv, n_heads, G, qh;  // local (this device's) KV heads / query heads, vectors per KV head, floats per q head row
     int max_rows;
@@ -280,6 +281,7 @@ int rq_cuda_init(int device, const RqCudaModel *model, int max_rows, RqCuda **ct
     RqCuda *c = new (std::nothrow) RqCuda();
     if (!c) return RQ_CUDA_ERR_NOMEM;
     c->device = device;
+    c->n_sm = prop.multiProcessorCount;
     c->m = m;
     c->n_kv = m.n_attn ? nkv_local : 0;
     c->G = m.n_attn ? m.n_heads / m.n_kv_heads : 0;
@@ -896,7 +898,7 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
         if ((rcg = grow(c, (void **)&c->d_tcq, &c->tcq_bytes, (size_t)c->nrows * c->n_kv * TCD_QT_BYTES))) return rcg;
         if ((rcg = grow(c, (void **)&c->d_blk2row, &c->blk2row_bytes, (size_t)c->total_blocks * sizeof(int)))) return rcg;
         AttnPartTcArgs t;
-        t.qt = c->d_tcq, t.blk2row = c->d_blk2row, t.maps = c->d_maps8;
+        t.qt = c->d_tcq, t.blk2row = c->d_blk2row, t.maps = c->d_maps8, t.n_sm = c->n_sm;
         t.rows = a.rows, t.nrows = a.nrows, t.total_blocks = a.total_blocks, t.layer = a.layer, t.n_kv = a.n_kv, t.G = a.G;
         t.q = a.q, t.qh = a.qh, t.n_heads = a.n_heads, t.scale = a.scale, t.part = a.part, t.err = a.err;
         e = launch_attn_part_tc(t, c->stream);
