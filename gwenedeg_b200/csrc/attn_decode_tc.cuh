@@ -41,7 +41,7 @@ struct TcdCfg {
     // halves as the operand wants them (2 x 16 KB: 128 rows = dims of 128 keys) | V levels (2 x 16 KB: 128 rows = positions of 128
     // dims, swizzled by the TMA) | P^T (2 x NO rows of 128 bytes) | Q^T planes, two buffers of 2 KB, and their scales, 2 x 256 B | the rest
     static constexpr int KRAW = 0, KLEV = 16 * KTB, VLEV = KLEV + 32768, PT = VLEV + 32768, QT = PT + 2 * NO * 128, QS = QT + 4096;
-    static constexpr int MISC = QS + 512;  // red [3][8 warps][8] floats (768 B) | bars [6] (64 B) | TMEM slot (16 B) | items [4] (128 B)
+    static constexpr int MISC = QS + 512;  // red (768 B: two buffers of block maxima, 64 B each; at 256 B the warps' sums [8][8])  | bars [6] (64 B) | TMEM slot (16 B) | items [4] (128 B)
     static constexpr int SMEM = MISC + 768 + 64 + 16 + 128 + 1024;
     // TMEM columns: the score products of two blocks (2 x 8 NS) | the output products
     static constexpr int S_COL = 0, O_COL = 16 * NS, TM_COLS = NVT <= 4 ? 256 : 512;
@@ -163,6 +163,13 @@ __global__ void __launch_bounds__(128) tcd_q_prep_kernel(const PassRow *__restri
     }
 }
 
+// order-preserving map between floats and signed integers (its own inverse): integer maxima of mapped values are float maxima
+__device__ __forceinline__ int f32_ord(float f) {
+    const int b = __float_as_int(f);
+    return b >= 0 ? b : b ^ 0x7fffffff;
+}
+__device__ __forceinline__ float ord_f32(int b) { return __int_as_float(b >= 0 ? b : b ^ 0x7fffffff); }
+
 // One CTA's teardown wait for a copy that may still be in flight once a wait has expired: polls for at most ~2 ms whatever
 // the status word says, so that the CTA does not leave while a copy still writes its shared memory.
 __device__ __forceinline__ void mbar_drain(uint64_t *bar, uint32_t parity) {
@@ -187,8 +194,9 @@ __device__ __forceinline__ void mbar_drain(uint64_t *bar, uint32_t parity) {
 // complete when its turn comes (two score buffers in TMEM).  Per item two CTA barriers:
 //   S2  block maxima of every warp; next item's K levels in place  -> weights (all), next item's score MMAs (one thread)
 //   S3  P^T planes in place                                        -> output MMAs (the same thread)
-// The single-thread duties are spread over the first lanes of warps 4 .. 7 (warps 0 .. 3 store the partial results): V copies,
-// items + K and Q copies, (m, l), MMAs.
+// The single-thread duties are spread over the first lanes of warps 4 .. 7 (warps 0 .. 3 store the partial results, and thread 0
+// asks for the next V levels there, where it has waited for the output products anyway): (m, l), items + K and Q copies, output
+// MMAs, score MMAs.  (An MMA of these shapes keeps its issuing thread for ~150 cycles: the two batches of eight go to two warps.)
 // maps: per segment [4 seg + 1] the tensor map of its sequence's V cache: {128 bytes of levels, 16 positions, tiles} with
 // strides {128, tile bytes}, box 128 x 16 x 8, 128-byte swizzle.
 template <int NVT>
@@ -227,7 +235,7 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
     const uint32_t sbase = smem_u32(sm);
     const int h2 = tid >> 7, t = tid & 127, pos = 128 * h2 + t;  // this thread's key of a block
     const float c2 = scale * 1.44269504088896341f;
-    constexpr int T_V = 128, T_ITEMS = 160, T_ML = 192, T_MMA = 224;  // the threads with a duty of their own
+    constexpr int T_V = 0, T_ML = 128, T_ITEMS = 160, T_PV = 192, T_MMA = 224;  // the threads with a duty of their own
     bool ok = true;
     pdl_wait();
 
@@ -282,7 +290,7 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
             bulk_g2s(sm + C::QS + qb * 256, src + 2048, 256, bar_q + qb);
         }
     };
-    // item i's V levels (thread T_V), once the output products of item i - 1 have released the buffer
+    // item i's V levels (thread T_V), once the output products of item i - 1 have released the buffer (store_o)
     auto fetch_v = [&](int i) {
         const TcdItem d = items[i & 3];
         const int nh = (d.n + 127) >> 7;
@@ -338,8 +346,11 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
     };
     // the partial result of item i: o[hd] (unnormalised; m and l are stored by its softmax).  Thread = dim of group c = dim / 32
     // (uniform over the warp): the columns (c, v, plane) of O.  Warps 0 .. 3.
-    auto store_o = [&](int i, float back, long long pidx) {
-        if (lane == 0) ok = mbar_wait_bounded(bar_o, (uint32_t)i & 1u, err, 75) && ok;
+    auto store_o = [&](int i, float back, long long pidx, bool next_v) {
+        if (lane == 0) {
+            ok = mbar_wait_bounded(bar_o, (uint32_t)i & 1u, err, 75) && ok;
+            if (tid == T_V && next_v) fetch_v(i + 1);  // (the output products of item i have released the V buffer)
+        }
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
         uint32_t r[2 * NVT < 8 ? 8 : 2 * NVT];
@@ -355,6 +366,7 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
     };
 
     // ---- prologue: items 0 and 1 described and asked for, item 0's K in place and its score MMAs issued
+    if (tid < 32) reinterpret_cast<int *>(red)[tid] = (tid & 15) < 8 ? INT_MIN : 0;  // the two buffers of block maxima
     if (tid == T_ITEMS) describe(0);
     __syncthreads();
     if (tid == T_V) fetch_v(0);
@@ -376,10 +388,6 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         const bool valid = pos < n, more = it + 1 < cnt;
         const long long pidx = ((long long)d.gb * n_heads + (long long)d.g * G) * RQ_PSTRIDE(HD);
         const float *qsc = reinterpret_cast<const float *>(sm + C::QS + qb * 256);  // [8][4]
-        if (tid == T_V && it > 0) {
-            ok = mbar_wait_bounded(bar_o, (uint32_t)(it - 1) & 1u, err, 75) && ok;
-            fetch_v(it);
-        }
         // ---- the scales of this thread's key
         float dk[4], dv[4];
 #pragma unroll
@@ -387,24 +395,28 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         dv[0] = __uint_as_float(vs_n.x << 16), dv[1] = __uint_as_float(vs_n.x & 0xffff0000u);
         dv[2] = __uint_as_float(vs_n.y << 16), dv[3] = __uint_as_float(vs_n.y & 0xffff0000u);
         // ---- softmax of the block: thread (half h2, key t) holds the scores of its key for the G vectors
-        // the block's largest V scale per group: what the weight planes are scaled by
+        // the block's largest V scale per group, what the weight planes are scaled by (the scales are positive: their bits order
+        // like unsigned integers): one warp reduction each, then one shared-memory atomic of lane 8 + c
+        int *rb = reinterpret_cast<int *>(red) + (it & 1) * 16;  // this block's maxima: [0..7] scores per vector (mapped), [8..11] V scales
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            float mx = dv[c];
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            if (lane == 0) red[128 + warp * 8 + c] = mx;
+            const unsigned mx = __reduce_max_sync(0xffffffffu, __float_as_uint(dv[c]));
+            if (lane == 8 + c) atomicMax(reinterpret_cast<unsigned *>(rb) + 8 + c, mx);
         }
-        if (lane == 0) {  // (one poller per warp)
-            ok = mbar_wait_bounded(bar_q + qb, (uint32_t)(d.q >> 1) & 1u, err, 74) && ok;  // (the query scales)
-            ok = mbar_wait_bounded(bar_s, (uint32_t)it & 1u, err, 71) && ok;               // (the score products)
-        }
+        // (the score products complete only after their thread has seen the query planes land: no wait of its own for those)
+        if (lane == 0) ok = mbar_wait_bounded(bar_s, (uint32_t)it & 1u, err, 71) && ok;  // (one poller per warp)
         __syncwarp();
         tc_fence_after();
         float s[NVT], e[NVT];
 #pragma unroll
         for (int v = 0; v < NVT; v++) s[v] = 0.0f;
         if (h2 < nh) {  // (uniform per warp)
+            float qd[NVT][4];  // the query scales of (vector, group)
+#pragma unroll
+            for (int v = 0; v < NVT; v++) {
+                const float4 x = *reinterpret_cast<const float4 *>(qsc + v * 4);
+                qd[v][0] = x.x, qd[v][1] = x.y, qd[v][2] = x.z, qd[v][3] = x.w;
+            }
 #pragma unroll
             for (int c = 0; c < 4; c++) {
                 uint32_t r[NS];
@@ -413,18 +425,16 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
                 tmem_wait_ld();
 #pragma unroll
                 for (int v = 0; v < NVT; v++)
-                    s[v] = fmaf(dk[c] * qsc[v * 4 + c], (float)(((int)r[2 * v] << 8) + (int)r[2 * v + 1]), s[v]);
+                    s[v] = fmaf(dk[c] * qd[v][c], (float)(((int)r[2 * v] << 8) + (int)r[2 * v + 1]), s[v]);
             }
         }
 #pragma unroll
         for (int v = 0; v < NVT; v++) {
-            float mx = valid ? s[v] : -INFINITY;
-            s[v] = mx;
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            if (lane == 0) red[warp * 8 + v] = mx;
+            s[v] = valid ? s[v] : -INFINITY;
+            const int mx = __reduce_max_sync(0xffffffffu, f32_ord(s[v]));
+            if (lane == v) atomicMax(rb + v, mx);
         }
-        if (it > 0 && warp < 4) store_o(it - 1, back_prev, pidx_prev);
+        if (it > 0 && warp < 4) store_o(it - 1, back_prev, pidx_prev, true);
         // ---- the next item's K levels and this thread's scales of it (the score products of this item are complete: the K levels
         // it used may go)
         if (more) stage_k(it + 1);
@@ -438,21 +448,25 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         }
         if (tid == T_MMA && more) issue_s(it + 1);
         if (tid == T_ITEMS && it + 2 < cnt) describe(it + 2);
-        float m[NVT], ps_inv[4];
+        if (tid == T_ML) {  // the other buffer of maxima, for the next block
+            int4 *nb = reinterpret_cast<int4 *>(reinterpret_cast<int *>(red) + ((it + 1) & 1) * 16);
+            nb[0] = nb[1] = make_int4(INT_MIN, INT_MIN, INT_MIN, INT_MIN);
+            nb[2] = make_int4(0, 0, 0, 0);
+        }
+        float m[NVT], dvp[4];
         float ps_mine = 0.0f;
+        {
+            const float4 x = *reinterpret_cast<const float4 *>(rb + 8);
+            const float psc[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            float mx = red[128 + c];
-#pragma unroll
-            for (int wv = 1; wv < 8; wv++) mx = fmaxf(mx, red[128 + wv * 8 + c]);
-            if (c == (warp & 3)) ps_mine = mx;
-            ps_inv[c] = mx > 0.0f ? 65535.0f / mx : 0.0f;
+            for (int c = 0; c < 4; c++) {
+                if (c == (warp & 3)) ps_mine = psc[c];
+                dvp[c] = psc[c] > 0.0f ? dv[c] * __fdividef(65535.0f, psc[c]) : 0.0f;  // the key's V scale in units of the block's largest
+            }
         }
 #pragma unroll
         for (int v = 0; v < NVT; v++) {
-            float mx = red[v];
-#pragma unroll
-            for (int wv = 1; wv < 8; wv++) mx = fmaxf(mx, red[wv * 8 + v]);
+            const float mx = ord_f32(rb[v]);
             m[v] = mx;
             e[v] = valid ? ex2((s[v] - mx) * c2) : 0.0f;
             float sum = e[v];
@@ -469,7 +483,7 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
             for (int c = 0; c < 4; c++)
 #pragma unroll
                 for (int v = 0; v < NVT; v++) {
-                    const uint32_t u16 = (uint32_t)__float2int_rn(fminf(e[v] * dv[c] * ps_inv[c], 65535.0f));
+                    const uint32_t u16 = (uint32_t)__float2int_rn(fminf(e[v] * dvp[c], 65535.0f));
                     const int rw = (c * NVT + v) * 2;
                     pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)(u16 >> 8);
                     pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)(u16 & 255u);
@@ -478,7 +492,7 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();  // S3
-        if (tid == T_MMA) {
+        if (tid == T_PV) {
             // ---- O^T += V^T (half h) P^T (half h): 4 k-steps of 32 keys per half
             tc_fence_after();
             ok = mbar_wait_bounded(bar_v, (uint32_t)it & 1u, err, 73) && ok;  // (the item's V levels have landed)
@@ -511,7 +525,7 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         pidx_prev = pidx;
     }
     pdl_launch_dependents();
-    if (!failed && warp < 4) store_o(cnt - 1, back_prev, pidx_prev);  // the last item's partial result
+    if (!failed && warp < 4) store_o(cnt - 1, back_prev, pidx_prev, false);  // the last item's partial result
     if (failed && tid == T_MMA) {
         // a wait ran out: give what may still be in flight (the V levels of this item, the K tiles of the next, query planes,
         // the MMAs issued last) a bounded time to finish before the CTA's shared memory and TMEM are released
