@@ -41,7 +41,7 @@ struct TcdCfg {
     // halves as the operand wants them (2 x 16 KB: 128 rows = dims of 128 keys) | V levels (2 x 16 KB: 128 rows = positions of 128
     // dims, swizzled by the TMA) | P^T (2 x NO rows of 128 bytes) | Q^T planes, two buffers of 2 KB, and their scales, 2 x 256 B | the rest
     static constexpr int KRAW = 0, KLEV = 16 * KTB, VLEV = KLEV + 32768, PT = VLEV + 32768, QT = PT + 2 * NO * 128, QS = QT + 4096;
-    static constexpr int MISC = QS + 512;  // red (768 B: two buffers of block maxima, 64 B each; at 256 B the warps' sums [8][8])  | bars [6] (64 B) | TMEM slot (16 B) | items [4] (128 B)
+    static constexpr int MISC = QS + 512;  // red (768 B: two buffers of block reductions, 128 B each)  | bars [6] (64 B) | TMEM slot (16 B) | items [4] (128 B)
     static constexpr int SMEM = MISC + 768 + 64 + 16 + 128 + 1024;
     // TMEM columns: the score products of two blocks (2 x 8 NS) | the output products
     static constexpr int S_COL = 0, O_COL = 16 * NS, TM_COLS = NVT <= 4 ? 256 : 512;
@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
     };
 
     // ---- prologue: items 0 and 1 described and asked for, item 0's K in place and its score MMAs issued
-    if (tid < 32) reinterpret_cast<int *>(red)[tid] = (tid & 15) < 8 ? INT_MIN : 0;  // the two buffers of block maxima
+    if (tid < 64) reinterpret_cast<int *>(red)[tid] = (tid & 31) < 8 ? INT_MIN : 0;  // the two buffers of block reductions
     if (tid == T_ITEMS) describe(0);
     __syncthreads();
     if (tid == T_V) fetch_v(0);
@@ -397,7 +397,8 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         // ---- softmax of the block: thread (half h2, key t) holds the scores of its key for the G vectors
         // the block's largest V scale per group, what the weight planes are scaled by (the scales are positive: their bits order
         // like unsigned integers): one warp reduction each, then one shared-memory atomic of lane 8 + c
-        int *rb = reinterpret_cast<int *>(red) + (it & 1) * 16;  // this block's maxima: [0..7] scores per vector (mapped), [8..11] V scales
+        // this block's reductions: [0..7] largest score per vector (mapped), [8..11] largest V scales, [16..23] sums of weights (fixed point)
+        int *rb = reinterpret_cast<int *>(red) + (it & 1) * 32;
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             const unsigned mx = __reduce_max_sync(0xffffffffu, __float_as_uint(dv[c]));
@@ -448,31 +449,28 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         }
         if (tid == T_MMA && more) issue_s(it + 1);
         if (tid == T_ITEMS && it + 2 < cnt) describe(it + 2);
-        if (tid == T_ML) {  // the other buffer of maxima, for the next block
-            int4 *nb = reinterpret_cast<int4 *>(reinterpret_cast<int *>(red) + ((it + 1) & 1) * 16);
+        if (tid == T_ML) {  // the other buffer of reductions, for the next block
+            int4 *nb = reinterpret_cast<int4 *>(reinterpret_cast<int *>(red) + ((it + 1) & 1) * 32);
             nb[0] = nb[1] = make_int4(INT_MIN, INT_MIN, INT_MIN, INT_MIN);
-            nb[2] = make_int4(0, 0, 0, 0);
+            nb[2] = nb[4] = nb[5] = make_int4(0, 0, 0, 0);
         }
         float m[NVT], dvp[4];
-        float ps_mine = 0.0f;
-        {
-            const float4 x = *reinterpret_cast<const float4 *>(rb + 8);
-            const float psc[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                if (c == (warp & 3)) ps_mine = psc[c];
-                dvp[c] = psc[c] > 0.0f ? dv[c] * __fdividef(65535.0f, psc[c]) : 0.0f;  // the key's V scale in units of the block's largest
-            }
-        }
+        const float4 psc = *reinterpret_cast<const float4 *>(rb + 8);
+        const float ps_mine = (warp & 2) ? ((warp & 1) ? psc.w : psc.z) : ((warp & 1) ? psc.y : psc.x);
+        // the key's V scales in units of the block's largest
+        dvp[0] = psc.x > 0.0f ? dv[0] * __fdividef(65535.0f, psc.x) : 0.0f;
+        dvp[1] = psc.y > 0.0f ? dv[1] * __fdividef(65535.0f, psc.y) : 0.0f;
+        dvp[2] = psc.z > 0.0f ? dv[2] * __fdividef(65535.0f, psc.z) : 0.0f;
+        dvp[3] = psc.w > 0.0f ? dv[3] * __fdividef(65535.0f, psc.w) : 0.0f;
 #pragma unroll
         for (int v = 0; v < NVT; v++) {
             const float mx = ord_f32(rb[v]);
             m[v] = mx;
             e[v] = valid ? ex2((s[v] - mx) * c2) : 0.0f;
-            float sum = e[v];
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (lane == 0) red[64 + warp * 8 + v] = sum;
+            // l: the weights summed in 23-bit fixed point (integer sums: exact whatever their order, so that a block gives the same
+            // bits every time; the block's largest weight is 1, 256 of them stay below 2^32; error below 2^-16 relative)
+            const unsigned sum = __reduce_add_sync(0xffffffffu, (unsigned)__float2int_rn(e[v] * 8388608.0f));
+            if (lane == v) atomicAdd(reinterpret_cast<unsigned *>(rb) + 16 + v, sum);
         }
         // P^T: the B operand of O^T += V^T P^T, per half [NO rows][128 keys] uint8, K-major with the 128-byte swizzle: rows
         // ((c NVT + v) 2 + plane) hold the two planes of round(p[.][v] d_V[.][c] 65535 / ps[c])
@@ -513,12 +511,9 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
 #pragma unroll
             for (int v = 0; v < NVT; v++)
                 if (v < G) {
-                    float sum = red[64 + v];
-#pragma unroll
-                    for (int wv = 1; wv < 8; wv++) sum += red[64 + wv * 8 + v];
                     float *p = part + pidx + (long long)v * RQ_PSTRIDE(HD);
                     p[HD] = m[v] * scale;
-                    p[HD + 1] = sum;
+                    p[HD + 1] = (float)reinterpret_cast<const unsigned *>(rb)[16 + v] * (1.0f / 8388608.0f);
                 }
         }
         back_prev = ps_mine * (1.0f / 65535.0f);
