@@ -161,15 +161,18 @@ def cpu_leg(ctx_all, reps, sample_every):
 PF_LAYERS, PF_HEADS, PF_KV, PF_ROWS, PF_PREFIX = 28, 16, 8, 512, 3584
 
 
-def prefill_leg(device, steps, layers=None, warm=3):
-    """Qwen3-0.6B-shaped chunked prefill attention (512 new rows over a 3584-position f16 prefix, 28 layers, one
-    sequence): TFLOP/s of the tensor-core prefill path, flops = 4 x head_dim per causal (query, key) pair per query head."""
+def prefill_leg(device, steps, layers=None, warm=3, kv="f16", exact=False):
+    """Qwen3-0.6B-shaped chunked prefill attention (512 new rows over a 3584-position prefix, 28 layers, one
+    sequence): TFLOP/s of the tensor-core prefill path, flops = 4 x head_dim per causal (query, key) pair per query head.
+    kv: the cache type (quantised caches are expanded to f16 tiles once per layer call, inside the timed step; `roofline`
+    times the tensor-core kernel alone); exact: quantised caches row by row through the bit-exact decode kernels instead."""
     import gwenedeg_b200 as g
     from gwenedeg_b200 import synth
     PF_LAYERS = layers or globals()["PF_LAYERS"]
     c = g.Context(device, n_attn=PF_LAYERS, n_heads=PF_HEADS, n_kv_heads=PF_KV, head_dim=HD, max_rows=PF_ROWS)
-    s = c.new_seq(PF_PREFIX + PF_ROWS, g.KV_F16)
+    s = c.new_seq(PF_PREFIX + PF_ROWS, {"f16": g.KV_F16, "q8": g.KV_Q8, "q4": g.KV_Q4, "q4k4": g.KV_Q4K4}[kv])
     s.fill_synthetic(PF_PREFIX + PF_ROWS, 77)
+    c.set_exact(bool(exact))
     qn = PF_ROWS * PF_HEADS * HD
     q_host = c.pinned((PF_LAYERS, PF_ROWS, PF_HEADS, HD))
     q_host[:] = synth.normal(5, (PF_LAYERS, PF_ROWS, PF_HEADS, HD))
@@ -205,6 +208,12 @@ def prefill_leg(device, steps, layers=None, warm=3):
         peak, how = 1590.0, "fallback"
     tf_step = flops_layer * PF_LAYERS * steps / (ms * 1e-3) / 1e12
     tf_kern = flops_layer * kern_n / (kern_ms * 1e-3) / 1e12
+    if kv != "f16":
+        return {"workload": f"qwen3-0.6b-prefill-512-over-3584-{kv}", "tflops": tf_step, "ms_per_chunk_all_layers": ms / steps,
+                "kernels": "row by row through the bit-exact decode kernels" if exact else "f16 expansion + tensor-core prefill",
+                "roofline": {"bound": "tensor", "achieved": tf_kern, "peak": peak, "unit": "TFLOP/s", "frac": tf_kern / peak, "traffic": None,
+                             "peak_source": how, "kernel": "attn_part_kernel" if exact else "attn_prefill_kernel",
+                             "flops_per_launch": flops_layer, "launches_timed": kern_n}}
     return {"workload": "qwen3-0.6b-prefill-512-over-3584", "tflops": tf_step, "ms_per_chunk_all_layers": ms / steps,
             "roofline": {"bound": "tensor", "achieved": tf_kern, "peak": peak, "unit": "TFLOP/s", "frac": tf_kern / peak, "traffic": None,
                          "peak_source": how, "kernel": "attn_prefill_kernel", "flops_per_launch": flops_layer, "launches_timed": kern_n}}
@@ -636,7 +645,7 @@ def run_ours(args, rank, local_rank, world):
     achieved = reduce_sum(achieved) / world  # mean over ranks of the per-GPU figure
 
     c.close()
-    prefill = prefill_hd256 = deltanet = decode_q8 = decode_q8_sharded = None
+    prefill = prefill_q8 = prefill_hd256 = deltanet = decode_q8 = decode_q8_sharded = None
     if not args.small:
         # the quantised-cache configuration (32 sequences at context 40,960, q8): on one GPU the whole batch; on N GPUs split by
         # KV-head group over the same process group, outputs all-gathered
@@ -653,6 +662,10 @@ def run_ours(args, rank, local_rank, world):
             prefill = prefill_leg(local_rank, max(2, min(args.steps, 5)))
         except Exception as e:
             prefill = {"error": repr(e)}
+        try:
+            prefill_q8 = prefill_leg(local_rank, 2, kv="q8")
+        except Exception as e:
+            prefill_q8 = {"error": repr(e)}
         try:
             prefill_hd256 = prefill_hd256_leg(local_rank, 2)
         except Exception as e:
@@ -689,6 +702,7 @@ def run_ours(args, rank, local_rank, world):
             "decode_q8": decode_q8,
             "decode_q8_head_sharded": decode_q8_sharded,
             "prefill": prefill,
+            "prefill_q8": prefill_q8,
             "prefill_hd256": prefill_hd256,
             "deltanet": deltanet,
         }
@@ -706,7 +720,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--exact", action="store_true", help="quantised-cache workloads: the bit-exact CUDA-core kernels instead of the "
                     "int8 tensor-core ones")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill-hd256", "decode-q8", "decode-q4", "decode-q4k4", "deltanet"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill-q8", "prefill-q4", "prefill-q4k4", "prefill-hd256", "decode-q8", "decode-q4", "decode-q4k4", "deltanet"],
                     help="decode: the headline batched-decode benchmark (default); prefill: only the chunked-prefill leg "
                          "(512 rows over a 3584-position prefix), printed as its own line")
     ap.add_argument("--shard-of", type=int, default=1,
@@ -744,13 +758,14 @@ def main():
                               "data": "synthetic", "config": {"workload": r["workload"], "layers": r["layers"], "tokens": r["tokens"]},
                               "ms_per_step": r["ms_per_prompt_all_layers"], "tokens_per_s": r["tokens_per_s"], "roofline": r["roofline"]}), flush=True)
         return
-    if args.workload == "prefill":
+    if args.workload.startswith("prefill"):
         if rank == 0:
-            r = prefill_leg(local_rank, args.steps, layers=2 if args.small else None, warm=args.warmup)
-            print(json.dumps({"metric": "Qwen3-0.6B attn: prefill TFLOP/s (512 rows over 3584)", "value": r["tflops"], "unit": "TFLOP/s",
+            kv = args.workload[8:] or "f16"
+            r = prefill_leg(local_rank, args.steps, layers=2 if args.small else None, warm=args.warmup, kv=kv, exact=args.exact)
+            print(json.dumps({"metric": f"Qwen3-0.6B attn: prefill TFLOP/s (512 rows over 3584, {kv} cache)", "value": r["tflops"], "unit": "TFLOP/s",
                               "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "dtype": "f16",
                               "data": "synthetic", "config": {"workload": r["workload"], "layers": 2 if args.small else PF_LAYERS},
-                              "roofline": r["roofline"]}), flush=True)
+                              "ms_per_step": r["ms_per_chunk_all_layers"], "kernels": r.get("kernels"), "roofline": r["roofline"]}), flush=True)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         # started without torchrun: re-launch one rank per GPU

@@ -666,12 +666,26 @@ __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const Pass
 // partial per split of PF_SPLIT = 2,048 positions): one warp per (row, query head), lane L holds dims 4L .. 4L + 3 of every
 // 128-dim part of the row, so a launch is a few hundred CTAs instead of one per output row.  Arithmetic as
 // attn_combine_kernel: M = max of the m_b, c_b = exp_att(m_b - M), L and out as fma chains in partial order, out * (1 / L), gate.
+// With `unrot` (quantised caches, head_dim 128) the merged row is un-rotated before the gate as attn_combine_kernel does it.
 constexpr int COMBINE_ROWS_WARPS = 8;
+// the 128-point butterflies (h = 1, 2, 4, ..., 64) of att_q_rot / att_o_unrot over a warp: lane L holds dims 4L .. 4L + 3
+__device__ __forceinline__ void fwht128_warp(float4 &x, int lane) {
+    {  // h = 1, 2: inside the lane
+        const float a = x.x + x.y, b = x.x - x.y, c = x.z + x.w, d = x.z - x.w;
+        x = make_float4(a + c, b + d, a - c, b - d);
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {  // h = 4 o: lanes L and L ^ o
+        const float4 y = make_float4(__shfl_xor_sync(0xffffffffu, x.x, o), __shfl_xor_sync(0xffffffffu, x.y, o), __shfl_xor_sync(0xffffffffu, x.z, o),
+                                     __shfl_xor_sync(0xffffffffu, x.w, o));
+        x = (lane & o) ? make_float4(y.x - x.x, y.y - x.y, y.z - x.z, y.w - x.w) : make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+    }
+}
 template <int HD>
 __global__ void __launch_bounds__(32 * COMBINE_ROWS_WARPS) attn_combine_rows_kernel(const PassRow *__restrict__ rows, int nrows, int n_heads,
                                                                                  const float *__restrict__ part, const float *__restrict__ q,
                                                                                  int qh, int gated, float *__restrict__ out, int split_len,
-                                                                                 int fixed_stride, const int *err_src, int *err_dst, WoQuant wq) {
+                                                                                 int fixed_stride, const int *err_src, int *err_dst, WoQuant wq, int unrot) {
     static_assert(HD % 128 == 0, "a lane holds 4 dims of every 128 of the row");
     constexpr int NP = HD / 128;
     const int wi = blockIdx.x * COMBINE_ROWS_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -712,6 +726,14 @@ __global__ void __launch_bounds__(32 * COMBINE_ROWS_WARPS) attn_combine_rows_ker
         const float inv = 1.0f / L;
 #pragma unroll
         for (int c = 0; c < NP; c++) res[c] = make_float4(acc[c].x * inv, acc[c].y * inv, acc[c].z * inv, acc[c].w * inv);
+    }
+    if constexpr (HD == 128) {
+        if (unrot) {  // att_o_unrot: butterflies, signs, scaling by 1 / head_dim
+            fwht128_warp(res[0], lane);
+            const float f = 1.0f / (float)HD;
+            res[0].x = (kvq_neg(4 * lane) ? -res[0].x : res[0].x) * f, res[0].y = (kvq_neg(4 * lane + 1) ? -res[0].y : res[0].y) * f;
+            res[0].z = (kvq_neg(4 * lane + 2) ? -res[0].z : res[0].z) * f, res[0].w = (kvq_neg(4 * lane + 3) ? -res[0].w : res[0].w) * f;
+        }
     }
 #pragma unroll
     for (int c = 0; c < NP; c++) {

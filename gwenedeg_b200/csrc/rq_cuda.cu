@@ -23,6 +23,7 @@
 #include "attn_prefill256.cuh"
 #include "deltanet.cuh"
 #include "deltanet_chunk.cuh"
+#include "kv_dequant.cuh"
 #include "kv_store.cuh"
 
 using namespace rq;
@@ -111,6 +112,13 @@ struct RqCuda {
     PfWork *d_work; size_t work_bytes;
     std::vector<PfWork> h_work;
     int pf_ready, pf_max_splits;
+    // ... over quantised caches: the layer's tiles expanded to f16 in a scratch (pf_quant: the open pass takes that route)
+    bool pf_quant = false;
+    uint8_t *d_dq = nullptr; size_t dq_bytes = 0;   // the f16 tiles, K then V per segment
+    float *d_qrot = nullptr; size_t qrot_bytes = 0;  // the rotated query rows
+    DqSeg *d_dqseg = nullptr; size_t dqseg_bytes = 0;
+    std::vector<DqSeg> h_dqseg;
+    int dq_max_tiles = 0;
     int tc_ready;  // the open pass's tensor maps for the tensor-core decode kernel are on the device (1), or it does not qualify (-1)
     // DeltaNet weights of the steps around the recurrence (rq_cuda_dn_set_weights): per linear layer conv taps, A, dt
     // bias, norm weight
@@ -329,7 +337,7 @@ void rq_cuda_free(RqCuda *c) {
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->d_dnw) cudaFree(c->d_dnw);
     if (c->h_maps8) cudaFreeHost(c->h_maps8);
-    void *dev[] = {c->d_maps8, c->d_tcq, c->d_blk2row, c->d_chunks, c->d_ck, c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
+    void *dev[] = {c->d_dq, c->d_qrot, c->d_dqseg, c->d_maps8, c->d_tcq, c->d_blk2row, c->d_chunks, c->d_ck, c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
     if (c->h_maps) cudaFreeHost(c->h_maps);
     for (void *p : dev)
         if (p) cudaFree(p);
@@ -1038,16 +1046,60 @@ static int prefill_tables(RqCuda *c) {
     // tensor-core prefill kernel; pf_ready 1: made, -1: the pass does not qualify (cache type, head_dim)
     if (c->pf_ready) return RQ_CUDA_OK;
     c->pf_ready = -1;
-    if ((c->m.head_dim != 128 && c->m.head_dim != 256) || c->pass_kvt != KV_F16) return RQ_CUDA_OK;
-    for (auto &g : c->segs)
-        if (!g.seq->has_tm) return RQ_CUDA_OK;
-    const int rpt = 128 / c->G, nseg = (int)c->segs.size();
+    const int nseg = (int)c->segs.size();
+    c->pf_quant = false;
+    if (kv_quant(c->pass_kvt)) {
+        // quantised caches at head_dim 128: the tensor-core kernel over f16 copies of the layer's tiles, where the pass is a prompt
+        // pass (on average 16 rows or more per segment: below that the copies cost more than they save) and the copies fit 8 GB;
+        // not where the host asked for exact results
+        if (c->m.head_dim != 128 || c->exact || c->nrows < 16 * nseg || !tm_encode()) return RQ_CUDA_OK;
+        size_t tiles = 0;
+        for (auto &g : c->segs) tiles += (size_t)((g.pos0 + g.n + ATT_P - 1) / ATT_P) * ATT_PT * c->n_kv;
+        if (tiles * 8192 > ((size_t)8 << 30)) return RQ_CUDA_OK;
+        int rcq = grow(c, (void **)&c->d_dq, &c->dq_bytes, tiles * 8192);
+        if (rcq) return rcq;
+        if ((rcq = grow(c, (void **)&c->d_dqseg, &c->dqseg_bytes, sizeof(DqSeg) * nseg))) return rcq;
+        if ((rcq = grow(c, (void **)&c->d_qrot, &c->qrot_bytes, (size_t)c->nrows * c->n_heads * 128 * 4))) return rcq;
+        c->h_dqseg.resize(nseg);
+        c->dq_max_tiles = 0;
+        uint8_t *at = c->d_dq;
+        TmEncodeFn enc = tm_encode();
+        cuuint32_t es[2] = {1, 1};
+        for (int i = 0; i < nseg; i++) {
+            const RqCudaSegment &g = c->segs[i];
+            DqSeg &d = c->h_dqseg[i];
+            d.k = g.seq->k, d.v = g.seq->v, d.lk = g.seq->lk, d.lv = g.seq->lv;
+            d.len = g.pos0 + g.n;
+            d.tiles = (d.len + ATT_P - 1) / ATT_P * ATT_PT;
+            const size_t bytes = (size_t)d.tiles * c->n_kv * 4096;  // (tiles of 16 positions x 128 dims x 2 bytes)
+            d.ko = at, d.vo = at + bytes;
+            at += 2 * bytes;
+            c->dq_max_tiles = std::max(c->dq_max_tiles, d.tiles);
+            // the same views as an f16 cache of one layer (seq_make_maps)
+            cuuint64_t kd[2] = {16, (cuuint64_t)(bytes / 32)}, ks[1] = {32}, vd[2] = {128, (cuuint64_t)(bytes / 256)}, vs[1] = {256};
+            cuuint32_t kb[2] = {16, 256}, vb[2] = {64, 128};
+            if (enc(&c->h_maps[2 * i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d.ko, kd, ks, kb, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+                enc(&c->h_maps[2 * i + 1], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d.vo, vd, vs, vb, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return RQ_CUDA_OK;  // (the pass takes the row-by-row path)
+        }
+        CU(c, cudaMemcpyAsync(c->d_dqseg, c->h_dqseg.data(), sizeof(DqSeg) * nseg, cudaMemcpyHostToDevice, c->stream));
+        c->pf_quant = true;
+    } else {
+        if ((c->m.head_dim != 128 && c->m.head_dim != 256) || c->pass_kvt != KV_F16) return RQ_CUDA_OK;
+        for (auto &g : c->segs)
+            if (!g.seq->has_tm) return RQ_CUDA_OK;
+    }
+    const int rpt = 128 / c->G;
     c->h_work.clear();
     int row = 0;
     for (int i = 0; i < nseg; i++) {
         const RqCudaSegment &g = c->segs[i];
-        c->h_maps[2 * i] = g.seq->tm_k;
-        c->h_maps[2 * i + 1] = g.seq->tm_v;
+        if (!c->pf_quant) {
+            c->h_maps[2 * i] = g.seq->tm_k;
+            c->h_maps[2 * i + 1] = g.seq->tm_v;
+        }
         for (int m0 = 0; m0 < g.n; m0 += rpt) {
             int nr = std::min(rpt, g.n - m0), np_max = g.pos0 + m0 + nr;
             for (int k = 0; k * PF_SPLIT < np_max; k++) c->h_work.push_back(PfWork{i, row + m0, nr, k});
@@ -1094,6 +1146,23 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     a.max_splits = c->pf_max_splits;
     a.part = c->d_part;
     a.err = c->d_err;
+    if (c->pf_quant) {
+        // the layer's tiles as f16 (layer 0 of the scratch's views), the query rows rotated; the merge below un-rotates
+        const dim3 dgrid(c->dq_max_tiles, c->n_kv, (unsigned)c->segs.size());
+        cudaError_t de;
+        switch (c->pass_kvt) {
+            case KV_Q8: de = launch_pdl(kv_dequant_f16_kernel<KV_Q8>, dgrid, dim3(128), 0, c->stream, (const DqSeg *)c->d_dqseg, layer, c->n_kv); break;
+            case KV_Q4: de = launch_pdl(kv_dequant_f16_kernel<KV_Q4>, dgrid, dim3(128), 0, c->stream, (const DqSeg *)c->d_dqseg, layer, c->n_kv); break;
+            default: de = launch_pdl(kv_dequant_f16_kernel<KV_Q4K4>, dgrid, dim3(128), 0, c->stream, (const DqSeg *)c->d_dqseg, layer, c->n_kv); break;
+        }
+        if (de != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "cache expansion launch: %s", cudaGetErrorString(de));
+        const int nrh = c->nrows * c->n_heads;
+        CU(c, launch_pdl(q_rot_kernel, dim3((nrh + 7) / 8), dim3(256), 0, c->stream, q, c->qh, nrh, c->d_qrot));
+        c->launches += 2;
+        a.layer = 0;
+        a.q = c->d_qrot;
+        a.qh = 128;
+    }
     const bool prof = c->prof_on && (size_t)(2 * c->prof_n + 2) <= c->prof_ev.size();
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n], c->stream);
     cudaError_t e = hd == 128 ? launch_attn_prefill(a, c->stream) : launch_attn_prefill_hd256(a, c->stream);
@@ -1105,10 +1174,10 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     const dim3 cgrid((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), cblock(32 * COMBINE_ROWS_WARPS);
     if (hd == 128)
         CU(c, launch_pdl(attn_combine_rows_kernel<128>, cgrid, cblock, 0, c->stream, c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh,
-                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd, c->wo_quant));
+                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd, c->wo_quant, c->pf_quant ? 1 : 0));
     else
         CU(c, launch_pdl(attn_combine_rows_kernel<256>, cgrid, cblock, 0, c->stream, c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh,
-                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd, c->wo_quant));
+                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd, c->wo_quant, 0));
     c->launches++;
     return RQ_CUDA_OK;
 }

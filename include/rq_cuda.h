@@ -100,13 +100,18 @@ int rq_cuda_selftest_wait_expiry(RqCuda *ctx, unsigned int limit_us);
  * 0.49999997, .))): the bits quantize() gives on the same fp32 rows.  Both NULL: off.  Device pointers the host owns, sized
  * for the largest pass. */
 int rq_cuda_set_wo_quant(RqCuda *ctx, int gs, signed char *xq_dev, float *xs_dev);
-/* Which kernels attend over 8-bit (q8) caches at head_dim 128.  0 (the default): the integer tensor-core form: the cached int8
- * levels go into tcgen05.mma (kind::i8) as they are, with exact int32 accumulation; the query and the softmax weights are
- * 16-bit fixed point split into two int8 planes, the bf16 scales are applied in fp32.  Outputs agree with the reference's fp32
- * arithmetic to ~1e-4 relative (inside its acceptance bar of 2e-3 absolute / 1e-3 relative), not bit for bit.  Non-zero: the
- * CUDA-core kernels that follow attention_part_q (forward.c:1770-1804) operation for operation and give the reference's bits,
- * at ~0.85 of the speed.  f16, q4 and q4k4 caches and other head dims always take the bit-exact kernels, and so does
- * rq_cuda_attn_decode_noalloc.  Either way a row's result is independent of the other rows of the pass. */
+/* Which kernels attend over quantised caches at head_dim 128.  0 (the default): tensor cores within the reference's acceptance
+ * bar (2e-3 absolute / 1e-3 relative), not bit for bit:
+ *  - rq_cuda_attn_decode over q8 caches: the cached int8 levels go into tcgen05.mma (kind::i8) as they are, with exact int32
+ *    accumulation; the query and the softmax weights are 16-bit fixed point split into two int8 planes, the bf16 scales are
+ *    applied in fp32 (~1e-4 relative to the reference's fp32 arithmetic);
+ *  - rq_cuda_attn_prefill over q8 / q4 / q4k4 caches in prompt passes (on average 16 rows or more per segment): the layer's
+ *    tiles are expanded once per call to f16 (the reference's dequantised values, block_f32 of forward.c:1770-1804, rounded once)
+ *    and the f16 tensor-core kernel runs over them with rotated query rows (~3e-4 relative).
+ * Non-zero: the CUDA-core kernels that follow attention_part_q (forward.c:1770-1804) operation for operation and give the
+ * reference's bits (q8 decode at ~0.55 of the speed, prompt passes row by row).  f16 caches, q4 / q4k4 decode, other head dims
+ * and rq_cuda_attn_decode_noalloc always take the bit-exact kernels.  Either way a row's result is independent of the other
+ * rows of the pass. */
 int rq_cuda_set_exact(RqCuda *ctx, int exact);
 /* run this context's work on a caller-owned stream (a cudaStream_t; NULL: back to the context's own, a non-blocking stream:
  * it is not ordered with the legacy default stream, whose handle is NULL as well).  The attention and DeltaNet kernels are

@@ -144,3 +144,53 @@ def test_config2_shape_one_layer(checker):
     # every one of the 512 rows x 16 heads against the bit-exact path
     assert_close(got, exact, "config-2, all rows")
     c.close()
+
+
+@pytest.mark.parametrize("kvt,name", [(3, "q8"), (8, "q4"), (9, "q4k4")])
+@pytest.mark.parametrize("n_heads,n_kv,gated", [(8, 2, False), (4, 4, True)])
+def test_quantised_cache_prompt_chunks_on_tensor_cores(checker, kvt, name, n_heads, n_kv, gated):
+    """Prompt passes over q8 / q4 / q4k4 caches at head_dim 128: the layer's tiles expanded to f16 once per call, the query rows
+    rotated, the tensor-core kernel, the un-rotating merge.  Every row against the row-by-row path through the decode kernels
+    (rq_cuda_set_exact: the CPU code's bits), a few rows against the CPU code itself; a chunk from position 0, a chunk over a
+    prefix that crosses the 2,048-position split edge and ends inside a block, and a third segment."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    hd = 128
+    c = g.Context(0, n_attn=2, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, gated=gated, max_rows=512)
+    seqs = []
+    for i, n in enumerate((150, 2300, 700)):
+        s = c.new_seq(n, kvt)
+        k, v = synth.normal(40 + 2 * i, (n, n_kv, hd)), synth.normal(41 + 2 * i, (n, n_kv, hd))
+        for lo in range(0, n, 512):
+            hi = min(n, lo + 512)
+            c.pass_begin([(s, lo, hi - lo)])
+            for l in range(2):
+                c.kv_store(l, k[lo:hi] * np.float32(1 + l), v[lo:hi])
+            c.pass_end()
+        seqs.append(s)
+    a, b, d = seqs
+    segs = [(a, 0, 150), (b, 1990, 210), (d, 680, 20)]
+    rows = sum(n for _, _, n in segs)
+    q = synth.normal(19, (rows, n_heads, hd * (2 if gated else 1)))
+    for layer in (1, 0):
+        c.set_exact(False)
+        c.pass_begin(segs)
+        got = c.attn_prefill(layer, q)
+        c.pass_end(commit=False)
+        c.set_exact(True)
+        c.pass_begin(segs)
+        exact = c.attn_prefill(layer, q)
+        c.pass_end(commit=False)
+        assert not bit_equal(got, exact)  # (the two paths are different kernels)
+        assert_close(got, exact, f"{name} layer {layer}: tensor-core prompt pass against the row-by-row path")
+        r = 0
+        for s, pos0, n in segs:
+            pick = sorted(set(i for i in (0, 1, n // 2, n - 1) if i < n))
+            want = checker.attention(kvt, s.read_kv(layer, 0), s.read_kv(layer, 1), n_kv, n_heads, hd, q[r:r + n][pick],
+                                     np.array([pos0 + 1 + i for i in pick], np.int32), gated=gated)
+            assert_close(got[r:r + n][pick], want, f"{name} segment at {pos0}")
+            assert bit_equal(exact[r:r + n][pick], want)
+            r += n
+        print(name, "quantised prompt pass errors", errors(got, exact))
+    c.set_exact(False)
+    c.close()
