@@ -1,24 +1,27 @@
-// Split-K decode attention over q8 KV caches on the integer tensor cores (tcgen05.mma kind::i8 + TMEM), head_dim 128: the
-// fast form of attn_part_kernel for 8-bit caches.
+// Split-K decode attention over quantised KV caches (q8, q4, q4k4) on the integer tensor cores (tcgen05.mma kind::i8 + TMEM),
+// head_dim 128: the fast form of attn_part_kernel for these caches.
 //
 // Same work items and the same partial results as attn_part_kernel (one (o, m, l) record per (row, KV head, block of 256
 // positions), merged in block order by attn_combine_kernel, which also un-rotates and gates), so the split still
 // depends on a row's own length only and a row of a batch gives the bits it gives alone.  What changes is the arithmetic
 // inside a block.  The CUDA-core kernel spends ~8 instructions per cached level (conversion, scale, four multiply-adds).
-// Here the cached int8 levels are never converted at all: the tiles go from HBM to shared memory by TMA and from there
-// straight into tcgen05.mma as 8-bit operands, accumulated exactly in int32:
-//   V rows [position][128 dims] as cached, fetched through a 3-D tensor map with the 128-byte swizzle = an MN-major A operand:
+// Here the cached levels are never converted to floats at all: they go from HBM to shared memory by the copy engines and from
+// there into tcgen05.mma as 8-bit operands, accumulated exactly in int32:
+//   8-bit V rows [position][128 dims] as cached, fetched through a 3-D tensor map with the 128-byte swizzle = an MN-major A operand:
 //   O^T [128 dims x N'] += V^T [128 dims x 32 keys] P^T;
-//   K tiles [dim][16 positions] hold 16 keys per dim, and the fast operand form wants a dim's 128 keys in one 128-byte row (the
+//   8-bit K tiles [dim][16 positions] hold 16 keys per dim, and the fast operand form wants a dim's 128 keys in one 128-byte row (the
 //   tiles as they are, 8 dims x 16 positions per 128-byte core matrix without swizzle, are a valid operand too, but measured
-//   ~700 cycles per MMA): every thread moves 16-byte chunks from global memory to their place in the swizzled rows (8 loads and
-//   8 stores per thread and block, no arithmetic), then per 32-dim scale group c one MMA
-//   S_c^T [128 keys x N] = K_c [128 keys x 32 dims] Q_c^T.
+//   ~700 cycles per MMA): the block's 16 tiles arrive as cached by one bulk copy and every thread moves 16-byte chunks shared ->
+//   shared to their place in the swizzled rows (8 loads and 8 stores per thread and block, no arithmetic), then per 32-dim scale
+//   group c one MMA  S_c^T [128 keys x N] = K_c [128 keys x 32 dims] Q_c^T;
+//   4-bit levels n (stored + 8; K of q4k4, V of q4 and q4k4) are unpacked on that same way: the nibble in the high half of a byte
+//   with its top bit flipped is the int8 value 16 (n - 8) (shift, mask, xor per 4 levels), and 1 / 16 goes into the scale; 4-bit
+//   V tiles land as cached at the end of the V operand's place and are unpacked over it.
 // The other operands are 16-bit fixed point split into two int8 planes (the query per (vector, group), by tcd_q_prep_kernel;
-// the softmax weights times the V scale per (vector, group), scaled by the block's largest V scale of the group), so the
-// only roundings are those two quantisations to 16 bits; the scales (exact bf16 -> fp32) are applied in fp32 by the
+// the softmax weights times the V scale per (vector, group), scaled by the block's largest V scale magnitude of the group), so
+// the only roundings are those two quantisations to 16 bits; the scales (exact bf16 -> fp32) are applied in fp32 by the
 // softmax thread of a key (s = sum_c d_K[t][c] q_scale[v][c] S_c) and the epilogue thread of a dim.  Results agree with the
-// reference's fp32 arithmetic to ~1e-4 relative, inside the acceptance bar but not bit for bit; the bit-exact kernel stays
+// reference's fp32 arithmetic to ~1e-4 relative, inside the acceptance bar but not bit for bit; the bit-exact kernels stay
 // selectable (rq_cuda_set_exact).  With the keys on the TMEM lanes the softmax of a block is spread over all threads.
 #pragma once
 #include <cuda.h>
@@ -31,16 +34,19 @@ namespace rq {
 constexpr int TCD_THREADS = 256;
 constexpr int TCD_QT_BYTES = 2048 + 256;  // per (row, KV head): Q^T planes [16 rows][128 dims] int8 + scales [8 vectors][4 groups] fp32 (+ pad)
 
-template <int NVT>
+template <int NVT, int KF = KV_Q8, int VF = KV_Q8>  // KF, VF: 8-bit (KV_Q8) or 4-bit (KV_Q4) levels of K and of V
 struct TcdCfg {
     static constexpr int HD = 128;
-    static constexpr int KTB = kv_tile_bytes(KV_Q8, HD, 0), VTB = kv_tile_bytes(KV_Q8, HD, 1);  // 2176 each
+    static constexpr int KTB = HD * (KF == KV_Q8 ? 17 : 9), VTB = HD * (VF == KV_Q8 ? 17 : 9);  // 2176 (8-bit) or 1152 (4-bit)
+    static constexpr int KSC = (KF == KV_Q8 ? 16 : 8) * HD, VSC = (VF == KV_Q8 ? 16 : 8) * HD;  // the scales behind a tile's levels
+    // 4-bit V: the block's 16 tiles as cached land at the end of the V operand's place and are unpacked over it
+    static constexpr int VRAW_OFF = 32768 - 16 * (HD * 9);
     static constexpr int NS = NVT <= 4 ? 8 : 16;  // N of a score MMA: rows 2 v + plane
     static constexpr int NO = 8 * NVT;            // N of an output MMA: rows ((c NVT + v) 2 + plane)
     // shared memory (from a 1024-byte aligned base): the next block's 16 K tiles as cached (one bulk copy) | K levels of the two
     // halves as the operand wants them (2 x 16 KB: 128 rows = dims of 128 keys) | V levels (2 x 16 KB: 128 rows = positions of 128
     // dims, swizzled by the TMA) | P^T (2 x NO rows of 128 bytes) | Q^T planes, two buffers of 2 KB, and their scales, 2 x 256 B | the rest
-    static constexpr int KRAW = 0, KLEV = 16 * KTB, VLEV = KLEV + 32768, PT = VLEV + 32768, QT = PT + 2 * NO * 128, QS = QT + 4096;
+    static constexpr int KRAW = 0, KLEV = (16 * KTB + 1023) / 1024 * 1024, VLEV = KLEV + 32768, PT = VLEV + 32768, QT = PT + 2 * NO * 128, QS = QT + 4096;
     static constexpr int MISC = QS + 512;  // red (768 B: two buffers of block reductions, 128 B each)  | bars [6] (64 B) | TMEM slot (16 B) | items [4] (128 B)
     static constexpr int SMEM = MISC + 768 + 64 + 16 + 128 + 1024;
     // TMEM columns: the score products of two blocks (2 x 8 NS) | the output products
@@ -48,6 +54,8 @@ struct TcdCfg {
     static_assert(KLEV % 1024 == 0 && VLEV % 1024 == 0 && PT % 1024 == 0 && QT % 1024 == 0, "operand alignment");
     static_assert(O_COL + NO <= TM_COLS, "TMEM columns");
     static_assert(NVT > 4 || 2 * (SMEM + 1024) <= 228 * 1024, "two CTAs per SM");
+    static_assert(VRAW_OFF % 16 == 0 && VRAW_OFF > 0, "bulk copy alignment");
+    static_assert(KTB == kv_tile_bytes(KF == KV_Q8 ? KV_Q8 : KV_Q4K4, HD, 0) && VTB == kv_tile_bytes(VF == KV_Q8 ? KV_Q8 : KV_Q4K4, HD, 1), "tile bytes");
 };
 
 // a work item as the describing thread leaves it in shared memory for the others
@@ -61,6 +69,7 @@ struct TcdItem {
 static_assert(sizeof(TcdItem) == 32, "four items in 128 bytes");
 
 struct AttnPartTcArgs {
+    int kvt;  // KV_Q8, KV_Q4 (8-bit K, 4-bit V) or KV_Q4K4
     const PassRow *rows;
     int nrows, total_blocks, layer, n_kv, G;
     const float *q;
@@ -199,13 +208,19 @@ __device__ __forceinline__ void mbar_drain(uint64_t *bar, uint32_t parity) {
 // MMAs, score MMAs.  (An MMA of these shapes keeps its issuing thread for ~150 cycles: the two batches of eight go to two warps.)
 // maps: per segment [4 seg + 1] the tensor map of its sequence's V cache: {128 bytes of levels, 16 positions, tiles} with
 // strides {128, tile bytes}, box 128 x 16 x 8, 128-byte swizzle.
-template <int NVT>
+template <int NVT, int KF, int VF>
 __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
     attn_part_tc_kernel(const PassRow *__restrict__ rows, const int *__restrict__ blk2row, const uint8_t *__restrict__ qtg,
                         const CUtensorMap *__restrict__ maps, int layer, int n_kv, int G, int n_heads, float scale, float *__restrict__ part,
                         int total_blocks, int *err) {
-    using C = TcdCfg<NVT>;
+    using C = TcdCfg<NVT, KF, VF>;
     constexpr int HD = C::HD, NS = C::NS, NO = C::NO;
+    // 4-bit levels n (stored + 8) enter the MMAs as the int8 values 16 (n - 8): the nibble in the high half of a byte with its top bit
+    // flipped; the factor goes into the scales
+    constexpr float KMUL = KF == KV_Q8 ? 1.0f : 0.0625f, VMUL = VF == KV_Q8 ? 1.0f : 0.0625f;
+    // the weight planes: 8-bit V scales are positive (largest magnitude / 127): unsigned 16-bit weights; 4-bit scales carry a sign
+    // (first largest element / -8, src/forward.c:1901 kv_store): signed weights, +-(127 x 256 + 127), both planes signed
+    constexpr float PMAX = VF == KV_Q8 ? 65535.0f : 32639.0f;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *pt = sm + C::PT;
@@ -294,9 +309,15 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
     auto fetch_v = [&](int i) {
         const TcdItem d = items[i & 3];
         const int nh = (d.n + 127) >> 7;
-        const CUtensorMap *mv = maps + 4 * d.seg + 1;
-        mbar_expect_tx(bar_v, 16384u * (uint32_t)nh);
-        for (int h = 0; h < nh; h++) tma_load_3d(sm + C::VLEV + h * 16384, mv, 0, 0, d.vt + 8 * h, bar_v);
+        if constexpr (VF == KV_Q8) {
+            const CUtensorMap *mv = maps + 4 * d.seg + 1;
+            mbar_expect_tx(bar_v, 16384u * (uint32_t)nh);
+            for (int h = 0; h < nh; h++) tma_load_3d(sm + C::VLEV + h * 16384, mv, 0, 0, d.vt + 8 * h, bar_v);
+        } else {  // the tiles as cached, unpacked by the threads (unpack_v)
+            fence_proxy_async();
+            mbar_expect_tx(bar_v, 8u * C::VTB * (uint32_t)nh);
+            bulk_g2s(sm + C::VLEV + C::VRAW_OFF, (const uint8_t *)(uintptr_t)d.vs, 8u * C::VTB * (uint32_t)nh, bar_v);
+        }
     };
     // item i's K chunks from the tiles as cached to where the operand wants them (row = dim, chunk = tile ^ (dim % 8): the 128-byte
     // swizzle), and the scales of this thread's key: K [group][16 positions] behind the tile's levels in shared memory, V
@@ -308,18 +329,35 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         const int nh = (d.n + 127) >> 7;
         if (lane == 0) ok = mbar_wait_bounded(bar_k, (uint32_t)i & 1u, err, 72) && ok;
         __syncwarp();
+        if constexpr (KF == KV_Q8) {
 #pragma unroll
-        for (int k = 0; k < 8; k++) {  // chunk (tile u, dim i): 16 positions of one dim
-            const int idx = tid + TCD_THREADS * (k & 3), u = (idx >> 7) + 8 * (k >> 2), dim = idx & 127;
-            if ((k >> 2) < nh)
-                *reinterpret_cast<uint4 *>(sm + C::KLEV + (k >> 2) * 16384 + dim * 128 + (((u & 7) ^ (dim & 7)) << 4)) =
-                    *reinterpret_cast<const uint4 *>(sm + C::KRAW + u * C::KTB + dim * 16);
+            for (int k = 0; k < 8; k++) {  // chunk (tile u, dim i): 16 positions of one dim
+                const int idx = tid + TCD_THREADS * (k & 3), u = (idx >> 7) + 8 * (k >> 2), dim = idx & 127;
+                if ((k >> 2) < nh)
+                    *reinterpret_cast<uint4 *>(sm + C::KLEV + (k >> 2) * 16384 + dim * 128 + (((u & 7) ^ (dim & 7)) << 4)) =
+                        *reinterpret_cast<const uint4 *>(sm + C::KRAW + u * C::KTB + dim * 16);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; k++) {  // chunk (tile u, dim pair p): 16 positions, low nibbles dim 2p, high nibbles dim 2p + 1
+                const int idx = tid + TCD_THREADS * (k & 1), u = (idx >> 6) + 8 * (k >> 1), p = idx & 63;
+                if ((k >> 1) < nh) {
+                    const uint4 w = *reinterpret_cast<const uint4 *>(sm + C::KRAW + u * C::KTB + p * 16);
+                    uint8_t *dst = sm + C::KLEV + (k >> 1) * 16384 + (2 * p) * 128;
+                    *reinterpret_cast<uint4 *>(dst + (((u & 7) ^ ((2 * p) & 7)) << 4)) =
+                        make_uint4(((w.x << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((w.y << 4) & 0xF0F0F0F0u) ^ 0x80808080u,
+                                   ((w.z << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((w.w << 4) & 0xF0F0F0F0u) ^ 0x80808080u);
+                    *reinterpret_cast<uint4 *>(dst + 128 + (((u & 7) ^ ((2 * p + 1) & 7)) << 4)) =
+                        make_uint4((w.x & 0xF0F0F0F0u) ^ 0x80808080u, (w.y & 0xF0F0F0F0u) ^ 0x80808080u, (w.z & 0xF0F0F0F0u) ^ 0x80808080u,
+                                   (w.w & 0xF0F0F0F0u) ^ 0x80808080u);
+                }
+            }
         }
         if (pos < d.n) {
-            const uint16_t *ks = reinterpret_cast<const uint16_t *>(sm + C::KRAW + (pos >> 4) * C::KTB + 16 * HD) + (pos & 15);
+            const uint16_t *ks = reinterpret_cast<const uint16_t *>(sm + C::KRAW + (pos >> 4) * C::KTB + C::KSC) + (pos & 15);
 #pragma unroll
             for (int c = 0; c < 4; c++) ks_n[c] = ks[c * 16];
-            vs_n = __ldg(reinterpret_cast<const uint2 *>((const uint8_t *)(uintptr_t)d.vs + (size_t)(pos >> 4) * C::VTB + 16 * HD) + (pos & 15));
+            vs_n = __ldg(reinterpret_cast<const uint2 *>((const uint8_t *)(uintptr_t)d.vs + (size_t)(pos >> 4) * C::VTB + C::VSC) + (pos & 15));
         } else {
             ks_n[0] = ks_n[1] = ks_n[2] = ks_n[3] = 0u;
             vs_n = make_uint2(0u, 0u);
@@ -391,9 +429,9 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         // ---- the scales of this thread's key
         float dk[4], dv[4];
 #pragma unroll
-        for (int c = 0; c < 4; c++) dk[c] = bf16_bits_to_f32(ks_n[c]);
-        dv[0] = __uint_as_float(vs_n.x << 16), dv[1] = __uint_as_float(vs_n.x & 0xffff0000u);
-        dv[2] = __uint_as_float(vs_n.y << 16), dv[3] = __uint_as_float(vs_n.y & 0xffff0000u);
+        for (int c = 0; c < 4; c++) dk[c] = bf16_bits_to_f32(ks_n[c]) * KMUL;
+        dv[0] = __uint_as_float(vs_n.x << 16) * VMUL, dv[1] = __uint_as_float(vs_n.x & 0xffff0000u) * VMUL;
+        dv[2] = __uint_as_float(vs_n.y << 16) * VMUL, dv[3] = __uint_as_float(vs_n.y & 0xffff0000u) * VMUL;
         // ---- softmax of the block: thread (half h2, key t) holds the scores of its key for the G vectors
         // the block's largest V scale per group, what the weight planes are scaled by (the scales are positive: their bits order
         // like unsigned integers): one warp reduction each, then one shared-memory atomic of lane 8 + c
@@ -401,7 +439,7 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         int *rb = reinterpret_cast<int *>(red) + (it & 1) * 32;
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            const unsigned mx = __reduce_max_sync(0xffffffffu, __float_as_uint(dv[c]));
+            const unsigned mx = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(dv[c])));
             if (lane == 8 + c) atomicMax(reinterpret_cast<unsigned *>(rb) + 8 + c, mx);
         }
         // (the score products complete only after their thread has seen the query planes land: no wait of its own for those)
@@ -449,6 +487,19 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         }
         if (tid == T_MMA && more) issue_s(it + 1);
         if (tid == T_ITEMS && it + 2 < cnt) describe(it + 2);
+        // 4-bit V: this block's tiles as cached, from where they landed into registers (they are unpacked over that place once every
+        // thread has read its share: barrier S2b below); share k of a thread: position (tid / 4) + 64 k, scale group tid % 4
+        uint4 vraw[VF == KV_Q8 ? 1 : 4];
+        if constexpr (VF != KV_Q8) {
+            if (lane == 0) ok = mbar_wait_bounded(bar_v, (uint32_t)it & 1u, err, 73) && ok;
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int vp = (tid >> 2) + 64 * k;
+                vraw[k] = (k >> 1) < nh ? *reinterpret_cast<const uint4 *>(sm + C::VLEV + C::VRAW_OFF + (vp >> 4) * C::VTB + (vp & 15) * 64 + (tid & 3) * 16)
+                                        : make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
         if (tid == T_ML) {  // the other buffer of reductions, for the next block
             int4 *nb = reinterpret_cast<int4 *>(reinterpret_cast<int *>(red) + ((it + 1) & 1) * 32);
             nb[0] = nb[1] = make_int4(INT_MIN, INT_MIN, INT_MIN, INT_MIN);
@@ -458,10 +509,10 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         const float4 psc = *reinterpret_cast<const float4 *>(rb + 8);
         const float ps_mine = (warp & 2) ? ((warp & 1) ? psc.w : psc.z) : ((warp & 1) ? psc.y : psc.x);
         // the key's V scales in units of the block's largest
-        dvp[0] = psc.x > 0.0f ? dv[0] * __fdividef(65535.0f, psc.x) : 0.0f;
-        dvp[1] = psc.y > 0.0f ? dv[1] * __fdividef(65535.0f, psc.y) : 0.0f;
-        dvp[2] = psc.z > 0.0f ? dv[2] * __fdividef(65535.0f, psc.z) : 0.0f;
-        dvp[3] = psc.w > 0.0f ? dv[3] * __fdividef(65535.0f, psc.w) : 0.0f;
+        dvp[0] = psc.x > 0.0f ? dv[0] * __fdividef(PMAX, psc.x) : 0.0f;
+        dvp[1] = psc.y > 0.0f ? dv[1] * __fdividef(PMAX, psc.y) : 0.0f;
+        dvp[2] = psc.z > 0.0f ? dv[2] * __fdividef(PMAX, psc.z) : 0.0f;
+        dvp[3] = psc.w > 0.0f ? dv[3] * __fdividef(PMAX, psc.w) : 0.0f;
 #pragma unroll
         for (int v = 0; v < NVT; v++) {
             const float mx = ord_f32(rb[v]);
@@ -481,11 +532,37 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
             for (int c = 0; c < 4; c++)
 #pragma unroll
                 for (int v = 0; v < NVT; v++) {
-                    const uint32_t u16 = (uint32_t)__float2int_rn(fminf(e[v] * dvp[c], 65535.0f));
                     const int rw = (c * NVT + v) * 2;
-                    pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)(u16 >> 8);
-                    pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)(u16 & 255u);
+                    if constexpr (VF == KV_Q8) {
+                        const uint32_t u16 = (uint32_t)__float2int_rn(fminf(e[v] * dvp[c], PMAX));
+                        pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)(u16 >> 8);
+                        pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)(u16 & 255u);
+                    } else {
+                        const int p16 = __float2int_rn(fminf(fmaxf(e[v] * dvp[c], -PMAX), PMAX));
+                        const int plo = ((p16 + 128) & 255) - 128;
+                        pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)((p16 - plo) >> 8);
+                        pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)plo;
+                    }
                 }
+        }
+        if constexpr (VF != KV_Q8) {
+            __syncthreads();  // S2b: the tiles as cached are in registers
+            // per position and group 16 bytes, byte l = dims 32 c + l (low nibble) and 32 c + 16 + l (high): two 16-byte chunks of the
+            // position's row of the operand (row = position, chunk = dims / 16 ^ (position % 8): the 128-byte swizzle)
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int vp = (tid >> 2) + 64 * k, c = tid & 3, rw = vp & 127;
+                if ((k >> 1) < nh) {
+                    const uint4 w = vraw[k];
+                    uint8_t *dst = sm + C::VLEV + (vp >> 7) * 16384 + rw * 128;
+                    *reinterpret_cast<uint4 *>(dst + (((2 * c) ^ (rw & 7)) << 4)) =
+                        make_uint4(((w.x << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((w.y << 4) & 0xF0F0F0F0u) ^ 0x80808080u,
+                                   ((w.z << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((w.w << 4) & 0xF0F0F0F0u) ^ 0x80808080u);
+                    *reinterpret_cast<uint4 *>(dst + (((2 * c + 1) ^ (rw & 7)) << 4)) =
+                        make_uint4((w.x & 0xF0F0F0F0u) ^ 0x80808080u, (w.y & 0xF0F0F0F0u) ^ 0x80808080u, (w.z & 0xF0F0F0F0u) ^ 0x80808080u,
+                                   (w.w & 0xF0F0F0F0u) ^ 0x80808080u);
+                }
+            }
         }
         fence_proxy_async();
         tc_fence_before();
@@ -493,8 +570,8 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         if (tid == T_PV) {
             // ---- O^T += V^T (half h) P^T (half h): 4 k-steps of 32 keys per half
             tc_fence_after();
-            ok = mbar_wait_bounded(bar_v, (uint32_t)it & 1u, err, 73) && ok;  // (the item's V levels have landed)
-            constexpr uint32_t idesc_o = umma_idesc_i8(128, NO, 1, 0, 1, 0);
+            if constexpr (VF == KV_Q8) ok = mbar_wait_bounded(bar_v, (uint32_t)it & 1u, err, 73) && ok;  // (the item's V levels have landed)
+            constexpr uint32_t idesc_o = umma_idesc_i8(128, NO, 1, 0, 1, VF == KV_Q8 ? 0 : 1);
             for (int h = 0; h < nh; h++) {
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++) {
@@ -516,7 +593,7 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
                     p[HD + 1] = (float)reinterpret_cast<const unsigned *>(rb)[16 + v] * (1.0f / 8388608.0f);
                 }
         }
-        back_prev = ps_mine * (1.0f / 65535.0f);
+        back_prev = ps_mine * (1.0f / PMAX);
         pidx_prev = pidx;
     }
     pdl_launch_dependents();
@@ -536,14 +613,14 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(C::TM_COLS));
 }
 
-template <int NVT>
+template <int NVT, int KF, int VF>
 static cudaError_t launch_tc_one(const AttnPartTcArgs &a, cudaStream_t stream) {
-    constexpr int smem = TcdCfg<NVT>::SMEM;
+    constexpr int smem = TcdCfg<NVT, KF, VF>::SMEM;
     static_assert(smem <= 227 * 1024, "one CTA's shared memory");
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kern = attn_part_tc_kernel<NVT>;
+    auto kern = attn_part_tc_kernel<NVT, KF, VF>;
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
@@ -556,13 +633,22 @@ static cudaError_t launch_tc_one(const AttnPartTcArgs &a, cudaStream_t stream) {
     return launch_pdl(kern, dim3(grid), dim3(TCD_THREADS), (size_t)smem, stream, a.rows, (const int *)a.blk2row, (const uint8_t *)a.qt, a.maps, a.layer,
                       a.n_kv, a.G, a.n_heads, a.scale, a.part, a.total_blocks, a.err);
 }
+template <int KF, int VF>
+static cudaError_t launch_tc_fmt(const AttnPartTcArgs &a, cudaStream_t stream) {
+    if (a.G == 1) return launch_tc_one<1, KF, VF>(a, stream);
+    if (a.G == 2) return launch_tc_one<2, KF, VF>(a, stream);
+    if (a.G <= 4) return launch_tc_one<4, KF, VF>(a, stream);
+    return launch_tc_one<8, KF, VF>(a, stream);
+}
 
 cudaError_t launch_attn_part_tc(const AttnPartTcArgs &a, cudaStream_t stream) {
     if (a.G < 1 || a.G > 8) return cudaErrorInvalidValue;
-    if (a.G == 1) return launch_tc_one<1>(a, stream);
-    if (a.G == 2) return launch_tc_one<2>(a, stream);
-    if (a.G <= 4) return launch_tc_one<4>(a, stream);
-    return launch_tc_one<8>(a, stream);
+    switch (a.kvt) {
+        case KV_Q8: return launch_tc_fmt<KV_Q8, KV_Q8>(a, stream);
+        case KV_Q4: return launch_tc_fmt<KV_Q8, KV_Q4>(a, stream);
+        case KV_Q4K4: return launch_tc_fmt<KV_Q4, KV_Q4>(a, stream);
+        default: return cudaErrorInvalidValue;
+    }
 }
 #endif  // RQ_ATTN_DECODE_TC_INSTANTIATE
 

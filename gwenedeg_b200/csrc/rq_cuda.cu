@@ -191,6 +191,13 @@ static bool seq_make_maps(RqCuda *c, RqCudaSeq *s) {
         s->has_tm_q8 = true;
         return true;
     }
+    if (kv_quant(s->kvt) && hd == 128 && c->m.n_attn >= 1) {
+        // (4-bit V levels go to the tensor-core decode kernel by plain bulk copies: no view needed)
+        memset(&s->tm_v, 0, sizeof s->tm_v);
+        s->tm_k = s->tm_ks = s->tm_vs = s->tm_v;
+        s->has_tm_q8 = true;
+        return true;
+    }
     if (s->kvt != KV_F16 || (hd != 128 && hd != 256) || c->m.n_attn < 1) return true;
     TmEncodeFn enc = tm_encode();
     if (!enc) return false;
@@ -885,7 +892,7 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
     cudaError_t e;
     const bool prof = c->prof_on && (size_t)(2 * c->prof_n + 2) <= c->prof_ev.size();
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n], c->stream);
-    if (c->pass_kvt == KV_Q8 && hd == 128 && !c->exact && may_allocate && c->tc_ready == 0) {
+    if (kv_quant(c->pass_kvt) && hd == 128 && !c->exact && may_allocate && c->tc_ready == 0) {
         // once per pass: the tensor maps of the segments' sequences
         c->tc_ready = 1;
         for (auto &g : c->segs)
@@ -899,13 +906,14 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
             CU(c, cudaStreamSynchronize(c->stream));  // (the pinned table is reused by the next pass)
         }
     }
-    if (c->pass_kvt == KV_Q8 && hd == 128 && !c->exact && may_allocate && c->tc_ready == 1) {
-        // 8-bit caches at head_dim 128: the cached levels as int8 MMA operands (results inside the tolerance); the same partial
+    if (kv_quant(c->pass_kvt) && hd == 128 && !c->exact && may_allocate && c->tc_ready == 1) {
+        // quantised caches at head_dim 128: the cached levels as int8 MMA operands (results inside the tolerance); the same partial
         // records, merged by the same kernel
         int rcg;
         if ((rcg = grow(c, (void **)&c->d_tcq, &c->tcq_bytes, (size_t)c->nrows * c->n_kv * TCD_QT_BYTES))) return rcg;
         if ((rcg = grow(c, (void **)&c->d_blk2row, &c->blk2row_bytes, (size_t)c->total_blocks * sizeof(int)))) return rcg;
         AttnPartTcArgs t;
+        t.kvt = c->pass_kvt;
         t.qt = c->d_tcq, t.blk2row = c->d_blk2row, t.maps = c->d_maps8, t.n_sm = c->n_sm;
         t.rows = a.rows, t.nrows = a.nrows, t.total_blocks = a.total_blocks, t.layer = a.layer, t.n_kv = a.n_kv, t.G = a.G;
         t.q = a.q, t.qh = a.qh, t.n_heads = a.n_heads, t.scale = a.scale, t.part = a.part, t.err = a.err;
