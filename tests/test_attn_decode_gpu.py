@@ -88,8 +88,8 @@ def test_store_and_decode_match_cpu(checker, port, kvt, n_heads, n_kv, hd, gated
 @pytest.mark.parametrize("kvt", [Q8, Q4, Q4K4])
 @pytest.mark.parametrize("n_heads,n_kv,gated", [(4, 2, False), (8, 2, False), (8, 1, True), (6, 2, False), (2, 2, False)])
 def test_quantised_decode_on_tensor_cores_matches_cpu(checker, kvt, n_heads, n_kv, gated):
-    """The tensor-core path over quantised caches at head_dim 128 (levels dequantised to f16 operands, dot products on the tensor
-    cores) against the CPU code on the device's own cache bytes: inside the acceptance bar at every edge context, a row alone
+    """The tensor-core path over quantised caches at head_dim 128 (the cached levels as int8 MMA operands, 4-bit ones unpacked to
+    16 (n - 8); query and softmax weights as 16-bit fixed point in two int8 planes) against the CPU code on the device's own cache bytes: inside the acceptance bar at every edge context, a row alone
     equal to the same row in a batch, and equal bits from run to run."""
     from gwenedeg_b200 import synth
     hd, n = 128, 700
