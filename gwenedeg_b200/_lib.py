@@ -43,6 +43,10 @@ PROTOTYPES = {
     "rq_cuda_sync": (_i, [_vp]),
     "rq_cuda_reserve": (_i, [_vp, _i, C.c_longlong, _i]),
     "rq_cuda_selftest_wait_expiry": (_i, [_vp, C.c_uint]),
+    "rq_cuda_peer_export": (_i, [_vp, _i, _vp]),
+    "rq_cuda_peer_import": (_i, [_vp, _i, _i, _vp]),
+    "rq_cuda_attn_decode_gather_dev": (_i, [_vp, _i, _vp, C.POINTER(_vp)]),
+    "rq_cuda_selftest_peer_wait": (_i, [_vp, C.c_uint]),
     "rq_cuda_set_wo_quant": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_set_exact": (_i, [_vp, _i]),
     "rq_cuda_set_stream": (_i, [_vp, _vp]),

@@ -154,6 +154,24 @@ class Context:
     def attn_decode_dev(self, layer, q_dev, out_dev):
         self.check(self.L.rq_cuda_attn_decode_dev(self.h, layer, _ptr(q_dev), _ptr(out_dev)))
 
+    def peer_export(self, rows):
+        """This rank's row buffer for the fused gather of head-sharded contexts: the 64 bytes of its IPC handle."""
+        h = (C.c_ubyte * 64)()
+        self.check(self.L.rq_cuda_peer_export(self.h, rows, C.cast(h, C.c_void_p)))
+        return bytes(h)
+
+    def peer_import(self, rank, handles):
+        """handles: the ranks' 64-byte handles in rank order."""
+        buf = b"".join(handles)
+        self.check(self.L.rq_cuda_peer_import(self.h, rank, len(handles), C.cast(C.c_char_p(buf), C.c_void_p)))
+
+    def attn_decode_gather_dev(self, layer, q_dev):
+        """Decode attention of this rank's heads, stored into every rank's full-width row buffer by the merge kernel; returns the
+        device address of this rank's buffer of the step ([rows][n_heads][head_dim], all heads)."""
+        out = C.c_void_p()
+        self.check(self.L.rq_cuda_attn_decode_gather_dev(self.h, layer, _ptr(q_dev), C.byref(out)))
+        return out.value
+
     def attn_prefill_dev(self, layer, q_dev, out_dev):
         self.check(self.L.rq_cuda_attn_prefill_dev(self.h, layer, _ptr(q_dev), _ptr(out_dev)))
 

@@ -552,6 +552,15 @@ struct WoQuant {
     int gs;
 };
 
+// Head-sharded contexts (one GPU per group of KV heads): where the merge kernel stores its output rows when the gather over the
+// ranks is fused into it: the full-width row buffers [rows][n_heads_full][head_dim] of every rank (this rank's own among them;
+// the others are peer mappings over NVLink), this rank's heads starting at head0.  world 0: the plain local store.
+constexpr int RQ_MAX_PEERS = 8;
+struct PeerOut {
+    float *out[RQ_MAX_PEERS];
+    int world, n_heads_full, head0;
+};
+
 constexpr int COMBINE_NG = 4;  // thread groups of the merge kernel: each fetches a quarter of the partials
 
 // One CTA of COMBINE_NG x HD threads per (row, query head).  The partial results are fetched into shared memory by all
@@ -561,7 +570,7 @@ template <int HD, bool QUANT>
 __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const PassRow *__restrict__ rows, int n_heads,
                                                                       const float *__restrict__ part, const float *__restrict__ q, int qh,
                                                                       int gated, float *__restrict__ out, int split_len, int fixed_stride,
-                                                                      const int *err_src, int *err_dst, WoQuant wq) {
+                                                                      const int *err_src, int *err_dst, WoQuant wq, PeerOut po) {
     constexpr int CH = 8192 / HD;  // partials per chunk: 32 KB of shared memory
     const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, i = tid % HD, grp = tid / HD;
     pdl_wait();
@@ -642,7 +651,14 @@ __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const Pass
     }
     if (grp == 0) {
         if (gated) res = res * sigmoid_att(q[((size_t)r * n_heads + h) * qh + HD + i]);
-        out[((size_t)r * n_heads + h) * HD + i] = res;
+        if (po.world > 0) {  // the gather over the ranks, fused: this rank's heads of the row into every rank's full-width buffer
+            const size_t at = ((size_t)r * po.n_heads_full + po.head0 + h) * HD + i;
+#pragma unroll
+            for (int p = 0; p < RQ_MAX_PEERS; p++)
+                if (p < po.world) po.out[p][at] = res;
+        } else {
+            out[((size_t)r * n_heads + h) * HD + i] = res;
+        }
     }
     if (wq.xq) {  // (uniform over the CTA) the quantised copy for the `wo` matmul
         __shared__ float wmaxs[HD / 32];

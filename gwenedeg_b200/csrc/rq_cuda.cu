@@ -112,6 +112,14 @@ struct RqCuda {
     PfWork *d_work; size_t work_bytes;
     std::vector<PfWork> h_work;
     int pf_ready, pf_max_splits;
+    // head-sharded contexts: the gather of the output rows fused into the merge kernel (rq_cuda_peer_*): this rank's buffer
+    // (1 KB of flags, then two full-width row buffers used in turn) and the peers' mappings of theirs
+    uint8_t *peer_own = nullptr;
+    uint8_t *peer_base[RQ_MAX_PEERS] = {nullptr};
+    size_t peer_rows_bytes = 0;
+    int peer_rank = 0, peer_world = 0, peer_max_rows = 0;
+    unsigned peer_step = 0;
+    bool peer_now = false;  // the launch in progress stores to the peers
     // ... over quantised caches: the layer's tiles expanded to f16 in a scratch (pf_quant: the open pass takes that route)
     bool pf_quant = false;
     uint8_t *d_dq = nullptr; size_t dq_bytes = 0;   // the f16 tiles, K then V per segment
@@ -250,6 +258,34 @@ __global__ void wait_expiry_kernel(int *err, unsigned long long limit_ns, int co
     mbar_wait_bounded_ns(&bar, 0, err, code, limit_ns);
 }
 
+// After a merge kernel that stored this rank's heads into every rank's row buffer: lane p tells rank p that this rank's part of
+// step `step` is in place (a system-scope release store into rank p's flag word of this rank), then waits until rank p has told
+// this rank the same, with a time limit: a rank that never arrives makes the wait run out, the kernel records `code` in the
+// status word and returns by itself.  One warp; launched as an ordinary kernel, so the merge kernel before it has completed.
+struct PeerFlags {
+    unsigned *flags[RQ_MAX_PEERS];  // rank p's flag words [RQ_MAX_PEERS]; [rank]: this rank's own
+};
+__global__ void peer_sync_kernel(PeerFlags pf, int rank, int world, unsigned step, int *err, unsigned long long limit_ns, int code) {
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pf.flags[p] + rank), "r"(step) : "memory");
+    const unsigned *mine = pf.flags[rank] + p;
+    unsigned long long t0 = 0;
+    for (long long it = 0;; it++) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if ((int)(v - step) >= 0) return;
+        if ((it & 63) == 63) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            if (now - t0 > limit_ns) break;
+        }
+    }
+    atomicExch(err, code);
+}
+
 extern "C" {
 
 int rq_cuda_debug_build(void) {
@@ -342,6 +378,9 @@ void rq_cuda_free(RqCuda *c) {
     if (!c) return;
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
+    for (int p = 0; p < c->peer_world; p++)
+        if (p != c->peer_rank && c->peer_base[p]) cudaIpcCloseMemHandle(c->peer_base[p]);
+    if (c->peer_own) cudaFree(c->peer_own);
     if (c->d_dnw) cudaFree(c->d_dnw);
     if (c->h_maps8) cudaFreeHost(c->h_maps8);
     void *dev[] = {c->d_dq, c->d_qrot, c->d_dqseg, c->d_maps8, c->d_tcq, c->d_blk2row, c->d_chunks, c->d_ck, c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
@@ -386,6 +425,67 @@ int rq_cuda_selftest_wait_expiry(RqCuda *c, unsigned int limit_us) {
     wait_expiry_kernel<<<1, 32, 0, c->stream>>>(c->d_err, (unsigned long long)limit_us * 1000ull, 99);
     c->launches++;
     CU(c, cudaGetLastError());
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_peer_export(RqCuda *c, int rows, void *handle64) {
+    if (!c || !handle64 || rows < 1 || rows > c->max_rows) return c ? fail(c, RQ_CUDA_ERR_ARG, "peer_export: %d rows", rows) : RQ_CUDA_ERR_ARG;
+    if (c->peer_own) return fail(c, RQ_CUDA_ERR_STATE, "peer_export: already exported");
+    if (c->m.n_attn < 1) return fail(c, RQ_CUDA_ERR_ARG, "peer_export: no attention layers");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is 64 bytes");
+    CU(c, cudaSetDevice(c->device));
+    c->peer_rows_bytes = ((size_t)rows * c->m.n_heads * c->m.head_dim * 4 + 255) & ~(size_t)255;
+    CU(c, cudaMalloc((void **)&c->peer_own, 1024 + 2 * c->peer_rows_bytes));
+    CU(c, cudaMemset(c->peer_own, 0, 1024 + 2 * c->peer_rows_bytes));
+    CU(c, cudaDeviceSynchronize());
+    cudaIpcMemHandle_t h;
+    CU(c, cudaIpcGetMemHandle(&h, c->peer_own));
+    memcpy(handle64, &h, 64);
+    c->peer_max_rows = rows;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_peer_import(RqCuda *c, int rank, int world, const void *handles) {
+    if (!c || !handles || world < 1 || world > RQ_MAX_PEERS || rank < 0 || rank >= world)
+        return c ? fail(c, RQ_CUDA_ERR_ARG, "peer_import: rank %d of %d", rank, world) : RQ_CUDA_ERR_ARG;
+    if (!c->peer_own || c->peer_world) return fail(c, RQ_CUDA_ERR_STATE, "peer_import: export first, import once");
+    CU(c, cudaSetDevice(c->device));
+    for (int p = 0; p < world; p++) {
+        if (p == rank) {
+            c->peer_base[p] = c->peer_own;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)handles + 64 * (size_t)p, 64);
+        void *ptr = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            for (int x = 0; x < p; x++)
+                if (x != rank && c->peer_base[x]) cudaIpcCloseMemHandle(c->peer_base[x]), c->peer_base[x] = nullptr;
+            return fail(c, RQ_CUDA_ERR_DEVICE, "peer_import: rank %d's buffer: %s", p, cudaGetErrorString(e));
+        }
+        c->peer_base[p] = (uint8_t *)ptr;
+    }
+    c->peer_rank = rank, c->peer_world = world;
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_selftest_peer_wait(RqCuda *c, unsigned int limit_us) {
+    // a two-rank exchange whose other rank never arrives: both flag arrays are this context's own, nothing sets word [1]
+    if (!c || limit_us < 1 || limit_us > 1000000) return RQ_CUDA_ERR_ARG;
+    CU(c, cudaSetDevice(c->device));
+    unsigned *fl = nullptr;
+    CU(c, cudaMalloc((void **)&fl, 1024));
+    CU(c, cudaMemsetAsync(fl, 0, 1024, c->stream));
+    PeerFlags pf;
+    memset(&pf, 0, sizeof pf);
+    pf.flags[0] = fl, pf.flags[1] = fl + 64;
+    peer_sync_kernel<<<1, 32, 0, c->stream>>>(pf, 0, 2, 1u, c->d_err, (unsigned long long)limit_us * 1000ull, 97);
+    c->launches++;
+    cudaError_t e = cudaGetLastError();
+    cudaStreamSynchronize(c->stream);
+    cudaFree(fl);
+    CU(c, e);
     return RQ_CUDA_OK;
 }
 
@@ -937,9 +1037,15 @@ static int launch_combine(RqCuda *c, const float *q, float *out, const float *pa
     dim3 grid(c->nrows, c->n_heads);
     const bool quant = kv_quant(c->pass_kvt);
     cudaError_t ce = cudaSuccess;
+    PeerOut po;
+    memset(&po, 0, sizeof po);
+    if (c->peer_now) {
+        po.world = c->peer_world, po.n_heads_full = c->m.n_heads, po.head0 = c->m.kv_head0 * c->G;
+        for (int p = 0; p < c->peer_world; p++) po.out[p] = (float *)(c->peer_base[p] + 1024 + (size_t)(c->peer_step & 1) * c->peer_rows_bytes);
+    }
 #define COMBINE(HD_)                                                                                                          \
-    if (quant) ce = launch_pdl(attn_combine_kernel<HD_, true>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd, c->wo_quant); \
-    else ce = launch_pdl(attn_combine_kernel<HD_, false>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd, c->wo_quant);
+    if (quant) ce = launch_pdl(attn_combine_kernel<HD_, true>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd, c->wo_quant, po); \
+    else ce = launch_pdl(attn_combine_kernel<HD_, false>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd, c->wo_quant, po);
     switch (hd) {
         case 64: COMBINE(64) break;
         case 128: COMBINE(128) break;
@@ -959,6 +1065,30 @@ int rq_cuda_attn_decode_dev(RqCuda *c, int layer, const float *q, float *out) {
     CU(c, cudaSetDevice(c->device));
     return launch_decode(c, layer, q, out);
 }
+
+int rq_cuda_attn_decode_gather_dev(RqCuda *c, int layer, const float *q, float **out_full) {
+    int rc = need_pass(c, layer, c ? c->m.n_attn : 0, "attn_decode_gather");
+    if (rc) return rc;
+    if (!q || !out_full) return fail(c, RQ_CUDA_ERR_ARG, "attn_decode_gather: null rows");
+    if (!c->peer_world) return fail(c, RQ_CUDA_ERR_STATE, "attn_decode_gather: no peers imported");
+    if (c->nrows > c->peer_max_rows) return fail(c, RQ_CUDA_ERR_ARG, "attn_decode_gather: %d rows exceed the exported %d", c->nrows, c->peer_max_rows);
+    NEED_ALIGNED(c, "attn_decode_gather", q, q);
+    CU(c, cudaSetDevice(c->device));
+    c->peer_step++;
+    c->peer_now = true;
+    rc = launch_decode(c, layer, q, (float *)(c->peer_own + 1024));
+    c->peer_now = false;
+    if (rc) return rc;
+    PeerFlags pf;
+    memset(&pf, 0, sizeof pf);
+    for (int p = 0; p < c->peer_world; p++) pf.flags[p] = (unsigned *)c->peer_base[p];
+    peer_sync_kernel<<<1, 32, 0, c->stream>>>(pf, c->peer_rank, c->peer_world, c->peer_step, c->d_err, 2000000000ull, 97);
+    c->launches++;
+    CU(c, cudaGetLastError());
+    *out_full = (float *)(c->peer_own + 1024 + (size_t)(c->peer_step & 1) * c->peer_rows_bytes);
+    return RQ_CUDA_OK;
+}
+
 
 static int stage_q(RqCuda *c, const float *q, size_t qbytes, size_t obytes) {
     int rc;

@@ -92,6 +92,22 @@ int rq_cuda_reserve(RqCuda *ctx, int rows, long long positions_total, int max_ct
  * word and returns; the next rq_cuda_sync then reports RQ_CUDA_ERR_STATE exactly as it would after an expired wait inside
  * an attention kernel, and the context stays usable. */
 int rq_cuda_selftest_wait_expiry(RqCuda *ctx, unsigned int limit_us);
+/* Head-sharded contexts on several GPUs of one node (kv_head0 / kv_heads_local: each rank holds a group of KV heads of every
+ * sequence; the reference's workers share one address space, forward.c:2691-2715: this is what replaces it across GPUs): the
+ * gather of the output rows is fused into the merge kernel.  Every rank exports a row buffer (rq_cuda_peer_export: 64 bytes of
+ * cudaIpcMemHandle_t out, for passes of at most `rows` rows), the host exchanges the handles by whatever means it has, and every
+ * rank imports all of them in rank order (rq_cuda_peer_import: `handles` = world x 64 bytes; its own entry is ignored).
+ * rq_cuda_attn_decode_gather_dev is then rq_cuda_attn_decode_dev whose merge kernel stores this rank's heads of every row straight
+ * into every rank's buffer over NVLink (plain peer stores: no multicast, no library collective), followed by a one-warp kernel that
+ * tells every rank "my part of this step is in place" and waits for theirs with a limit of two seconds (a rank that never arrives
+ * ends the wait with RQ_CUDA_ERR_STATE at the next rq_cuda_sync; the context stays usable).  *out_full: this rank's buffer of the
+ * step, device memory [rows][n_heads][head_dim] with all heads, valid until the call after next; all ranks must make the same
+ * sequence of calls.  rq_cuda_selftest_peer_wait runs the wait of a two-rank exchange whose other rank never arrives, with a
+ * limit of `limit_us` microseconds, on one GPU (code 97 in the status word). */
+int rq_cuda_peer_export(RqCuda *ctx, int rows, void *handle64);
+int rq_cuda_peer_import(RqCuda *ctx, int rank, int world, const void *handles);
+int rq_cuda_attn_decode_gather_dev(RqCuda *ctx, int layer, const float *q_dev, float **out_full);
+int rq_cuda_selftest_peer_wait(RqCuda *ctx, unsigned int limit_us);
 /* The quantised copy of the attention's outputs that the reference makes right before the `wo` matmul (quantize,
  * forward.c:803, at :2716-2719 / :3616), fused into the merge kernels: with xq_dev / xs_dev set, every attention call of the
  * context (decode and prefill) also writes int8 levels xq [rows][heads_local * head_dim] and one fp32 scale per `gs`

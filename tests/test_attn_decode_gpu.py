@@ -255,6 +255,31 @@ def test_expired_device_wait_is_reported_and_the_context_stays_usable():
     c.close()
 
 
+def test_peer_wait_runs_out_when_a_rank_never_arrives():
+    """The wait of the fused gather (rq_cuda_attn_decode_gather_dev) on one GPU: a two-rank exchange whose other rank does not
+    exist.  The one-warp kernel gives up after its limit and returns; the sync reports RQ_CUDA_ERR_STATE with code 97, and the
+    context computes the same bits afterwards."""
+    from gwenedeg_b200 import synth
+    import gwenedeg_b200 as g
+    c = make_ctx(n_attn=1, n_heads=4, n_kv_heads=2, head_dim=128)
+    s = c.new_seq(300, F16)
+    s.fill_synthetic(300, 3)
+    q = synth.normal(8, (1, 4, 128))
+    c.pass_begin([(s, 299, 1)])
+    before = c.attn_decode(0, q)
+    c.pass_end(commit=False)
+    c.check(c.L.rq_cuda_selftest_peer_wait(c.h, 2000))
+    with pytest.raises(g.RqCudaError) as ei:
+        c.sync()
+    assert ei.value.code == -4 and "code 97" in str(ei.value)
+    c.sync()  # the status word was cleared by the failed call
+    c.pass_begin([(s, 299, 1)])
+    after = c.attn_decode(0, q)
+    c.pass_end(commit=False)
+    assert bit_equal(before, after)
+    c.close()
+
+
 @pytest.mark.parametrize("kvt", [F16, Q8])
 def test_page_locked_result_buffer_is_written_in_place(kvt):
     """rq_cuda_attn_decode / _prefill store straight into a page-locked (mapped) host buffer and copy into an ordinary one:

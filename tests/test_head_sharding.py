@@ -46,9 +46,15 @@ for lo in range(0, n, 512):
     sh.ctx.pass_end()
 t = sh.ctx.new_seq(n, kvt)
 t.copy_from(s, n)
+# three decode calls through the fused gather (the merge kernel stores into both ranks' row buffers, used in turn), one through
+# NCCL's all-gather: each must equal the single-GPU rows
+outs = []
 sh.ctx.pass_begin([(s, n - 1, 1), (t, 700, 1)])
-out = sh.attn_decode(0, torch.from_numpy(q).cuda())
-torch.cuda.synchronize()
+for i, mode in enumerate(("peer", "peer", "nccl", "peer")):
+    o = sh.attn_decode(0, torch.from_numpy(q * np.float32(1 + i)).cuda(), gather=mode)
+    torch.cuda.synchronize()
+    outs.append(o.cpu().numpy().copy())
+sh.ctx.sync()
 sh.ctx.pass_end(commit=False)
 if rank == 0:
     full = g.Context(0, n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd)
@@ -58,10 +64,10 @@ if rank == 0:
         full.pass_begin([(a, lo, hi - lo)]); full.kv_store(0, k[lo:hi], v[lo:hi]); full.pass_end()
     b = full.new_seq(n, kvt); b.copy_from(a, n)
     full.pass_begin([(a, n - 1, 1), (b, 700, 1)])
-    want = full.attn_decode(0, q)
+    for i, got in enumerate(outs):
+        want = full.attn_decode(0, q * np.float32(1 + i))
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (i, np.abs(got - want).max())
     full.pass_end(commit=False)
-    got = out.cpu().numpy()
-    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), np.abs(got - want).max()
     print("SHARDED_OK")
 dist.barrier()
 dist.destroy_process_group()
