@@ -54,6 +54,19 @@ def test_argument_checks_come_before_the_device():
         assert e.value.code == -1
 
 
+def test_peer_entry_points_refuse_a_missing_context():
+    """The fused-gather entry points check their arguments before anything else (no GPU needed to be told so)."""
+    import ctypes as C
+    import gwenedeg_b200 as g
+    L = g._lib.load()
+    buf = (C.c_ubyte * 128)()
+    out = C.c_void_p()
+    assert L.rq_cuda_peer_export(None, 4, C.cast(buf, C.c_void_p)) == -1
+    assert L.rq_cuda_peer_import(None, 0, 2, C.cast(buf, C.c_void_p)) == -1
+    assert L.rq_cuda_attn_decode_gather_dev(None, 0, C.cast(buf, C.c_void_p), C.byref(out)) == -1
+    assert L.rq_cuda_selftest_peer_wait(None, 100) == -1
+
+
 def test_reference_arm_of_the_benchmark_does_not_load_the_cuda_library():
     """bench.py --impl reference times the CPU code only: nothing on that path may import the package (whose import
     maps librq_cuda.so into the process)."""
