@@ -92,6 +92,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// the same poll, but the thread may be suspended by the hardware for up to `hint_ns` while the phase is incomplete (it is
+// woken when the phase completes): a waiting warp then issues a poll every `hint_ns` instead of every few cycles
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 // Wait for a phase of the barrier with a time limit (0.2 s, far beyond any healthy copy or MMA): on expiry the kernel
 // records `code` in *err and the caller carries on to its exit (results are then invalid and the host reports
 // RQ_CUDA_ERR_STATE).  Once any thread has recorded an expiry the other waits give up quickly as well.
@@ -114,6 +127,18 @@ __device__ __forceinline__ bool mbar_wait_bounded_ns(uint64_t *bar, uint32_t par
 }
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *err, int code) {
     return mbar_wait_bounded_ns(bar, parity, err, code, 200000000ull);
+}
+// mbar_wait_bounded for waits that normally last a microsecond or more (a copy, a batch of MMAs): polls through
+// mbar_try_wait_hint, so that the waiting warp leaves the issue slots to the others; the same 0.2 s limit, counted in polls of at
+// most 2 us each, and the same behaviour on expiry
+__device__ __forceinline__ bool mbar_wait_bounded_quiet(uint64_t *bar, uint32_t parity, int *err, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    for (int it = 0; it < 100000; it++) {
+        if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+        if ((it & 63) == 63 && *reinterpret_cast<volatile int *>(err) != 0) return false;
+    }
+    atomicExch(err, code);
+    return false;
 }
 // order earlier generic-proxy accesses of shared memory before later async-proxy (bulk copy) writes to it
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
