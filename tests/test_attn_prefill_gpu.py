@@ -194,3 +194,29 @@ def test_quantised_cache_prompt_chunks_on_tensor_cores(checker, kvt, name, n_hea
         print(name, "quantised prompt pass errors", errors(got, exact))
     c.set_exact(False)
     c.close()
+
+
+@pytest.mark.parametrize("kvt,name", [(3, "q8"), (9, "q4k4")])
+def test_quantised_cache_prompt_chunk_at_benchmark_shape(kvt, name):
+    """The 0.6B-model prompt chunk of the benchmark on a quantised cache: 512 new rows over a 3,584-position prefix, 16 query / 8
+    KV heads x 128; every row of the tensor-core pass (f16 expansion of the tiles) against the row-by-row pass through the
+    bit-exact decode kernels."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    n_heads, n_kv, hd = 16, 8, 128
+    c = g.Context(0, n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, max_rows=512)
+    s = c.new_seq(4096, kvt)
+    s.fill_synthetic(4096, 91)
+    q = synth.normal(92, (512, n_heads, hd))
+    c.set_exact(False)
+    c.pass_begin([(s, 3584, 512)])
+    got = c.attn_prefill(0, q)
+    c.pass_end(commit=False)
+    c.set_exact(True)
+    c.pass_begin([(s, 3584, 512)])
+    exact = c.attn_prefill(0, q)
+    c.pass_end(commit=False)
+    assert_close(got, exact, f"{name} prompt chunk, all 512 rows")
+    print(name, "benchmark-shape quantised prompt chunk errors", errors(got, exact))
+    c.set_exact(False)
+    c.close()
