@@ -507,6 +507,14 @@ int rq_cuda_reserve(RqCuda *c, int rows, long long positions_total, int max_ctx)
         if ((rc = grow(c, (void **)&c->d_out, &c->out_bytes, ob))) return rc;
         if ((rc = grow(c, (void **)&c->d_k, &c->k_bytes, kb))) return rc;
         if ((rc = grow(c, (void **)&c->d_v, &c->v_bytes, kb))) return rc;
+        if (c->m.head_dim == 128) {
+            // quantised caches on the tensor cores: the query planes and the block -> row table of a decode pass; the rotated
+            // query rows of a prompt pass (its f16 expansion of the cache tiles is sized by the pass itself: up to 8 KB per
+            // 16 cached positions and KV head of the segments)
+            if ((rc = grow(c, (void **)&c->d_tcq, &c->tcq_bytes, (size_t)rows * c->n_kv * TCD_QT_BYTES))) return rc;
+            if ((rc = grow(c, (void **)&c->d_blk2row, &c->blk2row_bytes, blocks * sizeof(int)))) return rc;
+            if ((rc = grow(c, (void **)&c->d_qrot, &c->qrot_bytes, (size_t)rows * c->n_heads * 128 * 4))) return rc;
+        }
     }
     if (c->m.n_lin > 0) {
         const RqCudaModel &m = c->m;
