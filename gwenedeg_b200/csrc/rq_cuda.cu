@@ -127,6 +127,17 @@ struct RqCuda {
     DqSeg *d_dqseg = nullptr; size_t dqseg_bytes = 0;
     std::vector<DqSeg> h_dqseg;
     int dq_max_tiles = 0;
+    // a quantised prompt pass is routed by segment: segments of 16 rows or more through the expansion + the tensor-core prefill
+    // kernel (runs of their rows: pf_runs_p), the others (decode rows riding in the same pass) through the decode kernels, run by
+    // run of adjacent rows, over a copy of their PassRow entries whose block numbers count from the run's first row
+    struct RowRun { int row0, nrows, blocks, table0; size_t part0; };
+    std::vector<RowRun> pf_runs_p, pf_runs_d;
+    PassRow *d_rows_d = nullptr; size_t rows_d_bytes = 0;
+    std::vector<PassRow> h_rows_d;
+    size_t pf_part_d = 0;  // floats of partial records the decode runs need, behind the prefill kernel's
+    // the rows a decode launch covers when it is not the whole pass (span_rows non-null)
+    const PassRow *span_rows = nullptr;
+    int span_nrows = 0, span_blocks = 0;
     int tc_ready;  // the open pass's tensor maps for the tensor-core decode kernel are on the device (1), or it does not qualify (-1)
     // DeltaNet weights of the steps around the recurrence (rq_cuda_dn_set_weights): per linear layer conv taps, A, dt
     // bias, norm weight
@@ -383,7 +394,7 @@ void rq_cuda_free(RqCuda *c) {
     if (c->peer_own) cudaFree(c->peer_own);
     if (c->d_dnw) cudaFree(c->d_dnw);
     if (c->h_maps8) cudaFreeHost(c->h_maps8);
-    void *dev[] = {c->d_dq, c->d_qrot, c->d_dqseg, c->d_maps8, c->d_tcq, c->d_blk2row, c->d_chunks, c->d_ck, c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
+    void *dev[] = {c->d_rows_d, c->d_dq, c->d_qrot, c->d_dqseg, c->d_maps8, c->d_tcq, c->d_blk2row, c->d_chunks, c->d_ck, c->d_rows, c->d_dseg, c->d_part, c->d_q, c->d_out, c->d_k, c->d_v, c->d_dn, c->d_err, c->d_maps, c->d_work, c->d_dnwork};
     if (c->h_maps) cudaFreeHost(c->h_maps);
     for (void *p : dev)
         if (p) cudaFree(p);
@@ -985,9 +996,9 @@ static int launch_decode(RqCuda *c, int layer, const float *q, float *out) {
 static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, float *part, bool may_allocate) {
     const int hd = c->m.head_dim;
     AttnPartArgs a;
-    a.rows = c->d_rows;
-    a.nrows = c->nrows;
-    a.total_blocks = c->total_blocks;
+    a.rows = c->span_rows ? c->span_rows : c->d_rows;
+    a.nrows = c->span_rows ? c->span_nrows : c->nrows;
+    a.total_blocks = c->span_rows ? c->span_blocks : c->total_blocks;
     a.layer = layer;
     a.n_kv = c->n_kv;
     a.G = c->G;
@@ -1018,6 +1029,7 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
         // quantised caches at head_dim 128: the cached levels as int8 MMA operands (results inside the tolerance); the same partial
         // records, merged by the same kernel
         int rcg;
+        // (sized for the whole pass also when the launch covers a run of its rows: the scratch is not regrown between runs)
         if ((rcg = grow(c, (void **)&c->d_tcq, &c->tcq_bytes, (size_t)c->nrows * c->n_kv * TCD_QT_BYTES))) return rcg;
         if ((rcg = grow(c, (void **)&c->d_blk2row, &c->blk2row_bytes, (size_t)c->total_blocks * sizeof(int)))) return rcg;
         AttnPartTcArgs t;
@@ -1042,7 +1054,8 @@ static int launch_decode_with(RqCuda *c, int layer, const float *q, float *out, 
 
 static int launch_combine(RqCuda *c, const float *q, float *out, const float *part, int split_len, int fixed_stride) {
     const int hd = c->m.head_dim;
-    dim3 grid(c->nrows, c->n_heads);
+    const PassRow *rows = c->span_rows ? c->span_rows : c->d_rows;
+    dim3 grid(c->span_rows ? c->span_nrows : c->nrows, c->n_heads);
     const bool quant = kv_quant(c->pass_kvt);
     cudaError_t ce = cudaSuccess;
     PeerOut po;
@@ -1052,8 +1065,8 @@ static int launch_combine(RqCuda *c, const float *q, float *out, const float *pa
         for (int p = 0; p < c->peer_world; p++) po.out[p] = (float *)(c->peer_base[p] + 1024 + (size_t)(c->peer_step & 1) * c->peer_rows_bytes);
     }
 #define COMBINE(HD_)                                                                                                          \
-    if (quant) ce = launch_pdl(attn_combine_kernel<HD_, true>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd, c->wo_quant, po); \
-    else ce = launch_pdl(attn_combine_kernel<HD_, false>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, c->d_rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd, c->wo_quant, po);
+    if (quant) ce = launch_pdl(attn_combine_kernel<HD_, true>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd, c->wo_quant, po); \
+    else ce = launch_pdl(attn_combine_kernel<HD_, false>, grid, dim3(COMBINE_NG * HD_), 0, c->stream, rows, c->n_heads, part, q, c->qh, c->m.gated, out, split_len, fixed_stride, (const int *)c->d_err, c->err_fwd, c->wo_quant, po);
     switch (hd) {
         case 64: COMBINE(64) break;
         case 128: COMBINE(128) break;
@@ -1198,10 +1211,13 @@ static int prefill_tables(RqCuda *c) {
         // quantised caches at head_dim 128: the tensor-core kernel over f16 copies of the layer's tiles, where the pass is a prompt
         // pass (on average 16 rows or more per segment: below that the copies cost more than they save) and the copies fit 8 GB;
         // not where the host asked for exact results
-        if (c->m.head_dim != 128 || c->exact || c->nrows < 16 * nseg || !tm_encode()) return RQ_CUDA_OK;
+        constexpr int PROMPT_ROWS = 16;  // a segment of fewer rows is not worth expanding its cache for
+        if (c->m.head_dim != 128 || c->exact || !tm_encode()) return RQ_CUDA_OK;
         size_t tiles = 0;
-        for (auto &g : c->segs) tiles += (size_t)((g.pos0 + g.n + ATT_P - 1) / ATT_P) * ATT_PT * c->n_kv;
-        if (tiles * 8192 > ((size_t)8 << 30)) return RQ_CUDA_OK;
+        int n_prompt = 0;
+        for (auto &g : c->segs)
+            if (g.n >= PROMPT_ROWS) tiles += (size_t)((g.pos0 + g.n + ATT_P - 1) / ATT_P) * ATT_PT * c->n_kv, n_prompt++;
+        if (!n_prompt || tiles * 8192 > ((size_t)8 << 30)) return RQ_CUDA_OK;
         int rcq = grow(c, (void **)&c->d_dq, &c->dq_bytes, tiles * 8192);
         if (rcq) return rcq;
         if ((rcq = grow(c, (void **)&c->d_dqseg, &c->dqseg_bytes, sizeof(DqSeg) * nseg))) return rcq;
@@ -1211,9 +1227,43 @@ static int prefill_tables(RqCuda *c) {
         uint8_t *at = c->d_dq;
         TmEncodeFn enc = tm_encode();
         cuuint32_t es[2] = {1, 1};
+        // the runs of rows of each kind, and the decode runs' own row table
+        c->pf_runs_p.clear(), c->pf_runs_d.clear(), c->h_rows_d.clear();
+        c->pf_part_d = 0;
+        {
+            int row = 0;
+            for (int i = 0; i < nseg; i++) {
+                const RqCudaSegment &g = c->segs[i];
+                const bool prompt = g.n >= PROMPT_ROWS;
+                auto &runs = prompt ? c->pf_runs_p : c->pf_runs_d;
+                const bool prev_same = i > 0 && (c->segs[i - 1].n >= PROMPT_ROWS) == prompt;
+                if (!prev_same) runs.push_back(RqCuda::RowRun{row, 0, 0, (int)c->h_rows_d.size(), 0});
+                RqCuda::RowRun &run = runs.back();
+                if (!prompt) {
+                    for (int j = 0; j < g.n; j++) {
+                        PassRow pr = c->h_rows[row + j];
+                        pr.blk0 = run.blocks;
+                        run.blocks += (pr.np + ATT_P - 1) / ATT_P;
+                        c->h_rows_d.push_back(pr);
+                    }
+                }
+                run.nrows += g.n;
+                row += g.n;
+            }
+            for (auto &run : c->pf_runs_d) {
+                run.part0 = c->pf_part_d;
+                c->pf_part_d += (size_t)run.blocks * c->n_heads * RQ_PSTRIDE(128);
+            }
+            if (!c->h_rows_d.empty()) {
+                if ((rcq = grow(c, (void **)&c->d_rows_d, &c->rows_d_bytes, sizeof(PassRow) * c->h_rows_d.size()))) return rcq;
+                CU(c, cudaMemcpyAsync(c->d_rows_d, c->h_rows_d.data(), sizeof(PassRow) * c->h_rows_d.size(), cudaMemcpyHostToDevice, c->stream));
+            }
+        }
         for (int i = 0; i < nseg; i++) {
             const RqCudaSegment &g = c->segs[i];
             DqSeg &d = c->h_dqseg[i];
+            memset(&d, 0, sizeof d);
+            if (g.n < PROMPT_ROWS) continue;  // (tiles 0: the expansion kernel's CTAs of this segment return at once)
             d.k = g.seq->k, d.v = g.seq->v, d.lk = g.seq->lk, d.lv = g.seq->lv;
             d.len = g.pos0 + g.n;
             d.tiles = (d.len + ATT_P - 1) / ATT_P * ATT_PT;
@@ -1246,10 +1296,11 @@ static int prefill_tables(RqCuda *c) {
             c->h_maps[2 * i] = g.seq->tm_k;
             c->h_maps[2 * i + 1] = g.seq->tm_v;
         }
-        for (int m0 = 0; m0 < g.n; m0 += rpt) {
-            int nr = std::min(rpt, g.n - m0), np_max = g.pos0 + m0 + nr;
-            for (int k = 0; k * PF_SPLIT < np_max; k++) c->h_work.push_back(PfWork{i, row + m0, nr, k});
-        }
+        if (!c->pf_quant || g.n >= 16)  // (a quantised pass: only its prompt segments)
+            for (int m0 = 0; m0 < g.n; m0 += rpt) {
+                int nr = std::min(rpt, g.n - m0), np_max = g.pos0 + m0 + nr;
+                for (int k = 0; k * PF_SPLIT < np_max; k++) c->h_work.push_back(PfWork{i, row + m0, nr, k});
+            }
         row += g.n;
     }
     c->pf_max_splits = (c->max_np + PF_SPLIT - 1) / PF_SPLIT;
@@ -1270,7 +1321,8 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     if (rc0) return rc0;
     if (c->pf_ready != 1) return launch_decode(c, layer, q, out);
     const int hd = c->m.head_dim;
-    size_t need = (size_t)c->nrows * c->pf_max_splits * c->n_heads * RQ_PSTRIDE(hd) * 4;
+    const size_t need_pf = (size_t)c->nrows * c->pf_max_splits * c->n_heads * RQ_PSTRIDE(hd) * 4;
+    const size_t need = need_pf + (c->pf_quant ? c->pf_part_d * 4 : 0);
     if (need > ((size_t)8 << 30))
         return fail(c, RQ_CUDA_ERR_ARG,
                     "attn_prefill: %d rows x %d splits of %d positions x %d heads need %zu MB of partial results; pass fewer rows at once",
@@ -1315,6 +1367,42 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     if (e != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "prefill attention launch: %s", cudaGetErrorString(e));
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n++ + 1], c->stream);
     c->launches++;
+    if (c->pf_quant) {
+        // the prompt segments' rows: merged (and un-rotated, gated) run by run; the other rows of the pass: the decode kernels over
+        // their own row table, run by run.  The status word goes to the host with the last launch only.
+        int *fwd = c->err_fwd;
+        const WoQuant wq = c->wo_quant;
+        const size_t nlast = c->pf_runs_p.size() + c->pf_runs_d.size();
+        size_t done = 0;
+        const size_t pst = RQ_PSTRIDE(128);
+        auto wq_at = [&](int row0) {
+            WoQuant w = wq;
+            if (w.xq) w.xq += (size_t)row0 * c->n_heads * 128, w.xs += (size_t)row0 * c->n_heads * 128 / w.gs;
+            return w;
+        };
+        for (const auto &run : c->pf_runs_p) {
+            const int nout = run.nrows * c->n_heads;
+            const dim3 cgrid((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), cblock(32 * COMBINE_ROWS_WARPS);
+            CU(c, launch_pdl(attn_combine_rows_kernel<128>, cgrid, cblock, 0, c->stream, (const PassRow *)(c->d_rows + run.row0), run.nrows, c->n_heads,
+                             (const float *)(c->d_part + (size_t)run.row0 * c->pf_max_splits * c->n_heads * pst),
+                             q + (size_t)run.row0 * c->n_heads * c->qh, c->qh, c->m.gated, out + (size_t)run.row0 * c->n_heads * 128, PF_SPLIT,
+                             c->pf_max_splits, (const int *)c->d_err, ++done == nlast ? fwd : (int *)nullptr, wq_at(run.row0), 1));
+            c->launches++;
+        }
+        int rcd = RQ_CUDA_OK;
+        for (const auto &run : c->pf_runs_d) {
+            c->span_rows = c->d_rows_d + run.table0, c->span_nrows = run.nrows, c->span_blocks = run.blocks;
+            c->err_fwd = ++done == nlast ? fwd : nullptr;
+            c->wo_quant = wq_at(run.row0);
+            rcd = launch_decode_with(c, layer, q + (size_t)run.row0 * c->n_heads * c->qh, out + (size_t)run.row0 * c->n_heads * 128,
+                                     c->d_part + need_pf / 4 + run.part0, true);
+            if (rcd) break;
+        }
+        c->span_rows = nullptr, c->span_nrows = c->span_blocks = 0;
+        c->err_fwd = fwd;
+        c->wo_quant = wq;
+        return rcd;
+    }
     // (a warp per output row merges its few partials, and applies the output gate)
     const int nout = c->nrows * c->n_heads;
     const dim3 cgrid((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), cblock(32 * COMBINE_ROWS_WARPS);

@@ -122,9 +122,10 @@ int rq_cuda_set_wo_quant(RqCuda *ctx, int gs, signed char *xq_dev, float *xs_dev
  *    accumulation: int8 levels as they are, 4-bit levels n as the int8 values 16 (n - 8) (one shift / mask / xor per word on their way
  *    to the operand's place); the query and the softmax weights are 16-bit fixed point split into two int8 planes, the bf16
  *    scales are applied in fp32 (~1e-4 relative to the reference's fp32 arithmetic);
- *  - rq_cuda_attn_prefill over q8 / q4 / q4k4 caches in prompt passes (on average 16 rows or more per segment): the layer's
- *    tiles are expanded once per call to f16 (the reference's dequantised values, block_f32 of forward.c:1770-1804, rounded once)
- *    and the f16 tensor-core kernel runs over them with rotated query rows (~3e-4 relative).
+ *  - rq_cuda_attn_prefill over q8 / q4 / q4k4 caches, segment by segment: for a segment of 16 rows or more (a prompt chunk) the
+ *    layer's tiles are expanded once per call to f16 (the reference's dequantised values, block_f32 of forward.c:1770-1804, rounded once)
+ *    and the f16 tensor-core kernel runs over them with rotated query rows (~3e-4 relative); the shorter segments of the same
+ *    pass (decode rows that ride along) take the decode kernels above.
  * Non-zero: the CUDA-core kernels that follow attention_part_q (forward.c:1770-1804) operation for operation and give the
  * reference's bits (decode at 0.55-0.75 of the speed, prompt passes row by row).  f16 caches, other head dims and
  * rq_cuda_attn_decode_noalloc always take the bit-exact kernels.  Either way a row's result is independent of the other

@@ -220,3 +220,51 @@ def test_quantised_cache_prompt_chunk_at_benchmark_shape(kvt, name):
     print(name, "benchmark-shape quantised prompt chunk errors", errors(got, exact))
     c.set_exact(False)
     c.close()
+
+
+@pytest.mark.parametrize("kvt,name", [(3, "q8"), (8, "q4")])
+def test_quantised_mixed_pass_routes_by_segment(checker, kvt, name):
+    """A pass that mixes prompt chunks with decode rows of other sequences over a quantised cache: the prompt segments go
+    through the f16 expansion and the tensor-core prefill kernel, the short segments through the tensor-core decode kernels, run by
+    run of adjacent rows; every row against the row-by-row bit-exact pass, and the quantised copy for the `wo` matmul equal to
+    quantize() of the rows that came out."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    n_heads, n_kv, hd, gs = 8, 2, 128, 64
+    c = g.Context(0, n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, max_rows=512)
+    lens = (150, 700, 2300, 301, 60, 900)
+    seqs = []
+    for i, n in enumerate(lens):
+        s = c.new_seq(n, kvt)
+        s.fill_synthetic(n, 50 + i)
+        seqs.append(s)
+    a, d, b, e, f, h = seqs
+    # decode row | prompt chunk | two decode-like segments | prompt chunk | decode row
+    segs = [(d, 699, 1), (a, 0, 150), (e, 300, 1), (f, 57, 3), (b, 1990, 210), (h, 899, 1)]
+    rows = sum(n for _, _, n in segs)
+    q = synth.normal(29, (rows, n_heads, hd))
+    xq_dev, xs_dev = c.malloc(rows * n_heads * hd), c.malloc(rows * n_heads * hd // gs * 4)
+    c.set_wo_quant(gs, xq_dev, xs_dev)
+    c.set_exact(False)
+    c.pass_begin(segs)
+    got = c.attn_prefill(0, q)
+    xq, xs = np.empty((rows, n_heads * hd), np.int8), np.empty((rows, n_heads * hd // gs), np.float32)
+    c.d2h(xq, xq_dev)
+    c.d2h(xs, xs_dev)
+    c.sync()
+    c.pass_end(commit=False)
+    c.set_wo_quant(0, None, None)
+    c.set_exact(True)
+    c.pass_begin(segs)
+    exact = c.attn_prefill(0, q)
+    c.pass_end(commit=False)
+    assert_close(got, exact, f"{name} mixed pass against the row-by-row path")
+    wq, ws = checker.quantize(got.reshape(rows, -1), gs)
+    assert np.array_equal(xq, wq) and bit_equal(xs.reshape(-1), ws)
+    # the decode rows took the decode kernels: the same bits as a decode call on those rows alone
+    c.set_exact(False)
+    c.pass_begin([(d, 699, 1)])
+    alone = c.attn_decode(0, q[0:1])
+    c.pass_end(commit=False)
+    assert bit_equal(alone, got[0:1])
+    c.close()
