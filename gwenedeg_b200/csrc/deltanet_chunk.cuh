@@ -61,9 +61,12 @@ cudaError_t launch_dn_chunk(const DnChunkArgs &a, cudaStream_t stream);
 namespace dnc {
 constexpr int AST = 68;  // floats per row of the fp32 64 x 64 matrices in shared memory
 // ---- prep kernel: shared memory (bytes from a 1024-byte aligned base); TMEM: K K^T | Q K^T (128 columns)
-constexpr int P_K16 = 0, P_Q16 = 16384, P_SLACK = 32768, P_AF = 49152, P_XF = P_AF + 64 * AST * 4, P_PF = P_XF + 64 * AST * 4,
-              P_LG = P_PF + 32 * AST * 4, P_BETA = P_LG + 256, P_BAR = P_BETA + 256, P_SLOT = P_BAR + 16, P_SMEM = P_SLOT + 16 + 1024;
-// (P_SLACK: 16 KB that the M = 128 products read past the 64 rows of Q16; never used otherwise)
+// (the fp32 matrices of the inverse take the place of the f16 operands, which are dead once the two products have completed:
+// four CTAs fit an SM, so that all chunks of a 2,048-row pass over 16 heads are resident at once)
+constexpr int P_K16 = 0, P_Q16 = 16384, P_SLACK = 32768, P_AF = 0, P_XF = P_AF + 64 * AST * 4, P_PF = P_XF + 64 * AST * 4,
+              P_LG = 49152, P_BETA = P_LG + 256, P_BAR = P_BETA + 256, P_SLOT = P_BAR + 16, P_SMEM = P_SLOT + 16 + 1024;
+static_assert(P_PF + 32 * AST * 4 <= P_LG, "the inverse's matrices fit the operands' place");
+// (P_SLACK: 16 KB that the M = 128 products read past the 64 rows of Q16)
 // ---- state kernel: two stages of operands (the record's first 64 KB, then the CTA's half of B V, then the gates)
 constexpr int ST_BV = 49152, ST_SC = ST_BV + DNC_BVH, ST_BYTES = 67584;
 constexpr int S_S16 = 2 * ST_BYTES, S_R16 = S_S16 + 16384, S_U16 = S_R16 + 8192, S_UK16 = S_U16 + 8192, S_BAR = S_UK16 + 8192,
@@ -83,6 +86,11 @@ __device__ __forceinline__ uint32_t dnc_pack(float a, float b) {
     return *reinterpret_cast<uint32_t *>(&h);
 }
 __device__ __forceinline__ uint2 dnc_pack4(float a, float b, float c, float d) { return make_uint2(dnc_pack(a, b), dnc_pack(c, d)); }
+__device__ __forceinline__ void dnc_tmem_ld8(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+}
 // 32 adjacent fp32 values r (columns 32 cb .. 32 cb + 31 of row `row`) -> f16 in a buffer of 128-byte rows
 __device__ __forceinline__ void dnc_store_row32(uint8_t *buf, int row, int cb, const float *r) {
 #pragma unroll
@@ -97,7 +105,7 @@ __device__ __forceinline__ void dnc_store_row32(uint8_t *buf, int row, int cb, c
 
 
 // grid: (chunk of the pass, value head)
-__global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg *__restrict__ segs, const DnChunk *__restrict__ chunks, int nk, int nv,
+__global__ void __launch_bounds__(DNC_THREADS, 4) dn_chunk_prep_kernel(const DnSeg *__restrict__ segs, const DnChunk *__restrict__ chunks, int nk, int nv,
                                                                   const float *__restrict__ rows, int lw, uint8_t *__restrict__ work, int *err) {
     using namespace dnc;
     constexpr int DK = 128, DV = 128;
@@ -129,12 +137,53 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
-    // gates -> inclusive log2 prefix sums (tokens past the end: eg 1, beta 0)
+    // gates (warp 0): the loads now, the inclusive log2 prefix sums after the warp's share of the rows, so that they wait under it
+    // (tokens past the end: eg 1, beta 0)
+    float ge0 = 1.0f, ge1 = 1.0f, gb0 = 0.0f, gb1 = 0.0f;
     if (warp == 0) {
         const float *r0 = rows + (size_t)(sg.row0 + c0 + lane) * lw, *r1 = r0 + (size_t)32 * lw;
-        float a0 = lane < cnt ? fmaxf(log2f(r0[oe]), -1.0e4f) : 0.0f, a1 = lane + 32 < cnt ? fmaxf(log2f(r1[oe]), -1.0e4f) : 0.0f;
-        s_beta[lane] = lane < cnt ? r0[ob] : 0.0f;
-        s_beta[lane + 32] = lane + 32 < cnt ? r1[ob] : 0.0f;
+        if (lane < cnt) ge0 = __ldg(r0 + oe), gb0 = __ldg(r0 + ob);
+        if (lane + 32 < cnt) ge1 = __ldg(r1 + oe), gb1 = __ldg(r1 + ob);
+    }
+    bool ok = true;
+    // rows -> f16: K and Q for the two products here and into the record (the state kernel applies the per-token
+    // scalings g_j, beta_j g_j, g_63 / g_j on the other side of its products); beta v in fp32.  Two rows of a warp's eight at a
+    // time: with four CTAs per SM a thread has 64 registers.  Nothing here waits for the gates or for the TMEM allocation.
+#pragma unroll 1
+    for (int i2 = 0; i2 < 8; i2 += 2) {
+        float4 qv[2], kv[2], vv[2];
+        float bt[2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int j = warp * 8 + i2 + i;
+            qv[i] = kv[i] = vv[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            bt[i] = 0.0f;
+            if (j < cnt) {
+                const float *r = rows + (size_t)(sg.row0 + c0 + j) * lw;
+                qv[i] = __ldg(reinterpret_cast<const float4 *>(r + oq) + lane);
+                kv[i] = __ldg(reinterpret_cast<const float4 *>(r + okk) + lane);
+                vv[i] = __ldg(reinterpret_cast<const float4 *>(r + ov) + lane);
+                bt[i] = __ldg(r + ob);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int j = warp * 8 + i2 + i, off = dnc_off4(j, lane);
+            const float bet = bt[i];
+            const uint2 k2 = dnc_pack4(kv[i].x, kv[i].y, kv[i].z, kv[i].w), q2 = dnc_pack4(qv[i].x, qv[i].y, qv[i].z, qv[i].w);
+            *reinterpret_cast<uint2 *>(sm + P_K16 + off) = k2;
+            *reinterpret_cast<uint2 *>(sm + P_Q16 + off) = q2;
+            *reinterpret_cast<uint2 *>(rec + DNC_K + off) = k2;
+            *reinterpret_cast<uint2 *>(rec + DNC_Q + off) = q2;
+            // beta v, fp32, per half of the dv columns: [half][token][64]
+            *reinterpret_cast<float4 *>(rec + DNC_BV + (lane >> 4) * DNC_BVH + (j * AST + 4 * (lane & 15)) * 4) =
+                make_float4(vv[i].x * bet, vv[i].y * bet, vv[i].z * bet, vv[i].w * bet);
+        }
+    }
+    if (warp == 0) {
+        float a0 = lane < cnt ? fmaxf(log2f(ge0), -1.0e4f) : 0.0f, a1 = lane + 32 < cnt ? fmaxf(log2f(ge1), -1.0e4f) : 0.0f;
+        s_beta[lane] = gb0;
+        s_beta[lane + 32] = gb1;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const float b0 = __shfl_up_sync(0xffffffffu, a0, o), b1 = __shfl_up_sync(0xffffffffu, a1, o);
@@ -145,44 +194,14 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
         s_lg[lane + 32] = a1;
         float *sc = reinterpret_cast<float *>(rec + DNC_SC);
         sc[lane] = a0, sc[lane + 32] = a1;
-        sc[64 + lane] = s_beta[lane], sc[96 + lane] = s_beta[lane + 32];
+        sc[64 + lane] = gb0, sc[96 + lane] = gb1;
     }
-    float4 qv[8], kv[8], vv[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int j = warp * 8 + i;
-        qv[i] = kv[i] = vv[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (j < cnt) {
-            const float *r = rows + (size_t)(sg.row0 + c0 + j) * lw;
-            qv[i] = __ldg(reinterpret_cast<const float4 *>(r + oq) + lane);
-            kv[i] = __ldg(reinterpret_cast<const float4 *>(r + okk) + lane);
-            vv[i] = __ldg(reinterpret_cast<const float4 *>(r + ov) + lane);
-        }
-    }
+    fence_proxy_async();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tbase = *tmem_slot;
     const uint32_t lane_addr = tbase + ((uint32_t)((warp & 3) * 32) << 16);
-    bool ok = true;
-    // rows -> f16: K and Q for the two products here and into the record (the state kernel applies the per-token
-    // scalings g_j, beta_j g_j, g_63 / g_j on the other side of its products)
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int j = warp * 8 + i, off = dnc_off4(j, lane);
-        const float bet = s_beta[j];
-        const uint2 k2 = dnc_pack4(kv[i].x, kv[i].y, kv[i].z, kv[i].w), q2 = dnc_pack4(qv[i].x, qv[i].y, qv[i].z, qv[i].w);
-        *reinterpret_cast<uint2 *>(sm + P_K16 + off) = k2;
-        *reinterpret_cast<uint2 *>(sm + P_Q16 + off) = q2;
-        *reinterpret_cast<uint2 *>(rec + DNC_K + off) = k2;
-        *reinterpret_cast<uint2 *>(rec + DNC_Q + off) = q2;
-        // beta v, fp32, per half of the dv columns: [half][token][64]
-        *reinterpret_cast<float4 *>(rec + DNC_BV + (lane >> 4) * DNC_BVH + (j * AST + 4 * (lane & 15)) * 4) =
-            make_float4(vv[i].x * bet, vv[i].y * bet, vv[i].z * bet, vv[i].w * bet);
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
     // K K^T and Q K^T (M 128, N 64, K 128)
     if (warp == 4 && (tc_fence_after(), elect_one())) {
         const uint32_t sbase = smem_u32(sm);
@@ -197,24 +216,31 @@ __global__ void __launch_bounds__(DNC_THREADS) dn_chunk_prep_kernel(const DnSeg 
     ok = mbar_wait_bounded(bar, 0, err, 31) && ok;
     tc_fence_after();
     // A (fp32, strictly lower) and M (f16, lower with the diagonal): row i, columns 32 cb .. + 31 per thread
+    // (every thread has seen the products complete: the fp32 matrices may take the operands' place)
     if ((warp & 3) < 2) {
-        uint32_t g[32], mq[32];
-        tmem_ld32(lane_addr + cb * 32, g);
-        tmem_ld32(lane_addr + 64 + cb * 32, mq);
-        tmem_wait_ld();
         const int i = trow;
         const float lgi = s_lg[i], bi = s_beta[i];
-        float mv[32], av[32];
+#pragma unroll 1
+        for (int x8 = 0; x8 < 4; x8++) {  // eight columns at a time
+            uint32_t g[8], mq[8];
+            dnc_tmem_ld8(lane_addr + cb * 32 + 8 * x8, g);
+            dnc_tmem_ld8(lane_addr + 64 + cb * 32 + 8 * x8, mq);
+            tmem_wait_ld();
+            float mv[8], av[8];
 #pragma unroll
-        for (int x = 0; x < 32; x++) {
-            const int j = 32 * cb + x;
-            const float ratio = j <= i ? ex2(lgi - s_lg[j]) : 0.0f;
-            av[x] = j < i ? bi * ratio * __uint_as_float(g[x]) : 0.0f;
-            mv[x] = j <= i ? ratio * __uint_as_float(mq[x]) : 0.0f;
+            for (int x = 0; x < 8; x++) {
+                const int j = 32 * cb + 8 * x8 + x;
+                const float ratio = j <= i ? ex2(lgi - s_lg[j]) : 0.0f;
+                av[x] = j < i ? bi * ratio * __uint_as_float(g[x]) : 0.0f;
+                mv[x] = j <= i ? ratio * __uint_as_float(mq[x]) : 0.0f;
+            }
+            *reinterpret_cast<float4 *>(s_a + i * AST + 32 * cb + 8 * x8) = make_float4(av[0], av[1], av[2], av[3]);
+            *reinterpret_cast<float4 *>(s_a + i * AST + 32 * cb + 8 * x8 + 4) = make_float4(av[4], av[5], av[6], av[7]);
+            const int ch = 4 * cb + x8;
+            uint4 w;
+            w.x = dnc_pack(mv[0], mv[1]), w.y = dnc_pack(mv[2], mv[3]), w.z = dnc_pack(mv[4], mv[5]), w.w = dnc_pack(mv[6], mv[7]);
+            *reinterpret_cast<uint4 *>(rec + DNC_M + i * 128 + ((ch ^ (i & 7)) << 4)) = w;
         }
-#pragma unroll
-        for (int x = 0; x < 32; x += 4) *reinterpret_cast<float4 *>(s_a + i * AST + 32 * cb + x) = make_float4(av[x], av[x + 1], av[x + 2], av[x + 3]);
-        dnc_store_row32(rec + DNC_M, i, cb, mv);
     }
     tc_fence_before();
     __syncthreads();
