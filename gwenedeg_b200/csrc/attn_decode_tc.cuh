@@ -202,7 +202,8 @@ __device__ __forceinline__ void mbar_drain(uint64_t *bar, uint32_t parity) {
 // operand's layout (shared -> shared) and its score MMAs issued while item i goes through its softmax, so a block's scores are
 // complete when its turn comes (two score buffers in TMEM).  Per item two CTA barriers:
 //   S2  block maxima of every warp; next item's K levels in place  -> weights (all), next item's score MMAs (one thread)
-//   S3  P^T planes in place                                        -> output MMAs (the same thread)
+//   S3  P^T planes in place                                        -> output MMAs (one thread)
+// (4-bit V: one more, S2b, between reading the V tiles as cached and writing the unpacked rows over them)
 // The single-thread duties are spread over the first lanes of warps 4 .. 7 (warps 0 .. 3 store the partial results, and thread 0
 // asks for the next V levels there, where it has waited for the output products anyway): (m, l), items + K and Q copies, output
 // MMAs, score MMAs.  (An MMA of these shapes keeps its issuing thread for ~150 cycles: the two batches of eight go to two warps.)
@@ -224,7 +225,7 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *pt = sm + C::PT;
-    float *red = reinterpret_cast<float *>(sm + C::MISC);               // [3][8][8]
+    float *red = reinterpret_cast<float *>(sm + C::MISC);               // two buffers of block reductions, used in turn
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm + C::MISC + 768);  // K tiles, V levels, Q^T buffer 0 / 1, scores, outputs
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + C::MISC + 768 + 64);
     TcdItem *items = reinterpret_cast<TcdItem *>(sm + C::MISC + 768 + 64 + 16);  // [4]: item i in items[i % 4]
