@@ -37,7 +37,8 @@ namespace rq {
 #ifndef RQ_PF_SPLIT
 #define RQ_PF_SPLIT 2048
 #endif
-constexpr int PF_SPLIT = RQ_PF_SPLIT;  // key positions per partial result (a multiple of the 128-position key block)
+constexpr int PF_SPLIT = RQ_PF_SPLIT;  // key positions per partial result where nothing better is known (a multiple of the 128-position key block)
+constexpr int PF_SPLIT_MIN = 1024;     // the shortest split the host chooses: bounds the partial records of a pass
 constexpr int PF_BN = 128;       // key positions per MMA block
 constexpr int PF_THREADS = 352;  // 2 streams x 4 softmax warps + the P V, S and TMA warps
 
@@ -45,7 +46,7 @@ struct PfWork {
     int seg;     // segment index (its tensor maps)
     int row0;    // first row of the tile (index in the pass)
     int nrows;   // rows of the tile (<= 128 / G)
-    int split;   // which split of PF_SPLIT key positions
+    int split;   // which split of split_len key positions
 };
 
 struct AttnPrefillArgs {
@@ -58,6 +59,7 @@ struct AttnPrefillArgs {
     int qh, n_heads;
     float scale;
     int max_splits;
+    int split_len;  // key positions per split (a multiple of 128; chosen per pass by the host)
     float *part;
     int *err;
 };
@@ -73,7 +75,7 @@ constexpr int PF_SMEM = 6 * 32768 + 1024 + 256 + 2048;  // Q | K x 3 stages | V 
 __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWork *__restrict__ work, const PassRow *__restrict__ rows,
                                                                   const CUtensorMap *__restrict__ maps, int layer, int n_kv, int G,
                                                                   const float *__restrict__ q, int qh, int n_heads, float scale,
-                                                                  int max_splits, float *__restrict__ part, int *err) {
+                                                                  int max_splits, int split_len, float *__restrict__ part, int *err) {
     // TMEM columns: S at 0 (128); P (f16 pairs) of key block j, stream h (the block's keys 64 h .. 64 h + 63) at
     // 128 + 64 (j % 2) + 32 h; O of stream h at 256 + 128 h
     constexpr int HD = 128, TM_COLS = 512, P_COL = 128, O_COL = 256;
@@ -96,11 +98,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
     const int g = blockIdx.y;
     const PassRow r0 = rows[w.row0];
     const int np_min = r0.np, np_max = r0.np + w.nrows - 1;  // rows of a tile are at consecutive positions
-    const int s0 = w.split * PF_SPLIT;                        // first key position of this split
-    const int s1 = min(s0 + PF_SPLIT, np_max);                // one past the last key position any row needs
+    const int s0 = w.split * split_len;                        // first key position of this split
+    const int s1 = min(s0 + split_len, np_max);                // one past the last key position any row needs
     const int nblk = (s1 - s0 + PF_BN - 1) / PF_BN;          // >= 1 by construction of the work list
     // (debug build) the split starts inside the tile's keys, the tile is one of at most 128 vectors, the KV head exists
-    RQ_CHECK(w.nrows >= 1 && w.nrows * G <= 128 && s0 >= 0 && s0 < np_max && nblk >= 1 && nblk <= PF_SPLIT / PF_BN && g < n_kv && w.split < max_splits, err, 43);
+    RQ_CHECK(w.nrows >= 1 && w.nrows * G <= 128 && s0 >= 0 && s0 < np_max && nblk >= 1 && nblk <= split_len / PF_BN && g < n_kv && w.split < max_splits, err, 43);
     const CUtensorMap *mk = maps + 2 * w.seg, *mv = mk + 1;
     // rows of the 2-D views: K rows are 32 bytes (one dim of a tile), V rows 256 bytes (one position)
     const long long k_layer_rows = (long long)(r0.lk / 32), v_layer_rows = (long long)(r0.lv / 256);
@@ -406,7 +408,7 @@ cudaError_t launch_attn_prefill(const AttnPrefillArgs &a, cudaStream_t stream) {
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     return launch_pdl(attn_prefill_kernel, dim3(a.n_work, a.n_kv), dim3(PF_THREADS), PF_SMEM, stream, a.work, a.rows, a.maps, a.layer, a.n_kv, a.G, a.q,
-                      a.qh, a.n_heads, a.scale, a.max_splits, a.part, a.err);
+                      a.qh, a.n_heads, a.scale, a.max_splits, a.split_len, a.part, a.err);
 }
 #endif  // RQ_ATTN_PREFILL_INSTANTIATE
 

@@ -36,7 +36,7 @@ constexpr int PF256_SMEM = PF256_BARS + 256 + 1024;  // Q | K x 3 half stages | 
 __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(const PfWork *__restrict__ work, const PassRow *__restrict__ rows,
                                                                             const CUtensorMap *__restrict__ maps, int layer, int n_kv, int G,
                                                                             const float *__restrict__ q, int qh, int n_heads, float scale,
-                                                                            int max_splits, float *__restrict__ part, int *err) {
+                                                                            int max_splits, int split_len, float *__restrict__ part, int *err) {
     constexpr int HD = 256, TM_COLS = 512, P_COL = 128, O_COL = 256;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -55,10 +55,10 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
     const int g = blockIdx.y;
     const PassRow r0 = rows[w.row0];
     const int np_min = r0.np, np_max = r0.np + w.nrows - 1;  // rows of a tile are at consecutive positions
-    const int s0 = w.split * PF_SPLIT;
-    const int s1 = min(s0 + PF_SPLIT, np_max);
+    const int s0 = w.split * split_len;
+    const int s1 = min(s0 + split_len, np_max);
     const int nblk = (s1 - s0 + PF_BN - 1) / PF_BN;  // >= 1 by construction of the work list
-    RQ_CHECK(w.nrows >= 1 && w.nrows * G <= 128 && s0 >= 0 && s0 < np_max && nblk >= 1 && nblk <= PF_SPLIT / PF_BN && g < n_kv && w.split < max_splits, err, 46);
+    RQ_CHECK(w.nrows >= 1 && w.nrows * G <= 128 && s0 >= 0 && s0 < np_max && nblk >= 1 && nblk <= split_len / PF_BN && g < n_kv && w.split < max_splits, err, 46);
     const int n_items = 2 * nblk;  // half stages of K (and of V) this CTA consumes
     const CUtensorMap *mk = maps + 2 * w.seg, *mv = mk + 1;
     // rows of the 2-D views: K rows are 32 bytes (one dim of a tile), V rows 512 bytes (one position)
@@ -363,7 +363,7 @@ cudaError_t launch_attn_prefill_hd256(const AttnPrefillArgs &a, cudaStream_t str
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     return launch_pdl(attn_prefill_hd256_kernel, dim3(a.n_work, a.n_kv), dim3(PF256_THREADS), PF256_SMEM, stream, a.work, a.rows, a.maps, a.layer, a.n_kv, a.G,
-                      a.q, a.qh, a.n_heads, a.scale, a.max_splits, a.part, a.err);
+                      a.q, a.qh, a.n_heads, a.scale, a.max_splits, a.split_len, a.part, a.err);
 }
 #endif  // RQ_ATTN_PREFILL_INSTANTIATE
 

@@ -12,6 +12,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <functional>
 #include <atomic>
 #include <new>
 #include <string>
@@ -112,6 +113,7 @@ struct RqCuda {
     PfWork *d_work; size_t work_bytes;
     std::vector<PfWork> h_work;
     int pf_ready, pf_max_splits;
+    int pf_split = PF_SPLIT;  // key positions per split of the open pass's prefill work items
     // head-sharded contexts: the gather of the output rows fused into the merge kernel (rq_cuda_peer_*): this rank's buffer
     // (1 KB of flags, then two full-width row buffers used in turn) and the peers' mappings of theirs
     uint8_t *peer_own = nullptr;
@@ -508,7 +510,7 @@ int rq_cuda_reserve(RqCuda *c, int rows, long long positions_total, int max_ctx)
     if (c->m.n_attn > 0) {
         const size_t rec = (size_t)c->n_heads * RQ_PSTRIDE(c->m.head_dim) * 4;
         const size_t blocks = (size_t)(positions_total / ATT_P) + rows;                       // decode: a record per 256-position block
-        const size_t splits = (size_t)rows * ((max_ctx + PF_SPLIT - 1) / PF_SPLIT);           // prefill: a record per (row, split)
+        const size_t splits = (size_t)rows * ((max_ctx + PF_SPLIT_MIN - 1) / PF_SPLIT_MIN);   // prefill: a record per (row, split)
         const size_t need = std::max(blocks, splits) * rec;
         if (need > ((size_t)8 << 30)) return fail(c, RQ_CUDA_ERR_ARG, "reserve: %zu MB of partial results", need >> 20);
         const size_t qb = (size_t)rows * c->n_heads * c->qh * 4, ob = (size_t)rows * c->n_heads * c->m.head_dim * 4;
@@ -1201,7 +1203,7 @@ int rq_cuda_attn_decode_noalloc(RqCuda *c, int layer, const float *q, float *out
 }
 
 static int prefill_tables(RqCuda *c) {
-    // once per pass: the segments' tensor maps and the work list (M tile of 128 / G rows x PF_SPLIT-position split) of the
+    // once per pass: the segments' tensor maps and the work list (M tile of 128 / G rows x split of the keys) of the
     // tensor-core prefill kernel; pf_ready 1: made, -1: the pass does not qualify (cache type, head_dim)
     if (c->pf_ready) return RQ_CUDA_OK;
     c->pf_ready = -1;
@@ -1288,6 +1290,45 @@ static int prefill_tables(RqCuda *c) {
             if (!g.seq->has_tm) return RQ_CUDA_OK;
     }
     const int rpt = 128 / c->G;
+    {
+        // The split length of the pass: the kernel's M tiles (128 / G rows of a segment x one KV head) are cut along the keys into
+        // items of `split` positions, one CTA each, so that short passes still fill the SMs; every item pays its own prologue and
+        // epilogue (loading and converting Q, storing a partial record per row: worth about six 128-key blocks of the main loop) and
+        // its rows one more partial to merge.  Chosen by scheduling the items of each candidate length onto the SMs as the hardware
+        // does (each to the SM that is free first) and taking the shortest finish.
+        std::vector<int> nblk;  // key blocks of every tile of the pass
+        for (int i = 0; i < nseg; i++) {
+            const RqCudaSegment &g = c->segs[i];
+            if (c->pf_quant && g.n < 16) continue;
+            for (int m0 = 0; m0 < g.n; m0 += rpt) nblk.push_back((g.pos0 + m0 + std::min(rpt, g.n - m0) + PF_BN - 1) / PF_BN);
+        }
+        const int cand[] = {1024, 1536, 2048, 3072, 4096, 6144, 8192, 16384, 32768, 65536};
+        const double overhead = 6.0;
+        const int sms = std::max(1, c->n_sm);
+        double best = 0.0;
+        c->pf_split = PF_SPLIT;
+        std::vector<double> sm_free(sms);
+        for (int L : cand) {
+            const int lb = L / PF_BN;
+            size_t items = 0;
+            for (int nb : nblk) items += (size_t)((nb + lb - 1) / lb) * c->n_kv;
+            if (items > (size_t)1 << 20) continue;
+            std::fill(sm_free.begin(), sm_free.end(), 0.0);
+            std::make_heap(sm_free.begin(), sm_free.end(), std::greater<double>());
+            auto put = [&](double cost) {
+                std::pop_heap(sm_free.begin(), sm_free.end(), std::greater<double>());
+                sm_free.back() += cost;
+                std::push_heap(sm_free.begin(), sm_free.end(), std::greater<double>());
+            };
+            // (launch order: tile by tile, its splits in order; the KV heads are the grid's second dimension: the same items n_kv times)
+            for (int h = 0; h < c->n_kv; h++)
+                for (int nb : nblk)
+                    for (int k = 0; k * lb < nb; k++) put(std::min(lb, nb - k * lb) + overhead);
+            const double finish = *std::max_element(sm_free.begin(), sm_free.end());
+            if (best == 0.0 || finish <= best) best = finish, c->pf_split = L;  // (ties go to the longer split: fewer partials to merge)
+            if (L >= c->max_np) break;  // (no longer split changes anything)
+        }
+    }
     c->h_work.clear();
     int row = 0;
     for (int i = 0; i < nseg; i++) {
@@ -1299,11 +1340,11 @@ static int prefill_tables(RqCuda *c) {
         if (!c->pf_quant || g.n >= 16)  // (a quantised pass: only its prompt segments)
             for (int m0 = 0; m0 < g.n; m0 += rpt) {
                 int nr = std::min(rpt, g.n - m0), np_max = g.pos0 + m0 + nr;
-                for (int k = 0; k * PF_SPLIT < np_max; k++) c->h_work.push_back(PfWork{i, row + m0, nr, k});
+                for (int k = 0; k * c->pf_split < np_max; k++) c->h_work.push_back(PfWork{i, row + m0, nr, k});
             }
         row += g.n;
     }
-    c->pf_max_splits = (c->max_np + PF_SPLIT - 1) / PF_SPLIT;
+    c->pf_max_splits = (c->max_np + c->pf_split - 1) / c->pf_split;
     size_t wb = c->h_work.size() * sizeof(PfWork);
     int rc = grow(c, (void **)&c->d_work, &c->work_bytes, wb);
     if (rc) return rc;
@@ -1326,7 +1367,7 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     if (need > ((size_t)8 << 30))
         return fail(c, RQ_CUDA_ERR_ARG,
                     "attn_prefill: %d rows x %d splits of %d positions x %d heads need %zu MB of partial results; pass fewer rows at once",
-                    c->nrows, c->pf_max_splits, PF_SPLIT, c->n_heads, need >> 20);
+                    c->nrows, c->pf_max_splits, c->pf_split, c->n_heads, need >> 20);
     int rc = grow(c, (void **)&c->d_part, &c->part_bytes, need);
     if (rc) return rc;
     AttnPrefillArgs a;
@@ -1342,6 +1383,7 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     a.n_heads = c->n_heads;
     a.scale = 1.0f / sqrtf((float)hd);
     a.max_splits = c->pf_max_splits;
+    a.split_len = c->pf_split;
     a.part = c->d_part;
     a.err = c->d_err;
     if (c->pf_quant) {
@@ -1385,7 +1427,7 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
             const dim3 cgrid((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), cblock(32 * COMBINE_ROWS_WARPS);
             CU(c, launch_pdl(attn_combine_rows_kernel<128>, cgrid, cblock, 0, c->stream, (const PassRow *)(c->d_rows + run.row0), run.nrows, c->n_heads,
                              (const float *)(c->d_part + (size_t)run.row0 * c->pf_max_splits * c->n_heads * pst),
-                             q + (size_t)run.row0 * c->n_heads * c->qh, c->qh, c->m.gated, out + (size_t)run.row0 * c->n_heads * 128, PF_SPLIT,
+                             q + (size_t)run.row0 * c->n_heads * c->qh, c->qh, c->m.gated, out + (size_t)run.row0 * c->n_heads * 128, c->pf_split,
                              c->pf_max_splits, (const int *)c->d_err, ++done == nlast ? fwd : (int *)nullptr, wq_at(run.row0), 1));
             c->launches++;
         }
@@ -1408,10 +1450,10 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     const dim3 cgrid((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), cblock(32 * COMBINE_ROWS_WARPS);
     if (hd == 128)
         CU(c, launch_pdl(attn_combine_rows_kernel<128>, cgrid, cblock, 0, c->stream, c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh,
-                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd, c->wo_quant, c->pf_quant ? 1 : 0));
+                         c->m.gated, out, c->pf_split, c->pf_max_splits, (const int *)c->d_err, c->err_fwd, c->wo_quant, c->pf_quant ? 1 : 0));
     else
         CU(c, launch_pdl(attn_combine_rows_kernel<256>, cgrid, cblock, 0, c->stream, c->d_rows, c->nrows, c->n_heads, (const float *)c->d_part, q, c->qh,
-                         c->m.gated, out, PF_SPLIT, c->pf_max_splits, (const int *)c->d_err, c->err_fwd, c->wo_quant, 0));
+                         c->m.gated, out, c->pf_split, c->pf_max_splits, (const int *)c->d_err, c->err_fwd, c->wo_quant, 0));
     c->launches++;
     return RQ_CUDA_OK;
 }
