@@ -1302,8 +1302,8 @@ static int prefill_tables(RqCuda *c) {
             if (c->pf_quant && g.n < 16) continue;
             for (int m0 = 0; m0 < g.n; m0 += rpt) nblk.push_back((g.pos0 + m0 + std::min(rpt, g.n - m0) + PF_BN - 1) / PF_BN);
         }
-        const int cand[] = {1024, 1536, 2048, 3072, 4096, 6144, 8192, 16384, 32768, 65536};
-        const double overhead = 6.0;
+        const int cand[] = {1024, 1280, 1536, 1792, 2048, 2560, 3072, 3584, 4096, 5120, 6144, 7168, 8192, 12288, 16384, 32768, 65536};
+        const double overhead = c->m.head_dim == 256 ? 4.0 : 6.0;  // (a block of head_dim 256 takes about twice as long)
         const int sms = std::max(1, c->n_sm);
         double best = 0.0;
         c->pf_split = PF_SPLIT;
