@@ -1304,7 +1304,8 @@ static int prefill_tables(RqCuda *c) {
         }
         const int cand[] = {1024, 1280, 1536, 1792, 2048, 2560, 3072, 3584, 4096, 5120, 6144, 7168, 8192, 12288, 16384, 32768, 65536};
         const double overhead = c->m.head_dim == 256 ? 4.0 : 6.0;  // (a block of head_dim 256 takes about twice as long)
-        const int sms = std::max(1, c->n_sm);
+        // (the KV heads are the grid's second dimension, the same items n_kv times: one head's items onto its share of the SMs)
+        const int sms = std::max(1, c->n_sm / std::max(1, c->n_kv));
         double best = 0.0;
         c->pf_split = PF_SPLIT;
         std::vector<double> sm_free(sms);
@@ -1320,10 +1321,9 @@ static int prefill_tables(RqCuda *c) {
                 sm_free.back() += cost;
                 std::push_heap(sm_free.begin(), sm_free.end(), std::greater<double>());
             };
-            // (launch order: tile by tile, its splits in order; the KV heads are the grid's second dimension: the same items n_kv times)
-            for (int h = 0; h < c->n_kv; h++)
-                for (int nb : nblk)
-                    for (int k = 0; k * lb < nb; k++) put(std::min(lb, nb - k * lb) + overhead);
+            // (launch order: tile by tile, its splits in order)
+            for (int nb : nblk)
+                for (int k = 0; k * lb < nb; k++) put(std::min(lb, nb - k * lb) + overhead);
             const double finish = *std::max_element(sm_free.begin(), sm_free.end());
             if (best == 0.0 || finish <= best) best = finish, c->pf_split = L;  // (ties go to the longer split: fewer partials to merge)
             if (L >= c->max_np) break;  // (no longer split changes anything)
