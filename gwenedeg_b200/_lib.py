@@ -49,6 +49,7 @@ PROTOTYPES = {
     "rq_cuda_selftest_peer_wait": (_i, [_vp, C.c_uint]),
     "rq_cuda_set_wo_quant": (_i, [_vp, _i, _vp, _vp]),
     "rq_cuda_set_exact": (_i, [_vp, _i]),
+    "rq_cuda_set_prefill_split": (_i, [_vp, _i]),
     "rq_cuda_set_stream": (_i, [_vp, _vp]),
     "rq_cuda_seq_new": (_i, [_vp, _i, _i, _pp]),
     "rq_cuda_seq_free": (None, [_vp]),

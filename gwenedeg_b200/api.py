@@ -102,6 +102,10 @@ class Context:
         """Quantised caches: the bit-exact CUDA-core kernels (True) or the tensor-core ones (False, the default)."""
         self.check(self.L.rq_cuda_set_exact(self.h, int(exact)))
 
+    def set_prefill_split(self, positions=0):
+        """Key positions per split of the tensor-core prefill kernels (0: chosen per pass)."""
+        self.check(self.L.rq_cuda_set_prefill_split(self.h, int(positions)))
+
     def set_stream(self, stream_ptr):
         self.check(self.L.rq_cuda_set_stream(self.h, C.c_void_p(stream_ptr)))
 

@@ -114,6 +114,7 @@ struct RqCuda {
     std::vector<PfWork> h_work;
     int pf_ready, pf_max_splits;
     int pf_split = PF_SPLIT;  // key positions per split of the open pass's prefill work items
+    int pf_split_fixed = 0;   // non-zero: the host fixed the split length (rq_cuda_set_prefill_split)
     // head-sharded contexts: the gather of the output rows fused into the merge kernel (rq_cuda_peer_*): this rank's buffer
     // (1 KB of flags, then two full-width row buffers used in turn) and the peers' mappings of theirs
     uint8_t *peer_own = nullptr;
@@ -534,6 +535,15 @@ int rq_cuda_reserve(RqCuda *c, int rows, long long positions_total, int max_ctx)
         const size_t lw = (size_t)2 * m.dn_nk * m.dn_dk + (size_t)2 * m.dn_nv * m.dn_dv + 2 * m.dn_nv;
         if ((rc = grow(c, (void **)&c->d_dn, &c->dn_bytes, (size_t)rows * (lw + (size_t)m.dn_nv * m.dn_dv) * 4))) return rc;
     }
+    return RQ_CUDA_OK;
+}
+
+int rq_cuda_set_prefill_split(RqCuda *c, int positions) {
+    if (!c) return RQ_CUDA_ERR_ARG;
+    if (positions != 0 && (positions < PF_SPLIT_MIN || positions % PF_BN || positions > (1 << 20)))
+        return fail(c, RQ_CUDA_ERR_ARG, "set_prefill_split: %d positions (0, or a multiple of %d from %d on)", positions, PF_BN, PF_SPLIT_MIN);
+    if (c->pass_open) return fail(c, RQ_CUDA_ERR_STATE, "set_prefill_split: a pass is open");
+    c->pf_split_fixed = positions;
     return RQ_CUDA_OK;
 }
 
@@ -1309,6 +1319,8 @@ static int prefill_tables(RqCuda *c) {
         double best = 0.0;
         c->pf_split = PF_SPLIT;
         std::vector<double> sm_free(sms);
+        if (c->pf_split_fixed) c->pf_split = c->pf_split_fixed;
+        else
         for (int L : cand) {
             const int lb = L / PF_BN;
             size_t items = 0;

@@ -131,6 +131,12 @@ int rq_cuda_set_wo_quant(RqCuda *ctx, int gs, signed char *xq_dev, float *xs_dev
  * rq_cuda_attn_decode_noalloc always take the bit-exact kernels.  Either way a row's result is independent of the other
  * rows of the pass. */
 int rq_cuda_set_exact(RqCuda *ctx, int exact);
+/* Prompt passes on the tensor-core prefill kernels cut each tile's keys into splits of equal length, one CTA each, and merge the
+ * splits' partial results (the reference splits lone long rows per 256-position block, prefill_plan forward.c:3273-3311; here the cut
+ * serves to fill the SMs).  By default the length is chosen per pass (by scheduling the items of each candidate length onto the
+ * device's SMs); a non-zero `positions` (a multiple of 128, at least 1024) fixes it, for tests and measurements.  Results are inside
+ * the kernel's tolerance for every length, not identical across lengths (the merge order changes). */
+int rq_cuda_set_prefill_split(RqCuda *ctx, int positions);
 /* run this context's work on a caller-owned stream (a cudaStream_t; NULL: back to the context's own, a non-blocking stream:
  * it is not ordered with the legacy default stream, whose handle is NULL as well).  The attention and DeltaNet kernels are
  * launched with programmatic stream serialization: each waits for the kernel before it in the stream before it touches

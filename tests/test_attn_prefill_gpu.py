@@ -268,3 +268,35 @@ def test_quantised_mixed_pass_routes_by_segment(checker, kvt, name):
     c.pass_end(commit=False)
     assert bit_equal(alone, got[0:1])
     c.close()
+
+
+@pytest.mark.parametrize("hd,n_heads,n_kv,gated", [(128, 8, 2, False), (256, 8, 2, True)])
+def test_prefill_split_lengths_agree(checker, hd, n_heads, n_kv, gated):
+    """The split length of a prompt pass is chosen per pass; every length gives the attention inside the tolerance: a chunk of
+    300 rows over a 5,000-position prefix with the length fixed to 1,024, 1,280, 2,048, 4,096 and 8,192 positions and left to
+    the library, each against the bit-exact split-K path; a few rows against the CPU code."""
+    import gwenedeg_b200 as g
+    from gwenedeg_b200 import synth
+    c = g.Context(0, n_attn=1, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, gated=gated, max_rows=512)
+    s = c.new_seq(5300, F16)
+    s.fill_synthetic(5300, 61)
+    q = synth.normal(62, (300, n_heads, hd * (2 if gated else 1)))
+    c.pass_begin([(s, 5000, 300)])
+    exact = c.attn_decode(0, q)
+    c.pass_end(commit=False)
+    outs = []
+    for L in (1024, 1280, 2048, 4096, 8192, 0):
+        c.set_prefill_split(L)
+        c.pass_begin([(s, 5000, 300)])
+        got = c.attn_prefill(0, q)
+        c.pass_end(commit=False)
+        assert_close(got, exact, f"head_dim {hd}, split {L}")
+        outs.append(got)
+    assert not bit_equal(outs[0], outs[4])  # (five splits against one: the lengths really differ)
+    rows = [0, 150, 299]
+    want = checker.attention(F16, s.read_kv(0, 0), s.read_kv(0, 1), n_kv, n_heads, hd, q[rows], np.array([5001 + r for r in rows], np.int32), gated=gated)
+    assert_close(outs[-1][rows], want, "chosen split against the CPU code")
+    with pytest.raises(g.RqCudaError):
+        c.set_prefill_split(1000)
+    c.set_prefill_split(0)
+    c.close()
