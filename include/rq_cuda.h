@@ -98,7 +98,7 @@ int rq_cuda_selftest_wait_expiry(RqCuda *ctx, unsigned int limit_us);
  * cudaIpcMemHandle_t out, for passes of at most `rows` rows), the host exchanges the handles by whatever means it has, and every
  * rank imports all of them in rank order (rq_cuda_peer_import: `handles` = world x 64 bytes; its own entry is ignored).
  * rq_cuda_attn_decode_gather_dev is then rq_cuda_attn_decode_dev whose merge kernel stores this rank's heads of every row straight
- * into every rank's buffer over NVLink (plain peer stores: no multicast, no library collective), followed by a one-warp kernel that
+ * into every rank's buffer over NVLink (plain peer stores, no library collective), followed by a one-warp kernel that
  * tells every rank "my part of this step is in place" and waits for theirs with a limit of two seconds (a rank that never arrives
  * ends the wait with RQ_CUDA_ERR_STATE at the next rq_cuda_sync; the context stays usable).  *out_full: this rank's buffer of the
  * step, device memory [rows][n_heads][head_dim] with all heads, valid until the call after next; all ranks must make the same
