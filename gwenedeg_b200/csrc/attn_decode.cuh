@@ -682,7 +682,7 @@ __global__ void __launch_bounds__(COMBINE_NG *HD) attn_combine_kernel(const Pass
 // partial per split of PF_SPLIT = 2,048 positions): one warp per (row, query head), lane L holds dims 4L .. 4L + 3 of every
 // 128-dim part of the row, so a launch is a few hundred CTAs instead of one per output row.  Arithmetic as
 // attn_combine_kernel: M = max of the m_b, c_b = exp_att(m_b - M), L and out as fma chains in partial order, out * (1 / L), gate.
-// With `unrot` (quantised caches, head_dim 128) the merged row is un-rotated before the gate as attn_combine_kernel does it.
+// With `unrot` (quantised caches) the merged row is un-rotated before the gate as attn_combine_kernel does it.
 constexpr int COMBINE_ROWS_WARPS = 8;
 // the 128-point butterflies (h = 1, 2, 4, ..., 64) of att_q_rot / att_o_unrot over a warp: lane L holds dims 4L .. 4L + 3
 __device__ __forceinline__ void fwht128_warp(float4 &x, int lane) {
@@ -695,6 +695,17 @@ __device__ __forceinline__ void fwht128_warp(float4 &x, int lane) {
         const float4 y = make_float4(__shfl_xor_sync(0xffffffffu, x.x, o), __shfl_xor_sync(0xffffffffu, x.y, o), __shfl_xor_sync(0xffffffffu, x.z, o),
                                      __shfl_xor_sync(0xffffffffu, x.w, o));
         x = (lane & o) ? make_float4(y.x - x.x, y.y - x.y, y.z - x.z, y.w - x.w) : make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+    }
+}
+// ... of 128 NP points (NP = 1 or 2): the 128-point butterflies on each part, then h = 128 between the parts
+template <int NP>
+__device__ __forceinline__ void fwht_warp(float4 *x, int lane) {
+#pragma unroll
+    for (int c = 0; c < NP; c++) fwht128_warp(x[c], lane);
+    if constexpr (NP == 2) {
+        const float4 a = x[0], b = x[1];
+        x[0] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+        x[1] = make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w);
     }
 }
 template <int HD>
@@ -743,12 +754,14 @@ __global__ void __launch_bounds__(32 * COMBINE_ROWS_WARPS) attn_combine_rows_ker
 #pragma unroll
         for (int c = 0; c < NP; c++) res[c] = make_float4(acc[c].x * inv, acc[c].y * inv, acc[c].z * inv, acc[c].w * inv);
     }
-    if constexpr (HD == 128) {
-        if (unrot) {  // att_o_unrot: butterflies, signs, scaling by 1 / head_dim
-            fwht128_warp(res[0], lane);
-            const float f = 1.0f / (float)HD;
-            res[0].x = (kvq_neg(4 * lane) ? -res[0].x : res[0].x) * f, res[0].y = (kvq_neg(4 * lane + 1) ? -res[0].y : res[0].y) * f;
-            res[0].z = (kvq_neg(4 * lane + 2) ? -res[0].z : res[0].z) * f, res[0].w = (kvq_neg(4 * lane + 3) ? -res[0].w : res[0].w) * f;
+    if (unrot) {  // att_o_unrot: butterflies, signs, scaling by 1 / head_dim
+        fwht_warp<NP>(res, lane);
+        const float f = 1.0f / (float)HD;
+#pragma unroll
+        for (int c = 0; c < NP; c++) {
+            const int i = 128 * c + 4 * lane;
+            res[c].x = (kvq_neg(i) ? -res[c].x : res[c].x) * f, res[c].y = (kvq_neg(i + 1) ? -res[c].y : res[c].y) * f;
+            res[c].z = (kvq_neg(i + 2) ? -res[c].z : res[c].z) * f, res[c].w = (kvq_neg(i + 3) ? -res[c].w : res[c].w) * f;
         }
     }
 #pragma unroll

@@ -14,7 +14,7 @@ namespace rq {
 struct DqSeg {
     const uint8_t *k, *v;         // the segment's sequence: K / V cache of layer 0
     unsigned long long lk, lv;    // bytes from one layer to the next
-    uint8_t *ko, *vo;             // the f16 tiles of the segment in the scratch: [block][KV head][16 tiles] of 16 positions x 128 dims
+    uint8_t *ko, *vo;             // the f16 tiles of the segment in the scratch: [block][KV head][16 tiles] of 16 positions x head_dim
     int len;                      // positions to expand: 0 .. len - 1 (the rest of the last block is zero-filled)
     int tiles;                    // tiles per KV head: 16 x blocks
 };
@@ -49,11 +49,11 @@ __device__ __forceinline__ void levels16_to_f16(uint4 w, int hi_nibble, const fl
     dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
 }
 
-// One CTA of 128 threads per (tile of 16 positions, KV head, segment).  K: thread = dim (its 16 positions: one 16-byte word of
-// levels in, one 32-byte row of the f16 tile out); V: thread = (position, 16 dims of one scale group).
-template <int KVT>
-__global__ void __launch_bounds__(128) kv_dequant_f16_kernel(const DqSeg *__restrict__ segs, int layer, int n_kv) {
-    constexpr int HD = 128, KF = kv_fmt(KVT, 0), VF = kv_fmt(KVT, 1);
+// One CTA of head_dim threads per (tile of 16 positions, KV head, segment).  K: thread = dim (its 16 positions: one 16-byte word
+// of levels in, one 32-byte row of the f16 tile out); V: thread = (position, 16 dims of one scale group).
+template <int KVT, int HD>
+__global__ void __launch_bounds__(HD) kv_dequant_f16_kernel(const DqSeg *__restrict__ segs, int layer, int n_kv) {
+    constexpr int KF = kv_fmt(KVT, 0), VF = kv_fmt(KVT, 1);
     constexpr int KTB = kv_tile_bytes(KVT, HD, 0), VTB = kv_tile_bytes(KVT, HD, 1);
     const DqSeg sg = segs[blockIdx.z];
     const int u = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;  // tile of the segment (of this head), head
@@ -78,9 +78,10 @@ __global__ void __launch_bounds__(128) kv_dequant_f16_kernel(const DqSeg *__rest
         }
         levels16_to_f16<KF>(w, tid & 1, d, false, reinterpret_cast<uint4 *>(ko + (size_t)tid * 32));
     }
-    {  // V: position tid / 8, dims 16 (tid % 8) .. + 15.  q8: [position][128 dims]; 4-bit: per position and group 16 bytes, byte l =
+    {  // V: position tid / (head_dim / 16), 16 dims.  q8: [position][head_dim]; 4-bit: per position and group 16 bytes, byte l =
        // dims 32 c + l (low nibble) and 32 c + 16 + l (high)
-        const int j = tid >> 3, i0 = (tid & 7) * 16, c = i0 >> 5;
+        constexpr int PCS = HD / 16;  // 16-dim pieces of a position
+        const int j = tid / PCS, i0 = (tid % PCS) * 16, c = i0 >> 5;
         const uint4 w = *reinterpret_cast<const uint4 *>(VF == KV_Q8 ? vt + (size_t)j * HD + i0 : vt + (size_t)j * (HD / 2) + c * 16);
         float d = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(vt + (VF == KV_Q8 ? 16 : 8) * HD + (j * (HD / 32) + c) * 2));
         if (j >= live) d = 0.0f;
@@ -89,19 +90,28 @@ __global__ void __launch_bounds__(128) kv_dequant_f16_kernel(const DqSeg *__rest
 }
 
 // The query rows rotated as att_q_rot does for the quantised cache types (signs, butterflies h = 1, 2, 4, ..., scaling by
-// 1 / head_dim), fp32: q [rows][n_heads][qh] -> qr [rows][n_heads][128].  One warp per (row, head): lane L holds dims 4L .. 4L + 3.
+// 1 / head_dim), fp32: q [rows][n_heads][qh] -> qr [rows][n_heads][head_dim].  One warp per (row, head): lane L holds dims
+// 4L .. 4L + 3 of every 128-dim part.
+template <int HD>
 __global__ void __launch_bounds__(256) q_rot_kernel(const float *__restrict__ q, int qh, int n_rows_heads, float *__restrict__ qr) {
-    constexpr int HD = 128;
+    constexpr int NP = HD / 128;
     const int wi = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     pdl_wait();
     pdl_launch_dependents();
     if (wi >= n_rows_heads) return;
-    float4 x = *reinterpret_cast<const float4 *>(q + (size_t)wi * qh + 4 * lane);
-    x.x = kvq_neg(4 * lane) ? -x.x : x.x, x.y = kvq_neg(4 * lane + 1) ? -x.y : x.y;
-    x.z = kvq_neg(4 * lane + 2) ? -x.z : x.z, x.w = kvq_neg(4 * lane + 3) ? -x.w : x.w;
-    fwht128_warp(x, lane);
+    float4 x[NP];
+#pragma unroll
+    for (int c = 0; c < NP; c++) {
+        x[c] = *reinterpret_cast<const float4 *>(q + (size_t)wi * qh + 128 * c + 4 * lane);
+        const int i = 128 * c + 4 * lane;
+        x[c].x = kvq_neg(i) ? -x[c].x : x[c].x, x[c].y = kvq_neg(i + 1) ? -x[c].y : x[c].y;
+        x[c].z = kvq_neg(i + 2) ? -x[c].z : x[c].z, x[c].w = kvq_neg(i + 3) ? -x[c].w : x[c].w;
+    }
+    fwht_warp<NP>(x, lane);
     const float f = 1.0f / (float)HD;
-    *reinterpret_cast<float4 *>(qr + (size_t)wi * HD + 4 * lane) = make_float4(x.x * f, x.y * f, x.z * f, x.w * f);
+#pragma unroll
+    for (int c = 0; c < NP; c++)
+        *reinterpret_cast<float4 *>(qr + (size_t)wi * HD + 128 * c + 4 * lane) = make_float4(x[c].x * f, x[c].y * f, x[c].z * f, x[c].w * f);
 }
 
 }  // namespace rq

@@ -1224,16 +1224,18 @@ static int prefill_tables(RqCuda *c) {
         // pass (on average 16 rows or more per segment: below that the copies cost more than they save) and the copies fit 8 GB;
         // not where the host asked for exact results
         constexpr int PROMPT_ROWS = 16;  // a segment of fewer rows is not worth expanding its cache for
-        if (c->m.head_dim != 128 || c->exact || !tm_encode()) return RQ_CUDA_OK;
+        const int hdq = c->m.head_dim;
+        if ((hdq != 128 && hdq != 256) || c->exact || !tm_encode()) return RQ_CUDA_OK;
+        const size_t tile_f16 = (size_t)hdq * 32;  // bytes of an f16 tile: 16 positions x head_dim
         size_t tiles = 0;
         int n_prompt = 0;
         for (auto &g : c->segs)
             if (g.n >= PROMPT_ROWS) tiles += (size_t)((g.pos0 + g.n + ATT_P - 1) / ATT_P) * ATT_PT * c->n_kv, n_prompt++;
-        if (!n_prompt || tiles * 8192 > ((size_t)8 << 30)) return RQ_CUDA_OK;
-        int rcq = grow(c, (void **)&c->d_dq, &c->dq_bytes, tiles * 8192);
+        if (!n_prompt || tiles * 2 * tile_f16 > ((size_t)8 << 30)) return RQ_CUDA_OK;
+        int rcq = grow(c, (void **)&c->d_dq, &c->dq_bytes, tiles * 2 * tile_f16);
         if (rcq) return rcq;
         if ((rcq = grow(c, (void **)&c->d_dqseg, &c->dqseg_bytes, sizeof(DqSeg) * nseg))) return rcq;
-        if ((rcq = grow(c, (void **)&c->d_qrot, &c->qrot_bytes, (size_t)c->nrows * c->n_heads * 128 * 4))) return rcq;
+        if ((rcq = grow(c, (void **)&c->d_qrot, &c->qrot_bytes, (size_t)c->nrows * c->n_heads * hdq * 4))) return rcq;
         c->h_dqseg.resize(nseg);
         c->dq_max_tiles = 0;
         uint8_t *at = c->d_dq;
@@ -1264,7 +1266,7 @@ static int prefill_tables(RqCuda *c) {
             }
             for (auto &run : c->pf_runs_d) {
                 run.part0 = c->pf_part_d;
-                c->pf_part_d += (size_t)run.blocks * c->n_heads * RQ_PSTRIDE(128);
+                c->pf_part_d += (size_t)run.blocks * c->n_heads * RQ_PSTRIDE(hdq);
             }
             if (!c->h_rows_d.empty()) {
                 if ((rcq = grow(c, (void **)&c->d_rows_d, &c->rows_d_bytes, sizeof(PassRow) * c->h_rows_d.size()))) return rcq;
@@ -1279,13 +1281,14 @@ static int prefill_tables(RqCuda *c) {
             d.k = g.seq->k, d.v = g.seq->v, d.lk = g.seq->lk, d.lv = g.seq->lv;
             d.len = g.pos0 + g.n;
             d.tiles = (d.len + ATT_P - 1) / ATT_P * ATT_PT;
-            const size_t bytes = (size_t)d.tiles * c->n_kv * 4096;  // (tiles of 16 positions x 128 dims x 2 bytes)
+            const size_t bytes = (size_t)d.tiles * c->n_kv * tile_f16;
             d.ko = at, d.vo = at + bytes;
             at += 2 * bytes;
             c->dq_max_tiles = std::max(c->dq_max_tiles, d.tiles);
             // the same views as an f16 cache of one layer (seq_make_maps)
-            cuuint64_t kd[2] = {16, (cuuint64_t)(bytes / 32)}, ks[1] = {32}, vd[2] = {128, (cuuint64_t)(bytes / 256)}, vs[1] = {256};
-            cuuint32_t kb[2] = {16, 256}, vb[2] = {64, 128};
+            cuuint64_t kd[2] = {16, (cuuint64_t)(bytes / 32)}, ks[1] = {32}, vd[2] = {(cuuint64_t)hdq, (cuuint64_t)(bytes / (2 * hdq))},
+                       vs[1] = {(cuuint64_t)(2 * hdq)};
+            cuuint32_t kb[2] = {16, hdq == 128 ? 256u : 128u}, vb[2] = {64, 128};
             if (enc(&c->h_maps[2 * i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d.ko, kd, ks, kb, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
                 enc(&c->h_maps[2 * i + 1], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d.vo, vd, vs, vb, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1402,18 +1405,23 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
         // the layer's tiles as f16 (layer 0 of the scratch's views), the query rows rotated; the merge below un-rotates
         const dim3 dgrid(c->dq_max_tiles, c->n_kv, (unsigned)c->segs.size());
         cudaError_t de;
+#define DEQUANT(KVT_)                                                                                                                              \
+    de = hd == 128 ? launch_pdl(kv_dequant_f16_kernel<KVT_, 128>, dgrid, dim3(128), 0, c->stream, (const DqSeg *)c->d_dqseg, layer, c->n_kv) \
+                   : launch_pdl(kv_dequant_f16_kernel<KVT_, 256>, dgrid, dim3(256), 0, c->stream, (const DqSeg *)c->d_dqseg, layer, c->n_kv)
         switch (c->pass_kvt) {
-            case KV_Q8: de = launch_pdl(kv_dequant_f16_kernel<KV_Q8>, dgrid, dim3(128), 0, c->stream, (const DqSeg *)c->d_dqseg, layer, c->n_kv); break;
-            case KV_Q4: de = launch_pdl(kv_dequant_f16_kernel<KV_Q4>, dgrid, dim3(128), 0, c->stream, (const DqSeg *)c->d_dqseg, layer, c->n_kv); break;
-            default: de = launch_pdl(kv_dequant_f16_kernel<KV_Q4K4>, dgrid, dim3(128), 0, c->stream, (const DqSeg *)c->d_dqseg, layer, c->n_kv); break;
+            case KV_Q8: DEQUANT(KV_Q8); break;
+            case KV_Q4: DEQUANT(KV_Q4); break;
+            default: DEQUANT(KV_Q4K4); break;
         }
+#undef DEQUANT
         if (de != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "cache expansion launch: %s", cudaGetErrorString(de));
         const int nrh = c->nrows * c->n_heads;
-        CU(c, launch_pdl(q_rot_kernel, dim3((nrh + 7) / 8), dim3(256), 0, c->stream, q, c->qh, nrh, c->d_qrot));
+        if (hd == 128) CU(c, launch_pdl(q_rot_kernel<128>, dim3((nrh + 7) / 8), dim3(256), 0, c->stream, q, c->qh, nrh, c->d_qrot));
+        else CU(c, launch_pdl(q_rot_kernel<256>, dim3((nrh + 7) / 8), dim3(256), 0, c->stream, q, c->qh, nrh, c->d_qrot));
         c->launches += 2;
         a.layer = 0;
         a.q = c->d_qrot;
-        a.qh = 128;
+        a.qh = hd;
     }
     const bool prof = c->prof_on && (size_t)(2 * c->prof_n + 2) <= c->prof_ev.size();
     if (prof) cudaEventRecord(c->prof_ev[2 * c->prof_n], c->stream);
@@ -1428,19 +1436,23 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
         const WoQuant wq = c->wo_quant;
         const size_t nlast = c->pf_runs_p.size() + c->pf_runs_d.size();
         size_t done = 0;
-        const size_t pst = RQ_PSTRIDE(128);
+        const size_t pst = RQ_PSTRIDE(hd);
         auto wq_at = [&](int row0) {
             WoQuant w = wq;
-            if (w.xq) w.xq += (size_t)row0 * c->n_heads * 128, w.xs += (size_t)row0 * c->n_heads * 128 / w.gs;
+            if (w.xq) w.xq += (size_t)row0 * c->n_heads * hd, w.xs += (size_t)row0 * c->n_heads * hd / w.gs;
             return w;
         };
         for (const auto &run : c->pf_runs_p) {
             const int nout = run.nrows * c->n_heads;
             const dim3 cgrid((nout + COMBINE_ROWS_WARPS - 1) / COMBINE_ROWS_WARPS), cblock(32 * COMBINE_ROWS_WARPS);
-            CU(c, launch_pdl(attn_combine_rows_kernel<128>, cgrid, cblock, 0, c->stream, (const PassRow *)(c->d_rows + run.row0), run.nrows, c->n_heads,
-                             (const float *)(c->d_part + (size_t)run.row0 * c->pf_max_splits * c->n_heads * pst),
-                             q + (size_t)run.row0 * c->n_heads * c->qh, c->qh, c->m.gated, out + (size_t)run.row0 * c->n_heads * 128, c->pf_split,
-                             c->pf_max_splits, (const int *)c->d_err, ++done == nlast ? fwd : (int *)nullptr, wq_at(run.row0), 1));
+#define ROWS_MERGE(HD_)                                                                                                                       \
+    CU(c, launch_pdl(attn_combine_rows_kernel<HD_>, cgrid, cblock, 0, c->stream, (const PassRow *)(c->d_rows + run.row0), run.nrows, c->n_heads,       \
+                     (const float *)(c->d_part + (size_t)run.row0 * c->pf_max_splits * c->n_heads * pst),                                              \
+                     q + (size_t)run.row0 * c->n_heads * c->qh, c->qh, c->m.gated, out + (size_t)run.row0 * c->n_heads * HD_, c->pf_split,             \
+                     c->pf_max_splits, (const int *)c->d_err, ++done == nlast ? fwd : (int *)nullptr, wq_at(run.row0), 1))
+            if (hd == 128) ROWS_MERGE(128);
+            else ROWS_MERGE(256);
+#undef ROWS_MERGE
             c->launches++;
         }
         int rcd = RQ_CUDA_OK;
@@ -1448,7 +1460,7 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
             c->span_rows = c->d_rows_d + run.table0, c->span_nrows = run.nrows, c->span_blocks = run.blocks;
             c->err_fwd = ++done == nlast ? fwd : nullptr;
             c->wo_quant = wq_at(run.row0);
-            rcd = launch_decode_with(c, layer, q + (size_t)run.row0 * c->n_heads * c->qh, out + (size_t)run.row0 * c->n_heads * 128,
+            rcd = launch_decode_with(c, layer, q + (size_t)run.row0 * c->n_heads * c->qh, out + (size_t)run.row0 * c->n_heads * hd,
                                      c->d_part + need_pf / 4 + run.part0, true);
             if (rcd) break;
         }

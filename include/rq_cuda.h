@@ -116,7 +116,7 @@ int rq_cuda_selftest_peer_wait(RqCuda *ctx, unsigned int limit_us);
  * 0.49999997, .))): the bits quantize() gives on the same fp32 rows.  Both NULL: off.  Device pointers the host owns, sized
  * for the largest pass. */
 int rq_cuda_set_wo_quant(RqCuda *ctx, int gs, signed char *xq_dev, float *xs_dev);
-/* Which kernels attend over quantised caches at head_dim 128.  0 (the default): tensor cores within the reference's acceptance
+/* Which kernels attend over quantised caches at head_dim 128 (prompt passes: 128 and 256).  0 (the default): tensor cores within the reference's acceptance
  * bar (2e-3 absolute / 1e-3 relative), not bit for bit:
  *  - rq_cuda_attn_decode over q8 / q4 / q4k4 caches: the cached levels go into tcgen05.mma (kind::i8) with exact int32
  *    accumulation: int8 levels as they are, 4-bit levels n as the int8 values 16 (n - 8) (one shift / mask / xor per word on their way

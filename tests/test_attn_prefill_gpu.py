@@ -147,15 +147,14 @@ def test_config2_shape_one_layer(checker):
 
 
 @pytest.mark.parametrize("kvt,name", [(3, "q8"), (8, "q4"), (9, "q4k4")])
-@pytest.mark.parametrize("n_heads,n_kv,gated", [(8, 2, False), (4, 4, True)])
-def test_quantised_cache_prompt_chunks_on_tensor_cores(checker, kvt, name, n_heads, n_kv, gated):
-    """Prompt passes over q8 / q4 / q4k4 caches at head_dim 128: the layer's tiles expanded to f16 once per call, the query rows
+@pytest.mark.parametrize("n_heads,n_kv,gated,hd", [(8, 2, False, 128), (4, 4, True, 128), (8, 2, True, 256)])
+def test_quantised_cache_prompt_chunks_on_tensor_cores(checker, kvt, name, n_heads, n_kv, gated, hd):
+    """Prompt passes over q8 / q4 / q4k4 caches at head_dim 128 and 256: the layer's tiles expanded to f16 once per call, the query rows
     rotated, the tensor-core kernel, the un-rotating merge.  Every row against the row-by-row path through the decode kernels
     (rq_cuda_set_exact: the CPU code's bits), a few rows against the CPU code itself; a chunk from position 0, a chunk over a
     prefix that crosses the 2,048-position split edge and ends inside a block, and a third segment."""
     import gwenedeg_b200 as g
     from gwenedeg_b200 import synth
-    hd = 128
     c = g.Context(0, n_attn=2, n_heads=n_heads, n_kv_heads=n_kv, head_dim=hd, gated=gated, max_rows=512)
     seqs = []
     for i, n in enumerate((150, 2300, 700)):
