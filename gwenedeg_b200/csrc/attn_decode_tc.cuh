@@ -463,9 +463,19 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
                 tmem_ld8(lane_addr + C::S_COL + (it & 1) * 8 * NS + (4 * h2 + c) * NS, r);
                 if constexpr (NVT == 8) tmem_ld8(lane_addr + C::S_COL + (it & 1) * 8 * NS + (4 * h2 + c) * NS + 8, r + 8);
                 tmem_wait_ld();
+                if constexpr (NVT % 2 == 0) {  // (packed fp32x2 multiply and multiply-add over vector pairs)
 #pragma unroll
-                for (int v = 0; v < NVT; v++)
-                    s[v] = fmaf(dk[c] * qd[v][c], (float)(((int)r[2 * v] << 8) + (int)r[2 * v + 1]), s[v]);
+                    for (int v = 0; v < NVT; v += 2) {
+                        const float2 sc = __fmul2_rn(make_float2(dk[c], dk[c]), make_float2(qd[v][c], qd[v + 1][c]));
+                        const float2 val = make_float2((float)(((int)r[2 * v] << 8) + (int)r[2 * v + 1]), (float)(((int)r[2 * v + 2] << 8) + (int)r[2 * v + 3]));
+                        const float2 acc = __ffma2_rn(sc, val, make_float2(s[v], s[v + 1]));
+                        s[v] = acc.x, s[v + 1] = acc.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int v = 0; v < NVT; v++)
+                        s[v] = fmaf(dk[c] * qd[v][c], (float)(((int)r[2 * v] << 8) + (int)r[2 * v + 1]), s[v]);
+                }
             }
         }
 #pragma unroll
@@ -530,22 +540,34 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
             uint8_t *pb = pt + h2 * (NO * 128) + (t & 15);
             const int ch = t >> 4;
 #pragma unroll
-            for (int c = 0; c < 4; c++)
+            for (int c = 0; c < 4; c++) {
+                float pw[NVT];  // the weights of the vectors times the key's V scale of the group
+                if constexpr (NVT % 2 == 0) {
+#pragma unroll
+                    for (int v = 0; v < NVT; v += 2) {
+                        const float2 x = __fmul2_rn(make_float2(e[v], e[v + 1]), make_float2(dvp[c], dvp[c]));
+                        pw[v] = x.x, pw[v + 1] = x.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int v = 0; v < NVT; v++) pw[v] = e[v] * dvp[c];
+                }
 #pragma unroll
                 for (int v = 0; v < NVT; v++) {
                     const int rw = (c * NVT + v) * 2;
                     if constexpr (VF == KV_Q8) {
                         // (e <= 1 and d_V <= ps: the product stays within a quarter of an ulp-sized step of PMAX, no clamp needed)
-                        const uint32_t u16 = (uint32_t)__float2int_rn(e[v] * dvp[c]);
+                        const uint32_t u16 = (uint32_t)__float2int_rn(pw[v]);
                         pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)(u16 >> 8);
                         pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)(u16 & 255u);
                     } else {
-                        const int p16 = __float2int_rn(e[v] * dvp[c]);
+                        const int p16 = __float2int_rn(pw[v]);
                         const int plo = ((p16 + 128) & 255) - 128;
                         pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)((p16 - plo) >> 8);
                         pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)plo;
                     }
                 }
+            }
         }
         if constexpr (VF != KV_Q8) {
             __syncthreads();  // S2b: the tiles as cached are in registers
