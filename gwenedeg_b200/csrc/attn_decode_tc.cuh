@@ -396,12 +396,22 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         tmem_ld8(lane_addr + C::O_COL + warp * 2 * NVT, r);
         if constexpr (NVT == 8) tmem_ld8(lane_addr + C::O_COL + warp * 2 * NVT + 8, r + 8);
         tmem_wait_ld();
+        float o[NVT];
+        if constexpr (NVT % 2 == 0) {
+#pragma unroll
+            for (int v = 0; v < NVT; v += 2) {
+                const float2 x = __fmul2_rn(__ffma2_rn(make_float2((float)(int)r[2 * v], (float)(int)r[2 * v + 2]), make_float2(256.0f, 256.0f),
+                                                       make_float2((float)(int)r[2 * v + 1], (float)(int)r[2 * v + 3])),
+                                            make_float2(back, back));
+                o[v] = x.x, o[v + 1] = x.y;
+            }
+        } else {
+#pragma unroll
+            for (int v = 0; v < NVT; v++) o[v] = fmaf((float)(int)r[2 * v], 256.0f, (float)(int)r[2 * v + 1]) * back;
+        }
 #pragma unroll
         for (int v = 0; v < NVT; v++)
-            if (v < G) {
-                const float o = fmaf((float)(int)r[2 * v], 256.0f, (float)(int)r[2 * v + 1]) * back;
-                part[pidx + (long long)v * RQ_PSTRIDE(HD) + tid] = ok ? o : 0.0f;  // (tid = TMEM lane = dim)
-            }
+            if (v < G) part[pidx + (long long)v * RQ_PSTRIDE(HD) + tid] = ok ? o[v] : 0.0f;  // (tid = TMEM lane = dim)
     };
 
     // ---- prologue: items 0 and 1 described and asked for, item 0's K in place and its score MMAs issued
@@ -525,13 +535,35 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
         dvp[2] = psc.z > 0.0f ? dv[2] * __fdividef(PMAX, psc.z) : 0.0f;
         dvp[3] = psc.w > 0.0f ? dv[3] * __fdividef(PMAX, psc.w) : 0.0f;
 #pragma unroll
+        for (int v = 0; v < NVT; v++) m[v] = ord_f32(rb[v]);
+        float ea[NVT], ef[NVT];  // the exponentials' arguments; the weights in fixed point
+        if constexpr (NVT % 2 == 0) {
+#pragma unroll
+            for (int v = 0; v < NVT; v += 2) {
+                const float2 x = __fmul2_rn(__fadd2_rn(make_float2(s[v], s[v + 1]), make_float2(-m[v], -m[v + 1])), make_float2(c2, c2));
+                ea[v] = x.x, ea[v + 1] = x.y;
+            }
+        } else {
+#pragma unroll
+            for (int v = 0; v < NVT; v++) ea[v] = (s[v] - m[v]) * c2;
+        }
+#pragma unroll
+        for (int v = 0; v < NVT; v++) e[v] = valid ? ex2(ea[v]) : 0.0f;
+        if constexpr (NVT % 2 == 0) {
+#pragma unroll
+            for (int v = 0; v < NVT; v += 2) {
+                const float2 x = __fmul2_rn(make_float2(e[v], e[v + 1]), make_float2(8388608.0f, 8388608.0f));
+                ef[v] = x.x, ef[v + 1] = x.y;
+            }
+        } else {
+#pragma unroll
+            for (int v = 0; v < NVT; v++) ef[v] = e[v] * 8388608.0f;
+        }
+#pragma unroll
         for (int v = 0; v < NVT; v++) {
-            const float mx = ord_f32(rb[v]);
-            m[v] = mx;
-            e[v] = valid ? ex2((s[v] - mx) * c2) : 0.0f;
             // l: the weights summed in 23-bit fixed point (integer sums: exact whatever their order, so that a block gives the same
             // bits every time; the block's largest weight is 1, 256 of them stay below 2^32; error below 2^-16 relative)
-            const unsigned sum = __reduce_add_sync(0xffffffffu, (unsigned)__float2int_rn(e[v] * 8388608.0f));
+            const unsigned sum = __reduce_add_sync(0xffffffffu, (unsigned)__float2int_rn(ef[v]));
             if (lane == v) atomicAdd(reinterpret_cast<unsigned *>(rb) + 16 + v, sum);
         }
         // P^T: the B operand of O^T += V^T P^T, per half [NO rows][128 keys] uint8, K-major with the 128-byte swizzle: rows
