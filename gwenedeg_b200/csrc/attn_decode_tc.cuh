@@ -593,10 +593,10 @@ __global__ void __launch_bounds__(TCD_THREADS, NVT <= 4 ? 2 : 1)
                         pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)(u16 >> 8);
                         pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)(u16 & 255u);
                     } else {
+                        // p16 = 256 hi + lo with lo = the low byte read as a signed value: hi = (p16 + 128) >> 8
                         const int p16 = __float2int_rn(pw[v]);
-                        const int plo = ((p16 + 128) & 255) - 128;
-                        pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)((p16 - plo) >> 8);
-                        pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)plo;
+                        pb[rw * 128 + ((ch ^ (rw & 7)) << 4)] = (uint8_t)((p16 + 128) >> 8);
+                        pb[(rw + 1) * 128 + ((ch ^ ((rw + 1) & 7)) << 4)] = (uint8_t)p16;
                     }
                 }
             }
