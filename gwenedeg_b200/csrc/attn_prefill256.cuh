@@ -6,30 +6,34 @@
 // :2291-2295, applied here by the merge kernel).
 //
 // What differs from the head_dim 128 kernel is the budget: Q alone is 64 KB of shared memory and O needs 256 TMEM
-// columns, so there is one softmax stream (4 warps: thread t owns query vector t and all 128 keys of a block) with one
-// O accumulator, and K and V are staged in halves of 128 dims (32 KB each: the shared-memory layouts, tensor-map boxes
-// and descriptors of the head_dim 128 kernel):
+// columns, so there is one O accumulator and one running maximum per query vector; the softmax of a block is still spread
+// over eight warps: threads t and 128 + t own query vector t (TMEM lane t) and 64 keys of the block each, exchange their
+// block maxima through shared memory (one barrier of the softmax warps per block) and so scale their halves of P alike.
+// K and V are staged in halves of 128 dims (32 KB each: the shared-memory layouts, tensor-map boxes and descriptors of
+// the head_dim 128 kernel):
 //   TMA warp   K (j) dims 0-127, K (j) dims 128-255 into a ring of 3 half stages, V (j) likewise into a ring of 2,
 //              refilled as their consumers' MMAs complete (one lane polls both rings).
 //   S warp     S = Q K^T: 2 x 8 tcgen05.mma (M 128, N 128, K 16), the first 8 against the first K half.
-//   softmax    scores -> registers (S is freed at once), p = 2^((s - m) c) with the lazily moved running max, row sum,
-//              P (f16) -> TMEM, double-buffered over key blocks.
+//   softmax    scores -> registers (S is freed at once), p = 2^((s - m) c) with the lazily moved running max, row sums per
+//              half, P (f16) -> TMEM, double-buffered over key blocks.
 //   P V warp   O[:, 0:128] += P V[:, 0:128], then O[:, 128:256] += P V[:, 128:256]: 2 x 8 MMAs with P from TMEM.
-// TMEM: S 128 columns, P 2 x 64, O 256.  Per 128-key block the tensor cores have 2,048 cycles of work against ~1.5 k of
-// softmax, so unlike the head_dim 128 kernel the loop is bound by the MMAs.
+// TMEM: S 128 columns, P 2 x 64, O 256.  Per 128-key block the tensor cores have 2,048 cycles of work; with four softmax
+// warps (one per scheduler, 128 keys per thread) the softmax took longer than that, with eight it does not.
 #pragma once
 #include "attn_prefill.cuh"
 
 namespace rq {
 
-constexpr int PF256_THREADS = 224;  // 4 softmax warps + the P V, S and TMA warps
+constexpr int PF256_THREADS = 352;  // 8 softmax warps + the P V, S and TMA warps
 // launches attn_prefill_hd256_kernel (grid: work items x KV heads) on `stream`
 cudaError_t launch_attn_prefill_hd256(const AttnPrefillArgs &a, cudaStream_t stream);
 
 #ifdef RQ_ATTN_PREFILL_INSTANTIATE
 
 constexpr int PF256_Q = 65536, PF256_HALF = 32768, PF256_BARS = PF256_Q + 5 * PF256_HALF;
-constexpr int PF256_SMEM = PF256_BARS + 256 + 1024;  // Q | K x 3 half stages | V x 2 half stages | barriers, TMEM slot | alignment slack
+constexpr int PF256_XCH = PF256_BARS + 256;  // the softmax threads' exchange: [2 halves][128 vectors] floats
+constexpr int PF256_SMEM = PF256_XCH + 1024 + 1024;  // Q | K x 3 half stages | V x 2 half stages | barriers, TMEM slot | exchange | alignment slack
+static_assert(PF256_SMEM <= 227 * 1024, "one CTA's shared memory");
 
 // maps: per segment the tensor maps of its sequence's K cache ({16 positions, rows of 32 bytes}, 32-byte swizzle, box 16 x
 // 128: the 128-dim half of one tile) and V cache ({256 dims, rows of 512 bytes}, 128-byte swizzle, box 64 x 128).
@@ -82,11 +86,11 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
     };
 
     if (tid == 0) {
-        for (int i = 0; i < 16; i++) mbar_init(bars + i, (i == 11 || i >= 14) ? 128 : 1);
+        for (int i = 0; i < 16; i++) mbar_init(bars + i, (i == 11 || i >= 14) ? 256 : 1);
         mbar_fence_init();
     }
     __syncthreads();
-    if (warp == 6) {
+    if (warp == 10) {
         if (lane == 0) {  // the first half stages start loading while the other warps convert Q
             load_k(0);
             load_k(1);
@@ -102,11 +106,12 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
         // head g G + t % G; 16-byte chunk c of 32: k-block c / 8, physical chunk (c % 8) ^ (t % 8).  Six warps take the
         // vectors round robin, eight at a time (16 row loads per lane in flight: lane L holds dims 4L .. 4L + 3 and
         // 128 + 4L .. 128 + 4L + 3)
-        for (int tb = warp; tb < 128; tb += 48) {
+        constexpr int QW = 10;  // warps that convert
+        for (int tb = warp; tb < 128; tb += 8 * QW) {
             float4 a[8][2];
 #pragma unroll
             for (int u = 0; u < 8; u++) {
-                const int t = tb + 6 * u, rl = t / G, x = t % G;
+                const int t = tb + QW * u, rl = t / G, x = t % G;
                 a[u][0] = a[u][1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 if (t < 128 && rl < w.nrows) {
                     const float4 *src = reinterpret_cast<const float4 *>(q + ((size_t)(w.row0 + rl) * n_heads + (size_t)g * G + x) * qh);
@@ -116,7 +121,7 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
             }
 #pragma unroll
             for (int u = 0; u < 8; u++) {
-                const int t = tb + 6 * u;
+                const int t = tb + QW * u;
                 if (t < 128) {
 #pragma unroll
                     for (int hh = 0; hh < 2; hh++) {
@@ -136,9 +141,9 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
     const uint32_t tbase = *tmem_slot;
     bool ok = true;
 
-    if (warp >= 4) {
+    if (warp >= 8) {
         constexpr uint32_t idesc = umma_idesc(128, 128);
-        if (warp == 4) {
+        if (warp == 8) {
             // O[:, 128 h : 128 h + 128] += P (j) V (j)[:, 128 h : 128 h + 128]: 8 k-steps of 16 keys each
             const uint64_t dv = umma_desc(smem_u32(sV), 16384, 1024, 2);
             for (int j = 0; j < nblk; j++) {
@@ -158,7 +163,7 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
                     __syncwarp();
                 }
             }
-        } else if (warp == 5) {
+        } else if (warp == 9) {
             // S (j) = Q K (j)^T over the two K halves, once every softmax thread has read S (j - 1)
             const uint64_t dq = umma_desc(smem_u32(sQ), 16, 1024, 2), dk = umma_desc(smem_u32(sK), 4096, 256, 6);
             for (int j = 0; j < nblk; j++) {
@@ -214,20 +219,22 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
             __syncwarp();
         }
     } else {
-        // ---- softmax: thread t owns query vector t (TMEM lane t) and every key of the block
-        const int t = tid, rl = t / G;
+        // ---- softmax: threads t and 128 + t own query vector t (TMEM lane t); of every key block thread (h, t) takes keys
+        // 64 h .. 64 h + 63.  The two share the vector's running maximum (exchanged per block) and its O accumulator
+        const int h = warp >> 2, t = tid & 127, rl = t / G;
         const int np = rl < w.nrows ? np_min + rl : 0;  // positions this vector attends (0: a padding vector)
-        const uint32_t lane_addr = tbase + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_addr = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+        float *xch = reinterpret_cast<float *>(sm + PF256_XCH);  // [2][128]
         const float c = scale * 1.44269504088896341f;
         float m_used = -INFINITY, l = 0.0f;
         bool s_seen = false;
         for (int j = 0; j < nblk; j++) {
-            const int t0 = s0 + j * PF_BN;
+            const int t0 = s0 + j * PF_BN + 64 * h;  // first key of this thread's half of the block
             if (!s_seen) ok = mbar_wait_bounded(bar_s, j & 1, err, 61) && ok;
             tc_fence_after();
-            uint32_t r[4][32], pk[64];
-#pragma unroll
-            for (int cc = 0; cc < 4; cc++) tmem_ld32(lane_addr + cc * 32, r[cc]);
+            uint32_t r[2][32], pk[32];
+            tmem_ld32(lane_addr + h * 64, r[0]);
+            tmem_ld32(lane_addr + h * 64 + 32, r[1]);
             // P V (j - 2) was the last reader of the P buffer this block will store to
             const bool o_seen = j < 2 || mbar_try_wait(bar_o + (j & 1), ((j - 2) >> 1) & 1);
             tmem_wait_ld();
@@ -236,7 +243,7 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
             const bool need_mask = s0 + (j + 1) * PF_BN > np_min;  // (uniform over the CTA: only the blocks on the diagonal)
             if (need_mask) {
 #pragma unroll
-                for (int cc = 0; cc < 4; cc++)
+                for (int cc = 0; cc < 2; cc++)
 #pragma unroll
                     for (int x = 0; x < 32; x++)
                         if (t0 + cc * 32 + x >= np) r[cc][x] = 0xff800000u;  // -inf
@@ -245,7 +252,7 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
             auto sweep = [&](float mc) {
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                for (int cc = 0; cc < 4; cc++) {
+                for (int cc = 0; cc < 2; cc++) {
 #pragma unroll
                     for (int x = 0; x < 32; x += 2) {
                         const int i = cc * 16 + (x >> 1);  // pair index
@@ -262,18 +269,23 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
             };
             // the running max moves only when the block's maximum exceeds it by more than 8 in the exponent (as in the
             // head_dim 128 kernel): the sweep runs with the running max as it stands and is repeated, after O and l were
-            // rescaled, in the rare block where some row's max has to move (the first block with a valid key always)
+            // rescaled, in the rare block where some row's max has to move (the first block with a valid key always).
+            // The block's maximum of a vector is the larger of its two threads' (same m_used in both, so the same decision)
             const bool fresh = __any_sync(0xffffffffu, m_used == -INFINITY);
             if (fresh) {
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int cc = 0; cc < 4; cc++)
+                for (int cc = 0; cc < 2; cc++)
 #pragma unroll
                     for (int x = 0; x < 32; x++) mx4[x & 3] = fmaxf(mx4[x & 3], __uint_as_float(r[cc][x]));
                 mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             } else {
                 sweep(m_used * c);
             }
+            xch[h * 128 + t] = mx;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            mx = fmaxf(mx, xch[(h ^ 1) * 128 + t]);
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // (the exchange buffer may be written again)
             const bool move = mx > -INFINITY && (m_used == -INFINITY || (mx - m_used) * c > 8.0f);
             const bool any_move = __any_sync(0xffffffffu, move);
             if (fresh || any_move) {
@@ -283,18 +295,19 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
                     m_used = mx;
                 }
                 if (j > 0 && any_move) {
-                    // (P V (j - 1) must have completed before its accumulator is rescaled)
+                    // (P V (j - 1) must have completed before its accumulator is rescaled; each half rescales its 128 columns,
+                    // and P V (j) waits for both halves' P)
                     ok = mbar_wait_bounded(bar_o + ((j - 1) & 1), ((j - 1) >> 1) & 1, err, 63) && ok;
                     tc_fence_after();
                     l *= alpha;
 #pragma unroll 1
-                    for (int cc = 0; cc < 8; cc++) {
+                    for (int cc = 0; cc < 4; cc++) {
                         uint32_t o[32];
-                        tmem_ld32(lane_addr + O_COL + cc * 32, o);
+                        tmem_ld32(lane_addr + O_COL + h * 128 + cc * 32, o);
                         tmem_wait_ld();
 #pragma unroll
                         for (int x = 0; x < 32; x++) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
-                        tmem_st32(lane_addr + O_COL + cc * 32, o);
+                        tmem_st32(lane_addr + O_COL + h * 128 + cc * 32, o);
                     }
                     tmem_wait_st();
                 }
@@ -303,8 +316,7 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
             l += lsum;
             if (!o_seen) ok = mbar_wait_bounded(bar_o + (j & 1), ((j - 2) >> 1) & 1, err, 64) && ok;
             tc_fence_after();
-            tmem_st32(lane_addr + P_COL + (j & 1) * 64, pk);
-            tmem_st32(lane_addr + P_COL + (j & 1) * 64 + 32, pk + 32);
+            tmem_st32(lane_addr + P_COL + (j & 1) * 64 + h * 32, pk);
             s_seen = j + 1 < nblk && mbar_try_wait(bar_s, (j + 1) & 1);  // (answered while the stores complete)
             tmem_wait_st();
             tc_fence_before();
@@ -313,29 +325,33 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
         // ---- epilogue: the partial result (o unnormalised, m in scaled-score units, l) of every vector of the tile
         ok = mbar_wait_bounded(bar_o + ((nblk - 1) & 1), ((nblk - 1) >> 1) & 1, err, 62) && ok;
         tc_fence_after();
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // (the softmax warps only) every MMA of the CTA is complete
+        xch[h * 128 + t] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // (the softmax warps only) every MMA of the CTA is complete
         {
-            // every thread's row of O goes through shared memory (Q, K and V are no longer needed) so that the global stores
-            // are coalesced: a warp then writes one vector's 1 KB row per step
+            // the rows of O go through shared memory (Q, K and V are no longer needed) so that the global stores are coalesced:
+            // thread (h, t) stages columns 128 h .. 128 h + 127 of row t, then a warp writes one vector's 1 KB row per step
             constexpr int OST = HD + 4;  // floats per staged row (the padding spreads the rows over the banks)
             float *so = reinterpret_cast<float *>(sm);
+            const float l_all = l + xch[(h ^ 1) * 128 + t];
 #pragma unroll 1
-            for (int cc = 0; cc < 8; cc++) {
+            for (int cc = 0; cc < 4; cc++) {
                 uint32_t rr[32];
-                tmem_ld32(lane_addr + O_COL + cc * 32, rr);
+                tmem_ld32(lane_addr + O_COL + h * 128 + cc * 32, rr);
                 tmem_wait_ld();
 #pragma unroll
                 for (int y = 0; y < 32; y += 4)
-                    *reinterpret_cast<float4 *>(so + (size_t)t * OST + cc * 32 + y) =
+                    *reinterpret_cast<float4 *>(so + (size_t)t * OST + h * 128 + cc * 32 + y) =
                         make_float4(__uint_as_float(rr[y]), __uint_as_float(rr[y + 1]), __uint_as_float(rr[y + 2]), __uint_as_float(rr[y + 3]));
             }
-            so[(size_t)t * OST + HD] = m_used * scale;
-            so[(size_t)t * OST + HD + 1] = l;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            int rl2 = (warp * 32) / G, x = (warp * 32) % G - 1;
+            if (h == 0) {
+                so[(size_t)t * OST + HD] = m_used * scale;
+                so[(size_t)t * OST + HD + 1] = l_all;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            int rl2 = (warp * 16) / G, x = (warp * 16) % G - 1;
 #pragma unroll 4
-            for (int rr = 0; rr < 32; rr++) {
-                const int tt = warp * 32 + rr;
+            for (int rr = 0; rr < 16; rr++) {
+                const int tt = warp * 16 + rr;
                 if (++x == G) x = 0, rl2++;
                 if (rl2 >= w.nrows) continue;
                 float *p = part + (((size_t)(w.row0 + rl2) * max_splits + w.split) * n_heads + (size_t)g * G + x) * RQ_PSTRIDE(HD);
@@ -350,7 +366,7 @@ __global__ void __launch_bounds__(PF256_THREADS, 1) attn_prefill_hd256_kernel(co
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 6) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(TM_COLS));
+    if (warp == 10) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(TM_COLS));
 }
 
 cudaError_t launch_attn_prefill_hd256(const AttnPrefillArgs &a, cudaStream_t stream) {
