@@ -138,13 +138,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
     }
     __syncthreads();
     if (warp == 10) {
-        if (lane == 0) {  // the first K / V blocks start loading while the other warps convert Q
-            load_k(0);
-            if (nblk > 1) load_k(1);
-            load_v(0);
-            if (nblk > 2) load_k(2);
-            if (nblk > 1) load_v(1);
-        }
+        // The first K block starts loading while the other warps convert Q; the other stages are requested once Q is in
+        // (all SMs start at once and together take in ~4.5 TB/s: everything at once would put 160 KB per SM beside the
+        // 96 KB that the first MMA waits for)
+        if (lane == 0) load_k(0);
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
@@ -230,6 +227,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
             }
         } else if (warp == 10) {
             // K (j + 3) into the stage of K (j) once S (j) is complete; V (j + 2) into the stage of V (j) once P V (j) is
+            if (lane == 0) {
+                if (nblk > 1) load_k(1);
+                load_v(0);
+                if (nblk > 2) load_k(2);
+                if (nblk > 1) load_v(1);
+            }
+            __syncwarp();
             for (int j = 0; j < nblk; j++) {
                 if (j + 3 < nblk) {
                     ok = mbar_wait_sleepy(bar_kfree + j % 3, (j / 3) & 1, err, 15) && ok;
@@ -359,37 +363,43 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attn_prefill_kernel(const PfWor
         const float M = fmaxf(m_used, m_other);
         const float c_own = m_used == -INFINITY ? 0.0f : ex2((m_used - M) * c), c_other = m_other == -INFINITY ? 0.0f : ex2((m_other - M) * c);
         {
-            // every thread's row of c O goes through shared memory (Q, K and V are no longer needed) so that the global
-            // stores are coalesced: a warp then sums the two streams' rows and writes one 512-byte row per step
+            // The merged rows go through shared memory (Q, K and V are no longer needed) so that the global stores are
+            // coalesced.  Thread (h, t) merges dims 64 h .. 64 h + 63 of vector t: both streams' O are in its TMEM lane
             constexpr int OST = HD + 4;  // floats per staged row (the padding spreads the rows over the banks)
-            float *so = reinterpret_cast<float *>(sm), *so_own = so + (size_t)h * 128 * OST;
+            float *so = reinterpret_cast<float *>(sm);
+            const float c0 = h ? c_other : c_own, c1 = h ? c_own : c_other;  // the factors of stream 0's and stream 1's O
 #pragma unroll 1
-            for (int cc = 0; cc < 4; cc++) {
-                uint32_t r[32];
-                tmem_ld32(lane_addr + o_col + cc * 32, r);
+            for (int cc = 0; cc < 2; cc++) {
+                uint32_t r0[32], r1[32];
+                tmem_ld32(lane_addr + O_COL + h * 64 + cc * 32, r0);
+                tmem_ld32(lane_addr + O_COL + 128 + h * 64 + cc * 32, r1);
                 tmem_wait_ld();
 #pragma unroll
                 for (int y = 0; y < 32; y += 4)
-                    *reinterpret_cast<float4 *>(so_own + (size_t)t * OST + cc * 32 + y) =
-                        make_float4(__uint_as_float(r[y]) * c_own, __uint_as_float(r[y + 1]) * c_own, __uint_as_float(r[y + 2]) * c_own,
-                                    __uint_as_float(r[y + 3]) * c_own);
+                    *reinterpret_cast<float4 *>(so + (size_t)t * OST + h * 64 + cc * 32 + y) =
+                        make_float4(__uint_as_float(r0[y]) * c0 + __uint_as_float(r1[y]) * c1, __uint_as_float(r0[y + 1]) * c0 + __uint_as_float(r1[y + 1]) * c1,
+                                    __uint_as_float(r0[y + 2]) * c0 + __uint_as_float(r1[y + 2]) * c1, __uint_as_float(r0[y + 3]) * c0 + __uint_as_float(r1[y + 3]) * c1);
             }
             if (h == 0) {
                 so[(size_t)t * OST + HD] = M * scale;
                 so[(size_t)t * OST + HD + 1] = c_own * l + c_other * l_other;
             }
             asm volatile("bar.sync 1, 256;" ::: "memory");
-            int rl2 = (warp * 16) / G, x = (warp * 16) % G - 1;
-#pragma unroll 8
+            // a warp writes 16 vectors, one 512-byte row (+ m, l) per step; the steps are independent, so their shared-memory
+            // loads and global stores overlap
+            int rl2 = (warp * 16) / G, x = (warp * 16) % G;
+#pragma unroll
             for (int rr = 0; rr < 16; rr++) {
                 const int tt = warp * 16 + rr;
-                if (++x == G) x = 0, rl2++;
-                if (rl2 >= w.nrows) continue;
+                const bool valid = rl2 < w.nrows;
                 float *p = part + (((size_t)(w.row0 + rl2) * max_splits + w.split) * n_heads + (size_t)g * G + x) * RQ_PSTRIDE(HD);
                 const float4 a = *reinterpret_cast<const float4 *>(so + (size_t)tt * OST + 4 * lane);
-                const float4 b = *reinterpret_cast<const float4 *>(so + (size_t)(128 + tt) * OST + 4 * lane);
-                *reinterpret_cast<float4 *>(p + 4 * lane) = ok ? make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (lane < 2) p[HD + lane] = so[(size_t)tt * OST + HD + lane];
+                const float ml = so[(size_t)tt * OST + HD + (lane & 1)];
+                if (valid) {
+                    *reinterpret_cast<float4 *>(p + 4 * lane) = ok ? a : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (lane < 2) p[HD + lane] = ml;
+                }
+                if (++x == G) x = 0, rl2++;
             }
         }
     }
