@@ -49,16 +49,44 @@ __device__ __forceinline__ void levels16_to_f16(uint4 w, int hi_nibble, const fl
     dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
 }
 
+// The query vector of one (row, head) rotated as att_q_rot does for the quantised cache types (signs, butterflies h = 1, 2,
+// 4, ..., scaling by 1 / head_dim), fp32, by one warp: lane L holds dims 4L .. 4L + 3 of every 128-dim part.
+template <int HD>
+__device__ __forceinline__ void q_rot_warp(const float *__restrict__ q, int qh, size_t wi, float *__restrict__ qr, int lane) {
+    constexpr int NP = HD / 128;
+    float4 x[NP];
+#pragma unroll
+    for (int c = 0; c < NP; c++) {
+        x[c] = *reinterpret_cast<const float4 *>(q + wi * qh + 128 * c + 4 * lane);
+        const int i = 128 * c + 4 * lane;
+        x[c].x = kvq_neg(i) ? -x[c].x : x[c].x, x[c].y = kvq_neg(i + 1) ? -x[c].y : x[c].y;
+        x[c].z = kvq_neg(i + 2) ? -x[c].z : x[c].z, x[c].w = kvq_neg(i + 3) ? -x[c].w : x[c].w;
+    }
+    fwht_warp<NP>(x, lane);
+    const float f = 1.0f / (float)HD;
+#pragma unroll
+    for (int c = 0; c < NP; c++)
+        *reinterpret_cast<float4 *>(qr + wi * HD + 128 * c + 4 * lane) = make_float4(x[c].x * f, x[c].y * f, x[c].z * f, x[c].w * f);
+}
+
 // One CTA of head_dim threads per (tile of 16 positions, KV head, segment).  K: thread = dim (its 16 positions: one 16-byte word
 // of levels in, one 32-byte row of the f16 tile out); V: thread = (position, 16 dims of one scale group).
+// The grid's z slices past the segments rotate the pass's query rows (q [rows][n_heads][qh] -> qr [rows][n_heads][head_dim]), a
+// warp per (row, head): the two jobs are independent, and one launch saves the second one's turn on the stream.
 template <int KVT, int HD>
-__global__ void __launch_bounds__(HD) kv_dequant_f16_kernel(const DqSeg *__restrict__ segs, int layer, int n_kv) {
+__global__ void __launch_bounds__(HD) kv_dequant_f16_kernel(const DqSeg *__restrict__ segs, int n_segs, int layer, int n_kv, const float *__restrict__ q,
+                                                            int qh, int n_rows_heads, float *__restrict__ qr) {
     constexpr int KF = kv_fmt(KVT, 0), VF = kv_fmt(KVT, 1);
     constexpr int KTB = kv_tile_bytes(KVT, HD, 0), VTB = kv_tile_bytes(KVT, HD, 1);
-    const DqSeg sg = segs[blockIdx.z];
-    const int u = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;  // tile of the segment (of this head), head
     pdl_wait();
     pdl_launch_dependents();
+    if ((int)blockIdx.z >= n_segs) {
+        const size_t wi = ((((size_t)blockIdx.z - n_segs) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * (HD / 32) + (threadIdx.x >> 5);
+        if (wi < (size_t)n_rows_heads) q_rot_warp<HD>(q, qh, wi, qr, threadIdx.x & 31);
+        return;
+    }
+    const DqSeg sg = segs[blockIdx.z];
+    const int u = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;  // tile of the segment (of this head), head
     if (u >= sg.tiles) return;
     const size_t tile = ((size_t)(u / ATT_PT) * n_kv + g) * ATT_PT + (u % ATT_PT);  // [block][head][tile of the block]
     const uint8_t *kt = sg.k + (size_t)layer * sg.lk + tile * KTB, *vt = sg.v + (size_t)layer * sg.lv + tile * VTB;
@@ -87,31 +115,6 @@ __global__ void __launch_bounds__(HD) kv_dequant_f16_kernel(const DqSeg *__restr
         if (j >= live) d = 0.0f;
         levels16_to_f16<VF>(w, (i0 >> 4) & 1, &d, true, reinterpret_cast<uint4 *>(vo + ((size_t)j * HD + i0) * 2));
     }
-}
-
-// The query rows rotated as att_q_rot does for the quantised cache types (signs, butterflies h = 1, 2, 4, ..., scaling by
-// 1 / head_dim), fp32: q [rows][n_heads][qh] -> qr [rows][n_heads][head_dim].  One warp per (row, head): lane L holds dims
-// 4L .. 4L + 3 of every 128-dim part.
-template <int HD>
-__global__ void __launch_bounds__(256) q_rot_kernel(const float *__restrict__ q, int qh, int n_rows_heads, float *__restrict__ qr) {
-    constexpr int NP = HD / 128;
-    const int wi = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    pdl_wait();
-    pdl_launch_dependents();
-    if (wi >= n_rows_heads) return;
-    float4 x[NP];
-#pragma unroll
-    for (int c = 0; c < NP; c++) {
-        x[c] = *reinterpret_cast<const float4 *>(q + (size_t)wi * qh + 128 * c + 4 * lane);
-        const int i = 128 * c + 4 * lane;
-        x[c].x = kvq_neg(i) ? -x[c].x : x[c].x, x[c].y = kvq_neg(i + 1) ? -x[c].y : x[c].y;
-        x[c].z = kvq_neg(i + 2) ? -x[c].z : x[c].z, x[c].w = kvq_neg(i + 3) ? -x[c].w : x[c].w;
-    }
-    fwht_warp<NP>(x, lane);
-    const float f = 1.0f / (float)HD;
-#pragma unroll
-    for (int c = 0; c < NP; c++)
-        *reinterpret_cast<float4 *>(qr + (size_t)wi * HD + 128 * c + 4 * lane) = make_float4(x[c].x * f, x[c].y * f, x[c].z * f, x[c].w * f);
 }
 
 }  // namespace rq

@@ -1403,11 +1403,16 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
     a.err = c->d_err;
     if (c->pf_quant) {
         // the layer's tiles as f16 (layer 0 of the scratch's views), the query rows rotated; the merge below un-rotates
-        const dim3 dgrid(c->dq_max_tiles, c->n_kv, (unsigned)c->segs.size());
+        // (the same launch rotates the query rows, in z slices of its grid past the segments': a warp per (row, head))
+        const int nrh = c->nrows * c->n_heads, nsegs = (int)c->segs.size();
+        const size_t per_slice = (size_t)c->dq_max_tiles * c->n_kv * (hd / 32);
+        const dim3 dgrid(c->dq_max_tiles, c->n_kv, (unsigned)(nsegs + (nrh + per_slice - 1) / per_slice));
         cudaError_t de;
-#define DEQUANT(KVT_)                                                                                                                              \
-    de = hd == 128 ? launch_pdl(kv_dequant_f16_kernel<KVT_, 128>, dgrid, dim3(128), 0, c->stream, (const DqSeg *)c->d_dqseg, layer, c->n_kv) \
-                   : launch_pdl(kv_dequant_f16_kernel<KVT_, 256>, dgrid, dim3(256), 0, c->stream, (const DqSeg *)c->d_dqseg, layer, c->n_kv)
+#define DEQUANT(KVT_)                                                                                                                          \
+    de = hd == 128 ? launch_pdl(kv_dequant_f16_kernel<KVT_, 128>, dgrid, dim3(128), 0, c->stream, (const DqSeg *)c->d_dqseg, nsegs, layer, c->n_kv, \
+                                q, c->qh, nrh, c->d_qrot)                                                                                      \
+                   : launch_pdl(kv_dequant_f16_kernel<KVT_, 256>, dgrid, dim3(256), 0, c->stream, (const DqSeg *)c->d_dqseg, nsegs, layer, c->n_kv, \
+                                q, c->qh, nrh, c->d_qrot)
         switch (c->pass_kvt) {
             case KV_Q8: DEQUANT(KV_Q8); break;
             case KV_Q4: DEQUANT(KV_Q4); break;
@@ -1415,10 +1420,7 @@ static int launch_prefill(RqCuda *c, int layer, const float *q, float *out) {
         }
 #undef DEQUANT
         if (de != cudaSuccess) return fail(c, RQ_CUDA_ERR_DEVICE, "cache expansion launch: %s", cudaGetErrorString(de));
-        const int nrh = c->nrows * c->n_heads;
-        if (hd == 128) CU(c, launch_pdl(q_rot_kernel<128>, dim3((nrh + 7) / 8), dim3(256), 0, c->stream, q, c->qh, nrh, c->d_qrot));
-        else CU(c, launch_pdl(q_rot_kernel<256>, dim3((nrh + 7) / 8), dim3(256), 0, c->stream, q, c->qh, nrh, c->d_qrot));
-        c->launches += 2;
+        c->launches++;
         a.layer = 0;
         a.q = c->d_qrot;
         a.qh = hd;
